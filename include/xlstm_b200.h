@@ -1,0 +1,143 @@
+/*
+ * xlstm_b200 -- C ABI of the sm_100a recurrent-cell kernels for xLSTM.
+ *
+ * Every entry point takes plain device pointers, sizes and element strides,
+ * validates them on the host, enqueues its kernels on the given CUDA stream
+ * and returns immediately: 0 on success, a negative xl_status otherwise
+ * (nothing is launched when a negative code is returned).  No entry point
+ * synchronises, allocates or frees device memory.
+ *
+ * Conventions shared by all mLSTM entry points
+ *   - q,k are (B, NH, S, DHQK), v and h are (B, NH, S, DHV); the innermost
+ *     dimension is contiguous, the other three are given as ELEMENT strides,
+ *     so the transposed views the reference's layer produces
+ *     (xlstm/xlstm_large/model.py:415-419) are consumed without a copy.
+ *   - gate pre-activations are fp32 (B, NH, S) with element strides.
+ *   - states are fp32 and contiguous: C (N, NH, DHQK, DHV), n (N, NH, DHQK),
+ *     m (N, NH); an absent initial state means C = 0, n = 0, m = 0
+ *     (xlstm/blocks/mlstm/backends.py:185-194).
+ *   - the 1/sqrt(DHQK) factor is applied to q; C and n hold un-scaled keys
+ *     (xlstm/blocks/mlstm/backends.py:168).
+ *   - packed ragged batches: cu_seqlens (device, int32, num_docs + 1 entries)
+ *     lists document boundaries on the flattened (B * S) token axis; a
+ *     document must not straddle two rows.  Every document starts from the
+ *     zero state (or its own row of the initial-state arrays) and leaves its
+ *     own final state; states then have N = num_docs rows.  Without
+ *     cu_seqlens every batch row is one document and N = B.
+ */
+#ifndef XLSTM_B200_H
+#define XLSTM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum xl_status {
+  XL_OK = 0,
+  XL_ERR_NULL_POINTER = -1,
+  XL_ERR_BAD_SHAPE = -2,       /* a dimension is zero/negative or not supported by the kernel */
+  XL_ERR_BAD_STRIDE = -3,      /* stride not compatible with 16-byte vector / TMA access */
+  XL_ERR_BAD_ALIGNMENT = -4,   /* base pointer not 16-byte aligned */
+  XL_ERR_BAD_DTYPE = -5,
+  XL_ERR_UNSUPPORTED = -6,     /* valid request, but not by this entry point (use the one named in the docs) */
+  XL_ERR_CUDA = -7,            /* a CUDA runtime/driver call failed; see xl_last_cuda_error() */
+  XL_ERR_TOO_LARGE = -8,       /* exceeds a fixed capacity of the entry point */
+  XL_ERR_ALIASING = -9         /* an output overlaps an input that other thread blocks still read */
+} xl_status;
+
+typedef enum xl_dtype { XL_F32 = 0, XL_BF16 = 1 } xl_dtype;
+
+/* Human-readable text for a status code (never NULL). */
+const char* xl_strerror(int status);
+/* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
+const char* xl_last_cuda_error(void);
+/* ABI version of this header; bumped on any incompatible change. */
+int xl_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * mLSTM over a sequence (prefill).
+ * Replaces the kernels the reference selects through mLSTMBackendConfig.chunkwise_kernel and
+ * .sequence_kernel (xlstm/xlstm_large/model.py:56-64, call site model.py:425-434); arithmetic as in
+ * xlstm/blocks/mlstm/backends.py:149-263.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct xl_mlstm_seq_params {
+  const void* q; const void* k; const void* v;  /* dtype `dtype` */
+  void* h;                                      /* out, dtype `dtype` */
+  const float* igate; const float* fgate;       /* pre-activations */
+  const float* c0; const float* n0; const float* m0;   /* all three NULL, or all three set */
+  float* c_out; float* n_out; float* m_out;     /* final state per document; c_out may alias c0, but n_out and
+                                                   m_out must not alias n0/m0 (several thread blocks read those) */
+  const int32_t* cu_seqlens;                    /* device pointer or NULL */
+  int32_t* status;                              /* device word, or NULL: set non-zero if a bounded wait expired */
+  int32_t B, NH, S, DHQK, DHV;
+  int32_t num_docs;                             /* used only with cu_seqlens */
+  int64_t q_sb, q_sh, q_st;                     /* element strides: batch, head, token */
+  int64_t k_sb, k_sh, k_st;
+  int64_t v_sb, v_sh, v_st;
+  int64_t h_sb, h_sh, h_st;
+  int64_t g_sb, g_sh, g_st;                     /* shared by igate and fgate */
+  float eps;                                    /* normaliser epsilon (reference default 1e-6) */
+  int32_t dtype;                                /* xl_dtype of q,k,v,h */
+} xl_mlstm_seq_params;
+
+/* Chunkwise-parallel form on tcgen05 tensor cores (TMA-fed, C state resident in tensor memory).
+ * Requires dtype = XL_BF16, DHQK in {64,128,256}, DHV a multiple of 128, strides that are multiples
+ * of 8 elements and 16-byte aligned bases.  Any S >= 1 and any document lengths: a trailing partial
+ * chunk is handled inside the kernel, so the same call also covers what the reference hands to its
+ * sequence kernel.  Returns XL_ERR_UNSUPPORTED for other shapes (use xl_mlstm_recurrent). */
+int xl_mlstm_chunkwise(const xl_mlstm_seq_params* p, void* cuda_stream);
+
+/* Token-by-token recurrence with the C state held on chip (exact fp32 arithmetic; the reference's
+ * `native_sequence__native` contract).  dtype XL_F32 or XL_BF16, any DHQK <= 512, any DHV. */
+int xl_mlstm_recurrent(const xl_mlstm_seq_params* p, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * mLSTM single-token step (decode).  Replaces the kernel selected by mLSTMBackendConfig.step_kernel
+ * (xlstm/xlstm_large/model.py:65-68); arithmetic as in xlstm/blocks/mlstm/backends.py:93-146 with the
+ * scale moved to q.  One pass over C: read, update, reduce against q, write.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct xl_mlstm_step_params {
+  const void* q; const void* k; const void* v;  /* (B, NH, DHQK|DHV), dtype `dtype` */
+  void* h;                                      /* out (B, NH, DHV) */
+  const float* igate; const float* fgate;       /* (B, NH) */
+  const float* c_in; const float* n_in; const float* m_in;  /* state pool (NSLOT, NH, ...) */
+  float* c_out; float* n_out; float* m_out;     /* c_out may alias c_in (in-place update of the large state);
+                                                   n_out/m_out must not alias n_in/m_in */
+  const int32_t* slot;                          /* device (B) row of the pool per stream, or NULL = identity */
+  int32_t B, NH, DHQK, DHV;
+  int64_t q_sb, q_sh, k_sb, k_sh, v_sb, v_sh, h_sb, h_sh, g_sb, g_sh;
+  float eps;
+  int32_t dtype;
+} xl_mlstm_step_params;
+
+int xl_mlstm_step(const xl_mlstm_step_params* p, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * sLSTM forward over a sequence, one persistent kernel (recurrent matrix resident in shared memory,
+ * one thread-block cluster per head, one cluster barrier per time step).
+ * Replaces sLSTMFunc.forward (xlstm/blocks/slstm/src/cuda/slstm.cc:53-135), i.e. the host loop
+ * ForwardPass::Run (slstm_forward.cu:217-267) + SLSTMPointwiseForward (slstm_pointwise.cu:24-116).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct xl_slstm_params {
+  const void* wx;        /* (B, S, 4, NH, DH) gate pre-activations, gates ordered i,f,z,o; dtype `dtype` */
+  const void* R;         /* (NH, DH_in, 4, DH_out) recurrent matrix, dtype `dtype` */
+  const float* bias;     /* (NH, 4, DH) */
+  const float* state0;   /* (4, B, NH*DH) ordered h,c,n,m; or NULL = zeros */
+  void* h_out;           /* (B, NH, S, DH), dtype `dtype` */
+  float* state_out;      /* (4, B, NH*DH) final state */
+  const int32_t* cu_seqlens;  /* device, or NULL; boundaries on the flattened (B*S) axis reset h,c,n,m */
+  int32_t* status;
+  int32_t B, S, NH, DH;
+  int32_t num_docs;
+  int32_t dtype;
+} xl_slstm_params;
+
+/* Requires DH in {64,128,256} and B <= 32. */
+int xl_slstm_forward(const xl_slstm_params* p, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XLSTM_B200_H */

@@ -1,0 +1,165 @@
+"""Host-side checks that need no GPU: the C-ABI library loads and exports what the header declares,
+argument validation, and the drop-in boundary against the reference checkout when it is present."""
+import ctypes
+import os
+import re
+import sys
+
+import pytest
+import torch
+
+from conftest import ROOT, rel_l2
+
+REF = "/root/reference"
+has_ref = os.path.isdir(os.path.join(REF, "xlstm"))
+
+
+def test_library_exports_every_declared_symbol():
+    from xlstm_b200 import _lib
+    header = open(os.path.join(ROOT, "include", "xlstm_b200.h")).read()
+    declared = set(re.findall(r"\b(xl_[a-z_0-9]+)\s*\(", header))
+    assert declared == set(_lib.EXPORTS)
+    l = _lib.lib()
+    for name in declared:
+        assert hasattr(l, name), name
+    assert l.xl_abi_version() == 1
+    assert b"stride" in l.xl_strerror(-3)
+
+
+def test_struct_layouts_match_header_field_order():
+    from xlstm_b200 import _lib
+    header = open(os.path.join(ROOT, "include", "xlstm_b200.h")).read()
+    for cname, struct in (("xl_mlstm_seq_params", _lib.MlstmSeqParams), ("xl_mlstm_step_params", _lib.MlstmStepParams),
+                          ("xl_slstm_params", _lib.SlstmParams)):
+        body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), header, re.S).group(1)
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        names = []
+        for decl in body.split(";"):
+            decl = decl.strip()
+            if not decl:
+                continue
+            first, *rest = decl.split(",")
+            names.append(re.findall(r"[A-Za-z_0-9]+", first)[-1])
+            names += [re.findall(r"[A-Za-z_0-9]+", r)[-1] for r in rest]
+        assert names == [f[0] for f in struct._fields_], cname
+
+
+def test_entry_points_validate_before_launching():
+    from xlstm_b200 import _lib
+    l = _lib.lib()
+    p = _lib.MlstmSeqParams()
+    assert l.xl_mlstm_chunkwise(ctypes.byref(p), None) == -1  # null pointers
+    assert l.xl_mlstm_recurrent(ctypes.byref(p), None) == -1
+    sp = _lib.MlstmStepParams()
+    assert l.xl_mlstm_step(ctypes.byref(sp), None) == -1
+    sl = _lib.SlstmParams()
+    assert l.xl_slstm_forward(ctypes.byref(sl), None) == -1
+    # fake but non-null pointers: shape / dtype checks fire, nothing is launched
+    for name in ("q", "k", "v", "h", "igate", "fgate", "c_out", "n_out", "m_out"):
+        setattr(p, name, 0x1000)
+    assert l.xl_mlstm_chunkwise(ctypes.byref(p), None) == -2
+    p.B, p.NH, p.S, p.DHQK, p.DHV, p.dtype = 1, 1, 64, 96, 128, 1
+    assert l.xl_mlstm_chunkwise(ctypes.byref(p), None) == -6  # DHQK not covered by the tensor-core kernel
+    p.DHQK = 64
+    p.q_st = p.k_st = p.v_st = 100  # not a multiple of 8 elements
+    assert l.xl_mlstm_chunkwise(ctypes.byref(p), None) == -3
+    p.c0, p.n0, p.m0 = 0x2000, p.n_out, 0x3000
+    assert l.xl_mlstm_recurrent(ctypes.byref(p), None) == -9  # n_out aliases n0
+
+
+def test_ops_refuse_cpu_tensors():
+    import xlstm_b200
+    q = torch.zeros(1, 1, 64, 64)
+    with pytest.raises(ValueError, match="no CPU path"):
+        xlstm_b200.mlstm_sequence(q, q, q, torch.zeros(1, 1, 64), torch.zeros(1, 1, 64))
+
+
+def test_cu_seqlens_validation():
+    from xlstm_b200.ops import prepare_cu_seqlens
+    with pytest.raises(ValueError):
+        prepare_cu_seqlens([0, 5, 3, 16], 2, 8, "cpu")
+    with pytest.raises(ValueError):
+        prepare_cu_seqlens([0, 5, 12, 16], 2, 8, "cpu")  # straddles the row boundary at 8
+    with pytest.raises(ValueError):
+        prepare_cu_seqlens([0, 8], 2, 8, "cpu")
+    cu, nd = prepare_cu_seqlens([0, 3, 3, 8, 16], 2, 8, "cpu")
+    assert nd == 4 and cu.dtype == torch.int32
+
+
+def _register_native_oracle():
+    """The upstream 'native' kernel names, served by the CPU oracle (test infrastructure only)."""
+    from oracle import mlstm as O
+    from xlstm_b200 import backend_module as bm
+
+    def chunk(q, k, v, i, f, c_initial=None, n_initial=None, m_initial=None, chunk_size=64, eps=1e-6, **_):
+        h, st = O.mlstm_chunkwise(q, k, v, i, f, c_initial, n_initial, m_initial, chunk_size=chunk_size, eps=eps)
+        return h.to(q.dtype), st
+
+    def seq(q, k, v, i, f, c_initial=None, n_initial=None, m_initial=None, eps=1e-6, **_):
+        h, st = O.mlstm_sequence(q, k, v, i, f, c_initial, n_initial, m_initial, eps=eps)
+        return h.to(q.dtype), st
+
+    def step(q, k, v, i, f, c=None, n=None, m=None, eps=1e-6, **_):
+        h, st = O.mlstm_step(q, k, v, i, f, c, n, m, eps=eps)
+        return h.to(q.dtype), st
+
+    bm.register_kernel("chunkwise", "chunkwise--native_autograd", chunk)
+    bm.register_kernel("sequence", "native_sequence__native", seq)
+    bm.register_kernel("step", "native", step)
+
+
+@pytest.mark.skipif(not has_ref, reason="reference checkout not present")
+def test_reference_model_runs_unchanged_on_the_shim():
+    """BASELINE config 1 shape, shortened: the reference's xlstm_large/model.py imports the shim, builds with
+    the native triple (served by the oracle) and with the b200 names, and chunkwise == step-by-step."""
+    from xlstm_b200.integration import install_mlstm_backend
+    assert install_mlstm_backend() in ("shim", "registered")
+    _register_native_oracle()
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    from xlstm.xlstm_large.model import xLSTMLarge, xLSTMLargeConfig
+    torch.manual_seed(0)
+    cfg = xLSTMLargeConfig(embedding_dim=128, num_heads=4, num_blocks=2, vocab_size=256, return_last_states=True,
+                           mode="inference", chunkwise_kernel="chunkwise--native_autograd",
+                           sequence_kernel="native_sequence__native", step_kernel="native")
+    model = xLSTMLarge(cfg).eval()
+    x = torch.randint(0, 256, (2, 150))
+    with torch.no_grad():
+        logits, state = model(x)
+        assert logits.shape == (2, 150, 256) and len(state) == 2 and len(state[0]) == 3
+        # token-by-token through the step kernel (tests/template_chunkwise_vs_recurrent.py in the reference)
+        st = None
+        outs = []
+        for t in range(150):
+            lg, st = model(x[:, t:t + 1], st)
+            outs.append(lg)
+    torch.testing.assert_close(torch.cat(outs, 1), logits, atol=4e-3, rtol=5e-2)
+    # construction with the CUDA kernel names goes through the same selectors
+    cfg2 = xLSTMLargeConfig(embedding_dim=128, num_heads=4, num_blocks=1, vocab_size=64, mode="inference",
+                            chunkwise_kernel="chunkwise--b200", sequence_kernel="native_sequence__b200", step_kernel="b200")
+    xLSTMLarge(cfg2)
+    with pytest.raises(ValueError):
+        xLSTMLarge(xLSTMLargeConfig(embedding_dim=128, num_heads=4, num_blocks=1, vocab_size=64, step_kernel="nope"))
+
+
+@pytest.mark.skipif(not has_ref, reason="reference checkout not present")
+def test_reference_slstm_switch_accepts_b200():
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    from xlstm_b200.integration import install_slstm_backend
+    cls = install_slstm_backend()
+    from xlstm.blocks.slstm.cell import sLSTMCell, sLSTMCellConfig
+    cell = sLSTMCell(sLSTMCellConfig(hidden_size=128, num_heads=2, backend="b200", recurrent_weight_init="standard"))
+    assert isinstance(cell, cls)
+    assert cell._recurrent_kernel_.shape == (2, 64, 4, 64) and cell._bias_.shape == (2, 4, 64)
+    van = sLSTMCell(sLSTMCellConfig(hidden_size=128, num_heads=2, backend="vanilla"))
+    assert type(van).__name__ == "sLSTMCell_vanilla"
+    with pytest.raises(ValueError, match="no CPU path"):
+        cell(torch.zeros(1, 4, 512, dtype=torch.bfloat16))
+    # the whole block stack builds with the new backend name
+    from xlstm.xlstm_block_stack import xLSTMBlockStack, xLSTMBlockStackConfig
+    from xlstm.blocks.slstm.block import sLSTMBlockConfig
+    from xlstm.blocks.slstm.layer import sLSTMLayerConfig
+    cfg = xLSTMBlockStackConfig(slstm_block=sLSTMBlockConfig(slstm=sLSTMLayerConfig(num_heads=2, conv1d_kernel_size=4, backend="b200")),
+                                num_blocks=2, embedding_dim=128, slstm_at="all")
+    xLSTMBlockStack(cfg)

@@ -1,0 +1,193 @@
+"""Parity of the CUDA mLSTM kernels (through the C ABI) with the CPU oracle on identical seeded inputs.
+
+Tolerances (relative L2): bf16 outputs and states <= 1e-2, fp32 mode <= 1e-4 -- the bar BASELINE.json states.
+The bf16 oracle is "inputs rounded to bf16, arithmetic in fp32".
+"""
+import math
+
+import pytest
+import torch
+
+from conftest import load_golden, rel_l2
+from oracle import mlstm as O
+
+pytestmark = pytest.mark.gpu
+TOL_BF16, TOL_F32 = 1e-2, 1e-4
+
+
+def _inputs(seed, B, NH, S, DQ, DV, dtype, f_mean=3.0):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, NH, S, DQ, generator=g) / math.sqrt(DQ) * math.sqrt(DQ) ** 0  # N(0,1); scale applied below
+    k = torch.randn(B, NH, S, DQ, generator=g)
+    v = torch.randn(B, NH, S, DV, generator=g)
+    i = torch.randn(B, NH, S, generator=g)
+    f = torch.randn(B, NH, S, generator=g) + f_mean
+    q, k, v = (t.to(dtype) for t in (q, k, v))
+    return q, k, v, i, f
+
+
+def _state(seed, N, NH, DQ, DV):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(N, NH, DQ, DV, generator=g), torch.randn(N, NH, DQ, generator=g), torch.randn(N, NH, 1, generator=g))
+
+
+def _cuda(*ts):
+    return [None if t is None else t.cuda() for t in ts]
+
+
+def _check(h, st, h_ref, st_ref, tol):
+    assert torch.isfinite(h.float()).all()
+    assert rel_l2(h.float().cpu(), h_ref) < tol, rel_l2(h.float().cpu(), h_ref)
+    for a, b, name in zip(st, st_ref, "cnm"):
+        a = a.float().cpu().reshape(b.shape)
+        if name == "m":
+            assert torch.allclose(a, b, atol=1e-3, rtol=1e-4), (a - b).abs().max()
+        else:
+            assert rel_l2(a, b) < tol, (name, rel_l2(a, b))
+
+
+# ------------------------------------------------------------------------------------------------ step
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL_F32), (torch.bfloat16, TOL_BF16)])
+@pytest.mark.parametrize("B,NH,DQ,DV", [(3, 2, 64, 128), (2, 8, 256, 512), (1, 1, 32, 36)])
+def test_step_matches_oracle(dtype, tol, B, NH, DQ, DV):
+    import xlstm_b200
+    q, k, v, i, f = _inputs(1, B, NH, 1, DQ, DV, dtype, f_mean=1.0)
+    c0, n0, m0 = _state(2, B, NH, DQ, DV)
+    h_ref, st_ref = O.mlstm_step(q[:, :, 0], k[:, :, 0], v[:, :, 0], i, f, c0, n0, m0)
+    qc, kc, vc, ic, fc, cc, nc, mc = _cuda(q[:, :, 0], k[:, :, 0], v[:, :, 0], i, f, c0.clone(), n0, m0)
+    h, st = xlstm_b200.mlstm_step(qc, kc, vc, ic, fc, cc, nc, mc)
+    assert st[0] is cc  # the large state is updated in place and handed back as the same object
+    _check(h, st, h_ref, st_ref, tol)
+    # from the zero state
+    h_ref, st_ref = O.mlstm_step(q[:, :, 0], k[:, :, 0], v[:, :, 0], i, f)
+    h, st = xlstm_b200.mlstm_step(qc, kc, vc, ic, fc, None, None, None)
+    _check(h, st, h_ref, st_ref, tol)
+
+
+def test_step_slots_and_strided_views():
+    import xlstm_b200
+    B, NH, DQ, DV, N = 3, 2, 64, 128, 5
+    q, k, v, i, f = _inputs(3, B, NH, 1, DQ, DV, torch.bfloat16)
+    c0, n0, m0 = _state(4, N, NH, DQ, DV)
+    slot = torch.tensor([4, 0, 2], dtype=torch.int32)
+    h_ref, st_ref = O.mlstm_step(q[:, :, 0], k[:, :, 0], v[:, :, 0], i, f, c0[slot.long()], n0[slot.long()], m0[slot.long()])
+    # q,k,v as slices of one fused projection buffer (B, NH*(2DQ+DV)) -> strided (B,NH,D) views
+    fused = torch.cat([q[:, :, 0].reshape(B, -1), k[:, :, 0].reshape(B, -1), v[:, :, 0].reshape(B, -1)], dim=1).cuda()
+    qv = fused[:, : NH * DQ].view(B, NH, DQ)
+    kv = fused[:, NH * DQ: 2 * NH * DQ].view(B, NH, DQ)
+    vv = fused[:, 2 * NH * DQ:].view(B, NH, DV)
+    cc, nc, mc = c0.cuda(), n0.cuda(), m0.cuda()
+    h, (c, n, m) = xlstm_b200.mlstm_step(qv, kv, vv, i.cuda(), f.cuda(), cc, nc, mc, slot=slot.cuda())
+    _check(h, (c[slot.long().cuda()], n[slot.long().cuda()], m[slot.long().cuda()]), h_ref, st_ref, TOL_BF16)
+    untouched = torch.tensor([1, 3])
+    assert torch.equal(c[untouched.cuda()].cpu(), c0[untouched]) and torch.equal(n[untouched.cuda()].cpu(), n0[untouched])
+
+
+# ------------------------------------------------------------------------------------------------ recurrent
+@pytest.mark.parametrize("name", ["mlstm_chunk_zero", "mlstm_chunk_init", "hf_chunk", "hf_seq"])
+def test_recurrent_fp32_matches_reference_fixtures(name):
+    import xlstm_b200
+    g = load_golden(name)
+    init = _cuda(g.get("c0"), g.get("n0"), g.get("m0"))
+    h, st = xlstm_b200.mlstm_sequence(*_cuda(g["q"], g["k"], g["v"], g["i"], g["f"]), *init, kernel="recurrent")
+    _check(h, st, g["h"], (g["c"], g["n"], g["m"].reshape(g["c"].shape[0], -1, 1)), TOL_F32)
+
+
+def test_recurrent_fp32_config1_shape():
+    """B=3, NH=4, S=256, DHQK=64, DHV=128, fp32: the cell shape of BASELINE config 1."""
+    import xlstm_b200
+    q, k, v, i, f = _inputs(5, 3, 4, 256, 64, 128, torch.float32)
+    h_ref, st_ref = O.mlstm_chunkwise(q, k, v, i, f)
+    h, st = xlstm_b200.mlstm_sequence(*_cuda(q, k, v, i, f), kernel="auto")  # fp32 -> recurrence
+    _check(h, st, h_ref, st_ref, TOL_F32)
+
+
+# ------------------------------------------------------------------------------------------------ chunkwise (tcgen05)
+@pytest.mark.parametrize("B,NH,S,DQ,DV,with_state", [
+    (2, 2, 256, 64, 128, False),
+    (1, 2, 150, 128, 256, True),     # 2 full chunks + 22-token tail, initial state
+    (1, 1, 64, 256, 512, False),
+    (2, 3, 1000, 256, 512, True),
+    (1, 2, 7, 64, 128, False),       # shorter than one chunk
+])
+def test_chunkwise_matches_oracle(B, NH, S, DQ, DV, with_state):
+    import xlstm_b200
+    q, k, v, i, f = _inputs(7, B, NH, S, DQ, DV, torch.bfloat16)
+    init = _state(8, B, NH, DQ, DV) if with_state else (None, None, None)
+    h_ref, st_ref = O.mlstm_inference(q, k, v, i, f, *init)
+    h, st = xlstm_b200.mlstm_sequence(*_cuda(q, k, v, i, f), *_cuda(*init), kernel="chunkwise")
+    xlstm_b200.check_device_status()
+    _check(h, st, h_ref, st_ref, TOL_BF16)
+
+
+def test_chunkwise_harsh_gates_stay_finite_and_match():
+    """Forget gates around -6 (strong decay) and input gates with a wide spread exercise the stabilisers."""
+    import xlstm_b200
+    B, NH, S, DQ, DV = 1, 2, 320, 64, 128
+    q, k, v, i, f = _inputs(9, B, NH, S, DQ, DV, torch.bfloat16, f_mean=-6.0)
+    i = i * 6.0
+    h_ref, st_ref = O.mlstm_inference(q, k, v, i, f)
+    h, st = xlstm_b200.mlstm_sequence(*_cuda(q, k, v, i, f), kernel="chunkwise")
+    _check(h, st, h_ref, st_ref, TOL_BF16)
+
+
+def test_chunkwise_transposed_views_like_the_reference_layer():
+    """q,k,v arrive as (B,S,NH*D) projections viewed as (B,NH,S,D) -- xlstm_large/model.py:415-419."""
+    import xlstm_b200
+    B, NH, S, DQ, DV = 2, 4, 192, 64, 128
+    q, k, v, i, f = _inputs(10, B, NH, S, DQ, DV, torch.bfloat16)
+    h_ref, st_ref = O.mlstm_inference(q, k, v, i, f)
+    qc = q.transpose(1, 2).reshape(B, S, NH * DQ).cuda().reshape(B, S, NH, DQ).transpose(1, 2)
+    kc = k.transpose(1, 2).reshape(B, S, NH * DQ).cuda().reshape(B, S, NH, DQ).transpose(1, 2)
+    vc = v.transpose(1, 2).reshape(B, S, NH * DV).cuda().reshape(B, S, NH, DV).transpose(1, 2)
+    ic = i.transpose(1, 2).contiguous().cuda().transpose(1, 2)
+    fc = f.transpose(1, 2).contiguous().cuda().transpose(1, 2)
+    assert not qc.is_contiguous()
+    h, st = xlstm_b200.mlstm_sequence(qc, kc, vc, ic, fc, kernel="chunkwise")
+    _check(h, st, h_ref, st_ref, TOL_BF16)
+
+
+@pytest.mark.parametrize("kernel,dtype,tol", [("chunkwise", torch.bfloat16, TOL_BF16), ("recurrent", torch.float32, TOL_F32)])
+def test_packed_documents_reset_state_in_kernel(kernel, dtype, tol):
+    """Ragged documents packed into rows, boundaries anywhere (also inside a 64-token chunk), an empty
+    document, and a document that ends exactly at a row end.  Oracle = each document alone."""
+    import xlstm_b200
+    B, NH, S, DQ, DV = 2, 2, 256, 64, 128
+    cu = [0, 5, 5, 70, 200, 256, 256 + 64, 256 + 191, 512]
+    q, k, v, i, f = _inputs(11, B, NH, S, DQ, DV, dtype)
+    flat = lambda t: t.transpose(0, 1).reshape(NH, B * S, *t.shape[3:])
+    h_ref, st_ref = O.mlstm_packed(flat(q), flat(k), flat(v), flat(i), flat(f), cu)
+    h, st = xlstm_b200.mlstm_sequence(*_cuda(q, k, v, i, f), cu_seqlens=cu, kernel=kernel)
+    xlstm_b200.check_device_status()
+    assert st[0].shape == (len(cu) - 1, NH, DQ, DV)
+    _check(flat(h.cpu()), st, h_ref, st_ref, tol)
+
+
+def test_chunkwise_full_size_config2_properties():
+    """BASELINE config 2 at full size (B=4, NH=8, S=8192, DHQK=256, DHV=512, bf16).  Size-independent checks:
+    (1) the tensor-core kernel agrees with the on-device fp32 recurrence for one (batch, head) pair,
+    (2) splitting the sequence in two calls that hand the state over gives the same result,
+    (3) batch rows / heads are independent (same inputs in two rows -> identical outputs)."""
+    import xlstm_b200
+    B, NH, S, DQ, DV = 4, 8, 8192, 256, 512
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q = (torch.randn(B, NH, S, DQ, generator=g, device="cuda") / math.sqrt(DQ)).bfloat16()
+    k = (torch.randn(B, NH, S, DQ, generator=g, device="cuda") / math.sqrt(DQ)).bfloat16()
+    v = torch.randn(B, NH, S, DV, generator=g, device="cuda").bfloat16()
+    i = torch.randn(B, NH, S, generator=g, device="cuda")
+    f = torch.randn(B, NH, S, generator=g, device="cuda") + 3.0
+    q[3], k[3], v[3], i[3], f[3] = q[0], k[0], v[0], i[0], f[0]
+    h, (c, n, m) = xlstm_b200.mlstm_sequence(q, k, v, i, f, kernel="chunkwise")
+    xlstm_b200.check_device_status()
+    assert torch.isfinite(h.float()).all() and torch.isfinite(c).all()
+    assert torch.equal(h[3], h[0]) and torch.equal(c[3], c[0])
+    sl = (slice(1, 2), slice(2, 3))
+    hr, (cr, nr, mr) = xlstm_b200.mlstm_sequence(q[sl], k[sl], v[sl], i[sl], f[sl], kernel="recurrent")
+    assert rel_l2(h[sl].float(), hr.float()) < TOL_BF16
+    assert rel_l2(c[sl], cr) < TOL_BF16 and rel_l2(n[sl], nr) < TOL_BF16
+    assert torch.allclose(m[sl], mr, atol=1e-3)
+    half = 4096 + 37
+    h1, st1 = xlstm_b200.mlstm_sequence(q[:1, :, :half], k[:1, :, :half], v[:1, :, :half], i[:1, :, :half], f[:1, :, :half], kernel="chunkwise")
+    h2, st2 = xlstm_b200.mlstm_sequence(q[:1, :, half:], k[:1, :, half:], v[:1, :, half:], i[:1, :, half:], f[:1, :, half:], *st1, kernel="chunkwise")
+    assert rel_l2(torch.cat([h1, h2], 2).float(), h[:1].float()) < TOL_BF16
+    assert rel_l2(st2[0], c[:1]) < TOL_BF16

@@ -1,0 +1,101 @@
+"""ctypes binding of the C-ABI library declared in include/xlstm_b200.h.
+
+There is deliberately no fallback: if the shared library is missing or a call
+fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libxlstm_b200.so")
+
+XL_F32, XL_BF16 = 0, 1
+
+EXPORTS = (
+    "xl_strerror", "xl_last_cuda_error", "xl_abi_version",
+    "xl_mlstm_chunkwise", "xl_mlstm_recurrent", "xl_mlstm_step", "xl_slstm_forward",
+)
+
+
+class MlstmSeqParams(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("h", C.c_void_p),
+        ("igate", C.c_void_p), ("fgate", C.c_void_p),
+        ("c0", C.c_void_p), ("n0", C.c_void_p), ("m0", C.c_void_p),
+        ("c_out", C.c_void_p), ("n_out", C.c_void_p), ("m_out", C.c_void_p),
+        ("cu_seqlens", C.c_void_p), ("status", C.c_void_p),
+        ("B", C.c_int32), ("NH", C.c_int32), ("S", C.c_int32), ("DHQK", C.c_int32), ("DHV", C.c_int32),
+        ("num_docs", C.c_int32),
+        ("q_sb", C.c_int64), ("q_sh", C.c_int64), ("q_st", C.c_int64),
+        ("k_sb", C.c_int64), ("k_sh", C.c_int64), ("k_st", C.c_int64),
+        ("v_sb", C.c_int64), ("v_sh", C.c_int64), ("v_st", C.c_int64),
+        ("h_sb", C.c_int64), ("h_sh", C.c_int64), ("h_st", C.c_int64),
+        ("g_sb", C.c_int64), ("g_sh", C.c_int64), ("g_st", C.c_int64),
+        ("eps", C.c_float), ("dtype", C.c_int32),
+    ]
+
+
+class MlstmStepParams(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("h", C.c_void_p),
+        ("igate", C.c_void_p), ("fgate", C.c_void_p),
+        ("c_in", C.c_void_p), ("n_in", C.c_void_p), ("m_in", C.c_void_p),
+        ("c_out", C.c_void_p), ("n_out", C.c_void_p), ("m_out", C.c_void_p),
+        ("slot", C.c_void_p),
+        ("B", C.c_int32), ("NH", C.c_int32), ("DHQK", C.c_int32), ("DHV", C.c_int32),
+        ("q_sb", C.c_int64), ("q_sh", C.c_int64), ("k_sb", C.c_int64), ("k_sh", C.c_int64),
+        ("v_sb", C.c_int64), ("v_sh", C.c_int64), ("h_sb", C.c_int64), ("h_sh", C.c_int64),
+        ("g_sb", C.c_int64), ("g_sh", C.c_int64),
+        ("eps", C.c_float), ("dtype", C.c_int32),
+    ]
+
+
+class SlstmParams(C.Structure):
+    _fields_ = [
+        ("wx", C.c_void_p), ("R", C.c_void_p), ("bias", C.c_void_p), ("state0", C.c_void_p),
+        ("h_out", C.c_void_p), ("state_out", C.c_void_p), ("cu_seqlens", C.c_void_p), ("status", C.c_void_p),
+        ("B", C.c_int32), ("S", C.c_int32), ("NH", C.c_int32), ("DH", C.c_int32),
+        ("num_docs", C.c_int32), ("dtype", C.c_int32),
+    ]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Load (once) and return the library; raise if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m xlstm_b200.build` "
+                "(there is no fallback implementation)")
+        l = C.CDLL(LIB_PATH)
+        l.xl_strerror.restype = C.c_char_p
+        l.xl_strerror.argtypes = [C.c_int]
+        l.xl_last_cuda_error.restype = C.c_char_p
+        l.xl_abi_version.restype = C.c_int
+        for name, ptype in (("xl_mlstm_chunkwise", MlstmSeqParams), ("xl_mlstm_recurrent", MlstmSeqParams),
+                            ("xl_mlstm_step", MlstmStepParams), ("xl_slstm_forward", SlstmParams)):
+            fn = getattr(l, name)
+            fn.restype = C.c_int
+            fn.argtypes = [C.POINTER(ptype), C.c_void_p]
+        _lib = l
+    return _lib
+
+
+class XlError(RuntimeError):
+    def __init__(self, code: int, where: str):
+        l = lib()
+        msg = l.xl_strerror(code).decode()
+        if code == -7:
+            msg += ": " + l.xl_last_cuda_error().decode()
+        super().__init__(f"{where} failed with status {code}: {msg}")
+        self.code = code
+
+
+def check(code: int, where: str) -> None:
+    if code != 0:
+        raise XlError(code, where)

@@ -1,0 +1,329 @@
+// sLSTM forward over a whole sequence in ONE persistent kernel.
+//
+// Per time step (reference: slstm_pointwise.cu:60-115 / vanilla/slstm.py:19-37):
+//   raw_g = Wx_g + (h_{t-1} R)_g + b_g ,  g in {i,f,z,o}
+//   m' = (n == 0) ? i : max(i, m + logsig(f));  i' = min(1, e^{i-m'});  f' = min(1, e^{m + logsig(f) - m'})
+//   c' = f' c + i' tanh(z);  n' = f' n + i';  h' = sigmoid(o) c' / n'
+//
+// Mapping.  One thread-block CLUSTER of DH/32 CTAs serves one (head, 16-row batch group); heads and batch
+// groups never exchange data.  CTA r of the cluster owns hidden units [32r, 32r+32) and all four of their
+// gates: its slice of the recurrent matrix (DH x 128 bf16) is read once and stays in REGISTERS as
+// mma.sync B-fragments (a warp = 8 units x 4 gates = four n8 tiles x DH/16 k-steps).  The batch rows are
+// the M=16 side of m16n8k16.  Each thread ends a step holding all four gate pre-activations of its four
+// (row, unit) pairs in its accumulators, so the pointwise update runs in registers with c, n, m kept in
+// fp32 registers for the whole sequence.  The new h (bf16) is pushed into the double-buffered h tile of
+// EVERY CTA of the cluster through distributed shared memory, then one cluster barrier ends the step.
+// Wx is streamed through an 8-step cp.async ring so that HBM latency is off the dependency chain.
+// A document boundary (cu_seqlens) zeroes h, c, n, m of that batch row inside the kernel.
+#include "common.cuh"
+
+namespace xl {
+
+constexpr int SL_THREADS = 128;         // 4 warps; warp w owns units [8w, 8w+8) of the CTA's 32
+constexpr int SL_UNITS = 32;            // hidden units per CTA
+constexpr int SL_ROWS = 16;             // batch rows per cluster (mma M)
+constexpr int SL_RING = 8;              // Wx prefetch depth in time steps
+constexpr int SL_WX_ROW_BYTES = 4 * SL_UNITS * 2 + 16;  // 4 gates x 32 units bf16 + 16 B pad (bank spread)
+constexpr int SL_WX_STEP_BYTES = SL_ROWS * SL_WX_ROW_BYTES;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float fast_tanh(float x) {
+  // 1 - 2/(1+e^{2x}); saturates cleanly for large |x|
+  const float e = __expf(2.f * x);
+  return 1.f - __fdividef(2.f, 1.f + e);
+}
+__device__ __forceinline__ float fast_logsigmoid(float x) { return fminf(x, 0.f) - __logf(1.f + __expf(-fabsf(x))); }
+
+// Advance `idx` past every boundary at or before time index `t_now` of batch row `gb`; return the time index
+// of the next boundary inside the row, or INT_MAX.  Repeated offsets (empty documents) are skipped.
+__device__ __forceinline__ int next_boundary(const xl_slstm_params& p, int gb, int t_now, int& idx) {
+  const long long row0 = (long long)gb * p.S;
+  while (idx <= p.num_docs && (long long)p.cu_seqlens[idx] <= row0 + t_now) ++idx;
+  if (idx > p.num_docs) return 0x7fffffff;
+  const long long pos = p.cu_seqlens[idx];
+  return pos < row0 + p.S ? (int)(pos - row0) : 0x7fffffff;
+}
+
+template <int DH>
+__global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_slstm_params p) {
+  constexpr int KSTEPS = DH / 16;
+  constexpr int H_STRIDE = DH + 8;  // bf16 elements; +16 B keeps ldmatrix rows on distinct banks
+  extern __shared__ __align__(16) unsigned char sl_smem[];
+  __nv_bfloat16* s_h = reinterpret_cast<__nv_bfloat16*>(sl_smem);                    // 2 x 16 x H_STRIDE
+  unsigned char* s_wx = sl_smem + 2 * SL_ROWS * H_STRIDE * sizeof(__nv_bfloat16);    // SL_RING x SL_WX_STEP_BYTES
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t rank = cluster_ctarank();       // which 32-unit slice of the head
+  constexpr int NCTA = DH / SL_UNITS;
+  const int head = blockIdx.y, bgroup = blockIdx.z;
+  const int B = p.B, S = p.S, NH = p.NH, H = NH * DH;
+  const int row_a = lane >> 2, row_b = row_a + 8;             // the two batch rows (within the group) of this thread
+  const int unit_l = warp * 8 + (lane & 3) * 2;               // first of two adjacent units within the CTA
+  const int unit_h = (int)rank * SL_UNITS + unit_l;           // ... within the head
+  const int gb_a = bgroup * SL_ROWS + row_a, gb_b = bgroup * SL_ROWS + row_b;  // global batch rows
+  const bool ok_a = gb_a < B, ok_b = gb_b < B;
+
+  // ---- recurrent matrix slice -> registers (B fragments).  R is (NH, DH_in, 4, DH_out).
+  uint32_t rfrag[KSTEPS][4][2];
+  {
+    const __nv_bfloat16* R = reinterpret_cast<const __nv_bfloat16*>(p.R) + (size_t)head * DH * 4 * DH;
+    const int n_unit = (int)rank * SL_UNITS + warp * 8 + (lane >> 2);  // column n = lane/4 of every tile
+    const int k0 = (lane & 3) * 2;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks)
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const __nv_bfloat16* base = R + ((size_t)(ks * 16 + k0) * 4 + g) * DH + n_unit;
+        const uint16_t e0 = *reinterpret_cast<const uint16_t*>(base);
+        const uint16_t e1 = *reinterpret_cast<const uint16_t*>(base + 4 * DH);
+        const uint16_t e8 = *reinterpret_cast<const uint16_t*>(base + 8 * 4 * DH);
+        const uint16_t e9 = *reinterpret_cast<const uint16_t*>(base + 9 * 4 * DH);
+        rfrag[ks][g][0] = (uint32_t)e0 | ((uint32_t)e1 << 16);
+        rfrag[ks][g][1] = (uint32_t)e8 | ((uint32_t)e9 << 16);
+      }
+  }
+  // ---- bias for this thread's two units, four gates
+  float bias[4][2];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    bias[g][0] = p.bias[((size_t)head * 4 + g) * DH + unit_h];
+    bias[g][1] = p.bias[((size_t)head * 4 + g) * DH + unit_h + 1];
+  }
+
+  // ---- state registers: [pair] with pair = (row_a,u0), (row_a,u1), (row_b,u0), (row_b,u1)
+  float c_[4], n_[4], m_[4], hlast[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int gb = (i < 2) ? gb_a : gb_b;
+    const bool ok = (i < 2) ? ok_a : ok_b;
+    const size_t off = (size_t)gb * H + (size_t)head * DH + unit_h + (i & 1);
+    const bool have = p.state0 != nullptr && ok;
+    hlast[i] = have ? p.state0[0 * (size_t)B * H + off] : 0.f;
+    c_[i] = have ? p.state0[1 * (size_t)B * H + off] : 0.f;
+    n_[i] = have ? p.state0[2 * (size_t)B * H + off] : 0.f;
+    m_[i] = have ? p.state0[3 * (size_t)B * H + off] : 0.f;
+  }
+
+  // ---- next document boundary (as a time index within the row) for the two batch rows
+  int nxt_idx[2] = {0, 0};
+  int nxt_t[2] = {0x7fffffff, 0x7fffffff};
+  if (p.cu_seqlens) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int gb = r == 0 ? gb_a : gb_b;
+      const bool ok = r == 0 ? ok_a : ok_b;
+      if (!ok) continue;
+      // binary search for the first boundary beyond the start of row gb, then the shared helper
+      const long long row0 = (long long)gb * S;
+      int lo = 0, hi = p.num_docs + 1;
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if ((long long)p.cu_seqlens[mid] > row0) hi = mid; else lo = mid + 1;
+      }
+      nxt_idx[r] = lo;
+      nxt_t[r] = next_boundary(p, gb, 0, nxt_idx[r]);
+    }
+  }
+
+  // ---- h tile (both buffers) of this CTA: buffer 0 holds h_{-1}; every CTA fills its own copy completely
+  for (int i = tid; i < 2 * SL_ROWS * H_STRIDE; i += SL_THREADS) s_h[i] = __float2bfloat16_rn(0.f);
+  __syncthreads();
+  if (p.state0) {
+    for (int i = tid; i < SL_ROWS * DH; i += SL_THREADS) {
+      const int r = i / DH, d = i % DH;
+      const int gb = bgroup * SL_ROWS + r;
+      if (gb < B) s_h[r * H_STRIDE + d] = __float2bfloat16_rn(p.state0[(size_t)gb * H + (size_t)head * DH + d]);
+    }
+  }
+
+  // ---- Wx ring: each thread copies two 16-byte granules per step
+  const __nv_bfloat16* wx = reinterpret_cast<const __nv_bfloat16*>(p.wx);
+  const uint32_t s_wx_u32 = smem_u32(s_wx);
+  auto issue_wx = [&](int t) {
+    if (t < S) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int gidx = tid + j * SL_THREADS;            // 0..255
+        const int r = gidx >> 4, g = (gidx >> 2) & 3, part = gidx & 3;
+        int gb = bgroup * SL_ROWS + r;
+        gb = gb < B ? gb : B - 1;                          // padded rows re-read a valid row (result unused)
+        const __nv_bfloat16* src = wx + (((size_t)gb * S + t) * 4 + g) * H + (size_t)head * DH + rank * SL_UNITS + part * 8;
+        const uint32_t dst = s_wx_u32 + (t % SL_RING) * SL_WX_STEP_BYTES + r * SL_WX_ROW_BYTES + g * (SL_UNITS * 2) + part * 16;
+        cp_async16(dst, src);
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int t = 0; t < SL_RING - 1; ++t) issue_wx(t);
+  cp_async_wait<SL_RING - 2>();   // step 0 has landed (this thread's part)
+  cluster_barrier();              // all CTAs of the cluster initialised; also a CTA-wide barrier
+
+  // remote addresses of this thread's four h slots in every CTA of the cluster
+  const uint32_t s_h_u32 = smem_u32(s_h);
+  const uint32_t slot_a = (row_a * H_STRIDE + unit_h) * 2, slot_b = (row_b * H_STRIDE + unit_h) * 2;
+  // ldmatrix source row/column for this lane
+  const uint32_t ldm_off = ((lane & 15) * H_STRIDE + (lane >> 4) * 8) * 2;
+
+  __nv_bfloat16* hout = reinterpret_cast<__nv_bfloat16*>(p.h_out);
+
+  for (int t = 0; t < S; ++t) {
+    issue_wx(t + SL_RING - 1);
+    const int cur = t & 1, nxt = cur ^ 1;
+
+    // accumulators start from Wx + bias
+    float acc[4][4];
+    {
+      const unsigned char* wrow_a = s_wx + (t % SL_RING) * SL_WX_STEP_BYTES + row_a * SL_WX_ROW_BYTES + unit_l * 2;
+      const unsigned char* wrow_b = s_wx + (t % SL_RING) * SL_WX_STEP_BYTES + row_b * SL_WX_ROW_BYTES + unit_l * 2;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const float2 wa = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(wrow_a + g * (SL_UNITS * 2)));
+        const float2 wb = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(wrow_b + g * (SL_UNITS * 2)));
+        acc[g][0] = wa.x + bias[g][0];
+        acc[g][1] = wa.y + bias[g][1];
+        acc[g][2] = wb.x + bias[g][0];
+        acc[g][3] = wb.y + bias[g][1];
+      }
+    }
+    // h_{t-1} (16 x DH) times the register-resident R slice
+    const uint32_t hbase = s_h_u32 + cur * (SL_ROWS * H_STRIDE * 2) + ldm_off;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      uint32_t a0, a1, a2, a3;
+      ldmatrix_x4(hbase + ks * 32, a0, a1, a2, a3);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) mma_bf16_16816(acc[g], a0, a1, a2, a3, rfrag[ks][g][0], rfrag[ks][g][1]);
+    }
+    // pointwise update in registers
+    const bool reset_next_a = (t + 1) == nxt_t[0], reset_next_b = (t + 1) == nxt_t[1];
+    float hn[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float ir = acc[0][i], fr = acc[1][i], zr = acc[2][i], orr = acc[3][i];
+      const float lfm = m_[i] + fast_logsigmoid(fr);
+      const float mn = (n_[i] == 0.f) ? ir : fmaxf(ir, lfm);
+      const float ig = fminf(1.f, __expf(ir - mn));
+      const float fg = fminf(1.f, __expf(lfm - mn));
+      c_[i] = fmaf(fg, c_[i], ig * fast_tanh(zr));
+      n_[i] = fmaf(fg, n_[i], ig);
+      m_[i] = mn;
+      hn[i] = __fdividef(c_[i], n_[i]) * __fdividef(1.f, 1.f + __expf(-orr));
+    }
+    // output h_t, (B, NH, S, DH)
+    const uint32_t pa = pack_bf16x2(hn[0], hn[1]), pb = pack_bf16x2(hn[2], hn[3]);
+    if (ok_a) *reinterpret_cast<uint32_t*>(hout + (((size_t)gb_a * NH + head) * S + t) * DH + unit_h) = pa;
+    if (ok_b) *reinterpret_cast<uint32_t*>(hout + (((size_t)gb_b * NH + head) * S + t) * DH + unit_h) = pb;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) hlast[i] = hn[i];
+    // a row whose next token opens a new document restarts from the zero state
+    uint32_t push_a = pa, push_b = pb;
+    if (reset_next_a) {
+      push_a = 0u;
+      c_[0] = c_[1] = n_[0] = n_[1] = m_[0] = m_[1] = 0.f;
+      nxt_t[0] = next_boundary(p, gb_a, t + 1, nxt_idx[0]);
+    }
+    if (reset_next_b) {
+      push_b = 0u;
+      c_[2] = c_[3] = n_[2] = n_[3] = m_[2] = m_[3] = 0.f;
+      nxt_t[1] = next_boundary(p, gb_b, t + 1, nxt_idx[1]);
+    }
+    // broadcast h_t into buffer `nxt` of every CTA in the cluster
+    const uint32_t nb = s_h_u32 + nxt * (SL_ROWS * H_STRIDE * 2);
+#pragma unroll
+    for (int r = 0; r < NCTA; ++r) {
+      st_cluster_u32(map_to_cta(nb + slot_a, r), push_a);
+      st_cluster_u32(map_to_cta(nb + slot_b, r), push_b);
+    }
+    cp_async_wait<SL_RING - 2>();  // this thread's part of step t+1 has landed
+    cluster_barrier();
+  }
+
+  // final state (4, B, H): h, c, n, m
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int gb = (i < 2) ? gb_a : gb_b;
+    const bool ok = (i < 2) ? ok_a : ok_b;
+    if (!ok) continue;
+    const size_t off = (size_t)gb * H + (size_t)head * DH + unit_h + (i & 1);
+    p.state_out[0 * (size_t)B * H + off] = hlast[i];
+    p.state_out[1 * (size_t)B * H + off] = c_[i];
+    p.state_out[2 * (size_t)B * H + off] = n_[i];
+    p.state_out[3 * (size_t)B * H + off] = m_[i];
+  }
+}
+
+template <int DH>
+static int launch_slstm(const xl_slstm_params* p, cudaStream_t st) {
+  constexpr int NCTA = DH / SL_UNITS;
+  const size_t smem = 2 * SL_ROWS * (DH + 8) * 2 + (size_t)SL_RING * SL_WX_STEP_BYTES;
+  XL_CUDA_TRY(cudaFuncSetAttribute(slstm_forward_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(NCTA, p->NH, (p->B + SL_ROWS - 1) / SL_ROWS);
+  cfg.blockDim = dim3(SL_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = NCTA;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  XL_CUDA_TRY(cudaLaunchKernelEx(&cfg, slstm_forward_kernel<DH>, *p));
+  return check_launch("xl_slstm_forward");
+}
+
+}  // namespace xl
+
+extern "C" int xl_slstm_forward(const xl_slstm_params* p, void* cuda_stream) {
+  using namespace xl;
+  if (!p || !p->wx || !p->R || !p->bias || !p->h_out || !p->state_out) return XL_ERR_NULL_POINTER;
+  if (p->B <= 0 || p->S <= 0 || p->NH <= 0) return XL_ERR_BAD_SHAPE;
+  if (p->dtype != XL_BF16) return XL_ERR_BAD_DTYPE;
+  if (p->cu_seqlens && p->num_docs <= 0) return XL_ERR_BAD_SHAPE;
+  if (p->NH > 65535 || (p->B + SL_ROWS - 1) / SL_ROWS > 65535) return XL_ERR_TOO_LARGE;
+  if (!aligned16(p->wx) || (reinterpret_cast<uintptr_t>(p->h_out) & 3u)) return XL_ERR_BAD_ALIGNMENT;
+  if (p->state0 && p->state0 == p->state_out) return XL_ERR_ALIASING;
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  switch (p->DH) {
+    case 64: return launch_slstm<64>(p, st);
+    case 128: return launch_slstm<128>(p, st);
+    case 256: return launch_slstm<256>(p, st);
+    default: return XL_ERR_UNSUPPORTED;
+  }
+}

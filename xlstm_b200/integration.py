@@ -1,0 +1,125 @@
+"""Hooks that put the sm_100a kernels behind the reference package's own selectors.
+
+``install_mlstm_backend()``  makes ``import mlstm_kernels.torch.backend_module`` resolve to
+:mod:`xlstm_b200.backend_module` when the upstream package is not installed, or adds the b200
+kernel names to the upstream registries when it is.  After that
+``xLSTMLargeConfig(chunkwise_kernel="chunkwise--b200", sequence_kernel="native_sequence__b200",
+step_kernel="b200", mode="inference")`` selects the CUDA kernels and ``xlstm/xlstm_large/model.py``
+runs unchanged.
+
+``install_slstm_backend()`` teaches ``xlstm.blocks.slstm.cell.sLSTMCell`` the backend name
+``"b200"`` (the switch at ``cell.py:777-788``), so ``sLSTMLayerConfig(backend="b200")`` and
+``xLSTMBlockStack`` run unchanged.
+"""
+from __future__ import annotations
+
+import importlib
+import importlib.util
+import sys
+import types
+
+import torch
+
+from . import backend_module, ops
+
+
+def install_mlstm_backend() -> str:
+    """Returns "shim" when this package now provides ``mlstm_kernels.torch.backend_module`` and
+    "registered" when the b200 kernels were added to an installed upstream package."""
+    existing = sys.modules.get("mlstm_kernels.torch.backend_module")
+    if existing is backend_module:
+        return "shim"
+    if existing is None and importlib.util.find_spec("mlstm_kernels") is not None:
+        try:
+            up = importlib.import_module("mlstm_kernels.torch")
+            for attr, kind in (("_mlstm_chunkwise_kernel_registry", "chunkwise"), ("_mlstm_sequence_kernel_registry", "sequence"),
+                               ("_mlstm_step_kernel_registry", "step")):
+                reg = getattr(up, attr, None)
+                if isinstance(reg, dict):
+                    reg.update({n: f for n, f in backend_module._registry[kind].items() if "b200" in n})
+            return "registered"
+        except Exception:
+            pass
+    pkg = types.ModuleType("mlstm_kernels")
+    pkg.__path__ = []  # mark as package
+    sub = types.ModuleType("mlstm_kernels.torch")
+    sub.__path__ = []
+    sub.backend_module = backend_module
+    sub.get_available_mlstm_kernels = backend_module.get_available_mlstm_kernels
+    sub.get_available_mlstm_step_kernels = backend_module.get_available_mlstm_step_kernels
+    sub.get_available_mlstm_sequence_kernels = backend_module.get_available_mlstm_sequence_kernels
+    pkg.torch = sub
+    sys.modules["mlstm_kernels"] = pkg
+    sys.modules["mlstm_kernels.torch"] = sub
+    sys.modules["mlstm_kernels.torch.backend_module"] = backend_module
+    return "shim"
+
+
+_slstm_installed = False
+
+
+def install_slstm_backend():
+    """Adds backend="b200" to the reference's sLSTMCell switch and returns the new cell class."""
+    global _slstm_installed
+    cell_mod = importlib.import_module("xlstm.blocks.slstm.cell")
+    if _slstm_installed:
+        return cell_mod.sLSTMCell_b200
+
+    class sLSTMCell_b200(cell_mod.sLSTMCellBase):
+        """sLSTM cell on the persistent sm_100a kernel.  Parameters keep the reference's external layout
+        (R: (NH, DH_in, 4, DH_out), bias: (NH, 4, DH); ``cell.py:234-261``), which is also what the kernel
+        reads, so the four layout converters are the identity."""
+
+        config_class = cell_mod.sLSTMCellConfig
+
+        def __init__(self, config, skip_backend_init: bool = False):
+            super().__init__(config)
+            if config.function != "slstm":
+                raise ValueError("the b200 backend implements function='slstm' only")
+            self._cu_seqlens = None
+
+        def set_document_offsets(self, cu_seqlens):
+            """Document boundaries on the flattened (B*S) axis for the next forward calls (None to clear);
+            h, c, n, m are reset inside the kernel at each boundary."""
+            self._cu_seqlens = cu_seqlens
+
+        def _cast_inputs(self, x, state):
+            if self.config.input_shape != "BSGNH" or self.config.output_shape != "BNSH":
+                raise ValueError("the b200 backend supports input_shape='BSGNH' and output_shape='BNSH'")
+            wdt = self.config.torch_dtype_w
+            if wdt != torch.bfloat16:
+                raise ValueError("the b200 sLSTM kernel computes on bfloat16 inputs: use dtype='bfloat16'")
+            R = self._recurrent_kernel_.reshape(self.config.num_heads, self.head_dim, self.config.num_gates, self.head_dim)
+            b = self._bias_.reshape(self.config.num_heads, self.config.num_gates, self.head_dim)
+            return x.to(wdt), R.to(wdt), b.float(), (None if state is None else state.float())
+
+        def forward(self, input, state=None, lengths=None):
+            self._check_input(input)
+            if state is not None:
+                assert state.shape == (self.config.num_states, input.shape[0], self.config.hidden_size)
+            x, R, b, s0 = self._cast_inputs(input, state)
+            out, last = ops.slstm_forward(x, R, b, s0, cu_seqlens=self._cu_seqlens)
+            if torch.is_autocast_enabled():
+                return out, last
+            return out.to(input.dtype), last.to(input.dtype)
+
+        def step(self, input, state):
+            out, last = self.forward(input, state)
+            return out, last
+
+        def _impl(self, training, input, state):
+            raise NotImplementedError("the b200 backend overrides forward(); it never materialises all states")
+
+        _impl_step = _impl
+
+    cell_mod.sLSTMCell_b200 = sLSTMCell_b200
+    original_new = cell_mod.sLSTMCell.__new__
+
+    def __new__(cls, config, skip_backend_init: bool = False):
+        if config.backend == "b200":
+            return sLSTMCell_b200(config, skip_backend_init=skip_backend_init)
+        return original_new(cls, config, skip_backend_init=skip_backend_init)
+
+    cell_mod.sLSTMCell.__new__ = staticmethod(__new__)
+    _slstm_installed = True
+    return sLSTMCell_b200

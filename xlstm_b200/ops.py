@@ -1,0 +1,234 @@
+"""Tensor-level entry points: unpack torch tensors, call the C ABI on the current CUDA stream.
+
+PyTorch is used for device memory and streams only; all arithmetic happens in
+the sm_100a kernels behind ``include/xlstm_b200.h``.  Nothing here falls back
+to PyTorch math: unsupported inputs raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._lib import MlstmSeqParams, MlstmStepParams, SlstmParams, XL_BF16, XL_F32, check, lib
+
+_DTYPES = {torch.float32: XL_F32, torch.bfloat16: XL_BF16}
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 word that kernels set when one of their bounded waits expires."""
+    idx = torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    if idx not in _status_words:
+        _status_words[idx] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{idx}")
+    return _status_words[idx]
+
+
+def check_device_status(device=None) -> None:
+    """Synchronising check of the status word; raises if a kernel gave up on a wait."""
+    w = status_word(device if device is not None else torch.cuda.current_device())
+    v = int(w.item())
+    if v != 0:
+        w.zero_()
+        raise RuntimeError(f"xlstm_b200 kernel reported device status {v} (a bounded wait expired)")
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("xlstm_b200 kernels need CUDA tensors (there is no CPU path)")
+
+
+def _last_contig(t: torch.Tensor) -> torch.Tensor:
+    return t if t.stride(-1) == 1 else t.contiguous()
+
+
+def _gate(t: torch.Tensor) -> torch.Tensor:
+    return t if t.dtype == torch.float32 else t.float()
+
+
+def prepare_cu_seqlens(cu_seqlens, B: int, S: int, device) -> tuple[torch.Tensor, int]:
+    """Validate document offsets on the host and return (int32 device tensor, num_docs).
+
+    Offsets index the flattened (B*S) token axis; they must start at 0, end at B*S, be
+    non-decreasing, and no document may straddle two rows.  A tensor that already lives on
+    the device is trusted as is (validating it would force a synchronisation).
+    """
+    if torch.is_tensor(cu_seqlens) and cu_seqlens.is_cuda:
+        if cu_seqlens.dtype != torch.int32:
+            raise ValueError("cu_seqlens on the device must be int32")
+        return cu_seqlens.contiguous(), cu_seqlens.numel() - 1
+    cu = [int(x) for x in (cu_seqlens.tolist() if torch.is_tensor(cu_seqlens) else cu_seqlens)]
+    if len(cu) < 2 or cu[0] != 0 or cu[-1] != B * S:
+        raise ValueError(f"cu_seqlens must start at 0 and end at B*S={B * S}, got {cu[:1]}..{cu[-1:]}")
+    for a, b in zip(cu[:-1], cu[1:]):
+        if b < a:
+            raise ValueError("cu_seqlens must be non-decreasing")
+        if b > a and (a // S) != ((b - 1) // S):
+            raise ValueError(f"document [{a},{b}) straddles two rows of length {S}")
+    return torch.tensor(cu, dtype=torch.int32, device=device), len(cu) - 1
+
+
+def mlstm_sequence(q, k, v, i, f, c_initial=None, n_initial=None, m_initial=None, cu_seqlens=None,
+                   eps: float = 1e-6, kernel: str = "auto"):
+    """mLSTM over a sequence.  q,k (B,NH,S,DHQK), v (B,NH,S,DHV), i,f (B,NH,S).
+
+    kernel: "chunkwise" (tcgen05), "recurrent" (fp32 recurrence) or "auto" (chunkwise when the
+    shape/dtype is covered by it, else recurrent).  Returns h (B,NH,S,DHV) in q's dtype and the final
+    fp32 state (c,n,m) with one row per document: c (N,NH,DHQK,DHV), n (N,NH,DHQK), m (N,NH,1).
+    """
+    _require_cuda(q, k, v, i, f, c_initial, n_initial, m_initial)
+    if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError(f"q,k,v must share a dtype in {list(_DTYPES)}, got {q.dtype},{k.dtype},{v.dtype}")
+    B, NH, S, DHQK = q.shape
+    DHV = v.shape[-1]
+    if k.shape != q.shape or v.shape[:3] != q.shape[:3] or i.shape != (B, NH, S) or f.shape != (B, NH, S):
+        raise ValueError("inconsistent shapes for q,k,v,i,f")
+    dev = q.device
+    q, k, v = _last_contig(q), _last_contig(k), _last_contig(v)
+    i, f = _gate(i), _gate(f)
+    if i.stride() != f.stride():
+        i, f = i.contiguous(), f.contiguous()
+    chunk_ok = (q.dtype == torch.bfloat16 and DHQK in (64, 128, 256) and DHV % 128 == 0
+                and all(s % 8 == 0 for t in (q, k, v) for s in t.stride()[:3])
+                and all(t.data_ptr() % 16 == 0 for t in (q, k, v)))
+    if kernel == "auto":
+        kernel = "chunkwise" if chunk_ok else "recurrent"
+    if kernel not in ("chunkwise", "recurrent"):
+        raise ValueError(f"unknown kernel {kernel!r}")
+
+    cu_dev, nd = (None, B)
+    if cu_seqlens is not None:
+        cu_dev, nd = prepare_cu_seqlens(cu_seqlens, B, S, dev)
+    have0 = c_initial is not None
+    if have0:
+        if n_initial is None or m_initial is None:
+            raise ValueError("c_initial, n_initial and m_initial must be given together")
+        c0 = c_initial.float().contiguous()
+        n0 = n_initial.float().contiguous()
+        m0 = m_initial.float().contiguous()
+        if c0.shape != (nd, NH, DHQK, DHV) or n0.shape != (nd, NH, DHQK) or m0.numel() != nd * NH:
+            raise ValueError("initial state shapes must be (N,NH,DHQK,DHV), (N,NH,DHQK), (N,NH[,1])")
+    h = torch.empty(B, NH, S, DHV, dtype=q.dtype, device=dev)
+    c = torch.empty(nd, NH, DHQK, DHV, dtype=torch.float32, device=dev)
+    n = torch.empty(nd, NH, DHQK, dtype=torch.float32, device=dev)
+    m = torch.empty(nd, NH, 1, dtype=torch.float32, device=dev)
+
+    p = MlstmSeqParams()
+    p.q, p.k, p.v, p.h = q.data_ptr(), k.data_ptr(), v.data_ptr(), h.data_ptr()
+    p.igate, p.fgate = i.data_ptr(), f.data_ptr()
+    if have0:
+        p.c0, p.n0, p.m0 = c0.data_ptr(), n0.data_ptr(), m0.data_ptr()
+    p.c_out, p.n_out, p.m_out = c.data_ptr(), n.data_ptr(), m.data_ptr()
+    p.cu_seqlens = cu_dev.data_ptr() if cu_dev is not None else None
+    p.status = status_word(dev).data_ptr()
+    p.B, p.NH, p.S, p.DHQK, p.DHV, p.num_docs = B, NH, S, DHQK, DHV, nd
+    p.q_sb, p.q_sh, p.q_st = q.stride()[:3]
+    p.k_sb, p.k_sh, p.k_st = k.stride()[:3]
+    p.v_sb, p.v_sh, p.v_st = v.stride()[:3]
+    p.h_sb, p.h_sh, p.h_st = h.stride()[:3]
+    p.g_sb, p.g_sh, p.g_st = i.stride()
+    p.eps, p.dtype = eps, _DTYPES[q.dtype]
+    fn = lib().xl_mlstm_chunkwise if kernel == "chunkwise" else lib().xl_mlstm_recurrent
+    with torch.cuda.device(dev):
+        check(fn(C.byref(p), _stream_ptr(dev)), f"xl_mlstm_{kernel}")
+    return h, (c, n, m)
+
+
+def mlstm_step(q, k, v, i, f, c, n, m, slot=None, eps: float = 1e-6, inplace: bool = True):
+    """One decode step.  q,k (B,NH,DHQK), v (B,NH,DHV), i,f (B,NH[,1]); state pool c (N,NH,DHQK,DHV),
+    n (N,NH,DHQK), m (N,NH[,1]) fp32; ``slot`` (B,) int32 selects each stream's pool row (default: row b).
+
+    With ``inplace`` the large C state is updated where it lives and the SAME tensor object is returned,
+    so a caller that copies the returned state back into its own buffers (xlstm_large/model.py:221-225)
+    performs a no-op for C.  n and m are always returned as new small tensors (several thread blocks
+    read the old values while one writes).  Without a pool (c is None) the state starts from zero.
+    """
+    _require_cuda(q, k, v, i, f, c, n, m)
+    B, NH, DHQK = q.shape
+    DHV = v.shape[-1]
+    dev = q.device
+    q, k, v = _last_contig(q), _last_contig(k), _last_contig(v)
+    i, f = _gate(i).reshape(B, NH), _gate(f).reshape(B, NH)
+    if i.stride() != f.stride():
+        i, f = i.contiguous(), f.contiguous()
+    have = c is not None
+    if have:
+        if c.dtype != torch.float32 or not c.is_contiguous() or not n.is_contiguous():
+            raise ValueError("state pool must be contiguous fp32")
+        N = c.shape[0]
+        m = m.reshape(N, NH, 1)
+        if not m.is_contiguous():
+            m = m.contiguous()
+        if slot is None and N != B:
+            raise ValueError("without `slot` the state pool must have one row per stream")
+    else:
+        N = B
+    c_out = c if (have and inplace) else torch.empty(N, NH, DHQK, DHV, dtype=torch.float32, device=dev)
+    if have and not inplace and slot is not None:
+        c_out.copy_(c)  # rows not addressed by `slot` keep their contents
+    n_out = n.clone() if (have and slot is not None) else torch.empty(N, NH, DHQK, dtype=torch.float32, device=dev)
+    m_out = m.clone() if (have and slot is not None) else torch.empty(N, NH, 1, dtype=torch.float32, device=dev)
+    h = torch.empty(B, NH, DHV, dtype=q.dtype, device=dev)
+
+    p = MlstmStepParams()
+    p.q, p.k, p.v, p.h = q.data_ptr(), k.data_ptr(), v.data_ptr(), h.data_ptr()
+    p.igate, p.fgate = i.data_ptr(), f.data_ptr()
+    if have:
+        p.c_in, p.n_in, p.m_in = c.data_ptr(), n.data_ptr(), m.data_ptr()
+    p.c_out, p.n_out, p.m_out = c_out.data_ptr(), n_out.data_ptr(), m_out.data_ptr()
+    p.slot = slot.data_ptr() if slot is not None else None
+    p.B, p.NH, p.DHQK, p.DHV = B, NH, DHQK, DHV
+    p.q_sb, p.q_sh = q.stride()[:2]
+    p.k_sb, p.k_sh = k.stride()[:2]
+    p.v_sb, p.v_sh = v.stride()[:2]
+    p.h_sb, p.h_sh = h.stride()[:2]
+    p.g_sb, p.g_sh = i.stride()
+    p.eps, p.dtype = eps, _DTYPES[q.dtype]
+    with torch.cuda.device(dev):
+        check(lib().xl_mlstm_step(C.byref(p), _stream_ptr(dev)), "xl_mlstm_step")
+    return h, (c_out, n_out, m_out)
+
+
+def slstm_forward(wx, R, bias, state0=None, cu_seqlens=None):
+    """sLSTM over a sequence.  wx (B,S,4*H) gate-major [i|f|z|o] each (NH,DH); R (NH,DH,4,DH); bias (NH,4,DH);
+    state0 (4,B,H) ordered (h,c,n,m) or None.  Returns h (B,NH,S,DH) in wx's dtype and the final fp32 state."""
+    _require_cuda(wx, R, bias, state0)
+    if wx.dtype != torch.bfloat16:
+        raise ValueError("the sLSTM kernel computes on bf16 inputs (fp32 state); cast wx and R to bfloat16")
+    B, S, H4 = wx.shape
+    NH, DH = R.shape[0], R.shape[1]
+    H = NH * DH
+    if H4 != 4 * H or R.shape != (NH, DH, 4, DH) or bias.numel() != NH * 4 * DH:
+        raise ValueError("inconsistent sLSTM shapes")
+    dev = wx.device
+    wx = wx.contiguous()
+    R = R.to(torch.bfloat16).contiguous()
+    bias = bias.float().contiguous()
+    out = torch.empty(B, NH, S, DH, dtype=wx.dtype, device=dev)
+    st = torch.empty(4, B, H, dtype=torch.float32, device=dev)
+    p = SlstmParams()
+    p.wx, p.R, p.bias = wx.data_ptr(), R.data_ptr(), bias.data_ptr()
+    if state0 is not None:
+        s0 = state0.float().contiguous()
+        if s0.shape != (4, B, H):
+            raise ValueError("state0 must be (4,B,H)")
+        p.state0 = s0.data_ptr()
+    p.h_out, p.state_out = out.data_ptr(), st.data_ptr()
+    nd = 0
+    if cu_seqlens is not None:
+        cu_dev, nd = prepare_cu_seqlens(cu_seqlens, B, S, dev)
+        p.cu_seqlens = cu_dev.data_ptr()
+    p.status = status_word(dev).data_ptr()
+    p.B, p.S, p.NH, p.DH, p.num_docs, p.dtype = B, S, NH, DH, nd, XL_BF16
+    with torch.cuda.device(dev):
+        check(lib().xl_slstm_forward(C.byref(p), _stream_ptr(dev)), "xl_slstm_forward")
+    return out, st
