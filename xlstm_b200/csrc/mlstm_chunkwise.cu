@@ -2,21 +2,35 @@
 //
 // One CTA owns a 128-column slice (of DHV) of one (document, head) and walks that document's 64-token
 // chunks in order.  Its slice of the matrix state lives TRANSPOSED in tensor memory for the whole
-// document, C^T[dv, dqk] (128 lanes x DHQK fp32 columns), and is never written to HBM between chunks.
-// Per chunk, with b_j the in-chunk cumulative log forget gate, a'_j = i_j - b_j, mu_j = max(m_prev,
-// max_{l<=j} a'_l), mu* = mu_63 and g = b_63 (equivalent to xlstm/blocks/mlstm/backends.py:173-258):
+// document, T[dv, dqk] (128 lanes x DHQK fp32 columns), and is never written to HBM between chunks.
 //
-//   S      = Q K^T                               UMMA  M=64  N=64   K=DHQK   (both operands K-major, TMA tiles)
-//   P_jl   = S_jl/sqrt(DHQK) * exp(a'_l - mu_j)  (l <= j)   CUDA cores, written as bf16 K-major tile
-//   H^T    = Cb^T (r_j q~_j)^T                   UMMA  M=128 N=64   K=DHQK   A = bf16 copy of C^T in TMEM,
-//                                                                           r_j = exp(m_prev - mu_j)
-//   H^T   += V^T P^T                             UMMA  M=128 N=64   K=64     A = V tile used MN-major
-//   C^T    = exp(m_prev - mu*) C^T + (w V)^T K   UMMA  M=128 N=DHQK K=64     w_l = exp(a'_l - mu*), both MN-major
-//   h_j    = H_j / (max(|q~_j.n_j|, exp(-(b_j + mu_j))) + eps) ,   m_new = g + mu*
+// Math per chunk (equivalent to xlstm/blocks/mlstm/backends.py:173-258).  With b_j the in-chunk cumulative
+// log forget gate, a'_j = i_j - b_j, mu_j = max(m_prev, max_{l<=j} a'_l), mu* = mu_63, g = b_63:
+//   S    = Q K^T                                    P_jl = S_jl/sqrt(DHQK) * exp(a'_l - mu_j)   (l <= j)
+//   H_j  = r_j q~_j C_prev + sum_l P_jl v_l          r_j  = exp(m_prev - mu_j)
+//   C    = exp(m_prev - mu*) C_prev + sum_l w_l k_l v_l^T ,  n likewise ,   w_l = exp(a'_l - mu*)
+//   h_j  = H_j / (max(|r_j q~_j.n_prev + sum_l P_jl|, exp(-(b_j + mu_j))) + eps) ,   m_new = g + mu*
+// The decay of C is applied lazily: tensor memory holds T with C = exp(rho) T; rho accumulates the log decay
+// and is folded into r_j and w_l, and T is rescaled in place only when rho drops below -30.
 //
-// All UMMAs run with M = 128 except S.  q, k, v tiles arrive by TMA (128-byte swizzle) straight from the
-// caller's strided (B, NH, S, D) views; documents are chunked from their own first token, so a chunk never
-// straddles a document boundary and the tail chunk is masked (i = -inf, log f = 0) instead of padded.
+// Tensor-core work per chunk (all operands bf16, fp32 accumulation in tensor memory):
+//   S    [64 x 64]     = Q K^T                  M=64  N=64   K=DHQK  A,B K-major TMA tiles
+//   H^T  [128 x 64]    = Tb (r q~)^T            M=128 N=64   K=DHQK  A = bf16 copy of T in tensor memory
+//   H^T               += V^T P^T                M=128 N=64   K=64    A = V tile used MN-major, B = P tile
+//   T    [128 x DHQK] += (w V)^T K              M=128 N=DHQK K=64    both MN-major
+//   qn   [64 x 8]      = (r q~) [n_hi n_lo]^T   M=64  N=8    K=DHQK  normaliser dot product, n split hi/lo
+//   nu   [DHQK x 8]    = K^T [w_hi w_lo]^T      M=64  N=8    K=64    n update, per 64-feature block
+// The two N=8 products land on the odd 16-lane halves of the S columns (an M=64 accumulator only occupies
+// the even halves), so the 512 tensor-memory columns are exactly: T 256 | Tb 128 | H^T 64 | S,qn,nu 64.
+//
+// Warp roles (448 threads): warps 0-3 gate group (gate scans, r-scaled q, P, denominators, n),
+// warps 4-7 state group (T -> bf16 copy / lazy rescale, w-scaled v), warps 8-11 epilogue group
+// (H^T -> normalised h in global memory), warp 12 issues every UMMA, warp 13 issues the TMA loads.
+// Groups hand work to each other through mbarriers only; every wait is bounded.
+//
+// q, k, v tiles arrive by TMA (128-byte swizzle) straight from the caller's strided (B, NH, S, D) views;
+// documents are chunked from their own first token, so a chunk never straddles a document boundary and the
+// tail chunk is masked (i = -inf, log f = 0) instead of padded.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -25,10 +39,21 @@ namespace xl {
 
 constexpr int CW_L = 64;         // tokens per chunk
 constexpr int CW_DV = 128;       // value columns per CTA (UMMA M)
-constexpr int CW_THREADS = 128;  // 4 warps; warp w owns TMEM lanes [32w, 32w+32)
+constexpr int CW_THREADS = 448;  // 14 warps, see roles above
 constexpr int CW_STAGES = 2;
 constexpr int CW_BOX_BYTES = 64 * 128;  // one TMA box: 64 rows x 64 bf16
 constexpr uint32_t CW_TMEM_COLS = 512;
+constexpr float CW_RESCALE_BELOW = -30.f;  // lazy-decay frame limit (natural log)
+constexpr float CW_LOG2E = 1.4426950408889634f;
+
+enum CwBar {  // mbarrier indices
+  BAR_FULL0 = 0, BAR_FULL1, BAR_EMPTY0, BAR_EMPTY1,
+  BAR_S, BAR_DN, BAR_H, BAR_C,                   // UMMA warp -> consumers (tcgen05.commit)
+  BAR_GATES, BAR_QS, BAR_NMAT, BAR_P, BAR_INV,   // gate group -> others
+  BAR_CB, BAR_VH,                                // state group -> UMMA warp
+  BAR_HFREE,                                     // epilogue group -> UMMA warp / gate group
+  BAR_COUNT
+};
 
 template <int DHQK>
 struct CwLayout {
@@ -40,16 +65,18 @@ struct CwLayout {
   static constexpr int OFF_QS = CW_STAGES * STAGE_BYTES;       // r_j-scaled q
   static constexpr int OFF_VH = OFF_QS + Q_BYTES;              // w_l-scaled v
   static constexpr int OFF_P = OFF_VH + V_BYTES;               // P tile
-  static constexpr int OFF_F32 = OFF_P + CW_BOX_BYTES;         // small fp32 arrays
-  static constexpr int N_F32 = 7 * CW_L + DHQK + 8;
+  static constexpr int OFF_NMAT = OFF_P + CW_BOX_BYTES;        // [8 x DHQK] bf16: rows n_hi, n_lo, zeros
+  static constexpr int OFF_WMAT = OFF_NMAT + NKB * 1024;       // 2 x [8 x 64] bf16: rows w_hi, w_lo, zeros
+  static constexpr int OFF_F32 = OFF_WMAT + 2 * 1024;
+  static constexpr int N_F32 = 4 * CW_L + 2 * 2 * CW_L + DHQK + 16 + 8;
   static constexpr int OFF_BAR = OFF_F32 + N_F32 * 4;          // mbarriers (8-byte aligned)
-  static constexpr int TOTAL = OFF_BAR + 8 * 8;
+  static constexpr int TOTAL = OFF_BAR + BAR_COUNT * 8 + 16;
   static constexpr int DYN_SMEM = TOTAL + 1024;                // slack to align the base to 1024 B
   // tensor-memory column map
-  static constexpr uint32_t T_C = 0;            // C^T fp32           DHQK columns
-  static constexpr uint32_t T_CB = 256;         // bf16 copy of C^T   DHQK/2 columns
-  static constexpr uint32_t T_H = 384;          // H^T accumulator    64 columns
-  static constexpr uint32_t T_S = 448;          // S accumulator      64 columns (M=64: lanes 0-15 of each warp)
+  static constexpr uint32_t T_C = 0;            // T (C^T in the lazy frame), fp32   DHQK columns
+  static constexpr uint32_t T_CB = 256;         // bf16 copy of T                    DHQK/2 columns
+  static constexpr uint32_t T_H = 384;          // H^T accumulator                   64 columns
+  static constexpr uint32_t T_S = 448;          // S (even 16-lane halves); qn, nu (odd halves)
 };
 
 struct CwMaps {
@@ -58,6 +85,48 @@ struct CwMaps {
   // ascending stride, which differs between a contiguous (B,NH,S,D) tensor and a transposed (B,S,NH,D) view
   int pos[3][3];  // [q|k|v][token|head|batch]
 };
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_log_sigmoid(float x) { return fminf(x, 0.f) - __logf(1.f + __expf(-fabsf(x))); }
+__device__ __forceinline__ void gate_group_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// 16 bytes of bf16 times a bf16x2 splat, rounded once per product
+__device__ __forceinline__ uint4 scale_bf16x8(uint4 raw, __nv_bfloat162 s) {
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&raw);
+  p[0] = __hmul2(p[0], s);
+  p[1] = __hmul2(p[1], s);
+  p[2] = __hmul2(p[2], s);
+  p[3] = __hmul2(p[3], s);
+  return raw;
+}
+
+// byte offset of element (row, col) in an [rows x 64] bf16 box with 128-byte swizzle
+__device__ __forceinline__ uint32_t sw128_off(int row, int col) {
+  return (uint32_t)(row * 128 + ((((col >> 3) ^ (row & 7)) << 4) | ((col & 7) << 1)));
+}
+
+// Optional per-role timestamps of one CTA (debug builds only; compiled out otherwise).
+#ifdef XL_CW_TIMELINE
+__device__ unsigned long long g_cw_timeline[5][256][12];
+#define CW_TL(role, ev)                                                                                         \
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && chunk < 256 && (threadIdx.x & 31) == 0 && (warp & 3) == 0) \
+    g_cw_timeline[role][chunk][ev] = clock64();
+#else
+#define CW_TL(role, ev)
+#endif
+
+// Wait used by the UMMA-issuing warp: after a first expired wait the later ones return at once.
+#define MMA_WAIT(idx, parity) (okm ? mbar_wait(bar0 + 8u * (uint32_t)(idx), (uint32_t)(parity)) : false)
+
+#define CW_WAIT(idx, parity)                                   \
+  if (!mbar_wait(bar0 + 8u * (uint32_t)(idx), (uint32_t)(parity))) { \
+    ok = false;                                                \
+    break;                                                     \
+  }
 
 template <int DHQK>
 __global__ void __launch_bounds__(CW_THREADS, 1)
@@ -69,19 +138,17 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(cw_smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
   float* s_f = reinterpret_cast<float*>(smem + LY::OFF_F32);
-  float* s_b = s_f;                  // b_j
-  float* s_ap = s_f + 1 * CW_L;      // a'_j
-  float* s_mu = s_f + 2 * CW_L;      // mu_j
-  float* s_r = s_f + 3 * CW_L;       // r_j * 1/sqrt(DHQK)
-  float* s_w = s_f + 4 * CW_L;       // w_l
-  float* s_qn = s_f + 5 * CW_L;      // q_j . n_prev (raw q)
-  float* s_inv = s_f + 6 * CW_L;     // 1 / denominator
-  float* s_n = s_f + 7 * CW_L;       // n state, DHQK
-  float* s_tmp = s_n + DHQK;         // 8 scratch words
-  const uint32_t bar_full0 = sbase + LY::OFF_BAR;        // +8*stage
-  const uint32_t bar_s = sbase + LY::OFF_BAR + 16;
-  const uint32_t bar_m2 = sbase + LY::OFF_BAR + 24;
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + LY::OFF_BAR + 32);
+  float* s_b = s_f;                   // b_j                               (gate group private)
+  float* s_apl = s_f + 1 * CW_L;      // a'_j * log2(e)                    (gate group private)
+  float* s_mul = s_f + 2 * CW_L;      // mu_j * log2(e)                    (gate group private)
+  float* s_r = s_f + 3 * CW_L;        // r_j * exp(rho_prev) / sqrt(DHQK)  (gate group private)
+  float* s_w = s_f + 4 * CW_L;        // [2][64] w_l * exp(-rho_new)       (read by the state group)
+  float* s_inv = s_f + 6 * CW_L;      // [2][64] 1 / denominator           (read by the epilogue group)
+  float* s_n = s_f + 8 * CW_L;        // n state in the lazy frame, DHQK
+  float* s_tmp = s_n + DHQK;          // 16 scratch words of the gate group
+  float* s_scal = s_tmp + 16;         // [2][4]: rescale multiplier, rho_new
+  const uint32_t bar0 = sbase + LY::OFF_BAR;
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + LY::OFF_BAR + BAR_COUNT * 8);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int slice = blockIdx.x, head = blockIdx.y, doc = blockIdx.z;
@@ -100,12 +167,13 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     b = doc; tok0 = 0; len = p.S;
   }
   const long long sidx = (long long)doc * p.NH + head;
-  const int dv = warp * 32 + lane;                      // this thread's TMEM lane = value column within the slice
-  const float* c0 = p.c0 ? p.c0 + (sidx * DHQK) * DHV + col0 + dv : nullptr;
-  float* c_out = p.c_out + (sidx * DHQK) * DHV + col0 + dv;
 
   if (len <= 0) {  // empty document: the state passes through unchanged
-    for (int d = 0; d < DHQK; ++d) c_out[(long long)d * DHV] = c0 ? c0[(long long)d * DHV] : 0.f;
+    if (tid < CW_DV) {
+      const float* c0 = p.c0 ? p.c0 + (sidx * DHQK) * DHV + col0 + tid : nullptr;
+      float* c_out = p.c_out + (sidx * DHQK) * DHV + col0 + tid;
+      for (int d = 0; d < DHQK; ++d) c_out[(long long)d * DHV] = c0 ? c0[(long long)d * DHV] : 0.f;
+    }
     if (slice == 0) {
       for (int d = tid; d < DHQK; d += CW_THREADS) p.n_out[sidx * DHQK + d] = p.n0 ? p.n0[sidx * DHQK + d] : 0.f;
       if (tid == 0) p.m_out[sidx] = p.m0 ? p.m0[sidx] : 0.f;
@@ -114,18 +182,22 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   }
   const int nchunks = (int)((len + CW_L - 1) / CW_L);
 
-  // ---- one-time setup: barriers, tensor memory
+  // ---- one-time setup: barriers, tensor memory, constant zero rows of the N=8 operands
   if (tid == 0) {
-    mbar_init(bar_full0, 1);
-    mbar_init(bar_full0 + 8, 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_m2, 1);
+    for (int i = 0; i < BAR_COUNT; ++i) {
+      uint32_t cnt = 128;
+      if (i == BAR_FULL0 || i == BAR_FULL1 || i == BAR_S || i == BAR_DN || i == BAR_H || i == BAR_C) cnt = 1;
+      if (i == BAR_EMPTY0 || i == BAR_EMPTY1) cnt = 257;  // UMMA commit + gate group + state group
+      mbar_init(bar0 + 8u * i, cnt);
+    }
     fence_barrier_init();
     tma_prefetch_desc(&maps.q);
     tma_prefetch_desc(&maps.k);
     tma_prefetch_desc(&maps.v);
   }
-  if (warp == 0) {
+  for (int i = tid; i < (NKB * 1024 + 2 * 1024) / 16; i += CW_THREADS)
+    reinterpret_cast<uint4*>(smem + LY::OFF_NMAT)[i] = make_uint4(0u, 0u, 0u, 0u);
+  if (warp == 12) {
     __syncwarp();
     tmem_alloc(smem_u32(s_tmem), CW_TMEM_COLS);
     tmem_relinquish();
@@ -134,336 +206,524 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
-  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;  // tcgen05.ld/st: a warp reaches lanes 32*(warp%4)..+31
   const uint32_t tC = tmem + LY::T_C + lane_base, tCb = tmem + LY::T_CB + lane_base;
   const uint32_t tH = tmem + LY::T_H + lane_base, tS = tmem + LY::T_S + lane_base;
-
-  auto issue_tma = [&](int chunk) {  // thread 0 only
-    const int st = chunk % CW_STAGES;
-    const uint32_t bar = bar_full0 + 8 * st;
-    const uint32_t dst = sbase + LY::OFF_STAGE + st * LY::STAGE_BYTES;
-    const int t = (int)(tok0 + (long long)chunk * CW_L);
-    mbar_expect_tx(bar, LY::STAGE_BYTES);
-    int cq[4], ck[4], cv[4];
-    cq[maps.pos[0][0]] = t; cq[maps.pos[0][1]] = head; cq[maps.pos[0][2]] = b;
-    ck[maps.pos[1][0]] = t; ck[maps.pos[1][1]] = head; ck[maps.pos[1][2]] = b;
-    cv[maps.pos[2][0]] = t; cv[maps.pos[2][1]] = head; cv[maps.pos[2][2]] = b;
-#pragma unroll
-    for (int kb = 0; kb < NKB; ++kb) {
-      tma_load_4d(dst + kb * CW_BOX_BYTES, &maps.q, bar, kb * 64, cq[1], cq[2], cq[3]);
-      tma_load_4d(dst + LY::Q_BYTES + kb * CW_BOX_BYTES, &maps.k, bar, kb * 64, ck[1], ck[2], ck[3]);
-    }
-#pragma unroll
-    for (int vb = 0; vb < 2; ++vb)
-      tma_load_4d(dst + 2 * LY::Q_BYTES + vb * CW_BOX_BYTES, &maps.v, bar, col0 + vb * 64, cv[1], cv[2], cv[3]);
-  };
-  if (tid == 0) {
-    issue_tma(0);
-    if (nchunks > 1) issue_tma(1);
-  }
-
-  // ---- initial state: C^T into tensor memory, n into shared memory
-#pragma unroll 1
-  for (int cb = 0; cb < DHQK / 32; ++cb) {
-    uint32_t r[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) r[i] = c0 ? __float_as_uint(c0[(long long)(cb * 32 + i) * DHV]) : 0u;
-    tmem_st_x32(tC + cb * 32, r);
-  }
-  tc_wait_st();
-  for (int d = tid; d < DHQK; d += CW_THREADS) s_n[d] = p.n0 ? p.n0[sidx * DHQK + d] : 0.f;
-  float m_prev = p.m0 ? p.m0[sidx] : 0.f;
   const float qscale = rsqrtf((float)DHQK);
-
-  const float* ig = p.igate + b * p.g_sb + head * p.g_sh + tok0 * p.g_st;
-  const float* fg = p.fgate + b * p.g_sb + head * p.g_sh + tok0 * p.g_st;
-  __nv_bfloat16* hout = reinterpret_cast<__nv_bfloat16*>(p.h) + b * p.h_sb + head * p.h_sh + tok0 * p.h_st + col0 + dv;
-
-  // gate prefetch for chunk 0 (threads 0..63 own token j = tid)
-  float g_i = -INFINITY, g_f = 0.f;
-  if (tid < CW_L && tid < len) {
-    g_i = ig[(long long)tid * p.g_st];
-    g_f = fg[(long long)tid * p.g_st];
-  }
-  tc_fence_before();
-  __syncthreads();
-
-  constexpr uint32_t IDESC_S = umma_idesc_bf16(64, 64, 0, 0);
-  constexpr uint32_t IDESC_HI = umma_idesc_bf16(128, 64, 0, 0);
-  constexpr uint32_t IDESC_HV = umma_idesc_bf16(128, 64, 1, 0);
-  constexpr uint32_t IDESC_C = umma_idesc_bf16(128, DHQK, 1, 1);
-
   bool ok = true;
-#pragma unroll 1
-  for (int chunk = 0; chunk < nchunks; ++chunk) {
-    const int st = chunk % CW_STAGES;
-    const uint32_t par_full = (uint32_t)(chunk / CW_STAGES) & 1u, par = (uint32_t)chunk & 1u;
-    const uint32_t s_q = sbase + LY::OFF_STAGE + st * LY::STAGE_BYTES, s_k = s_q + LY::Q_BYTES, s_v = s_k + LY::Q_BYTES;
-    const long long rem = len - (long long)chunk * CW_L;
-    const int len_c = rem < CW_L ? (int)rem : CW_L;
 
-    // this chunk's gates (prefetched), then prefetch the next chunk's
-    const float cur_i = g_i, cur_f = g_f;
-    {
-      const long long jn = (long long)(chunk + 1) * CW_L + tid;
-      g_i = -INFINITY; g_f = 0.f;
-      if (tid < CW_L && jn < len) {
-        g_i = ig[jn * p.g_st];
-        g_f = fg[jn * p.g_st];
-      }
-    }
-
-    // (A) operands of this chunk have landed
-    if (!mbar_wait(bar_full0 + 8 * st, par_full)) { ok = false; break; }
-
-    // (B) S = Q K^T
-    if (tid == 0) {
-      tc_fence_after();
-#pragma unroll
-      for (int kb = 0; kb < NKB; ++kb)
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const uint64_t ad = umma_desc_sw128(s_q + kb * CW_BOX_BYTES + kk * 32, 16, 1024);
-          const uint64_t bd = umma_desc_sw128(s_k + kb * CW_BOX_BYTES + kk * 32, 16, 1024);
-          umma_ss(tmem + LY::T_S, ad, bd, IDESC_S, (kb | kk) != 0);
-        }
-      umma_commit(bar_s);
-    }
-
-    // (C) gate scans over the chunk (threads 0..63 carry token j = tid; all threads run the shuffles)
-    float lf = (tid < len_c) ? log_sigmoid(cur_f) : 0.f;
-    float bj = lf;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const float t = __shfl_up_sync(0xffffffffu, bj, o);
-      if (lane >= o) bj += t;
-    }
-    if (tid == 31) s_tmp[0] = bj;
-    __syncthreads();
-    if (warp == 1) bj += s_tmp[0];
-    const float ap = (tid < len_c) ? cur_i - bj : -INFINITY;
-    float cm = ap;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const float t = __shfl_up_sync(0xffffffffu, cm, o);
-      if (lane >= o) cm = fmaxf(cm, t);
-    }
-    if (tid == 31) s_tmp[1] = cm;
-    __syncthreads();
-    if (warp == 1) cm = fmaxf(cm, s_tmp[1]);
-    const float mu = fmaxf(m_prev, cm);
-    if (tid < CW_L) {
-      s_b[tid] = bj;
-      s_ap[tid] = ap;
-      s_mu[tid] = mu;
-      s_r[tid] = expf(m_prev - mu) * qscale;
-    }
-    if (tid == CW_L - 1) { s_tmp[2] = mu; s_tmp[3] = bj; }
-    __syncthreads();
-    const float mu_star = s_tmp[2], gsum = s_tmp[3];
-    if (tid < CW_L) s_w[tid] = expf(ap - mu_star);
-    const float decay = expf(m_prev - mu_star);
-    const float m_new = gsum + mu_star;
-    __syncthreads();
-
-    // (D) r_j-scaled q (bf16, same swizzled layout), q~_j . n_prev, and w_l-scaled v
-    {
-      const int j = tid >> 1, half = tid & 1;
-      const float rj = s_r[j];
-      float dot = 0.f;
-      constexpr int CH = NKB * 4;  // 16-byte pieces per thread
-#pragma unroll 4
-      for (int i = 0; i < CH; ++i) {
-        const int cidx = half * CH + i;
-        const int box = cidx >> 3;
-        const int c = (NKB >= 2) ? ((cidx & 7) ^ (half << 2)) : (cidx & 7);
-        const uint32_t off = box * CW_BOX_BYTES + j * 128 + ((c ^ (j & 7)) << 4);
-        const uint4 raw = *reinterpret_cast<const uint4*>(smem + (s_q - sbase) + off);
-        const float4 n0 = *reinterpret_cast<const float4*>(s_n + box * 64 + c * 8);
-        const float4 n1 = *reinterpret_cast<const float4*>(s_n + box * 64 + c * 8 + 4);
-        const float2 e0 = unpack_bf16x2(raw.x), e1 = unpack_bf16x2(raw.y), e2 = unpack_bf16x2(raw.z), e3 = unpack_bf16x2(raw.w);
-        dot += e0.x * n0.x + e0.y * n0.y + e1.x * n0.z + e1.y * n0.w + e2.x * n1.x + e2.y * n1.y + e3.x * n1.z + e3.y * n1.w;
-        uint4 o;
-        o.x = pack_bf16x2(e0.x * rj, e0.y * rj);
-        o.y = pack_bf16x2(e1.x * rj, e1.y * rj);
-        o.z = pack_bf16x2(e2.x * rj, e2.y * rj);
-        o.w = pack_bf16x2(e3.x * rj, e3.y * rj);
-        *reinterpret_cast<uint4*>(smem + LY::OFF_QS + off) = o;
-      }
-      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-      if (half == 0) s_qn[j] = dot;
-      // v tile: row l = j, this thread's box = half
-      const float wl = s_w[j];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int c = i ^ (half << 2);
-        const uint32_t off = half * CW_BOX_BYTES + j * 128 + ((c ^ (j & 7)) << 4);
-        const uint4 raw = *reinterpret_cast<const uint4*>(smem + (s_v - sbase) + off);
-        const float2 e0 = unpack_bf16x2(raw.x), e1 = unpack_bf16x2(raw.y), e2 = unpack_bf16x2(raw.z), e3 = unpack_bf16x2(raw.w);
-        uint4 o;
-        o.x = pack_bf16x2(e0.x * wl, e0.y * wl);
-        o.y = pack_bf16x2(e1.x * wl, e1.y * wl);
-        o.z = pack_bf16x2(e2.x * wl, e2.y * wl);
-        o.w = pack_bf16x2(e3.x * wl, e3.y * wl);
-        *reinterpret_cast<uint4*>(smem + LY::OFF_VH + off) = o;
-      }
-    }
+  if (warp < 4) {
+    // =========================================================================================== gate group
+    const int g = tid;  // 0..127
+    const float* ig = p.igate + b * p.g_sb + head * p.g_sh + tok0 * p.g_st;
+    const float* fg = p.fgate + b * p.g_sb + head * p.g_sh + tok0 * p.g_st;
+    for (int d = g; d < DHQK; d += 128) s_n[d] = p.n0 ? p.n0[sidx * DHQK + d] : 0.f;
+    auto publish_n = [&](int d, float nv) {  // hi/lo bf16 split of n[d] into rows 0/1 of the N=8 operand
+      const __nv_bfloat16 hi = __float2bfloat16_rn(nv);
+      const __nv_bfloat16 lo = __float2bfloat16_rn(nv - __bfloat162float(hi));
+      unsigned char* box = smem + LY::OFF_NMAT + (d >> 6) * 1024;
+      *reinterpret_cast<__nv_bfloat16*>(box + sw128_off(0, d & 63)) = hi;
+      *reinterpret_cast<__nv_bfloat16*>(box + sw128_off(1, d & 63)) = lo;
+    };
+    for (int d = g; d < DHQK; d += 128) publish_n(d, s_n[d]);
     fence_proxy_async_smem();
+    mbar_arrive(bar0 + 8u * BAR_NMAT);  // operand for chunk 0
+    // warp 0 carries the gate recurrence: lane L owns tokens 2L and 2L+1 of the chunk
+    float m_prev = p.m0 ? p.m0[sidx] : 0.f;
+    float rho = 0.f;
+    float gi0 = -INFINITY, gi1 = -INFINITY, gf0 = 0.f, gf1 = 0.f;
+    if (warp == 0) {
+      const long long t0 = 2 * lane;
+      if (t0 < len) { gi0 = ig[t0 * p.g_st]; gf0 = fg[t0 * p.g_st]; }
+      if (t0 + 1 < len) { gi1 = ig[(t0 + 1) * p.g_st]; gf1 = fg[(t0 + 1) * p.g_st]; }
+    }
+#pragma unroll 1
+    for (int chunk = 0; chunk < nchunks; ++chunk) {
+      const int st = chunk & 1, buf = chunk & 1;
+      const uint32_t par = (uint32_t)chunk & 1u, par_full = (uint32_t)(chunk >> 1) & 1u;
+      const long long rem = len - (long long)chunk * CW_L;
+      const int len_c = rem < CW_L ? (int)rem : CW_L;
+      CW_TL(0, 0);
+      // warp 0 is about to overwrite the gate arrays the other gate-group warps read in their P / denominator passes
+      gate_group_sync();
+      // The state group must be done with the gate data of the previous chunk.  (Waiting one phase back, not two:
+      // an mbarrier parity wait is only meaningful while the producer is at most one phase ahead of the waiter.)
+      if (chunk >= 1) CW_WAIT(BAR_VH, par ^ 1u);
+      if (warp == 0) {
+        // ---- gate scans over the chunk
+        const float ci0 = gi0, ci1 = gi1, cf0 = gf0, cf1 = gf1;
+        {
+          const long long t0 = (long long)(chunk + 1) * CW_L + 2 * lane;
+          gi0 = gi1 = -INFINITY; gf0 = gf1 = 0.f;
+          if (t0 < len) { gi0 = ig[t0 * p.g_st]; gf0 = fg[t0 * p.g_st]; }
+          if (t0 + 1 < len) { gi1 = ig[(t0 + 1) * p.g_st]; gf1 = fg[(t0 + 1) * p.g_st]; }
+        }
+        const int t0 = 2 * lane, t1 = t0 + 1;
+        const float lf0 = (t0 < len_c) ? fast_log_sigmoid(cf0) : 0.f;
+        const float lf1 = (t1 < len_c) ? fast_log_sigmoid(cf1) : 0.f;
+        float incl = lf0 + lf1;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float t = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += t;
+        }
+        const float b1 = incl, b0 = incl - lf1;
+        const float ap0 = (t0 < len_c) ? ci0 - b0 : -INFINITY;
+        const float ap1 = (t1 < len_c) ? ci1 - b1 : -INFINITY;
+        float cmx = fmaxf(ap0, ap1);
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float t = __shfl_up_sync(0xffffffffu, cmx, o);
+          if (lane >= o) cmx = fmaxf(cmx, t);
+        }
+        float prevmax = __shfl_up_sync(0xffffffffu, cmx, 1);
+        if (lane == 0) prevmax = -INFINITY;
+        const float mu0 = fmaxf(m_prev, fmaxf(prevmax, ap0));
+        const float mu1 = fmaxf(m_prev, cmx);
+        const float mu_star = __shfl_sync(0xffffffffu, mu1, 31);
+        const float gsum = __shfl_sync(0xffffffffu, b1, 31);
+        // lazy decay frame: C = exp(rho) T
+        const float cand = rho + (m_prev - mu_star);
+        const bool rescale = cand < CW_RESCALE_BELOW;
+        const float mult = rescale ? __expf(cand) : 1.f;
+        const float rho_new = rescale ? 0.f : cand;
+        *reinterpret_cast<float2*>(s_b + t0) = make_float2(b0, b1);
+        *reinterpret_cast<float2*>(s_apl + t0) = make_float2(ap0 * CW_LOG2E, ap1 * CW_LOG2E);
+        *reinterpret_cast<float2*>(s_mul + t0) = make_float2(mu0 * CW_LOG2E, mu1 * CW_LOG2E);
+        *reinterpret_cast<float2*>(s_r + t0) = make_float2(__expf(m_prev - mu0 + rho) * qscale, __expf(m_prev - mu1 + rho) * qscale);
+        const float w0 = __expf(ap0 - mu_star - rho_new), w1 = __expf(ap1 - mu_star - rho_new);
+        *reinterpret_cast<float2*>(s_w + buf * CW_L + t0) = make_float2(w0, w1);
+        {
+          const __nv_bfloat162 hi = __floats2bfloat162_rn(w0, w1);
+          const float2 hif = __bfloat1622float2(hi);
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(w0 - hif.x, w1 - hif.y);
+          unsigned char* wm = smem + LY::OFF_WMAT + buf * 1024;
+          *reinterpret_cast<__nv_bfloat162*>(wm + sw128_off(0, t0)) = hi;
+          *reinterpret_cast<__nv_bfloat162*>(wm + sw128_off(1, t0)) = lo;
+        }
+        if (lane == 0) { s_scal[buf * 4 + 0] = mult; s_scal[buf * 4 + 1] = rho_new; }
+        m_prev = gsum + mu_star;
+        rho = rho_new;
+      }
+      fence_proxy_async_smem();
+      gate_group_sync();
+      mbar_arrive(bar0 + 8u * BAR_GATES);
+      CW_TL(0, 1);
 
-    // (E) C^T: bf16 copy for the inter-chunk product, then decay in place
+      // ---- r-scaled q, same swizzled layout (thread: row j = g/2, half of the row)
+      CW_WAIT(BAR_FULL0 + st, par_full);
+      if (chunk >= 1) CW_WAIT(BAR_H, par ^ 1u);  // UMMAs of chunk-1 no longer read the scaled-q and P tiles
+      CW_TL(0, 2);
+      {
+        const int j = g >> 1, half = g & 1;
+        const __nv_bfloat162 rr = __float2bfloat162_rn(s_r[j]);
+        const unsigned char* qt = smem + LY::OFF_STAGE + st * LY::STAGE_BYTES;
+        constexpr int CH = NKB * 4;              // 16-byte pieces per thread
+        constexpr int BATCH = CH < 8 ? CH : 8;   // loads first, then stores: the two tiles may not alias in the compiler's eyes
+#pragma unroll
+        for (int i0 = 0; i0 < CH; i0 += BATCH) {
+          uint4 v[BATCH];
+          uint32_t off[BATCH];
+#pragma unroll
+          for (int i = 0; i < BATCH; ++i) {
+            const int cidx = half * CH + i0 + i;
+            const int box = cidx >> 3;
+            const int c = (NKB >= 2) ? ((cidx & 7) ^ (half << 2)) : (cidx & 7);
+            off[i] = box * CW_BOX_BYTES + j * 128 + ((c ^ (j & 7)) << 4);
+            v[i] = *reinterpret_cast<const uint4*>(qt + off[i]);
+          }
+#pragma unroll
+          for (int i = 0; i < BATCH; ++i) *reinterpret_cast<uint4*>(smem + LY::OFF_QS + off[i]) = scale_bf16x8(v[i], rr);
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(bar0 + 8u * BAR_QS);
+      mbar_arrive(bar0 + 8u * (BAR_EMPTY0 + st));  // this thread is done reading the q tile of this stage
+      CW_TL(0, 3);
+
+      // ---- n of the previous chunk: n = mult n + nu, then the hi/lo operand for this chunk's normaliser product
+      if (chunk >= 1) {
+        CW_WAIT(BAR_C, par ^ 1u);
+        tc_fence_after();
+        uint32_t r[32];
+        tmem_ld_x32(tS + 8, r);
+        CW_TL(0, 4);
+        const float mult_last = s_scal[(buf ^ 1) * 4 + 0];
+        tc_wait_ld();
+        if (lane >= 16) {
+#pragma unroll
+          for (int gq = 0; gq < NKB; ++gq) {
+            const int d = 64 * gq + 16 * warp + (lane - 16);
+            const float nv = fmaf(s_n[d], mult_last, __uint_as_float(r[8 * gq]) + __uint_as_float(r[8 * gq + 1]));
+            s_n[d] = nv;
+            publish_n(d, nv);
+          }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(bar0 + 8u * BAR_NMAT);
+      }
+      CW_TL(0, 5);
+
+      // ---- P from S (rows of this warp: j = 16 warp + lane for lanes 0..15)
+      CW_WAIT(BAR_S, par);
+      CW_TL(0, 6);
+      tc_fence_after();
+      const int j = warp * 16 + (lane & 15);
+      const float mulj = s_mul[j];
+      float rowsum = 0.f;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        if (32 * half > 16 * warp + 15) {  // warp-uniform: this half lies wholly above the diagonal
+          if (lane < 16) {
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+              const int c = half * 4 + c4;
+              *reinterpret_cast<uint4*>(smem + LY::OFF_P + j * 128 + ((c ^ (j & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+            }
+          }
+          continue;
+        }
+        uint32_t sv[32];
+        tmem_ld_x32(tS + 32 * half, sv);
+        float4 a4[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a4[i] = *reinterpret_cast<const float4*>(s_apl + 32 * half + 4 * i);
+        tc_wait_ld();
+        if (lane < 16) {
+          uint4 o[4];
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            const int c = half * 4 + c4;
+            o[c4] = make_uint4(0u, 0u, 0u, 0u);
+            if (8 * c <= 16 * warp + 15) {  // warp-uniform: blocks wholly above the diagonal stay zero
+              const float av[8] = {a4[2 * c4].x, a4[2 * c4].y, a4[2 * c4].z, a4[2 * c4].w,
+                                   a4[2 * c4 + 1].x, a4[2 * c4 + 1].y, a4[2 * c4 + 1].z, a4[2 * c4 + 1].w};
+              float e[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int l = c * 8 + i;
+                const float x = __uint_as_float(sv[c4 * 8 + i]) * qscale * ex2_approx(av[i] - mulj);
+                e[i] = (l <= j) ? x : 0.f;
+              }
+              o[c4].x = pack_bf16x2(e[0], e[1]);
+              o[c4].y = pack_bf16x2(e[2], e[3]);
+              o[c4].z = pack_bf16x2(e[4], e[5]);
+              o[c4].w = pack_bf16x2(e[6], e[7]);
+              const float2 f0 = unpack_bf16x2(o[c4].x), f1 = unpack_bf16x2(o[c4].y), f2 = unpack_bf16x2(o[c4].z),
+                           f3 = unpack_bf16x2(o[c4].w);
+              rowsum += (f0.x + f0.y) + (f1.x + f1.y) + (f2.x + f2.y) + (f3.x + f3.y);
+            }
+          }
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            const int c = half * 4 + c4;
+            *reinterpret_cast<uint4*>(smem + LY::OFF_P + j * 128 + ((c ^ (j & 7)) << 4)) = o[c4];
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(bar0 + 8u * BAR_P);
+      CW_TL(0, 7);
+
+      // ---- denominators: the normaliser product sits on lanes 16..31, the row sums on lanes 0..15
+      const float lower = __expf(-(s_b[j] + mulj * (1.f / CW_LOG2E)));
+      CW_WAIT(BAR_DN, par);
+      CW_TL(0, 8);
+      tc_fence_after();
+      {
+        uint32_t dn[8];
+        tmem_ld_x8(tS, dn);
+        tc_wait_ld();
+        const float dot = __shfl_down_sync(0xffffffffu, __uint_as_float(dn[0]) + __uint_as_float(dn[1]), 16);
+        if (chunk >= 1) CW_WAIT(BAR_HFREE, par ^ 1u);  // the epilogue group is done with the previous chunk's s_inv
+        if (lane < 16) s_inv[buf * CW_L + j] = __fdividef(1.f, fmaxf(fabsf(rowsum + dot), lower) + p.eps);
+      }
+      tc_fence_before();
+      mbar_arrive(bar0 + 8u * BAR_INV);
+      CW_TL(0, 9);
+    }
+    // ---- final n, m
+    if (ok) {
+      do {
+        CW_WAIT(BAR_C, (uint32_t)(nchunks - 1) & 1u);
+        tc_fence_after();
+        uint32_t r[32];
+        tmem_ld_x32(tS + 8, r);
+        tc_wait_ld();
+        const int lb = (nchunks - 1) & 1;
+        if (slice == 0 && lane >= 16) {
+          const float mult_last = s_scal[lb * 4 + 0], back = expf(s_scal[lb * 4 + 1]);
+#pragma unroll
+          for (int gq = 0; gq < NKB; ++gq) {
+            const int d = 64 * gq + 16 * warp + (lane - 16);
+            const float nv = fmaf(s_n[d], mult_last, __uint_as_float(r[8 * gq]) + __uint_as_float(r[8 * gq + 1]));
+            p.n_out[sidx * DHQK + d] = nv * back;
+          }
+        }
+        if (slice == 0 && g == 0) p.m_out[sidx] = m_prev;
+      } while (false);
+    }
+  } else if (warp < 8) {
+    // =========================================================================================== state group
+    const int t = tid - 128;
+    const int dv = (warp & 3) * 32 + lane;  // tensor-memory lane = value column within the slice
+    const float* c0 = p.c0 ? p.c0 + (sidx * DHQK) * DHV + col0 + dv : nullptr;
+    float* c_out = p.c_out + (sidx * DHQK) * DHV + col0 + dv;
 #pragma unroll 1
     for (int cb = 0; cb < DHQK / 32; ++cb) {
       uint32_t r[32];
-      tmem_ld_x32(tC + cb * 32, r);
-      tc_wait_ld();
-      uint32_t pk[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-      tmem_st_x16(tCb + cb * 16, pk);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * decay);
+      for (int i = 0; i < 32; ++i) r[i] = c0 ? __float_as_uint(c0[(long long)(cb * 32 + i) * DHV]) : 0u;
       tmem_st_x32(tC + cb * 32, r);
     }
     tc_wait_st();
-    tc_fence_before();
-    __syncthreads();
-
-    // (F) H^T = Cb^T (r q~)^T
-    if (tid == 0) {
+    float rho_last = 0.f;
+#pragma unroll 1
+    for (int chunk = 0; chunk < nchunks; ++chunk) {
+      const int st = chunk & 1, buf = chunk & 1;
+      const uint32_t par = (uint32_t)chunk & 1u, par_full = (uint32_t)(chunk >> 1) & 1u;
+      CW_WAIT(BAR_GATES, par);
+      CW_TL(1, 1);
+      const float mult = s_scal[buf * 4 + 0];
+      rho_last = s_scal[buf * 4 + 1];
+      const __nv_bfloat162 ww = __float2bfloat162_rn(s_w[buf * CW_L + (t >> 1)]);
+      if (chunk >= 1) CW_WAIT(BAR_C, par ^ 1u);  // T holds chunk-1; its UMMAs no longer read Tb or the scaled-v tile
+      CW_TL(1, 2);
       tc_fence_after();
-#pragma unroll
-      for (int ks = 0; ks < DHQK / 16; ++ks) {
-        const uint64_t bd = umma_desc_sw128(sbase + LY::OFF_QS + (ks >> 2) * CW_BOX_BYTES + (ks & 3) * 32, 16, 1024);
-        umma_ts(tmem + LY::T_H, tmem + LY::T_CB + ks * 8, bd, IDESC_HI, ks != 0);
-      }
-    }
-
-    // (G) P from S; denominators
-    if (!mbar_wait(bar_s, par)) { ok = false; break; }
-    tc_fence_after();
-    {
-      uint32_t sv[64];
-      {
-        uint32_t t0[32], t1[32];
-        tmem_ld_x32(tS, t0);
-        tmem_ld_x32(tS + 32, t1);
+      // ---- T -> bf16 copy (operand of the inter-chunk product); rescale T only when the frame ran out
+#pragma unroll 1
+      for (int cb = 0; cb < DHQK / 64; ++cb) {
+        uint32_t r0[32], r1[32];
+        tmem_ld_x32(tC + cb * 64, r0);
+        tmem_ld_x32(tC + cb * 64 + 32, r1);
         tc_wait_ld();
+        uint32_t pk[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { sv[i] = t0[i]; sv[32 + i] = t1[i]; }
-      }
-      if (lane < 16) {
-        const int j = warp * 16 + lane;
-        const float muj = s_mu[j];
-        float rowsum = 0.f;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          float e[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int l = c * 8 + i;
-            const float x = __uint_as_float(sv[l]) * qscale * __expf(s_ap[l] - muj);
-            e[i] = (l <= j) ? x : 0.f;
-          }
-          uint4 o;
-          o.x = pack_bf16x2(e[0], e[1]);
-          o.y = pack_bf16x2(e[2], e[3]);
-          o.z = pack_bf16x2(e[4], e[5]);
-          o.w = pack_bf16x2(e[6], e[7]);
-          const float2 f0 = unpack_bf16x2(o.x), f1 = unpack_bf16x2(o.y), f2 = unpack_bf16x2(o.z), f3 = unpack_bf16x2(o.w);
-          rowsum += (f0.x + f0.y) + (f1.x + f1.y) + (f2.x + f2.y) + (f3.x + f3.y);
-          *reinterpret_cast<uint4*>(smem + LY::OFF_P + j * 128 + ((c ^ (j & 7)) << 4)) = o;
+        for (int i = 0; i < 16; ++i) {
+          pk[i] = pack_bf16x2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+          pk[16 + i] = pack_bf16x2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
         }
-        const float qn = rowsum + s_r[j] * s_qn[j];  // s_r already carries 1/sqrt(DHQK)
-        const float den = fmaxf(fabsf(qn), expf(-(s_b[j] + muj))) + p.eps;
-        s_inv[j] = 1.f / den;
-      }
-    }
-    fence_proxy_async_smem();
-    tc_fence_before();
-    __syncthreads();
-
-    // (H) H^T += V^T P^T ;  C^T += (w V)^T K
-    if (tid == 0) {
-      tc_fence_after();
+        tmem_st_x32(tCb + cb * 32, pk);
+        if (mult != 1.f) {
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        const uint64_t ad = umma_desc_sw128(s_v + kk * 2048, CW_BOX_BYTES, 1024);
-        const uint64_t bd = umma_desc_sw128(sbase + LY::OFF_P + kk * 32, 16, 1024);
-        umma_ss(tmem + LY::T_H, ad, bd, IDESC_HV, 1);
+          for (int i = 0; i < 32; ++i) {
+            r0[i] = __float_as_uint(__uint_as_float(r0[i]) * mult);
+            r1[i] = __float_as_uint(__uint_as_float(r1[i]) * mult);
+          }
+          tmem_st_x32(tC + cb * 64, r0);
+          tmem_st_x32(tC + cb * 64 + 32, r1);
+        }
       }
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        const uint64_t ad = umma_desc_sw128(sbase + LY::OFF_VH + kk * 2048, CW_BOX_BYTES, 1024);
-        const uint64_t bd = umma_desc_sw128(s_k + kk * 2048, CW_BOX_BYTES, 1024);
-        umma_ss(tmem + LY::T_C, ad, bd, IDESC_C, 1);
-      }
-      umma_commit(bar_m2);
-    }
-
-    // (I) n = decay n + sum_l w_l k_l   (thread owns two adjacent key features)
-    if (2 * tid < DHQK) {
-      const int d = 2 * tid, box = d >> 6, c = (d & 63) >> 3, within = (d & 7) * 2;
-      const unsigned char* kt = smem + (s_k - sbase) + box * CW_BOX_BYTES + within;
-      float a0 = 0.f, a1 = 0.f;
-#pragma unroll 8
-      for (int l = 0; l < CW_L; ++l) {
-        const float2 kv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(kt + l * 128 + ((c ^ (l & 7)) << 4)));
-        const float wl = s_w[l];
-        a0 = fmaf(wl, kv.x, a0);
-        a1 = fmaf(wl, kv.y, a1);
-      }
-      s_n[d] = fmaf(decay, s_n[d], a0);
-      s_n[d + 1] = fmaf(decay, s_n[d + 1], a1);
-    }
-
-    // (J) epilogue: normalise and store this chunk's h (thread = value column, loop over tokens)
-    if (!mbar_wait(bar_m2, par)) { ok = false; break; }
-    tc_fence_after();
-    {
-      uint32_t hv[64];
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar0 + 8u * BAR_CB);
+      CW_TL(1, 3);
+      // ---- w-scaled v (thread: row l = t/2, box = t&1)
+      CW_WAIT(BAR_FULL0 + st, par_full);
+      CW_TL(1, 4);
       {
-        uint32_t t0[32], t1[32];
-        tmem_ld_x32(tH, t0);
-        tmem_ld_x32(tH + 32, t1);
-        tc_wait_ld();
+        const int l = t >> 1, half = t & 1;
+        const unsigned char* vt = smem + LY::OFF_STAGE + st * LY::STAGE_BYTES + 2 * LY::Q_BYTES;
+        uint4 v[8];
+        uint32_t off[8];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { hv[i] = t0[i]; hv[32 + i] = t1[i]; }
+        for (int i = 0; i < 8; ++i) {
+          const int c = i ^ (half << 2);
+          off[i] = half * CW_BOX_BYTES + l * 128 + ((c ^ (l & 7)) << 4);
+          v[i] = *reinterpret_cast<const uint4*>(vt + off[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(smem + LY::OFF_VH + off[i]) = scale_bf16x8(v[i], ww);
       }
+      fence_proxy_async_smem();
+      mbar_arrive(bar0 + 8u * BAR_VH);
+      mbar_arrive(bar0 + 8u * (BAR_EMPTY0 + st));
+      CW_TL(1, 5);
+    }
+    // ---- final C = exp(rho) T
+    if (ok) {
+      do {
+        CW_WAIT(BAR_C, (uint32_t)(nchunks - 1) & 1u);
+        tc_fence_after();
+        const float back = expf(rho_last);
+#pragma unroll 1
+        for (int cb = 0; cb < DHQK / 32; ++cb) {
+          uint32_t r[32];
+          tmem_ld_x32(tC + cb * 32, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) c_out[(long long)(cb * 32 + i) * DHV] = __uint_as_float(r[i]) * back;
+        }
+      } while (false);
+    }
+  } else if (warp < 12) {
+    // =========================================================================================== epilogue group
+    const int dv = (warp & 3) * 32 + lane;
+    __nv_bfloat16* hout = reinterpret_cast<__nv_bfloat16*>(p.h) + b * p.h_sb + head * p.h_sh + tok0 * p.h_st + col0 + dv;
+#pragma unroll 1
+    for (int chunk = 0; chunk < nchunks; ++chunk) {
+      const int buf = chunk & 1;
+      const uint32_t par = (uint32_t)chunk & 1u;
+      const long long rem = len - (long long)chunk * CW_L;
+      const int len_c = rem < CW_L ? (int)rem : CW_L;
+      CW_WAIT(BAR_H, par);
+      CW_WAIT(BAR_INV, par);
+      CW_TL(2, 1);
+      tc_fence_after();
       __nv_bfloat16* ho = hout + (long long)chunk * CW_L * p.h_st;
 #pragma unroll
-      for (int j = 0; j < CW_L; ++j)
-        if (j < len_c) ho[(long long)j * p.h_st] = __float2bfloat16_rn(__uint_as_float(hv[j]) * s_inv[j]);
+      for (int half = 0; half < 2; ++half) {
+        uint32_t hv[32];
+        tmem_ld_x32(tH + 32 * half, hv);
+        float4 iv[8];  // the reciprocal denominators first: loads from shared memory must not wait behind global stores
+#pragma unroll
+        for (int i = 0; i < 8; ++i) iv[i] = *reinterpret_cast<const float4*>(s_inv + buf * CW_L + 32 * half + 4 * i);
+        tc_wait_ld();
+        if (half == 1) {  // everything is in registers: release the accumulator before the stores go out
+          tc_fence_before();
+          mbar_arrive(bar0 + 8u * BAR_HFREE);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float sc[4] = {iv[i].x, iv[i].y, iv[i].z, iv[i].w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int jj = 4 * i + u, jt = half * 32 + jj;
+#if defined(XL_EG_VARIANT) && XL_EG_VARIANT == 1
+            { const float xv = __uint_as_float(hv[jj]) * sc[u]; if (jt < len_c && xv != xv) ho[(long long)jt * p.h_st] = __float2bfloat16_rn(xv); }
+#elif defined(XL_EG_VARIANT) && XL_EG_VARIANT == 2
+            if (jt < len_c) { const __nv_bfloat16 xb = __float2bfloat16_rn(__uint_as_float(hv[jj]) * sc[u]); asm volatile("st.global.cs.b16 [%0], %1;" ::"l"(ho + (long long)jt * p.h_st), "h"(*reinterpret_cast<const unsigned short*>(&xb)) : "memory"); }
+#else
+            if (jt < len_c) ho[(long long)jt * p.h_st] = __float2bfloat16_rn(__uint_as_float(hv[jj]) * sc[u]);
+#endif
+          }
+        }
+      }
+      CW_TL(2, 3);
     }
-    m_prev = m_new;
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0 && chunk + CW_STAGES < nchunks) issue_tma(chunk + CW_STAGES);
+  } else if (warp == 12) {
+    // =========================================================================================== UMMA issuer
+    // The whole warp runs this code (warp-uniform control flow); one elected lane issues each instruction.
+    constexpr uint32_t IDESC_S = umma_idesc_bf16(64, 64, 0, 0);
+    constexpr uint32_t IDESC_HI = umma_idesc_bf16(128, 64, 0, 0);
+    constexpr uint32_t IDESC_HV = umma_idesc_bf16(128, 64, 1, 0);
+    constexpr uint32_t IDESC_C = umma_idesc_bf16(128, DHQK, 1, 1);
+    constexpr uint32_t IDESC_DN = umma_idesc_bf16(64, 8, 0, 0);
+    constexpr uint32_t IDESC_NU = umma_idesc_bf16(64, 8, 1, 0);
+    const uint32_t t_odd = tmem + LY::T_S + (16u << 16);  // odd 16-lane halves of the S columns
+    const uint64_t d_qs = umma_desc_sw128(sbase + LY::OFF_QS, 16, 1024);
+    const uint64_t d_p = umma_desc_sw128(sbase + LY::OFF_P, 16, 1024);
+    const uint64_t d_vh = umma_desc_sw128(sbase + LY::OFF_VH, CW_BOX_BYTES, 1024);
+    const uint64_t d_nm = umma_desc_sw128(sbase + LY::OFF_NMAT, 16, 1024);
+    auto issue_S = [&](int chunk) {
+      const uint32_t s_q = sbase + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES;
+      const uint64_t dq = umma_desc_sw128(s_q, 16, 1024), dk = umma_desc_sw128(s_q + LY::Q_BYTES, 16, 1024);
+#pragma unroll
+      for (int kb = 0; kb < NKB; ++kb)
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss_elect(tmem + LY::T_S, umma_desc_advance(dq, kb * CW_BOX_BYTES + kk * 32),
+                        umma_desc_advance(dk, kb * CW_BOX_BYTES + kk * 32), IDESC_S, (kb | kk) != 0);
+      umma_commit_elect(bar0 + 8u * BAR_S);
+    };
+    bool okm = true;  // waits never change the control flow of this warp: it must stay provably uniform
+    okm &= mbar_wait(bar0 + 8u * BAR_FULL0, 0);
+    tc_fence_after();
+    issue_S(0);
+#pragma unroll 1
+    for (int chunk = 0; chunk < nchunks; ++chunk) {
+      const int st = chunk & 1, buf = chunk & 1;
+      const uint32_t par = (uint32_t)chunk & 1u;
+      const uint32_t s_k = sbase + LY::OFF_STAGE + st * LY::STAGE_BYTES + LY::Q_BYTES, s_v = s_k + LY::Q_BYTES;
+      const uint64_t dk_mn = umma_desc_sw128(s_k, CW_BOX_BYTES, 1024), dv_mn = umma_desc_sw128(s_v, CW_BOX_BYTES, 1024);
+      const uint64_t d_wm = umma_desc_sw128(sbase + LY::OFF_WMAT + buf * 1024, 16, 1024);
+      // H^T = Tb (r q~)^T
+      okm &= MMA_WAIT(BAR_CB, par);
+      okm &= MMA_WAIT(BAR_QS, par);
+      if (chunk >= 1) okm &= MMA_WAIT(BAR_HFREE, par ^ 1u);
+      CW_TL(3, 1);
+      tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < DHQK / 16; ++ks)
+        umma_ts_elect(tmem + LY::T_H, tmem + LY::T_CB + ks * 8, umma_desc_advance(d_qs, (ks >> 2) * CW_BOX_BYTES + (ks & 3) * 32),
+                      IDESC_HI, ks != 0);
+      // qn = (r q~) [n_hi n_lo]^T
+      okm &= MMA_WAIT(BAR_NMAT, par);
+      CW_TL(3, 3);
+      tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < DHQK / 16; ++ks)
+        umma_ss_elect(t_odd, umma_desc_advance(d_qs, (ks >> 2) * CW_BOX_BYTES + (ks & 3) * 32),
+                      umma_desc_advance(d_nm, (ks >> 2) * 1024 + (ks & 3) * 32), IDESC_DN, ks != 0);
+      umma_commit_elect(bar0 + 8u * BAR_DN);
+      // H^T += V^T P^T
+      okm &= MMA_WAIT(BAR_P, par);
+      CW_TL(3, 4);
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        umma_ss_elect(tmem + LY::T_H, umma_desc_advance(dv_mn, kk * 2048), umma_desc_advance(d_p, kk * 32), IDESC_HV, 1);
+      umma_commit_elect(bar0 + 8u * BAR_H);
+      // T += (w V)^T K ;  nu = K^T [w_hi w_lo]^T
+      okm &= MMA_WAIT(BAR_VH, par);
+      CW_TL(3, 5);
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        umma_ss_elect(tmem + LY::T_C, umma_desc_advance(d_vh, kk * 2048), umma_desc_advance(dk_mn, kk * 2048), IDESC_C, 1);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+        for (int gq = 0; gq < NKB; ++gq)
+          umma_ss_elect(t_odd + 8 + 8 * gq, umma_desc_advance(dk_mn, gq * CW_BOX_BYTES + kk * 2048), umma_desc_advance(d_wm, kk * 32),
+                        IDESC_NU, kk != 0);
+      umma_commit_elect(bar0 + 8u * BAR_C);
+      umma_commit_elect(bar0 + 8u * (BAR_EMPTY0 + st));
+      CW_TL(3, 6);
+      // S of the next chunk (its P pass then overlaps this chunk's tail and the next T -> bf16 copy)
+      if (chunk + 1 < nchunks) {
+        okm &= MMA_WAIT(BAR_FULL0 + ((chunk + 1) & 1), (uint32_t)((chunk + 1) >> 1) & 1u);
+        CW_TL(3, 7);
+        tc_fence_after();
+        issue_S(chunk + 1);
+      }
+    }
+    ok = okm;
+  } else {
+    // =========================================================================================== TMA issuer
+    if (lane == 0) {
+#pragma unroll 1
+      for (int chunk = 0; chunk < nchunks; ++chunk) {
+        const int st = chunk & 1;
+        const uint32_t use = (uint32_t)(chunk >> 1);
+        CW_WAIT(BAR_EMPTY0 + st, (use & 1u) ^ 1u);  // passes at once for the first use of a stage
+        const uint32_t bar = bar0 + 8u * (BAR_FULL0 + st);
+        const uint32_t dst = sbase + LY::OFF_STAGE + st * LY::STAGE_BYTES;
+        const int tk = (int)(tok0 + (long long)chunk * CW_L);
+        mbar_expect_tx(bar, LY::STAGE_BYTES);
+        int cq[4], ck[4], cv[4];
+        cq[maps.pos[0][0]] = tk; cq[maps.pos[0][1]] = head; cq[maps.pos[0][2]] = b;
+        ck[maps.pos[1][0]] = tk; ck[maps.pos[1][1]] = head; ck[maps.pos[1][2]] = b;
+        cv[maps.pos[2][0]] = tk; cv[maps.pos[2][1]] = head; cv[maps.pos[2][2]] = b;
+#pragma unroll
+        for (int kb = 0; kb < NKB; ++kb) {
+          tma_load_4d(dst + kb * CW_BOX_BYTES, &maps.q, bar, kb * 64, cq[1], cq[2], cq[3]);
+          tma_load_4d(dst + LY::Q_BYTES + kb * CW_BOX_BYTES, &maps.k, bar, kb * 64, ck[1], ck[2], ck[3]);
+        }
+#pragma unroll
+        for (int vb = 0; vb < 2; ++vb)
+          tma_load_4d(dst + 2 * LY::Q_BYTES + vb * CW_BOX_BYTES, &maps.v, bar, col0 + vb * 64, cv[1], cv[2], cv[3]);
+      }
+    }
+    __syncwarp();
   }
 
-  // ---- final state
-  if (ok) {
-    tc_fence_after();
-#pragma unroll 1
-    for (int cb = 0; cb < DHQK / 32; ++cb) {
-      uint32_t r[32];
-      tmem_ld_x32(tC + cb * 32, r);
-      tc_wait_ld();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) c_out[(long long)(cb * 32 + i) * DHV] = __uint_as_float(r[i]);
-    }
-    if (slice == 0) {
-      for (int d = tid; d < DHQK; d += CW_THREADS) p.n_out[sidx * DHQK + d] = s_n[d];
-      if (tid == 0) p.m_out[sidx] = m_prev;
-    }
-  } else {
-    if (p.status && tid == 0) atomicExch(p.status, 1);
-    // give copies that may still be in flight a bounded chance to land before the CTA's memory is released
-    (void)mbar_wait(bar_full0, 0);
-    (void)mbar_wait(bar_full0 + 8, 0);
-  }
+  if (!ok && p.status) atomicExch(p.status, 1);
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, CW_TMEM_COLS);
+  if (warp == 12) tmem_dealloc(tmem, CW_TMEM_COLS);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -543,6 +803,12 @@ static int launch_chunkwise(const CwMaps& maps, const xl_mlstm_seq_params* p, cu
 }
 
 }  // namespace xl
+
+#ifdef XL_CW_TIMELINE
+extern "C" int xl_debug_copy_timeline(void* dst) {
+  return (int)cudaMemcpyFromSymbol(dst, xl::g_cw_timeline, sizeof(xl::g_cw_timeline));
+}
+#endif
 
 extern "C" int xl_mlstm_chunkwise(const xl_mlstm_seq_params* p, void* cuda_stream) {
   using namespace xl;
