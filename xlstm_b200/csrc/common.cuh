@@ -72,7 +72,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
+#ifdef XL_WAIT_TEST
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -80,7 +84,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: returns false if the phase did not complete within the poll budget (~ a second).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// (Not inlined on purpose: kernels wait at dozens of sites and the poll loop would be duplicated at each.)
+static __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   for (uint32_t it = 0; it < (1u << 22); ++it) {
     if (mbar_try_wait(bar, parity)) return true;
 #ifdef XL_WAIT_SLEEP_NS

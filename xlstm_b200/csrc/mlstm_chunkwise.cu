@@ -25,7 +25,8 @@
 //
 // Warp roles (448 threads): warps 0-3 gate group (gate scans, r-scaled q, P, denominators, n),
 // warps 4-7 state group (T -> bf16 copy / lazy rescale, w-scaled v), warps 8-11 epilogue group
-// (H^T -> normalised h in global memory), warp 12 issues every UMMA, warp 13 issues the TMA loads.
+// (H^T -> normalised bf16 tile in shared memory -> 16-byte global stores), warp 12 issues every UMMA,
+// warp 13 issues the TMA loads.  q is scaled by r_j in place in its TMA stage once S has consumed it.
 // Groups hand work to each other through mbarriers only; every wait is bounded.
 //
 // q, k, v tiles arrive by TMA (128-byte swizzle) straight from the caller's strided (B, NH, S, D) views;
@@ -45,6 +46,10 @@ constexpr int CW_BOX_BYTES = 64 * 128;  // one TMA box: 64 rows x 64 bf16
 constexpr uint32_t CW_TMEM_COLS = 512;
 constexpr float CW_RESCALE_BELOW = -30.f;  // lazy-decay frame limit (natural log)
 constexpr float CW_LOG2E = 1.4426950408889634f;
+#ifndef XL_CW_SCAN_WARP
+#define XL_CW_SCAN_WARP 0
+#endif
+constexpr int CW_SCAN_WARP = XL_CW_SCAN_WARP;  // gate-group warp that carries the gate recurrence
 
 enum CwBar {  // mbarrier indices
   BAR_FULL0 = 0, BAR_FULL1, BAR_EMPTY0, BAR_EMPTY1,
@@ -62,12 +67,13 @@ struct CwLayout {
   static constexpr int V_BYTES = 2 * CW_BOX_BYTES;
   static constexpr int STAGE_BYTES = 2 * Q_BYTES + V_BYTES;    // q, k, v of one chunk
   static constexpr int OFF_STAGE = 0;
-  static constexpr int OFF_QS = CW_STAGES * STAGE_BYTES;       // r_j-scaled q
-  static constexpr int OFF_VH = OFF_QS + Q_BYTES;              // w_l-scaled v
+  static constexpr int OFF_VH = CW_STAGES * STAGE_BYTES;       // w_l-scaled v
   static constexpr int OFF_P = OFF_VH + V_BYTES;               // P tile
   static constexpr int OFF_NMAT = OFF_P + CW_BOX_BYTES;        // [8 x DHQK] bf16: rows n_hi, n_lo, zeros
   static constexpr int OFF_WMAT = OFF_NMAT + NKB * 1024;       // 2 x [8 x 64] bf16: rows w_hi, w_lo, zeros
-  static constexpr int OFF_F32 = OFF_WMAT + 2 * 1024;
+  static constexpr int HST_ROW = CW_DV * 2 + 16;               // staged h row: 128 bf16 + 16 B pad
+  static constexpr int OFF_HST = OFF_WMAT + 2 * 1024;          // [64][HST_ROW] normalised h of one chunk
+  static constexpr int OFF_F32 = OFF_HST + CW_L * HST_ROW;
   static constexpr int N_F32 = 4 * CW_L + 2 * 2 * CW_L + DHQK + 16 + 8;
   static constexpr int OFF_BAR = OFF_F32 + N_F32 * 4;          // mbarriers (8-byte aligned)
   static constexpr int TOTAL = OFF_BAR + BAR_COUNT * 8 + 16;
@@ -93,6 +99,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 __device__ __forceinline__ float fast_log_sigmoid(float x) { return fminf(x, 0.f) - __logf(1.f + __expf(-fabsf(x))); }
 __device__ __forceinline__ void gate_group_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_group_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
 
 // 16 bytes of bf16 times a bf16x2 splat, rounded once per product
 __device__ __forceinline__ uint4 scale_bf16x8(uint4 raw, __nv_bfloat162 s) {
@@ -111,9 +118,13 @@ __device__ __forceinline__ uint32_t sw128_off(int row, int col) {
 
 // Optional per-role timestamps of one CTA (debug builds only; compiled out otherwise).
 #ifdef XL_CW_TIMELINE
-__device__ unsigned long long g_cw_timeline[5][256][12];
+#ifndef XL_TL_SMSP
+#define XL_TL_SMSP 0
+#endif
+__device__ unsigned long long g_cw_timeline[5][256][16];
+__device__ unsigned long long g_cw_cta[4096][4];
 #define CW_TL(role, ev)                                                                                         \
-  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && chunk < 256 && (threadIdx.x & 31) == 0 && (warp & 3) == 0) \
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && chunk < 256 && (threadIdx.x & 31) == 0 && (warp & 3) == XL_TL_SMSP) \
     g_cw_timeline[role][chunk][ev] = clock64();
 #else
 #define CW_TL(role, ev)
@@ -135,7 +146,9 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   constexpr int NKB = LY::NKB;
   extern __shared__ unsigned char cw_smem_raw[];
   // 128-byte-swizzled tiles need 1024-byte aligned bases
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(cw_smem_raw) + 1023) & ~uintptr_t(1023));
+  // (pointer arithmetic on the __shared__ array, not an integer round trip, so that every access below is
+  // compiled as a shared-memory instruction rather than a generic one)
+  unsigned char* smem = cw_smem_raw + ((1024u - (smem_u32(cw_smem_raw) & 1023u)) & 1023u);
   const uint32_t sbase = smem_u32(smem);
   float* s_f = reinterpret_cast<float*>(smem + LY::OFF_F32);
   float* s_b = s_f;                   // b_j                               (gate group private)
@@ -152,6 +165,10 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int slice = blockIdx.x, head = blockIdx.y, doc = blockIdx.z;
+#ifdef XL_CW_TIMELINE
+  const unsigned long long cta_t0 = clock64();
+  unsigned long long cta_g0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(cta_g0));
+#endif
   const int col0 = slice * CW_DV;
   const int DHV = p.DHV;
 
@@ -231,11 +248,13 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     // warp 0 carries the gate recurrence: lane L owns tokens 2L and 2L+1 of the chunk
     float m_prev = p.m0 ? p.m0[sidx] : 0.f;
     float rho = 0.f;
-    float gi0 = -INFINITY, gi1 = -INFINITY, gf0 = 0.f, gf1 = 0.f;
-    if (warp == 0) {
-      const long long t0 = 2 * lane;
-      if (t0 < len) { gi0 = ig[t0 * p.g_st]; gf0 = fg[t0 * p.g_st]; }
-      if (t0 + 1 < len) { gi1 = ig[(t0 + 1) * p.g_st]; gf1 = fg[(t0 + 1) * p.g_st]; }
+    // Gate loads are issued one chunk ahead, unconditionally and from clamped addresses: the tail mask is applied
+    // when the values are used, so nothing has to wait for the load when it is issued.
+    float gi0 = 0.f, gi1 = 0.f, gf0 = 0.f, gf1 = 0.f;
+    if (warp == CW_SCAN_WARP) {
+      const long long t0 = 2 * lane, ta = t0 < len ? t0 : len - 1, tb = t0 + 1 < len ? t0 + 1 : len - 1;
+      gi0 = ig[ta * p.g_st]; gf0 = fg[ta * p.g_st];
+      gi1 = ig[tb * p.g_st]; gf1 = fg[tb * p.g_st];
     }
 #pragma unroll 1
     for (int chunk = 0; chunk < nchunks; ++chunk) {
@@ -246,18 +265,15 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       CW_TL(0, 0);
       // warp 0 is about to overwrite the gate arrays the other gate-group warps read in their P / denominator passes
       gate_group_sync();
+      CW_TL(0, 10);
       // The state group must be done with the gate data of the previous chunk.  (Waiting one phase back, not two:
       // an mbarrier parity wait is only meaningful while the producer is at most one phase ahead of the waiter.)
       if (chunk >= 1) CW_WAIT(BAR_VH, par ^ 1u);
-      if (warp == 0) {
+      CW_TL(0, 11);
+      if (warp == CW_SCAN_WARP) {
         // ---- gate scans over the chunk
         const float ci0 = gi0, ci1 = gi1, cf0 = gf0, cf1 = gf1;
-        {
-          const long long t0 = (long long)(chunk + 1) * CW_L + 2 * lane;
-          gi0 = gi1 = -INFINITY; gf0 = gf1 = 0.f;
-          if (t0 < len) { gi0 = ig[t0 * p.g_st]; gf0 = fg[t0 * p.g_st]; }
-          if (t0 + 1 < len) { gi1 = ig[(t0 + 1) * p.g_st]; gf1 = fg[(t0 + 1) * p.g_st]; }
-        }
+        CW_TL(4, 2);
         const int t0 = 2 * lane, t1 = t0 + 1;
         const float lf0 = (t0 < len_c) ? fast_log_sigmoid(cf0) : 0.f;
         const float lf1 = (t1 < len_c) ? fast_log_sigmoid(cf1) : 0.f;
@@ -267,6 +283,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
           const float t = __shfl_up_sync(0xffffffffu, incl, o);
           if (lane >= o) incl += t;
         }
+        CW_TL(4, 3);
         const float b1 = incl, b0 = incl - lf1;
         const float ap0 = (t0 < len_c) ? ci0 - b0 : -INFINITY;
         const float ap1 = (t1 < len_c) ? ci1 - b1 : -INFINITY;
@@ -276,12 +293,14 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
           const float t = __shfl_up_sync(0xffffffffu, cmx, o);
           if (lane >= o) cmx = fmaxf(cmx, t);
         }
+        CW_TL(4, 4);
         float prevmax = __shfl_up_sync(0xffffffffu, cmx, 1);
         if (lane == 0) prevmax = -INFINITY;
         const float mu0 = fmaxf(m_prev, fmaxf(prevmax, ap0));
         const float mu1 = fmaxf(m_prev, cmx);
         const float mu_star = __shfl_sync(0xffffffffu, mu1, 31);
         const float gsum = __shfl_sync(0xffffffffu, b1, 31);
+        CW_TL(4, 5);
         // lazy decay frame: C = exp(rho) T
         const float cand = rho + (m_prev - mu_star);
         const bool rescale = cand < CW_RESCALE_BELOW;
@@ -291,6 +310,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         *reinterpret_cast<float2*>(s_apl + t0) = make_float2(ap0 * CW_LOG2E, ap1 * CW_LOG2E);
         *reinterpret_cast<float2*>(s_mul + t0) = make_float2(mu0 * CW_LOG2E, mu1 * CW_LOG2E);
         *reinterpret_cast<float2*>(s_r + t0) = make_float2(__expf(m_prev - mu0 + rho) * qscale, __expf(m_prev - mu1 + rho) * qscale);
+        CW_TL(4, 6);
         const float w0 = __expf(ap0 - mu_star - rho_new), w1 = __expf(ap1 - mu_star - rho_new);
         *reinterpret_cast<float2*>(s_w + buf * CW_L + t0) = make_float2(w0, w1);
         {
@@ -301,26 +321,36 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
           *reinterpret_cast<__nv_bfloat162*>(wm + sw128_off(0, t0)) = hi;
           *reinterpret_cast<__nv_bfloat162*>(wm + sw128_off(1, t0)) = lo;
         }
+        CW_TL(4, 7);
         if (lane == 0) { s_scal[buf * 4 + 0] = mult; s_scal[buf * 4 + 1] = rho_new; }
+        {  // next chunk's gate values (clamped addresses; the tail mask is applied at use)
+          const long long tn = (long long)(chunk + 1) * CW_L + 2 * lane;
+          const long long ta = tn < len ? tn : len - 1, tb = tn + 1 < len ? tn + 1 : len - 1;
+          gi0 = ig[ta * p.g_st]; gf0 = fg[ta * p.g_st];
+          gi1 = ig[tb * p.g_st]; gf1 = fg[tb * p.g_st];
+        }
         m_prev = gsum + mu_star;
         rho = rho_new;
       }
+      CW_TL(0, 12);
       fence_proxy_async_smem();
+      CW_TL(0, 13);
       gate_group_sync();
       mbar_arrive(bar0 + 8u * BAR_GATES);
       CW_TL(0, 1);
 
-      // ---- r-scaled q, same swizzled layout (thread: row j = g/2, half of the row)
+      // ---- q <- r_j q IN PLACE in the stage tile (thread: row j = g/2, half of the row).  S of this chunk, the
+      // only consumer of the un-scaled q, has been issued one iteration ahead and must have completed.
       CW_WAIT(BAR_FULL0 + st, par_full);
-      if (chunk >= 1) CW_WAIT(BAR_H, par ^ 1u);  // UMMAs of chunk-1 no longer read the scaled-q and P tiles
+      CW_WAIT(BAR_S, par);
       CW_TL(0, 2);
       {
         const int j = g >> 1, half = g & 1;
         const __nv_bfloat162 rr = __float2bfloat162_rn(s_r[j]);
-        const unsigned char* qt = smem + LY::OFF_STAGE + st * LY::STAGE_BYTES;
+        unsigned char* qt = smem + LY::OFF_STAGE + st * LY::STAGE_BYTES;
         constexpr int CH = NKB * 4;              // 16-byte pieces per thread
         constexpr int BATCH = CH < 8 ? CH : 8;   // loads first, then stores: the two tiles may not alias in the compiler's eyes
-#pragma unroll
+#pragma unroll 1
         for (int i0 = 0; i0 < CH; i0 += BATCH) {
           uint4 v[BATCH];
           uint32_t off[BATCH];
@@ -333,9 +363,10 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
             v[i] = *reinterpret_cast<const uint4*>(qt + off[i]);
           }
 #pragma unroll
-          for (int i = 0; i < BATCH; ++i) *reinterpret_cast<uint4*>(smem + LY::OFF_QS + off[i]) = scale_bf16x8(v[i], rr);
+          for (int i = 0; i < BATCH; ++i) *reinterpret_cast<uint4*>(qt + off[i]) = scale_bf16x8(v[i], rr);
         }
       }
+      CW_TL(0, 14);
       fence_proxy_async_smem();
       mbar_arrive(bar0 + 8u * BAR_QS);
       mbar_arrive(bar0 + 8u * (BAR_EMPTY0 + st));  // this thread is done reading the q tile of this stage
@@ -366,13 +397,13 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       CW_TL(0, 5);
 
       // ---- P from S (rows of this warp: j = 16 warp + lane for lanes 0..15)
-      CW_WAIT(BAR_S, par);
+      if (chunk >= 1) CW_WAIT(BAR_H, par ^ 1u);  // the UMMAs of chunk-1 no longer read the P tile
       CW_TL(0, 6);
       tc_fence_after();
       const int j = warp * 16 + (lane & 15);
       const float mulj = s_mul[j];
       float rowsum = 0.f;
-#pragma unroll
+#pragma unroll 1
       for (int half = 0; half < 2; ++half) {
         if (32 * half > 16 * warp + 15) {  // warp-uniform: this half lies wholly above the diagonal
           if (lane < 16) {
@@ -422,6 +453,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
           }
         }
       }
+      CW_TL(0, 15);
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(bar0 + 8u * BAR_P);
@@ -462,7 +494,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
             p.n_out[sidx * DHQK + d] = nv * back;
           }
         }
-        if (slice == 0 && g == 0) p.m_out[sidx] = m_prev;
+        if (slice == 0 && g == CW_SCAN_WARP * 32) p.m_out[sidx] = m_prev;
       } while (false);
     }
   } else if (warp < 8) {
@@ -560,8 +592,13 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     }
   } else if (warp < 12) {
     // =========================================================================================== epilogue group
+    // H^T sits in tensor memory with one value column per lane.  Each thread normalises its 64 tokens, writes them
+    // as bf16 into a [token][column] staging tile in shared memory, and the group then streams the tile out with
+    // 16-byte stores (a row of the tile is 256 contiguous bytes of h).
+    const int t = tid - 256;
     const int dv = (warp & 3) * 32 + lane;
-    __nv_bfloat16* hout = reinterpret_cast<__nv_bfloat16*>(p.h) + b * p.h_sb + head * p.h_sh + tok0 * p.h_st + col0 + dv;
+    unsigned char* hst = smem + LY::OFF_HST;
+    __nv_bfloat16* hbase = reinterpret_cast<__nv_bfloat16*>(p.h) + b * p.h_sb + head * p.h_sh + tok0 * p.h_st + col0;
 #pragma unroll 1
     for (int chunk = 0; chunk < nchunks; ++chunk) {
       const int buf = chunk & 1;
@@ -572,40 +609,45 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       CW_WAIT(BAR_INV, par);
       CW_TL(2, 1);
       tc_fence_after();
-      __nv_bfloat16* ho = hout + (long long)chunk * CW_L * p.h_st;
-#pragma unroll
+#pragma unroll 1
       for (int half = 0; half < 2; ++half) {
         uint32_t hv[32];
         tmem_ld_x32(tH + 32 * half, hv);
-        float4 iv[8];  // the reciprocal denominators first: loads from shared memory must not wait behind global stores
+        float4 iv[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) iv[i] = *reinterpret_cast<const float4*>(s_inv + buf * CW_L + 32 * half + 4 * i);
         tc_wait_ld();
-        if (half == 1) {  // everything is in registers: release the accumulator before the stores go out
+        if (half == 1) {  // the accumulator is in registers: release it before the stores go out
           tc_fence_before();
           mbar_arrive(bar0 + 8u * BAR_HFREE);
         }
+        unsigned char* col = hst + (32 * half) * LY::HST_ROW + dv * 2;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float sc[4] = {iv[i].x, iv[i].y, iv[i].z, iv[i].w};
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int jj = 4 * i + u, jt = half * 32 + jj;
-#if defined(XL_EG_VARIANT) && XL_EG_VARIANT == 1
-            { const float xv = __uint_as_float(hv[jj]) * sc[u]; if (jt < len_c && xv != xv) ho[(long long)jt * p.h_st] = __float2bfloat16_rn(xv); }
-#elif defined(XL_EG_VARIANT) && XL_EG_VARIANT == 2
-            if (jt < len_c) { const __nv_bfloat16 xb = __float2bfloat16_rn(__uint_as_float(hv[jj]) * sc[u]); asm volatile("st.global.cs.b16 [%0], %1;" ::"l"(ho + (long long)jt * p.h_st), "h"(*reinterpret_cast<const unsigned short*>(&xb)) : "memory"); }
-#else
-            if (jt < len_c) ho[(long long)jt * p.h_st] = __float2bfloat16_rn(__uint_as_float(hv[jj]) * sc[u]);
-#endif
-          }
+          for (int u = 0; u < 4; ++u)
+            *reinterpret_cast<__nv_bfloat16*>(col + (4 * i + u) * LY::HST_ROW) = __float2bfloat16_rn(__uint_as_float(hv[4 * i + u]) * sc[u]);
         }
       }
+      epilogue_group_sync();
+      __nv_bfloat16* ho = hbase + (long long)chunk * CW_L * p.h_st;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int idx = i * 128 + t, row = idx >> 4, c = idx & 15;
+        if (row < len_c)
+          *reinterpret_cast<uint4*>(ho + (long long)row * p.h_st + c * 8) = *reinterpret_cast<const uint4*>(hst + row * LY::HST_ROW + c * 16);
+      }
+      epilogue_group_sync();  // the tile is rewritten by the next chunk
       CW_TL(2, 3);
     }
   } else if (warp == 12) {
     // =========================================================================================== UMMA issuer
-    // The whole warp runs this code (warp-uniform control flow); one elected lane issues each instruction.
+    // The whole warp runs this code (warp-uniform control flow, waits never branch out of it); one elected lane
+    // issues each instruction.  Every descriptor is formed from one runtime base plus compile-time constants so
+    // that the address arithmetic stays on the uniform datapath.  Iteration `it` finishes chunk it-1 (H^T, qn,
+    // T, nu) and starts chunk `it` (S) in between, so the P pass and the in-place q scaling of a chunk overlap
+    // the state update of the previous one.
     constexpr uint32_t IDESC_S = umma_idesc_bf16(64, 64, 0, 0);
     constexpr uint32_t IDESC_HI = umma_idesc_bf16(128, 64, 0, 0);
     constexpr uint32_t IDESC_HV = umma_idesc_bf16(128, 64, 1, 0);
@@ -613,81 +655,80 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     constexpr uint32_t IDESC_DN = umma_idesc_bf16(64, 8, 0, 0);
     constexpr uint32_t IDESC_NU = umma_idesc_bf16(64, 8, 1, 0);
     const uint32_t t_odd = tmem + LY::T_S + (16u << 16);  // odd 16-lane halves of the S columns
-    const uint64_t d_qs = umma_desc_sw128(sbase + LY::OFF_QS, 16, 1024);
-    const uint64_t d_p = umma_desc_sw128(sbase + LY::OFF_P, 16, 1024);
-    const uint64_t d_vh = umma_desc_sw128(sbase + LY::OFF_VH, CW_BOX_BYTES, 1024);
-    const uint64_t d_nm = umma_desc_sw128(sbase + LY::OFF_NMAT, 16, 1024);
-    auto issue_S = [&](int chunk) {
-      const uint32_t s_q = sbase + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES;
-      const uint64_t dq = umma_desc_sw128(s_q, 16, 1024), dk = umma_desc_sw128(s_q + LY::Q_BYTES, 16, 1024);
+    bool okm = true;
+#pragma unroll 1
+    for (int it = 0; it <= nchunks; ++it) {
+      if (it >= 1) {
+        const int chunk = it - 1;
+        const uint32_t par = (uint32_t)chunk & 1u;
+        const uint32_t stg = sbase + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES;  // q | k | v of this chunk
+        const uint32_t s_k = stg + LY::Q_BYTES, s_v = s_k + LY::Q_BYTES;
+        const uint32_t wm = sbase + LY::OFF_WMAT + (chunk & 1) * 1024;
+        // H^T = Tb (r q~)^T
+        okm &= MMA_WAIT(BAR_CB, par);
+        okm &= MMA_WAIT(BAR_QS, par);
+        if (chunk >= 1) okm &= MMA_WAIT(BAR_HFREE, par ^ 1u);
+        CW_TL(3, 1);
+        tc_fence_after();
 #pragma unroll
-      for (int kb = 0; kb < NKB; ++kb)
+        for (int ks = 0; ks < DHQK / 16; ++ks)
+          umma_ts_elect(tmem + LY::T_H, tmem + LY::T_CB + ks * 8,
+                        umma_desc_sw128(stg + (ks >> 2) * CW_BOX_BYTES + (ks & 3) * 32, 16, 1024), IDESC_HI, ks != 0);
+        // qn = (r q~) [n_hi n_lo]^T
+        okm &= MMA_WAIT(BAR_NMAT, par);
+        CW_TL(3, 3);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < DHQK / 16; ++ks)
+          umma_ss_elect(t_odd, umma_desc_sw128(stg + (ks >> 2) * CW_BOX_BYTES + (ks & 3) * 32, 16, 1024),
+                        umma_desc_sw128(sbase + LY::OFF_NMAT + (ks >> 2) * 1024 + (ks & 3) * 32, 16, 1024), IDESC_DN, ks != 0);
+        umma_commit_elect(bar0 + 8u * BAR_DN);
+        // H^T += V^T P^T
+        okm &= MMA_WAIT(BAR_P, par);
+        CW_TL(3, 4);
+        tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ss_elect(tmem + LY::T_S, umma_desc_advance(dq, kb * CW_BOX_BYTES + kk * 32),
-                        umma_desc_advance(dk, kb * CW_BOX_BYTES + kk * 32), IDESC_S, (kb | kk) != 0);
-      umma_commit_elect(bar0 + 8u * BAR_S);
-    };
-    bool okm = true;  // waits never change the control flow of this warp: it must stay provably uniform
-    okm &= mbar_wait(bar0 + 8u * BAR_FULL0, 0);
-    tc_fence_after();
-    issue_S(0);
-#pragma unroll 1
-    for (int chunk = 0; chunk < nchunks; ++chunk) {
-      const int st = chunk & 1, buf = chunk & 1;
-      const uint32_t par = (uint32_t)chunk & 1u;
-      const uint32_t s_k = sbase + LY::OFF_STAGE + st * LY::STAGE_BYTES + LY::Q_BYTES, s_v = s_k + LY::Q_BYTES;
-      const uint64_t dk_mn = umma_desc_sw128(s_k, CW_BOX_BYTES, 1024), dv_mn = umma_desc_sw128(s_v, CW_BOX_BYTES, 1024);
-      const uint64_t d_wm = umma_desc_sw128(sbase + LY::OFF_WMAT + buf * 1024, 16, 1024);
-      // H^T = Tb (r q~)^T
-      okm &= MMA_WAIT(BAR_CB, par);
-      okm &= MMA_WAIT(BAR_QS, par);
-      if (chunk >= 1) okm &= MMA_WAIT(BAR_HFREE, par ^ 1u);
-      CW_TL(3, 1);
-      tc_fence_after();
-#pragma unroll
-      for (int ks = 0; ks < DHQK / 16; ++ks)
-        umma_ts_elect(tmem + LY::T_H, tmem + LY::T_CB + ks * 8, umma_desc_advance(d_qs, (ks >> 2) * CW_BOX_BYTES + (ks & 3) * 32),
-                      IDESC_HI, ks != 0);
-      // qn = (r q~) [n_hi n_lo]^T
-      okm &= MMA_WAIT(BAR_NMAT, par);
-      CW_TL(3, 3);
-      tc_fence_after();
-#pragma unroll
-      for (int ks = 0; ks < DHQK / 16; ++ks)
-        umma_ss_elect(t_odd, umma_desc_advance(d_qs, (ks >> 2) * CW_BOX_BYTES + (ks & 3) * 32),
-                      umma_desc_advance(d_nm, (ks >> 2) * 1024 + (ks & 3) * 32), IDESC_DN, ks != 0);
-      umma_commit_elect(bar0 + 8u * BAR_DN);
-      // H^T += V^T P^T
-      okm &= MMA_WAIT(BAR_P, par);
-      CW_TL(3, 4);
-      tc_fence_after();
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk)
-        umma_ss_elect(tmem + LY::T_H, umma_desc_advance(dv_mn, kk * 2048), umma_desc_advance(d_p, kk * 32), IDESC_HV, 1);
-      umma_commit_elect(bar0 + 8u * BAR_H);
-      // T += (w V)^T K ;  nu = K^T [w_hi w_lo]^T
-      okm &= MMA_WAIT(BAR_VH, par);
-      CW_TL(3, 5);
-      tc_fence_after();
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk)
-        umma_ss_elect(tmem + LY::T_C, umma_desc_advance(d_vh, kk * 2048), umma_desc_advance(dk_mn, kk * 2048), IDESC_C, 1);
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk)
-#pragma unroll
-        for (int gq = 0; gq < NKB; ++gq)
-          umma_ss_elect(t_odd + 8 + 8 * gq, umma_desc_advance(dk_mn, gq * CW_BOX_BYTES + kk * 2048), umma_desc_advance(d_wm, kk * 32),
-                        IDESC_NU, kk != 0);
-      umma_commit_elect(bar0 + 8u * BAR_C);
-      umma_commit_elect(bar0 + 8u * (BAR_EMPTY0 + st));
-      CW_TL(3, 6);
-      // S of the next chunk (its P pass then overlaps this chunk's tail and the next T -> bf16 copy)
-      if (chunk + 1 < nchunks) {
-        okm &= MMA_WAIT(BAR_FULL0 + ((chunk + 1) & 1), (uint32_t)((chunk + 1) >> 1) & 1u);
+          umma_ss_elect(tmem + LY::T_H, umma_desc_sw128(s_v + kk * 2048, CW_BOX_BYTES, 1024),
+                        umma_desc_sw128(sbase + LY::OFF_P + kk * 32, 16, 1024), IDESC_HV, 1);
+        umma_commit_elect(bar0 + 8u * BAR_H);
+      }
+      if (it < nchunks) {
+        const int chunk = it;
+        const uint32_t s_q = sbase + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES, s_k = s_q + LY::Q_BYTES;
+        okm &= MMA_WAIT(BAR_FULL0 + (chunk & 1), (uint32_t)(chunk >> 1) & 1u);
         CW_TL(3, 7);
         tc_fence_after();
-        issue_S(chunk + 1);
+#pragma unroll
+        for (int kb = 0; kb < NKB; ++kb)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ss_elect(tmem + LY::T_S, umma_desc_sw128(s_q + kb * CW_BOX_BYTES + kk * 32, 16, 1024),
+                          umma_desc_sw128(s_k + kb * CW_BOX_BYTES + kk * 32, 16, 1024), IDESC_S, (kb | kk) != 0);
+        umma_commit_elect(bar0 + 8u * BAR_S);
+      }
+      if (it >= 1) {
+        const int chunk = it - 1;
+        const uint32_t par = (uint32_t)chunk & 1u;
+        const uint32_t s_k = sbase + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES + LY::Q_BYTES;
+        const uint32_t wm = sbase + LY::OFF_WMAT + (chunk & 1) * 1024;
+        // T += (w V)^T K ;  nu = K^T [w_hi w_lo]^T
+        okm &= MMA_WAIT(BAR_VH, par);
+        CW_TL(3, 5);
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss_elect(tmem + LY::T_C, umma_desc_sw128(sbase + LY::OFF_VH + kk * 2048, CW_BOX_BYTES, 1024),
+                        umma_desc_sw128(s_k + kk * 2048, CW_BOX_BYTES, 1024), IDESC_C, 1);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+          for (int gq = 0; gq < NKB; ++gq)
+            umma_ss_elect(t_odd + 8 + 8 * gq, umma_desc_sw128(s_k + gq * CW_BOX_BYTES + kk * 2048, CW_BOX_BYTES, 1024),
+                          umma_desc_sw128(wm + kk * 32, 16, 1024), IDESC_NU, kk != 0);
+        umma_commit_elect(bar0 + 8u * BAR_C);
+        umma_commit_elect(bar0 + 8u * (BAR_EMPTY0 + (chunk & 1)));
+        CW_TL(3, 6);
       }
     }
     ok = okm;
@@ -720,6 +761,13 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     __syncwarp();
   }
 
+#ifdef XL_CW_TIMELINE
+  if (tid == 0) {
+    const int lin = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    unsigned smid; asm("mov.u32 %0, %%smid;" : "=r"(smid));
+    if (lin < 4096) { g_cw_cta[lin][0] = clock64() - cta_t0; g_cw_cta[lin][1] = smid; g_cw_cta[lin][2] = cta_t0; unsigned long long g1; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1)); g_cw_cta[lin][3] = g1 - cta_g0; }
+  }
+#endif
   if (!ok && p.status) atomicExch(p.status, 1);
   tc_fence_before();
   __syncthreads();
@@ -805,6 +853,9 @@ static int launch_chunkwise(const CwMaps& maps, const xl_mlstm_seq_params* p, cu
 }  // namespace xl
 
 #ifdef XL_CW_TIMELINE
+extern "C" int xl_debug_copy_cta(void* dst) {
+  return (int)cudaMemcpyFromSymbol(dst, xl::g_cw_cta, sizeof(xl::g_cw_cta));
+}
 extern "C" int xl_debug_copy_timeline(void* dst) {
   return (int)cudaMemcpyFromSymbol(dst, xl::g_cw_timeline, sizeof(xl::g_cw_timeline));
 }
@@ -820,7 +871,8 @@ extern "C" int xl_mlstm_chunkwise(const xl_mlstm_seq_params* p, void* cuda_strea
   for (int64_t s : strides)
     if (s < 0 || s % 8 != 0) return XL_ERR_BAD_STRIDE;  // TMA: strides are multiples of 16 bytes
   if (p->q_st < p->DHQK || p->k_st < p->DHQK || p->v_st < p->DHV) return XL_ERR_BAD_STRIDE;
-  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v)) return XL_ERR_BAD_ALIGNMENT;
+  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->h)) return XL_ERR_BAD_ALIGNMENT;
+  if (p->h_sb % 8 || p->h_sh % 8 || p->h_st % 8) return XL_ERR_BAD_STRIDE;  // h leaves in 16-byte pieces
   CwMaps maps;
   if ((rc = make_map(&maps.q, maps.pos[0], p->q, p->DHQK, p->S, p->NH, p->B, p->q_sb, p->q_sh, p->q_st)) != XL_OK) return rc;
   if ((rc = make_map(&maps.k, maps.pos[1], p->k, p->DHQK, p->S, p->NH, p->B, p->k_sb, p->k_sh, p->k_st)) != XL_OK) return rc;
