@@ -180,7 +180,9 @@ def build_case(name, dev, rank):
                     metric="mlstm_chunkwise_prefill_tokens_per_s", workload="mlstm_chunkwise_7b_heads", cfg=cfg,
                     bytes=chunkwise_bytes(**cfg), flops=chunkwise_flops(**cfg), kernel="mlstm_chunkwise_kernel<256>",
                     h2d=sum(t.numel() * t.element_size() for t in host), d2h=h_host.numel() * 2 + c_host.numel() * 4,
-                    l2="inputs (%d MB per step) exceed the 126 MB L2" % (chunkwise_bytes(**cfg) // 10 ** 6), launches=1)
+                    l2="inputs (%d MB per step) exceed the 126 MB L2" % (chunkwise_bytes(**cfg) // 10 ** 6), launches=1,
+                    # dram read+write of one captured launch at B=1 (profiles/mlstm_chunkwise_config2.md), scaled by B
+                    traffic=178.2e6 * cfg["B"])
     if name == "step":
         cfg = dict(STEP_CFG)
         B, NH, DQ, DV = cfg["B"], cfg["NH"], cfg["DHQK"], cfg["DHV"]
@@ -208,7 +210,8 @@ def build_case(name, dev, rank):
                     metric="mlstm_step_stream_steps_per_s", workload="mlstm_step_7b_heads", cfg=cfg, bytes=step_bytes(**cfg),
                     flops=B * NH * 4 * DQ * DV, kernel="mlstm_step_kernel<bf16>",
                     h2d=sum(t.numel() * t.element_size() for t in host), d2h=h_host.numel() * 2,
-                    l2="state pool (%d MB) exceeds the 126 MB L2" % (B * NH * DQ * DV * 4 // 10 ** 6), launches=1)
+                    l2="state pool (%d MB) exceeds the 126 MB L2" % (B * NH * DQ * DV * 4 // 10 ** 6), launches=1,
+                    traffic=2.101e9)  # profiles/mlstm_step_256streams.md
     if name == "slstm":
         cfg = dict(SLSTM_CFG)
         B, S, NH, DH = cfg["B"], cfg["S"], cfg["NH"], cfg["DH"]
@@ -231,7 +234,8 @@ def build_case(name, dev, rank):
         return dict(step=step, e2e_step=e2e_step, units=B * S, unit="tokens/s", metric="slstm_forward_tokens_per_s",
                     workload="slstm_cell_config3", cfg=cfg, bytes=slstm_bytes(**cfg), flops=S * B * NH * 2 * DH * 4 * DH,
                     kernel="slstm_forward_kernel<256>", h2d=wx_h.numel() * 2, d2h=o_host.numel() * 2,
-                    l2="inputs (%d MB) exceed the 126 MB L2" % (slstm_bytes(**cfg) // 10 ** 6), launches=1)
+                    l2="inputs (%d MB) exceed the 126 MB L2" % (slstm_bytes(**cfg) // 10 ** 6), launches=1,
+                    traffic=323.9e6)  # profiles/slstm_forward_config3.md
     raise SystemExit(f"unknown case {name}")
 
 
@@ -331,7 +335,8 @@ def main():
             "gpu_launches": args.steps * case["launches"],
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_kind, "kernel": case["kernel"], "kernel_ms": kernel_ms,
+                         "traffic": case.get("traffic"), "traffic_source": "ncu dram__bytes_read+write of one launch, see profiles/",
+                         "peak_source": peak_kind, "kernel": case["kernel"], "kernel_ms": kernel_ms,
                          "algorithmic_bytes": case["bytes"], "tensor_tflops": case["flops"] / (kernel_ms * 1e-3) / 1e12},
         }
         if not args.no_e2e:

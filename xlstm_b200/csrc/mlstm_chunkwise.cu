@@ -46,6 +46,9 @@ constexpr int CW_BOX_BYTES = 64 * 128;  // one TMA box: 64 rows x 64 bf16
 constexpr uint32_t CW_TMEM_COLS = 512;
 constexpr float CW_RESCALE_BELOW = -30.f;  // lazy-decay frame limit (natural log)
 constexpr float CW_LOG2E = 1.4426950408889634f;
+#ifndef XL_ABL
+#define XL_ABL 0  // timing experiments: skip one phase (wrong results); 0 = product
+#endif
 #ifndef XL_CW_SCAN_WARP
 #define XL_CW_SCAN_WARP 0
 #endif
@@ -132,6 +135,8 @@ __device__ unsigned long long g_cw_cta[4096][4];
 
 // Wait used by the UMMA-issuing warp: after a first expired wait the later ones return at once.
 #define MMA_WAIT(idx, parity) (okm ? mbar_wait(bar0 + 8u * (uint32_t)(idx), (uint32_t)(parity)) : false)
+
+#define MMA_WAIT_U(idx, parity) (okm ? mbar_wait(bar_u + 8u * (uint32_t)(idx), (uint32_t)(parity)) : false)
 
 #define CW_WAIT(idx, parity)                                   \
   if (!mbar_wait(bar0 + 8u * (uint32_t)(idx), (uint32_t)(parity))) { \
@@ -279,7 +284,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         const float lf1 = (t1 < len_c) ? fast_log_sigmoid(cf1) : 0.f;
         float incl = lf0 + lf1;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
+        for (int o = 1; o < (XL_ABL == 5 ? 1 : 32); o <<= 1) {
           const float t = __shfl_up_sync(0xffffffffu, incl, o);
           if (lane >= o) incl += t;
         }
@@ -289,11 +294,27 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         const float ap1 = (t1 < len_c) ? ci1 - b1 : -INFINITY;
         float cmx = fmaxf(ap0, ap1);
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
+        for (int o = 1; o < (XL_ABL == 5 ? 1 : 32); o <<= 1) {
           const float t = __shfl_up_sync(0xffffffffu, cmx, o);
           if (lane >= o) cmx = fmaxf(cmx, t);
         }
         CW_TL(4, 4);
+#ifdef XL_CW_TIMELINE
+        {  // experiment: the same scan a second time in a loop body that has just run (warm instruction cache)
+          float inc2 = lf0 + lf1;
+#pragma unroll 1
+          for (int rep = 0; rep < 2; ++rep) {
+            CW_TL(4, 8 + rep);
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+              const float t = __shfl_up_sync(0xffffffffu, inc2, o);
+              if (lane >= o) inc2 += t;
+            }
+          }
+          CW_TL(4, 10);
+          if (inc2 == 123.456f) s_tmp[5] = inc2;
+        }
+#endif
         float prevmax = __shfl_up_sync(0xffffffffu, cmx, 1);
         if (lane == 0) prevmax = -INFINITY;
         const float mu0 = fmaxf(m_prev, fmaxf(prevmax, ap0));
@@ -351,7 +372,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         constexpr int CH = NKB * 4;              // 16-byte pieces per thread
         constexpr int BATCH = CH < 8 ? CH : 8;   // loads first, then stores: the two tiles may not alias in the compiler's eyes
 #pragma unroll 1
-        for (int i0 = 0; i0 < CH; i0 += BATCH) {
+        for (int i0 = 0; i0 < (XL_ABL == 1 ? 0 : CH); i0 += BATCH) {
           uint4 v[BATCH];
           uint32_t off[BATCH];
 #pragma unroll
@@ -404,7 +425,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       const float mulj = s_mul[j];
       float rowsum = 0.f;
 #pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
+      for (int half = 0; half < (XL_ABL == 3 ? 0 : 2); ++half) {
         if (32 * half > 16 * warp + 15) {  // warp-uniform: this half lies wholly above the diagonal
           if (lane < 16) {
 #pragma unroll
@@ -526,7 +547,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       tc_fence_after();
       // ---- T -> bf16 copy (operand of the inter-chunk product); rescale T only when the frame ran out
 #pragma unroll 1
-      for (int cb = 0; cb < DHQK / 64; ++cb) {
+      for (int cb = 0; cb < (XL_ABL == 2 ? 0 : DHQK / 64); ++cb) {
         uint32_t r0[32], r1[32];
         tmem_ld_x32(tC + cb * 64, r0);
         tmem_ld_x32(tC + cb * 64 + 32, r1);
@@ -567,7 +588,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
           v[i] = *reinterpret_cast<const uint4*>(vt + off[i]);
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(smem + LY::OFF_VH + off[i]) = scale_bf16x8(v[i], ww);
+        for (int i = 0; i < (XL_ABL == 6 ? 0 : 8); ++i) *reinterpret_cast<uint4*>(smem + LY::OFF_VH + off[i]) = scale_bf16x8(v[i], ww);
       }
       fence_proxy_async_smem();
       mbar_arrive(bar0 + 8u * BAR_VH);
@@ -610,7 +631,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       CW_TL(2, 1);
       tc_fence_after();
 #pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
+      for (int half = (XL_ABL == 4 ? 1 : 0); half < 2; ++half) {
         uint32_t hv[32];
         tmem_ld_x32(tH + 32 * half, hv);
         float4 iv[8];
@@ -633,7 +654,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       epilogue_group_sync();
       __nv_bfloat16* ho = hbase + (long long)chunk * CW_L * p.h_st;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < (XL_ABL == 4 ? 0 : 8); ++i) {
         const int idx = i * 128 + t, row = idx >> 4, c = idx & 15;
         if (row < len_c)
           *reinterpret_cast<uint4*>(ho + (long long)row * p.h_st + c * 8) = *reinterpret_cast<const uint4*>(hst + row * LY::HST_ROW + c * 16);
@@ -654,80 +675,88 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     constexpr uint32_t IDESC_C = umma_idesc_bf16(128, DHQK, 1, 1);
     constexpr uint32_t IDESC_DN = umma_idesc_bf16(64, 8, 0, 0);
     constexpr uint32_t IDESC_NU = umma_idesc_bf16(64, 8, 1, 0);
-    const uint32_t t_odd = tmem + LY::T_S + (16u << 16);  // odd 16-lane halves of the S columns
+    // Values that are warp-uniform in fact but not provably so (read from shared or global memory) are broadcast
+    // with a shuffle: that is what lets the compiler keep UMMA operands in uniform registers.
+    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0), sbase_u = __shfl_sync(0xffffffffu, sbase, 0);
+    const uint32_t bar_u = __shfl_sync(0xffffffffu, bar0, 0);
+    const int nchunks_u = __shfl_sync(0xffffffffu, nchunks, 0);
+    const uint32_t t_odd = tmem_u + LY::T_S + (16u << 16);  // odd 16-lane halves of the S columns
+    // lower descriptor words (start address >> 4 | leading offset); K-major tiles use leading offset 16 B,
+    // MN-major tiles one 8 KiB box
+    constexpr uint32_t LBO_K = (16u >> 4) << 16, LBO_MN = ((uint32_t)CW_BOX_BYTES >> 4) << 16;
     bool okm = true;
 #pragma unroll 1
-    for (int it = 0; it <= nchunks; ++it) {
+    for (int it = 0; it <= nchunks_u; ++it) {
       if (it >= 1) {
         const int chunk = it - 1;
         const uint32_t par = (uint32_t)chunk & 1u;
-        const uint32_t stg = sbase + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES;  // q | k | v of this chunk
+        const uint32_t stg = sbase_u + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES;  // q | k | v of this chunk
         const uint32_t s_k = stg + LY::Q_BYTES, s_v = s_k + LY::Q_BYTES;
-        const uint32_t wm = sbase + LY::OFF_WMAT + (chunk & 1) * 1024;
+        const uint32_t wm = sbase_u + LY::OFF_WMAT + (chunk & 1) * 1024;
         // H^T = Tb (r q~)^T
-        okm &= MMA_WAIT(BAR_CB, par);
-        okm &= MMA_WAIT(BAR_QS, par);
-        if (chunk >= 1) okm &= MMA_WAIT(BAR_HFREE, par ^ 1u);
+        okm &= MMA_WAIT_U(BAR_CB, par);
+        okm &= MMA_WAIT_U(BAR_QS, par);
+        if (chunk >= 1) okm &= MMA_WAIT_U(BAR_HFREE, par ^ 1u);
         CW_TL(3, 1);
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < DHQK / 16; ++ks)
-          umma_ts_elect(tmem + LY::T_H, tmem + LY::T_CB + ks * 8,
-                        umma_desc_sw128(stg + (ks >> 2) * CW_BOX_BYTES + (ks & 3) * 32, 16, 1024), IDESC_HI, ks != 0);
+          umma_ts_lo(tmem_u + LY::T_H, tmem_u + LY::T_CB + ks * 8,
+                        (LBO_K + ((stg + (ks >> 2) * CW_BOX_BYTES + (ks & 3) * 32) >> 4)), IDESC_HI, ks != 0);
         // qn = (r q~) [n_hi n_lo]^T
-        okm &= MMA_WAIT(BAR_NMAT, par);
+        okm &= MMA_WAIT_U(BAR_NMAT, par);
         CW_TL(3, 3);
         tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < DHQK / 16; ++ks)
-          umma_ss_elect(t_odd, umma_desc_sw128(stg + (ks >> 2) * CW_BOX_BYTES + (ks & 3) * 32, 16, 1024),
-                        umma_desc_sw128(sbase + LY::OFF_NMAT + (ks >> 2) * 1024 + (ks & 3) * 32, 16, 1024), IDESC_DN, ks != 0);
-        umma_commit_elect(bar0 + 8u * BAR_DN);
+        for (int ks = 0; ks < (XL_ABL == 7 ? 1 : DHQK / 16); ++ks)
+          umma_ss_lo(t_odd, (LBO_K + ((stg + (ks >> 2) * CW_BOX_BYTES + (ks & 3) * 32) >> 4)),
+                        (LBO_K + ((sbase_u + LY::OFF_NMAT + (ks >> 2) * 1024 + (ks & 3) * 32) >> 4)), IDESC_DN, ks != 0);
+        umma_commit_elect(bar_u + 8u * BAR_DN);
         // H^T += V^T P^T
-        okm &= MMA_WAIT(BAR_P, par);
+        okm &= MMA_WAIT_U(BAR_P, par);
         CW_TL(3, 4);
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ss_elect(tmem + LY::T_H, umma_desc_sw128(s_v + kk * 2048, CW_BOX_BYTES, 1024),
-                        umma_desc_sw128(sbase + LY::OFF_P + kk * 32, 16, 1024), IDESC_HV, 1);
-        umma_commit_elect(bar0 + 8u * BAR_H);
+          umma_ss_lo(tmem_u + LY::T_H, (LBO_MN + ((s_v >> 4) + ((kk * 2048) >> 4))),
+                        (LBO_K + ((sbase_u >> 4) + ((LY::OFF_P + kk * 32) >> 4))), IDESC_HV, 1);
+        umma_commit_elect(bar_u + 8u * BAR_H);
       }
-      if (it < nchunks) {
+      if (it < nchunks_u) {
         const int chunk = it;
-        const uint32_t s_q = sbase + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES, s_k = s_q + LY::Q_BYTES;
-        okm &= MMA_WAIT(BAR_FULL0 + (chunk & 1), (uint32_t)(chunk >> 1) & 1u);
+        const uint32_t s_q = sbase_u + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES, s_k = s_q + LY::Q_BYTES;
+        okm &= MMA_WAIT_U(BAR_FULL0 + (chunk & 1), (uint32_t)(chunk >> 1) & 1u);
         CW_TL(3, 7);
         tc_fence_after();
 #pragma unroll
         for (int kb = 0; kb < NKB; ++kb)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_ss_elect(tmem + LY::T_S, umma_desc_sw128(s_q + kb * CW_BOX_BYTES + kk * 32, 16, 1024),
-                          umma_desc_sw128(s_k + kb * CW_BOX_BYTES + kk * 32, 16, 1024), IDESC_S, (kb | kk) != 0);
-        umma_commit_elect(bar0 + 8u * BAR_S);
+            umma_ss_lo(tmem_u + LY::T_S, (LBO_K + ((s_q >> 4) + ((kb * CW_BOX_BYTES + kk * 32) >> 4))),
+                          (LBO_K + ((s_k >> 4) + ((kb * CW_BOX_BYTES + kk * 32) >> 4))), IDESC_S, (kb | kk) != 0);
+        umma_commit_elect(bar_u + 8u * BAR_S);
       }
       if (it >= 1) {
         const int chunk = it - 1;
         const uint32_t par = (uint32_t)chunk & 1u;
-        const uint32_t s_k = sbase + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES + LY::Q_BYTES;
-        const uint32_t wm = sbase + LY::OFF_WMAT + (chunk & 1) * 1024;
+        const uint32_t s_k = sbase_u + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES + LY::Q_BYTES;
+        const uint32_t wm = sbase_u + LY::OFF_WMAT + (chunk & 1) * 1024;
         // T += (w V)^T K ;  nu = K^T [w_hi w_lo]^T
-        okm &= MMA_WAIT(BAR_VH, par);
+        okm &= MMA_WAIT_U(BAR_VH, par);
         CW_TL(3, 5);
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ss_elect(tmem + LY::T_C, umma_desc_sw128(sbase + LY::OFF_VH + kk * 2048, CW_BOX_BYTES, 1024),
-                        umma_desc_sw128(s_k + kk * 2048, CW_BOX_BYTES, 1024), IDESC_C, 1);
+          umma_ss_lo(tmem_u + LY::T_C, (LBO_MN + ((sbase_u >> 4) + ((LY::OFF_VH + kk * 2048) >> 4))),
+                        (LBO_MN + ((s_k >> 4) + ((kk * 2048) >> 4))), IDESC_C, 1);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
+        for (int kk = 0; kk < (XL_ABL == 7 ? 1 : 4); ++kk)
 #pragma unroll
-          for (int gq = 0; gq < NKB; ++gq)
-            umma_ss_elect(t_odd + 8 + 8 * gq, umma_desc_sw128(s_k + gq * CW_BOX_BYTES + kk * 2048, CW_BOX_BYTES, 1024),
-                          umma_desc_sw128(wm + kk * 32, 16, 1024), IDESC_NU, kk != 0);
-        umma_commit_elect(bar0 + 8u * BAR_C);
-        umma_commit_elect(bar0 + 8u * (BAR_EMPTY0 + (chunk & 1)));
+          for (int gq = 0; gq < (XL_ABL == 7 ? 1 : NKB); ++gq)
+            umma_ss_lo(t_odd + 8 + 8 * gq, (LBO_MN + ((s_k >> 4) + ((gq * CW_BOX_BYTES + kk * 2048) >> 4))),
+                          (LBO_K + ((wm >> 4) + ((kk * 32) >> 4))), IDESC_NU, kk != 0);
+        umma_commit_elect(bar_u + 8u * BAR_C);
+        umma_commit_elect(bar_u + 8u * (BAR_EMPTY0 + (chunk & 1)));
         CW_TL(3, 6);
       }
     }
