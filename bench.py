@@ -12,6 +12,8 @@ Other cases print the same kind of line for the other kernels of the path:
   step          mLSTM decode step, 256 streams x 8 heads (xLSTM-7B head shapes), state resident in HBM
   slstm         sLSTM forward, BASELINE config 3 cell shape (B=16, S=2048, NH=4, DH=256)
   chunkwise_b1  the headline kernel on one sequence (B=1): the size used for profiler captures
+  model7b       BASELINE config 4: xLSTM-7B-shaped model (random init, bf16), prefill 8 x 8192 tokens + 512 greedy
+                tokens; heads tensor-parallel over the ranks (strong scaling); use e.g. --steps 2 --warmup 3
 
 `--impl reference` times the reference's native CPU formulation (the oracle port) on the host cores.
 """
@@ -236,6 +238,35 @@ def build_case(name, dev, rank):
                     kernel="slstm_forward_kernel<256>", h2d=wx_h.numel() * 2, d2h=o_host.numel() * 2,
                     l2="inputs (%d MB) exceed the 126 MB L2" % (slstm_bytes(**cfg) // 10 ** 6), launches=1,
                     traffic=323.9e6)  # profiles/slstm_forward_config3.md
+    if name == "model7b":
+        # BASELINE config 4: xLSTM-7B-shaped model, random-init bf16, prefill 8 x 8192 tokens then 512 greedy tokens.
+        # Heads are tensor-parallel over the ranks (strong scaling): dense layers are library GEMMs, the cell is ours.
+        from xlstm_b200.large_model import LargeConfig, LargeModel, procedural_state_dict
+        import torch.distributed as dist
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        mcfg = LargeConfig(embedding_dim=4096, num_heads=8, num_blocks=32, vocab_size=50304)
+        sd = procedural_state_dict(mcfg, seed=0, dtype=torch.bfloat16, device=dev, gen_device=dev)
+        model = LargeModel(mcfg, sd, dev, torch.bfloat16, tp_rank=rank if world > 1 else 0, tp_world=world)
+        del sd
+        torch.cuda.empty_cache()
+        B, S, GEN = 8, 8192, 512
+        tok_host = torch.randint(0, mcfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(5)).pin_memory()
+        tok_dev = tok_host.to(dev)
+        out_host = torch.empty(B, GEN, dtype=torch.long).pin_memory()
+
+        def step():
+            return model.generate(tok_dev, GEN)[0]
+
+        def e2e_step():
+            out_host.copy_(model.generate(tok_host.to(dev, non_blocking=True), GEN)[0], non_blocking=True)
+
+        cfg = dict(model="xLSTM-7B-shaped (random init)", embedding_dim=4096, num_heads=8, num_blocks=32, vocab_size=50304,
+                   global_batch=B, seq_len=S, decode_tokens=GEN)
+        return dict(step=step, e2e_step=e2e_step, units=B * (S + GEN), unit="tokens/s", metric="xlstm7b_prefill_decode_tokens_per_s",
+                    workload="xlstm7b_prefill8x8192_decode512", cfg=cfg, bytes=32 * (chunkwise_bytes(B, 8 // world, S, 256, 512)),
+                    flops=0, kernel="mlstm_chunkwise_kernel<256> (32 launches per step)", h2d=tok_host.numel() * 8, d2h=out_host.numel() * 8,
+                    l2="weights (13.7 GB) and activations exceed the 126 MB L2", launches=32 + 32 * GEN, scaling="strong",
+                    parallelism="tp", heavy=True)
     raise SystemExit(f"unknown case {name}")
 
 
@@ -245,7 +276,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--case", default="chunkwise", choices=["chunkwise", "chunkwise_b1", "step", "slstm"])
+    ap.add_argument("--case", default="chunkwise", choices=["chunkwise", "chunkwise_b1", "step", "slstm", "model7b"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="profiling runs: device-resident loop only")
     args = ap.parse_args()
@@ -298,13 +329,13 @@ def main():
             t_end = time.time() + 3.0
             base = sampler.count()
             while sampler.count() < base + 8 and time.time() < t_end:
-                for _ in range(20):
+                for _ in range(1 if case.get("heavy") else 20):
                     step()
                 torch.cuda.synchronize()
         clocks = sampler.stop() if rank == 0 else None
         # ---- end to end through the public call with HOST buffers (pinned H2D of the inputs, kernel, D2H of the result)
-        e2e_steps = max(3, min(args.steps, 10))
-        for _ in range(2):
+        e2e_steps = 1 if case.get("heavy") else max(3, min(args.steps, 10))
+        for _ in range(0 if case.get("heavy") else 2):
             case["e2e_step"]()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
@@ -324,14 +355,17 @@ def main():
     xlstm_b200.check_device_status(dev)
 
     if rank == 0:
-        value = world * case["units"] * args.steps / (total_ms * 1e-3)
+        strong = case.get("scaling") == "strong"
+        nrep = 1 if strong else world   # weak scaling: every rank processes its own units
+        value = nrep * case["units"] * args.steps / (total_ms * 1e-3)
         peak, peak_kind = measured_peak_hbm()
         achieved = case["bytes"] / (kernel_ms * 1e-3) / 1e9
         line = {
             "metric": case["metric"], "value": value, "unit": case["unit"], "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "strong" if strong else "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": case["workload"], **case["cfg"], "parallelism": f"dp{world}", "l2": case["l2"]},
+            "config": {"workload": case["workload"], **case["cfg"], "parallelism": f"{case.get('parallelism', 'dp')}{world}", "l2": case["l2"]},
             "gpu_launches": args.steps * case["launches"],
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -340,7 +374,7 @@ def main():
                          "algorithmic_bytes": case["bytes"], "tensor_tflops": case["flops"] / (kernel_ms * 1e-3) / 1e12},
         }
         if not args.no_e2e:
-            line["e2e"] = {"value": world * case["units"] * e2e_steps / (e2e_ms * 1e-3), "unit": case["unit"],
+            line["e2e"] = {"value": nrep * case["units"] * e2e_steps / (e2e_ms * 1e-3), "unit": case["unit"],
                            "h2d_bytes_per_step": case["h2d"], "d2h_bytes_per_step": case["d2h"], "steps": e2e_steps}
         if args.case == "chunkwise" and not args.no_cpu_baseline and world == 1 and not args.no_e2e:
             threads = os.cpu_count() or 1

@@ -1,0 +1,121 @@
+"""The host-side mirror of the reference's xLSTM-Large model.
+
+CPU: with the CPU oracle as its cell, the mirror must reproduce the golden outputs of the unchanged reference
+model (tests/golden/make_golden_model.py, BASELINE config 1), and two gloo ranks in head-parallel mode must
+reproduce the single-rank logits.  GPU: the same golden with the CUDA kernels as the cell."""
+import os
+import random
+import types
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import load_golden, rel_l2
+from xlstm_b200.large_model import LargeConfig, LargeModel, procedural_state_dict
+
+CFG1 = LargeConfig(embedding_dim=512, num_heads=4, num_blocks=6, vocab_size=2048)
+
+
+def _oracle_cell():
+    from oracle import mlstm as O
+
+    def seq(q, k, v, i, f, c=None, n=None, m=None, cu_seqlens=None, eps=1e-6):
+        h, st = O.mlstm_inference(q, k, v, i, f, c, n, m, eps=eps)
+        return h.to(q.dtype), st
+
+    def step(q, k, v, i, f, c, n, m, slot=None, eps=1e-6):
+        h, st = O.mlstm_step(q, k, v, i, f, c, n, m, eps=eps)
+        return h.to(q.dtype), st
+
+    return types.SimpleNamespace(mlstm_sequence=seq, mlstm_step=step)
+
+
+def _check_against_golden(model, g, tol_logits, device):
+    tokens = g["tokens"].to(device)
+    with torch.no_grad():
+        logits, state = model.forward(tokens)
+        gen, _ = model.generate(tokens, 32)
+    assert rel_l2(logits[:, -1].float().cpu(), g["logits_last"]) < tol_logits
+    assert rel_l2(logits[:, ::37, ::16].float().cpu(), g["logits_sub"]) < tol_logits
+    assert rel_l2(state[5][0].float().cpu(), g["c5"]) < tol_logits
+    return gen.cpu(), g["generated"]
+
+
+def test_mirror_matches_reference_model_on_cpu():
+    g = load_golden("model_config1")
+    model = LargeModel(CFG1, procedural_state_dict(CFG1, 0), "cpu", torch.float32, cell_ops=_oracle_cell())
+    gen, ref = _check_against_golden(model, g, 1e-4, "cpu")
+    assert torch.equal(gen, ref)  # identical greedy tokens over 32 decode steps
+
+
+def _tp_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    cfg = LargeConfig(embedding_dim=256, num_heads=4, num_blocks=2, vocab_size=128)
+    sd = procedural_state_dict(cfg, 3)
+    model = LargeModel(cfg, sd, "cpu", torch.float32, tp_rank=rank, tp_world=world, cell_ops=_oracle_cell())
+    tokens = torch.randint(0, 128, (2, 70), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        logits, state = model.forward(tokens)
+        gen, _ = model.generate(tokens, 4)
+    if rank == 0:
+        q.put((logits, gen, state[1][0].shape))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_head_parallel_two_ranks_equal_single_rank():
+    cfg = LargeConfig(embedding_dim=256, num_heads=4, num_blocks=2, vocab_size=128)
+    single = LargeModel(cfg, procedural_state_dict(cfg, 3), "cpu", torch.float32, cell_ops=_oracle_cell())
+    tokens = torch.randint(0, 128, (2, 70), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref_logits, _ = single.forward(tokens)
+        ref_gen, _ = single.generate(tokens, 4)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31000 + random.randint(0, 2000)
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    logits, gen, cshape = q.get(timeout=300)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert cshape[1] == 2  # each rank keeps the state of its own two heads
+    assert rel_l2(logits, ref_logits) < 1e-5 and torch.equal(gen, ref_gen)
+
+
+@pytest.mark.gpu
+def test_mirror_fp32_on_gpu_matches_reference_model_tokens_and_logits():
+    g = load_golden("model_config1")
+    model = LargeModel(CFG1, procedural_state_dict(CFG1, 0), "cuda", torch.float32)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        gen, ref = _check_against_golden(model, g, 1e-4, "cuda")
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    assert torch.equal(gen, ref)  # identical greedy-argmax tokens over the first 32 decode steps
+
+
+@pytest.mark.gpu
+def test_mirror_bf16_on_gpu_close_to_fp32_reference():
+    """bf16 weights and activations (tensor-core chunkwise kernel + step kernel) against the fp32 reference run:
+    logits within bf16 model noise; greedy tokens of a random-init model have near-zero margins, so token
+    identity is asserted in the fp32 test above and only reported as an agreement rate here."""
+    import xlstm_b200
+    g = load_golden("model_config1")
+    model = LargeModel(CFG1, procedural_state_dict(CFG1, 0), "cuda", torch.bfloat16)
+    tokens = g["tokens"].cuda()
+    with torch.no_grad():
+        logits, state = model.forward(tokens)
+        gen, _ = model.generate(tokens, 32)
+    xlstm_b200.check_device_status()
+    assert rel_l2(logits[:, -1].float().cpu(), g["logits_last"]) < 5e-2
+    assert rel_l2(state[5][0].float().cpu(), g["c5"]) < 5e-2
+    agree = float((gen.cpu() == g["generated"]).float().mean())
+    print("bf16 greedy-token agreement with the fp32 reference:", agree)
+    assert agree > 0.5

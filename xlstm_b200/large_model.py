@@ -1,0 +1,209 @@
+"""Host-side mirror of the reference's xLSTM-Large (xLSTM-7B architecture) forward and greedy decode.
+
+The reference drives the cell kernels from ``xlstm/xlstm_large/model.py`` (embedding -> blocks of
+[RMSNorm, mLSTM layer, residual, RMSNorm, SwiGLU FFN, residual] -> RMSNorm -> lm_head -> soft cap,
+``model.py:126-153, 379-452, 499-510``) and ``generate.py:27-90``.  That file runs unchanged on the
+kernels of this package; this mirror exists because benchmarks and GPU tests must
+run where the reference checkout is not available, and because it adds what the reference has no code
+for: head-parallel execution over several GPUs (one process per GPU, NCCL all-reduce after the
+row-parallel projections) and slot-indexed states.
+
+It consumes a state dict with the reference's "single" weight-mode key names
+(``backbone.blocks.{i}.mlstm_layer.q.weight`` ...), so real checkpoints and the reference's own
+modules are interchangeable with it.  Dense layers are plain library GEMMs (``torch.nn.functional.linear``);
+the recurrent cell is the only part computed by this package's CUDA kernels.
+"""
+from __future__ import annotations
+
+import hashlib
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import ops
+
+
+@dataclass
+class LargeConfig:
+    """Subset of ``xLSTMLargeConfig`` (``model.py:30-109``) that determines the computation."""
+    embedding_dim: int
+    num_heads: int
+    num_blocks: int
+    vocab_size: int
+    qk_dim_factor: float = 0.5
+    v_dim_factor: float = 1.0
+    ffn_proj_factor: float = 2.6667
+    ffn_round_up_to_multiple_of: int = 64
+    gate_soft_cap: float = 15.0
+    output_logit_soft_cap: float = 30.0
+    norm_eps: float = 1e-6
+    eps: float = 1e-6
+
+    @property
+    def qk_dim(self):
+        return int(self.embedding_dim * self.qk_dim_factor)
+
+    @property
+    def v_dim(self):
+        return int(self.embedding_dim * self.v_dim_factor)
+
+    @property
+    def ffn_dim(self):
+        m = self.ffn_round_up_to_multiple_of
+        return int(math.ceil(self.embedding_dim * self.ffn_proj_factor / m) * m)
+
+
+def parameter_shapes(cfg: LargeConfig) -> dict:
+    D, NH, F_, V = cfg.embedding_dim, cfg.num_heads, cfg.ffn_dim, cfg.vocab_size
+    shapes = {"embedding.weight": (V, D), "backbone.out_norm.weight": (D,), "lm_head.weight": (V, D)}
+    for i in range(cfg.num_blocks):
+        b = f"backbone.blocks.{i}."
+        shapes.update({
+            b + "norm_mlstm.weight": (D,), b + "norm_ffn.weight": (D,),
+            b + "mlstm_layer.q.weight": (cfg.qk_dim, D), b + "mlstm_layer.k.weight": (cfg.qk_dim, D),
+            b + "mlstm_layer.v.weight": (cfg.v_dim, D), b + "mlstm_layer.ogate_preact.weight": (cfg.v_dim, D),
+            b + "mlstm_layer.igate_preact.weight": (NH, D), b + "mlstm_layer.igate_preact.bias": (NH,),
+            b + "mlstm_layer.fgate_preact.weight": (NH, D), b + "mlstm_layer.fgate_preact.bias": (NH,),
+            b + "mlstm_layer.multihead_norm.weight": (cfg.v_dim,), b + "mlstm_layer.out_proj.weight": (D, cfg.v_dim),
+            b + "ffn.proj_up_gate.weight": (F_, D), b + "ffn.proj_up.weight": (F_, D), b + "ffn.proj_down.weight": (D, F_),
+        })
+    return shapes
+
+
+def procedural_state_dict(cfg: LargeConfig, seed: int = 0, dtype=torch.float32, device="cpu", gen_device="cpu") -> dict:
+    """Random-init weights that depend only on (seed, parameter name, shape): the same tensors can be produced in
+    any process without shipping a checkpoint.  Linear weights ~ N(0, 1/fan_in), norm weights 1 + small noise,
+    forget-gate biases around +3 (long memory), input-gate biases around 0."""
+    out = {}
+    for name, shape in parameter_shapes(cfg).items():
+        h = int.from_bytes(hashlib.sha256(f"{seed}:{name}".encode()).digest()[:8], "little") % (2 ** 63)
+        # values are drawn on `gen_device`: "cpu" gives bit-identical tensors everywhere (fixtures), a CUDA device is
+        # much faster for multi-billion-parameter shapes (benchmarks) but yields a different stream of numbers
+        g = torch.Generator(device=gen_device).manual_seed(h)
+        if name.endswith("norm.weight") or "norm_" in name:
+            t = 1.0 + 0.05 * torch.randn(shape, generator=g, device=gen_device)
+        elif name.endswith("fgate_preact.bias"):
+            t = 3.0 + torch.randn(shape, generator=g, device=gen_device)
+        elif name.endswith("bias"):
+            t = 0.5 * torch.randn(shape, generator=g, device=gen_device)
+        elif name == "embedding.weight":
+            t = torch.randn(shape, generator=g, device=gen_device)
+        else:
+            t = torch.randn(shape, generator=g, device=gen_device) / math.sqrt(shape[-1])
+        out[name] = t.to(dtype).to(device)
+    return out
+
+
+def _soft_cap(x, cap):
+    return cap * torch.tanh(x / cap)
+
+
+def _rms_norm(x, w, eps):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+class LargeModel:
+    """Inference-only mirror.  With ``tp_world > 1`` each rank holds ``num_heads / tp_world`` heads (column-parallel
+    q/k/v/o-gate/gate projections, per-head norm, row-parallel out_proj) and a 1/tp_world slice of the FFN width;
+    the two partial sums per block are all-reduced over ``group``."""
+
+    def __init__(self, cfg: LargeConfig, state_dict: dict, device, dtype=torch.bfloat16, tp_rank: int = 0,
+                 tp_world: int = 1, group=None, cell_ops=ops):
+        # `cell_ops` provides mlstm_sequence / mlstm_step; the default is this package's CUDA kernels (the test
+        # suite substitutes the CPU oracle to check the dense part of this mirror against the reference on a CPU)
+        self.cell = cell_ops
+        if cfg.num_heads % tp_world or cfg.ffn_dim % tp_world:
+            raise ValueError("num_heads and the FFN width must be divisible by the tensor-parallel world size")
+        self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
+        self.tp_rank, self.tp_world, self.group = tp_rank, tp_world, group
+        NH, NHl = cfg.num_heads, cfg.num_heads // tp_world
+        self.nh_local = NHl
+        dq, dv = cfg.qk_dim // NH, cfg.v_dim // NH
+        self.dq, self.dv = dq, dv
+        h0, h1 = tp_rank * NHl, (tp_rank + 1) * NHl
+        f0, f1 = tp_rank * cfg.ffn_dim // tp_world, (tp_rank + 1) * cfg.ffn_dim // tp_world
+
+        def W(name):
+            return state_dict[name].to(self.device, dtype)
+
+        self.embedding, self.out_norm, self.lm_head = W("embedding.weight"), W("backbone.out_norm.weight"), W("lm_head.weight")
+        self.blocks = []
+        for i in range(cfg.num_blocks):
+            b = f"backbone.blocks.{i}."
+            qkvo = torch.cat([W(b + "mlstm_layer.q.weight")[h0 * dq:h1 * dq], W(b + "mlstm_layer.k.weight")[h0 * dq:h1 * dq],
+                              W(b + "mlstm_layer.v.weight")[h0 * dv:h1 * dv], W(b + "mlstm_layer.ogate_preact.weight")[h0 * dv:h1 * dv]], 0)
+            blk = dict(
+                norm_mlstm=W(b + "norm_mlstm.weight"), norm_ffn=W(b + "norm_ffn.weight"), qkvo=qkvo.contiguous(),
+                if_w=torch.cat([W(b + "mlstm_layer.igate_preact.weight")[h0:h1], W(b + "mlstm_layer.fgate_preact.weight")[h0:h1]], 0).contiguous(),
+                if_b=torch.cat([W(b + "mlstm_layer.igate_preact.bias")[h0:h1], W(b + "mlstm_layer.fgate_preact.bias")[h0:h1]], 0).contiguous(),
+                mh_norm=W(b + "mlstm_layer.multihead_norm.weight")[h0 * dv:h1 * dv].contiguous(),
+                out_proj=W(b + "mlstm_layer.out_proj.weight")[:, h0 * dv:h1 * dv].contiguous(),
+                up=torch.cat([W(b + "ffn.proj_up_gate.weight")[f0:f1], W(b + "ffn.proj_up.weight")[f0:f1]], 0).contiguous(),
+                down=W(b + "ffn.proj_down.weight")[:, f0:f1].contiguous(),
+            )
+            self.blocks.append(blk)
+
+    # ------------------------------------------------------------------------------------------------
+    def _all_reduce(self, x):
+        if self.tp_world > 1:
+            torch.distributed.all_reduce(x, group=self.group)
+        return x
+
+    def _mlstm_layer(self, blk, x, state, cu_seqlens, slot):
+        cfg, NHl, dq, dv = self.cfg, self.nh_local, self.dq, self.dv
+        B, S, _ = x.shape
+        qkvo = F.linear(x, blk["qkvo"])
+        q, k, v, o = torch.split(qkvo, [NHl * dq, NHl * dq, NHl * dv, NHl * dv], dim=-1)
+        gates = _soft_cap(F.linear(x, blk["if_w"], blk["if_b"]).float(), cfg.gate_soft_cap)   # (B,S,2*NHl) fp32
+        ig, fg = gates[..., :NHl].transpose(1, 2), gates[..., NHl:].transpose(1, 2)          # (B,NHl,S) views
+        q = q.reshape(B, S, NHl, dq).transpose(1, 2)     # strided views, no copies (model.py:415-417)
+        k = k.reshape(B, S, NHl, dq).transpose(1, 2)
+        v = v.reshape(B, S, NHl, dv).transpose(1, 2)
+        if S == 1 and cu_seqlens is None:
+            c, n, m = state if state is not None else (None, None, None)
+            h, new_state = self.cell.mlstm_step(q[:, :, 0], k[:, :, 0], v[:, :, 0], ig, fg, c, n, m, slot=slot, eps=cfg.eps)
+            h = h[:, :, None]
+        else:
+            c, n, m = state if state is not None else (None, None, None)
+            h, new_state = self.cell.mlstm_sequence(q, k, v, ig, fg, c, n, m, cu_seqlens=cu_seqlens, eps=cfg.eps)
+        h = h.transpose(1, 2)                            # (B,S,NHl,dv)
+        hf = h.float()
+        hn = (hf - hf.mean(-1, keepdim=True)) * torch.rsqrt(hf.var(-1, keepdim=True, unbiased=False) + cfg.norm_eps)
+        hn = hn.to(x.dtype).reshape(B, S, NHl * dv) * blk["mh_norm"]
+        y = F.linear(torch.sigmoid(o) * hn, blk["out_proj"])
+        return self._all_reduce(y), new_state
+
+    def forward(self, tokens, state: Optional[dict] = None, cu_seqlens=None, slot=None, last_only: bool = False):
+        """tokens (B,S) int64 -> logits (B,S,V) (or (B,1,V) with ``last_only``) and the per-block state dict
+        ``{i: (c,n,m)}`` exactly as ``xLSTMLarge.forward`` returns it (``model.py:126-153``)."""
+        cfg = self.cfg
+        x = self.embedding[tokens]
+        new_state = {}
+        for i, blk in enumerate(self.blocks):
+            y, st = self._mlstm_layer(blk, _rms_norm(x, blk["norm_mlstm"], cfg.norm_eps), None if state is None else state[i],
+                                      cu_seqlens, slot)
+            x = x + y
+            new_state[i] = st
+            u = F.linear(_rms_norm(x, blk["norm_ffn"], cfg.norm_eps), blk["up"])
+            g, z = u.chunk(2, dim=-1)
+            x = x + self._all_reduce(F.linear(F.silu(g) * z, blk["down"]))
+        if last_only:
+            x = x[:, -1:]
+        logits = F.linear(_rms_norm(x, self.out_norm, cfg.norm_eps), self.lm_head)
+        return _soft_cap(logits, cfg.output_logit_soft_cap), new_state
+
+    @torch.no_grad()
+    def generate(self, prefill_tokens, max_length: int, state=None):
+        """Greedy decoding as ``generate_tokens`` does it (``generate.py:79-85``): the first iteration consumes the
+        prefill, every iteration appends argmax of the last position."""
+        out = torch.empty(prefill_tokens.shape[0], max_length, dtype=torch.long, device=self.device)
+        last = prefill_tokens
+        for i in range(max_length):
+            logits, state = self.forward(last, state, last_only=True)
+            last = torch.argmax(logits[:, -1:], dim=-1)
+            out[:, i:i + 1] = last
+        return out, state
