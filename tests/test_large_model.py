@@ -119,3 +119,17 @@ def test_mirror_bf16_on_gpu_close_to_fp32_reference():
     agree = float((gen.cpu() == g["generated"]).float().mean())
     print("bf16 greedy-token agreement with the fp32 reference:", agree)
     assert agree > 0.5
+
+
+@pytest.mark.gpu
+def test_graphed_decode_equals_eager_decode():
+    """Replaying the captured decode step must give the same tokens and state as the host-driven loop."""
+    cfg = LargeConfig(embedding_dim=512, num_heads=4, num_blocks=3, vocab_size=512)
+    model = LargeModel(cfg, procedural_state_dict(cfg, 7), "cuda", torch.bfloat16)
+    tokens = torch.randint(0, 512, (4, 100), generator=torch.Generator().manual_seed(2)).cuda()
+    eager, st_e = model.generate(tokens, 24)
+    graphed, st_g = model.generate(tokens, 24, use_cuda_graph=True)
+    assert torch.equal(eager, graphed)
+    assert rel_l2(st_g[2][0], st_e[2][0]) < 1e-6
+    again, _ = model.generate(tokens, 24, use_cuda_graph=True)   # second call reuses the captured graph
+    assert torch.equal(eager, again)

@@ -196,14 +196,63 @@ class LargeModel:
         logits = F.linear(_rms_norm(x, self.out_norm, cfg.norm_eps), self.lm_head)
         return _soft_cap(logits, cfg.output_logit_soft_cap), new_state
 
+    # ------------------------------------------------------------------------------------------------
+    def _capture_decode_graph(self, state, batch: int):
+        """Capture one decode step (all blocks, lm_head, argmax) in a CUDA graph.  The reference's decode loop
+        (``generate.py:79-85``) launches every small operator from the host for every token; replaying a graph
+        removes that launch cost.  State lives in static buffers: C is updated in place by the step kernel, n and m
+        are copied back into their buffers inside the graph, and the sampled token feeds the next replay."""
+        dev = self.device
+        self._g_state = {i: tuple(t for t in st) for i, st in state.items()}
+        self._g_tok = torch.zeros(batch, 1, dtype=torch.long, device=dev)
+
+        def body():
+            logits, st = self.forward(self._g_tok, self._g_state, last_only=True)
+            for i, (c, n, m) in st.items():
+                assert c is self._g_state[i][0]
+                self._g_state[i][1].copy_(n)
+                self._g_state[i][2].copy_(m.reshape(self._g_state[i][2].shape))
+            self._g_tok.copy_(torch.argmax(logits[:, -1:], dim=-1))
+
+        snapshot = {i: tuple(t.clone() for t in st) for i, st in self._g_state.items()}
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):   # warm-up outside capture (lazy initialisations, allocator pools)
+                body()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            body()
+        for i, st in snapshot.items():   # undo the state changes of the warm-up and capture runs
+            for dst, src in zip(self._g_state[i], st):
+                dst.copy_(src)
+        self._graph, self._graph_batch = graph, batch
+
     @torch.no_grad()
-    def generate(self, prefill_tokens, max_length: int, state=None):
+    def generate(self, prefill_tokens, max_length: int, state=None, use_cuda_graph: bool = False):
         """Greedy decoding as ``generate_tokens`` does it (``generate.py:79-85``): the first iteration consumes the
-        prefill, every iteration appends argmax of the last position."""
+        prefill, every iteration appends argmax of the last position.  With ``use_cuda_graph`` the single-token
+        iterations replay a captured graph (same arithmetic, far fewer host launches)."""
         out = torch.empty(prefill_tokens.shape[0], max_length, dtype=torch.long, device=self.device)
         last = prefill_tokens
         for i in range(max_length):
+            if use_cuda_graph and i >= 1:
+                if i == 1:
+                    B = prefill_tokens.shape[0]
+                    if getattr(self, "_graph", None) is None or self._graph_batch != B:
+                        self._capture_decode_graph(state, B)
+                    else:   # load the fresh prefill state into the graph's static buffers
+                        for j, st in state.items():
+                            for dst, src in zip(self._g_state[j], st):
+                                dst.copy_(src.reshape(dst.shape))
+                    self._g_tok.copy_(last)
+                self._graph.replay()
+                out[:, i:i + 1] = self._g_tok
+                continue
             logits, state = self.forward(last, state, last_only=True)
             last = torch.argmax(logits[:, -1:], dim=-1)
             out[:, i:i + 1] = last
+        if use_cuda_graph and max_length > 1:
+            state = self._g_state
         return out, state
