@@ -131,6 +131,28 @@ def test_chunkwise_harsh_gates_stay_finite_and_match():
     _check(h, st, h_ref, st_ref, TOL_BF16)
 
 
+@pytest.mark.parametrize("jump", [20.0, 40.0, 120.0])
+def test_chunkwise_stabiliser_jumps_inside_a_chunk(jump):
+    """An input gate that leaps by `jump` nats in the middle of a chunk: the rows before the leap must keep their
+    own scale (the kernel switches that chunk to its per-row frame), the rows after it forget the past."""
+    import xlstm_b200
+    B, NH, S, DQ, DV = 1, 2, 256, 64, 128
+    q, k, v, i, f = _inputs(21, B, NH, S, DQ, DV, torch.bfloat16)
+    # a common component in q and k keeps q.n away from zero, so that h is well conditioned where only a few
+    # tokens carry weight
+    q = (q.float() + 1.0).to(torch.bfloat16)
+    k = (k.float() + 1.0).to(torch.bfloat16)
+    i = i.clone()
+    i[:, :, 100:] += jump          # inside chunk 1
+    i[:, 1, 200:] -= 2 * jump      # and back down inside chunk 3 for one head
+    h_ref, st_ref = O.mlstm_inference(q, k, v, i, f)
+    h, st = xlstm_b200.mlstm_sequence(*_cuda(q, k, v, i, f), kernel="chunkwise")
+    assert torch.isfinite(h.float()).all()
+    _check(h, st, h_ref, st_ref, TOL_BF16)
+    # the rows before the leap alone
+    assert rel_l2(h[:, :, 64:100].float().cpu(), h_ref[:, :, 64:100].float()) <= TOL_BF16
+
+
 def test_chunkwise_transposed_views_like_the_reference_layer():
     """q,k,v arrive as (B,S,NH*D) projections viewed as (B,NH,S,D) -- xlstm_large/model.py:415-419."""
     import xlstm_b200

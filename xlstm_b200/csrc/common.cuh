@@ -84,17 +84,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: returns false if the phase did not complete within the poll budget (~ a second).
-// (Not inlined on purpose: kernels wait at dozens of sites and the poll loop would be duplicated at each.)
-static __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t it = 0; it < (1u << 22); ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
+// Fully inline on purpose.  A call to a non-inlined function anywhere in a warp's path makes the compiler give up
+// the uniform datapath for that path: every tcgen05.mma then expands to ~35 instructions instead of ~4 and the
+// issuing warp, not the tensor pipe, sets the pace.  A satisfied wait costs ~35 cycles this way (~140 through a call).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  uint32_t it = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if (++it > (1u << 22)) return false;
 #ifdef XL_WAIT_SLEEP_NS
     __nanosleep(XL_WAIT_SLEEP_NS);
 #else
     if (it > 64) __nanosleep(64);
 #endif
   }
-  return false;
+  return true;
 }
 
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }

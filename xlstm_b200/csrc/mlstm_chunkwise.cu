@@ -23,11 +23,14 @@
 // The two N=8 products land on the odd 16-lane halves of the S columns (an M=64 accumulator only occupies
 // the even halves), so the 512 tensor-memory columns are exactly: T 256 | Tb 128 | H^T 64 | S,qn,nu 64.
 //
-// Warp roles (448 threads): warps 0-3 gate group (gate scans, r-scaled q, P, denominators, n),
-// warps 4-7 state group (T -> bf16 copy / lazy rescale, w-scaled v), warps 8-11 epilogue group
-// (H^T -> normalised bf16 tile in shared memory -> 16-byte global stores), warp 12 issues every UMMA,
-// warp 13 issues the TMA loads.  q is scaled by r_j in place in its TMA stage once S has consumed it.
-// Groups hand work to each other through mbarriers only; every wait is bounded.
+// Warp roles (480 threads): warp 14 carries the gate recurrence (scans, r, w, frame) one to two chunks ahead;
+// warps 0-3 gate group (P from S, denominators, n and its hi/lo operand); warps 4-7 state group (T -> bf16
+// copy / lazy rescale, r-scaled q in place in its TMA stage once S has consumed it, w-scaled v); warps 8-11
+// epilogue group (H^T -> registers -> normalised bf16 tile in shared memory -> 16-byte global stores); warp 12
+// issues every UMMA; warp 13 issues the TMA loads.  Per chunk the tensor pipe runs H^T (inter, intra), T and
+// nu, then S of the next chunk and the normaliser product of this one: the last two need neither T nor its
+// bf16 copy, so they fill the time the state group spends converting T.  Groups hand work to each other
+// through mbarriers only; every wait is bounded, and no waiter is ever more than one phase behind its producer.
 //
 // q, k, v tiles arrive by TMA (128-byte swizzle) straight from the caller's strided (B, NH, S, D) views;
 // documents are chunked from their own first token, so a chunk never straddles a document boundary and the
@@ -40,26 +43,56 @@ namespace xl {
 
 constexpr int CW_L = 64;         // tokens per chunk
 constexpr int CW_DV = 128;       // value columns per CTA (UMMA M)
-constexpr int CW_THREADS = 448;  // 14 warps, see roles above
+constexpr int CW_THREADS = 480;  // 15 warps, see roles above
 constexpr int CW_STAGES = 2;
 constexpr int CW_BOX_BYTES = 64 * 128;  // one TMA box: 64 rows x 64 bf16
 constexpr uint32_t CW_TMEM_COLS = 512;
 constexpr float CW_RESCALE_BELOW = -30.f;  // lazy-decay frame limit (natural log)
 constexpr float CW_LOG2E = 1.4426950408889634f;
+constexpr float CW_FAST_SPREAD = 30.f;     // largest in-chunk spread of the stabiliser the common-frame path accepts
+
+// Per-chunk gate data published by the scan warp (float offsets into one parity's slot).  Every row j of a chunk
+// is computed in a frame exp(-phi_j); h_j = H_j / den_j does not depend on the choice.
+//   exact frame  phi_j = mu_j        : q is scaled by r_j in place, P_jl = S_jl e^{a'_l - mu_j}, H^T += V^T P^T
+//   common frame phi_j = mu* + rho'  : q stays as loaded, the bf16 copy of T carries the scalar, P_jl = S_jl and
+//                                      H^T += (wV)^T P^T with the w-scaled v the state update needs anyway
+// The common frame is used whenever mu* - mu_0 <= CW_FAST_SPREAD (rows then differ by at most e^-30 in scale,
+// which fp32 accumulators and bf16 operands carry without loss); the exact frame covers chunks in which the
+// stabiliser jumps further.  Both produce P_jl = S_jl/sqrt(d) 2^(x_l - y_j) and rowsum_j = sum_l P_jl z_l.
+enum GateSlot {
+  G_LOWER = 0 * CW_L,  // exp(-(b_j + phi_j)): lower bound of the denominator
+  G_X = 1 * CW_L,      // x_l (log2 units; -inf for tokens past the end of the document)
+  G_Y = 2 * CW_L,      // y_j (log2 units)
+  G_R = 3 * CW_L,      // r_j exp(rho) / sqrt(d) (exact frame only)
+  G_W = 4 * CW_L,      // w_l = exp(a'_l - mu* - rho')
+  G_Z = 5 * CW_L,      // z_l
+  G_EPS = 6 * CW_L,    // exp(mu_j - phi_j): eps of the denominator in the row's frame
+  G_MULT = 7 * CW_L,   // rescale multiplier of T (1 unless the lazy frame ran out)
+  G_RHO = G_MULT + 1,  // rho'
+  G_EXACT = G_MULT + 2,  // 1.0 = exact frame
+  G_CB = G_MULT + 3,     // scale of the bf16 copy of T
+  G_QN = G_MULT + 4,     // scale of the normaliser product
+};
 #ifndef XL_ABL
 #define XL_ABL 0  // timing experiments: skip one phase (wrong results); 0 = product
 #endif
-#ifndef XL_CW_SCAN_WARP
-#define XL_CW_SCAN_WARP 0
-#endif
-constexpr int CW_SCAN_WARP = XL_CW_SCAN_WARP;  // gate-group warp that carries the gate recurrence
 
-enum CwBar {  // mbarrier indices
-  BAR_FULL0 = 0, BAR_FULL1, BAR_EMPTY0, BAR_EMPTY1,
-  BAR_S, BAR_DN, BAR_H, BAR_C,                   // UMMA warp -> consumers (tcgen05.commit)
-  BAR_GATES, BAR_QS, BAR_NMAT, BAR_P, BAR_INV,   // gate group -> others
-  BAR_CB, BAR_VH,                                // state group -> UMMA warp
-  BAR_HFREE,                                     // epilogue group -> UMMA warp / gate group
+enum CwWarp { W_GATE_GROUP = 0, W_STATE_GROUP = 4, W_EPI_GROUP = 8, W_UMMA = 12, W_TMA = 13, W_SCAN = 14 };
+
+enum CwBar {  // mbarrier indices.  Barriers whose producer may run two chunks ahead of a waiter come in pairs
+              // indexed by chunk parity (a parity wait is only meaningful one phase back).  A satisfied wait
+              // still costs the UMMA warp ~35 cycles and a commit ~40, so everything one phase of UMMAs needs
+              // arrives on ONE barrier, whatever group it comes from.
+  BAR_FULL0 = 0, BAR_FULL1, BAR_EMPTY0, BAR_EMPTY1,   // TMA stage of q,k,v: landed / consumed
+  BAR_GFULL0, BAR_GFULL1, BAR_GEMPTY0, BAR_GEMPTY1,   // gate data of a chunk: published / consumed
+  BAR_A,     // phase A may issue: bf16 copy of T (state + gate group), q final (state group), H^T drained
+             // (epilogue group), n operand published and nu columns read (gate group): 5 x 128 arrivals
+  BAR_B,     // phase B may issue: P (gate group), w-scaled v (state group): 2 x 128 arrivals
+  BAR_NU,    // commit after phase A: nu complete
+  BAR_HC,    // commit after phase B: H^T and T complete
+  BAR_SDN,   // commit after phase C: S of the next chunk and qn of this one complete (completion k = S(k), qn(k-1))
+  BAR_INV,   // gate group -> epilogue group: 1/denominator published
+  BAR_EGDONE,  // epilogue group -> gate group: 1/denominator consumed
   BAR_COUNT
 };
 
@@ -72,12 +105,13 @@ struct CwLayout {
   static constexpr int OFF_STAGE = 0;
   static constexpr int OFF_VH = CW_STAGES * STAGE_BYTES;       // w_l-scaled v
   static constexpr int OFF_P = OFF_VH + V_BYTES;               // P tile
-  static constexpr int OFF_NMAT = OFF_P + CW_BOX_BYTES;        // [8 x DHQK] bf16: rows n_hi, n_lo, zeros
-  static constexpr int OFF_WMAT = OFF_NMAT + NKB * 1024;       // 2 x [8 x 64] bf16: rows w_hi, w_lo, zeros
+  static constexpr int OFF_NMAT = OFF_P + CW_BOX_BYTES;        // 2 x [8 x DHQK] bf16: rows n_hi, n_lo, zeros
+  static constexpr int OFF_WMAT = OFF_NMAT + 2 * NKB * 1024;      // 2 x [8 x 64] bf16: rows w_hi, w_lo, zeros
   static constexpr int HST_ROW = CW_DV * 2 + 16;               // staged h row: 128 bf16 + 16 B pad
   static constexpr int OFF_HST = OFF_WMAT + 2 * 1024;          // [64][HST_ROW] normalised h of one chunk
   static constexpr int OFF_F32 = OFF_HST + CW_L * HST_ROW;
-  static constexpr int N_F32 = 4 * CW_L + 2 * 2 * CW_L + DHQK + 16 + 8;
+  static constexpr int GATE_F32 = 7 * CW_L + 8;                // per parity: see GateSlot
+  static constexpr int N_F32 = 2 * GATE_F32 + CW_L + DHQK;     // + 1/denominator + n state
   static constexpr int OFF_BAR = OFF_F32 + N_F32 * 4;          // mbarriers (8-byte aligned)
   static constexpr int TOTAL = OFF_BAR + BAR_COUNT * 8 + 16;
   static constexpr int DYN_SMEM = TOTAL + 1024;                // slack to align the base to 1024 B
@@ -129,8 +163,12 @@ __device__ unsigned long long g_cw_cta[4096][4];
 #define CW_TL(role, ev)                                                                                         \
   if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && chunk < 256 && (threadIdx.x & 31) == 0 && (warp & 3) == XL_TL_SMSP) \
     g_cw_timeline[role][chunk][ev] = clock64();
+#define CW_TLS(role, ev)                                                                                        \
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && chunk < 256 && (threadIdx.x & 31) == 0) \
+    g_cw_timeline[role][chunk][ev] = clock64();
 #else
 #define CW_TL(role, ev)
+#define CW_TLS(role, ev)
 #endif
 
 // Wait used by the UMMA-issuing warp: after a first expired wait the later ones return at once.
@@ -144,6 +182,39 @@ __device__ unsigned long long g_cw_cta[4096][4];
     break;                                                     \
   }
 
+// T -> bf16 copy (operand of the inter-chunk product) for 64-column blocks [b0, b1); T itself is rescaled only when
+// the lazy frame ran out.  The state group and the gate group each take half of the blocks at the same time.  One
+// non-inlined copy on purpose: the kernel's hot loops together must stay small enough for the instruction cache
+// (with every role's loop fully unrolled each pass ran mostly on instruction-fetch misses), and two groups running
+// the same code at the same moment share its lines.  (Never called from the UMMA-issuing warp: a call there
+// defeats the uniform datapath.)
+static __device__ __noinline__ void cw_convert_T(uint32_t tC, uint32_t tCb, int b0, int b1, float cb_scale, float mult) {
+#pragma unroll 1
+  for (int cb = b0; cb < b1; ++cb) {
+    uint32_t r0[32], r1[32];
+    tmem_ld_x32(tC + cb * 64, r0);
+    tmem_ld_x32(tC + cb * 64 + 32, r1);
+    tc_wait_ld();
+    uint32_t pk[32];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      pk[i] = pack_bf16x2(__uint_as_float(r0[2 * i]) * cb_scale, __uint_as_float(r0[2 * i + 1]) * cb_scale);
+      pk[16 + i] = pack_bf16x2(__uint_as_float(r1[2 * i]) * cb_scale, __uint_as_float(r1[2 * i + 1]) * cb_scale);
+    }
+    tmem_st_x32(tCb + cb * 32, pk);
+    if (mult != 1.f) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        r0[i] = __float_as_uint(__uint_as_float(r0[i]) * mult);
+        r1[i] = __float_as_uint(__uint_as_float(r1[i]) * mult);
+      }
+      tmem_st_x32(tC + cb * 64, r0);
+      tmem_st_x32(tC + cb * 64 + 32, r1);
+    }
+  }
+  tc_wait_st();
+}
+
 template <int DHQK>
 __global__ void __launch_bounds__(CW_THREADS, 1)
 mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_params p) {
@@ -156,24 +227,24 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   unsigned char* smem = cw_smem_raw + ((1024u - (smem_u32(cw_smem_raw) & 1023u)) & 1023u);
   const uint32_t sbase = smem_u32(smem);
   float* s_f = reinterpret_cast<float*>(smem + LY::OFF_F32);
-  float* s_b = s_f;                   // b_j                               (gate group private)
-  float* s_apl = s_f + 1 * CW_L;      // a'_j * log2(e)                    (gate group private)
-  float* s_mul = s_f + 2 * CW_L;      // mu_j * log2(e)                    (gate group private)
-  float* s_r = s_f + 3 * CW_L;        // r_j * exp(rho_prev) / sqrt(DHQK)  (gate group private)
-  float* s_w = s_f + 4 * CW_L;        // [2][64] w_l * exp(-rho_new)       (read by the state group)
-  float* s_inv = s_f + 6 * CW_L;      // [2][64] 1 / denominator           (read by the epilogue group)
-  float* s_n = s_f + 8 * CW_L;        // n state in the lazy frame, DHQK
-  float* s_tmp = s_n + DHQK;          // 16 scratch words of the gate group
-  float* s_scal = s_tmp + 16;         // [2][4]: rescale multiplier, rho_new
+  // gate data of a chunk, double buffered by chunk parity (see GateSlot)
+  auto gate_buf = [&](int parity) { return s_f + parity * LY::GATE_F32; };
+  float* s_inv = s_f + 2 * LY::GATE_F32;  // 1 / denominator of the chunk in the epilogue
+  float* s_n = s_inv + CW_L;              // n state in the lazy frame, DHQK
   const uint32_t bar0 = sbase + LY::OFF_BAR;
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + LY::OFF_BAR + BAR_COUNT * 8);
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int slice = blockIdx.x, head = blockIdx.y, doc = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31;
+  // The warp index is broadcast through a shuffle so that the compiler can PROVE the role branches below are
+  // warp-uniform: only then does it issue an UMMA as ~4 instructions on the uniform datapath; behind a branch on
+  // plain `threadIdx.x >> 5` every UMMA becomes a ~35-instruction sequence and the issuing warp, not the tensor
+  // pipe, sets the pace.
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
 #ifdef XL_CW_TIMELINE
   const unsigned long long cta_t0 = clock64();
   unsigned long long cta_g0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(cta_g0));
 #endif
+  const int slice = blockIdx.x, head = blockIdx.y, doc = blockIdx.z;
   const int col0 = slice * CW_DV;
   const int DHV = p.DHV;
 
@@ -207,9 +278,13 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   // ---- one-time setup: barriers, tensor memory, constant zero rows of the N=8 operands
   if (tid == 0) {
     for (int i = 0; i < BAR_COUNT; ++i) {
-      uint32_t cnt = 128;
-      if (i == BAR_FULL0 || i == BAR_FULL1 || i == BAR_S || i == BAR_DN || i == BAR_H || i == BAR_C) cnt = 1;
-      if (i == BAR_EMPTY0 || i == BAR_EMPTY1) cnt = 257;  // UMMA commit + gate group + state group
+      uint32_t cnt = 128;                                                        // one 4-warp group arrives
+      if (i == BAR_FULL0 || i == BAR_FULL1 || i == BAR_NU || i == BAR_HC || i == BAR_SDN) cnt = 1;
+      if (i == BAR_EMPTY0 || i == BAR_EMPTY1) cnt = 129;    // state group + UMMA commit
+      if (i == BAR_GFULL0 || i == BAR_GFULL1) cnt = 32;     // the scan warp
+      if (i == BAR_GEMPTY0 || i == BAR_GEMPTY1) cnt = 256;  // state group + gate group
+      if (i == BAR_A) cnt = 640;
+      if (i == BAR_B) cnt = 256;
       mbar_init(bar0 + 8u * i, cnt);
     }
     fence_barrier_init();
@@ -217,9 +292,9 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     tma_prefetch_desc(&maps.k);
     tma_prefetch_desc(&maps.v);
   }
-  for (int i = tid; i < (NKB * 1024 + 2 * 1024) / 16; i += CW_THREADS)
+  for (int i = tid; i < (2 * NKB * 1024 + 2 * 1024) / 16; i += CW_THREADS)
     reinterpret_cast<uint4*>(smem + LY::OFF_NMAT)[i] = make_uint4(0u, 0u, 0u, 0u);
-  if (warp == 12) {
+  if (warp == W_UMMA) {
     __syncwarp();
     tmem_alloc(smem_u32(s_tmem), CW_TMEM_COLS);
     tmem_relinquish();
@@ -233,292 +308,269 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   const uint32_t tH = tmem + LY::T_H + lane_base, tS = tmem + LY::T_S + lane_base;
   const float qscale = rsqrtf((float)DHQK);
   bool ok = true;
+  auto convert_T = [&](int b0, int b1, float cb_scale, float mult) { cw_convert_T(tC, tCb, b0, b1, cb_scale, mult); };
+  constexpr int CB_SPLIT = (DHQK / 64 + 1) / 2;  // blocks [0, CB_SPLIT) state group, [CB_SPLIT, DHQK/64) gate group
 
-  if (warp < 4) {
-    // =========================================================================================== gate group
-    const int g = tid;  // 0..127
+  if (warp == W_SCAN) {
+    // =========================================================================================== scan warp
+    // Carries the gate recurrence one or two chunks ahead of everybody else: lane L owns tokens 2L and 2L+1.
     const float* ig = p.igate + b * p.g_sb + head * p.g_sh + tok0 * p.g_st;
     const float* fg = p.fgate + b * p.g_sb + head * p.g_sh + tok0 * p.g_st;
-    for (int d = g; d < DHQK; d += 128) s_n[d] = p.n0 ? p.n0[sidx * DHQK + d] : 0.f;
-    auto publish_n = [&](int d, float nv) {  // hi/lo bf16 split of n[d] into rows 0/1 of the N=8 operand
-      const __nv_bfloat16 hi = __float2bfloat16_rn(nv);
-      const __nv_bfloat16 lo = __float2bfloat16_rn(nv - __bfloat162float(hi));
-      unsigned char* box = smem + LY::OFF_NMAT + (d >> 6) * 1024;
-      *reinterpret_cast<__nv_bfloat16*>(box + sw128_off(0, d & 63)) = hi;
-      *reinterpret_cast<__nv_bfloat16*>(box + sw128_off(1, d & 63)) = lo;
-    };
-    for (int d = g; d < DHQK; d += 128) publish_n(d, s_n[d]);
-    fence_proxy_async_smem();
-    mbar_arrive(bar0 + 8u * BAR_NMAT);  // operand for chunk 0
-    // warp 0 carries the gate recurrence: lane L owns tokens 2L and 2L+1 of the chunk
     float m_prev = p.m0 ? p.m0[sidx] : 0.f;
     float rho = 0.f;
-    // Gate loads are issued one chunk ahead, unconditionally and from clamped addresses: the tail mask is applied
-    // when the values are used, so nothing has to wait for the load when it is issued.
-    float gi0 = 0.f, gi1 = 0.f, gf0 = 0.f, gf1 = 0.f;
-    if (warp == CW_SCAN_WARP) {
+    // Gate loads are issued one chunk ahead, unconditionally and from clamped addresses; the tail mask is applied
+    // when the values are used.
+    float gi0, gi1, gf0, gf1;
+    {
       const long long t0 = 2 * lane, ta = t0 < len ? t0 : len - 1, tb = t0 + 1 < len ? t0 + 1 : len - 1;
       gi0 = ig[ta * p.g_st]; gf0 = fg[ta * p.g_st];
       gi1 = ig[tb * p.g_st]; gf1 = fg[tb * p.g_st];
     }
 #pragma unroll 1
     for (int chunk = 0; chunk < nchunks; ++chunk) {
-      const int st = chunk & 1, buf = chunk & 1;
-      const uint32_t par = (uint32_t)chunk & 1u, par_full = (uint32_t)(chunk >> 1) & 1u;
+      const int buf = chunk & 1;
       const long long rem = len - (long long)chunk * CW_L;
       const int len_c = rem < CW_L ? (int)rem : CW_L;
-      CW_TL(0, 0);
-      // warp 0 is about to overwrite the gate arrays the other gate-group warps read in their P / denominator passes
-      gate_group_sync();
-      CW_TL(0, 10);
-      // The state group must be done with the gate data of the previous chunk.  (Waiting one phase back, not two:
-      // an mbarrier parity wait is only meaningful while the producer is at most one phase ahead of the waiter.)
-      if (chunk >= 1) CW_WAIT(BAR_VH, par ^ 1u);
-      CW_TL(0, 11);
-      if (warp == CW_SCAN_WARP) {
-        // ---- gate scans over the chunk
-        const float ci0 = gi0, ci1 = gi1, cf0 = gf0, cf1 = gf1;
-        CW_TL(4, 2);
-        const int t0 = 2 * lane, t1 = t0 + 1;
-        const float lf0 = (t0 < len_c) ? fast_log_sigmoid(cf0) : 0.f;
-        const float lf1 = (t1 < len_c) ? fast_log_sigmoid(cf1) : 0.f;
-        float incl = lf0 + lf1;
+      float* gb = gate_buf(buf);
+      CW_TLS(4, 0);
+      CW_WAIT(BAR_GEMPTY0 + buf, ((uint32_t)(chunk >> 1) & 1u) ^ 1u);  // consumers of chunk-2 are done with this buffer
+      CW_TLS(4, 1);
+      const float ci0 = gi0, ci1 = gi1, cf0 = gf0, cf1 = gf1;
+      {
+        const long long tn = (long long)(chunk + 1) * CW_L + 2 * lane;
+        const long long ta = tn < len ? tn : len - 1, tb = tn + 1 < len ? tn + 1 : len - 1;
+        gi0 = ig[ta * p.g_st]; gf0 = fg[ta * p.g_st];
+        gi1 = ig[tb * p.g_st]; gf1 = fg[tb * p.g_st];
+      }
+      const int t0 = 2 * lane, t1 = t0 + 1;
+      const float lf0 = (t0 < len_c) ? fast_log_sigmoid(cf0) : 0.f;
+      const float lf1 = (t1 < len_c) ? fast_log_sigmoid(cf1) : 0.f;
+      float incl = lf0 + lf1;
 #pragma unroll
-        for (int o = 1; o < (XL_ABL == 5 ? 1 : 32); o <<= 1) {
-          const float t = __shfl_up_sync(0xffffffffu, incl, o);
-          if (lane >= o) incl += t;
-        }
-        CW_TL(4, 3);
-        const float b1 = incl, b0 = incl - lf1;
-        const float ap0 = (t0 < len_c) ? ci0 - b0 : -INFINITY;
-        const float ap1 = (t1 < len_c) ? ci1 - b1 : -INFINITY;
-        float cmx = fmaxf(ap0, ap1);
+      for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      const float b1 = incl, b0 = incl - lf1;
+      const float ap0 = (t0 < len_c) ? ci0 - b0 : -INFINITY;
+      const float ap1 = (t1 < len_c) ? ci1 - b1 : -INFINITY;
+      float cmx = fmaxf(ap0, ap1);
 #pragma unroll
-        for (int o = 1; o < (XL_ABL == 5 ? 1 : 32); o <<= 1) {
-          const float t = __shfl_up_sync(0xffffffffu, cmx, o);
-          if (lane >= o) cmx = fmaxf(cmx, t);
-        }
-        CW_TL(4, 4);
-#ifdef XL_CW_TIMELINE
-        {  // experiment: the same scan a second time in a loop body that has just run (warm instruction cache)
-          float inc2 = lf0 + lf1;
+      for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(0xffffffffu, cmx, o);
+        if (lane >= o) cmx = fmaxf(cmx, t);
+      }
+      float prevmax = __shfl_up_sync(0xffffffffu, cmx, 1);
+      if (lane == 0) prevmax = -INFINITY;
+      const float mu0 = fmaxf(m_prev, fmaxf(prevmax, ap0));
+      const float mu1 = fmaxf(m_prev, cmx);
+      const float mu_star = __shfl_sync(0xffffffffu, mu1, 31);
+      const float gsum = __shfl_sync(0xffffffffu, b1, 31);
+      CW_TLS(4, 2);
+      // lazy decay frame: C = exp(rho) T
+      const float cand = rho + (m_prev - mu_star);
+      const bool rescale = cand < CW_RESCALE_BELOW;
+      const float mult = rescale ? __expf(cand) : 1.f;
+      const float rho_new = rescale ? 0.f : cand;
+      const float mu_first = __shfl_sync(0xffffffffu, mu0, 0);
+      const bool exact = (mu_star - mu_first) > CW_FAST_SPREAD;
+      const float w0 = __expf(ap0 - mu_star - rho_new), w1 = __expf(ap1 - mu_star - rho_new);
+      *reinterpret_cast<float2*>(gb + G_W + t0) = make_float2(w0, w1);
+      if (exact) {
+        *reinterpret_cast<float2*>(gb + G_LOWER + t0) = make_float2(__expf(-(b0 + mu0)), __expf(-(b1 + mu1)));
+        *reinterpret_cast<float2*>(gb + G_X + t0) = make_float2(ap0 * CW_LOG2E, ap1 * CW_LOG2E);
+        *reinterpret_cast<float2*>(gb + G_Y + t0) = make_float2(mu0 * CW_LOG2E, mu1 * CW_LOG2E);
+        *reinterpret_cast<float2*>(gb + G_R + t0) =
+            make_float2(__expf(m_prev - mu0 + rho) * qscale, __expf(m_prev - mu1 + rho) * qscale);
+        *reinterpret_cast<float2*>(gb + G_Z + t0) = make_float2(1.f, 1.f);
+        *reinterpret_cast<float2*>(gb + G_EPS + t0) = make_float2(1.f, 1.f);
+      } else {
+        const float phi = mu_star + rho_new;
+        *reinterpret_cast<float2*>(gb + G_LOWER + t0) = make_float2(__expf(-(b0 + phi)), __expf(-(b1 + phi)));
+        *reinterpret_cast<float2*>(gb + G_X + t0) = make_float2(t0 < len_c ? 0.f : -INFINITY, t1 < len_c ? 0.f : -INFINITY);
+        *reinterpret_cast<float2*>(gb + G_Y + t0) = make_float2(0.f, 0.f);
+        *reinterpret_cast<float2*>(gb + G_Z + t0) = make_float2(w0, w1);
+        *reinterpret_cast<float2*>(gb + G_EPS + t0) = make_float2(__expf(mu0 - phi), __expf(mu1 - phi));
+      }
+      {
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(w0, w1);
+        const float2 hif = __bfloat1622float2(hi);
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(w0 - hif.x, w1 - hif.y);
+        unsigned char* wm = smem + LY::OFF_WMAT + buf * 1024;
+        *reinterpret_cast<__nv_bfloat162*>(wm + sw128_off(0, t0)) = hi;
+        *reinterpret_cast<__nv_bfloat162*>(wm + sw128_off(1, t0)) = lo;
+      }
+      if (lane == 0) {
+        gb[G_MULT] = mult;
+        gb[G_RHO] = rho_new;
+        gb[G_EXACT] = exact ? 1.f : 0.f;
+        // common frame: T q enters as exp(rho + m_prev - mu* - rho') T q / sqrt(d); that exponent is the rescale
+        // multiplier itself (1 whenever no rescale happens)
+        gb[G_CB] = exact ? 1.f : mult * qscale;
+        gb[G_QN] = exact ? 1.f : mult * qscale;
+      }
+      m_prev = gsum + mu_star;
+      rho = rho_new;
+      fence_proxy_async_smem();
+      mbar_arrive(bar0 + 8u * (BAR_GFULL0 + buf));
+      CW_TLS(4, 3);
+    }
+    if (ok && slice == 0 && lane == 0) p.m_out[sidx] = m_prev;
+  } else if (warp < W_STATE_GROUP) {
+    // =========================================================================================== gate group
+    // Iteration j: its half of the T -> bf16 conversion for chunk j; denominators of chunk j-1; P(j) from S(j);
+    // then, once nu of chunk j is complete, n(j) and its hi/lo operand for chunk j+1.
+    const int g = tid;  // 0..127
+    for (int d = g; d < DHQK; d += 128) s_n[d] = p.n0 ? p.n0[sidx * DHQK + d] : 0.f;
+    auto publish_n = [&](int nbuf, int d, float nv) {  // hi/lo bf16 split of n[d] into rows 0/1 of the N=8 operand
+      const __nv_bfloat16 hi = __float2bfloat16_rn(nv);
+      const __nv_bfloat16 lo = __float2bfloat16_rn(nv - __bfloat162float(hi));
+      unsigned char* box = smem + LY::OFF_NMAT + nbuf * (NKB * 1024) + (d >> 6) * 1024;
+      *reinterpret_cast<__nv_bfloat16*>(box + sw128_off(0, d & 63)) = hi;
+      *reinterpret_cast<__nv_bfloat16*>(box + sw128_off(1, d & 63)) = lo;
+    };
+    for (int d = g; d < DHQK; d += 128) publish_n(0, d, s_n[d]);
+    fence_proxy_async_smem();
+    mbar_arrive(bar0 + 8u * BAR_A);  // n operand for chunk 0
+    const int j = warp * 16 + (lane & 15);  // S row of this thread (lanes 0..15); lanes 16..31 see the N=8 products
+    float rowsum_prev = 0.f, lower_prev = 0.f, qn_scale_prev = 1.f, eps_prev = 0.f;
+    float back_last = 1.f;
+    // denominators of chunk c: |rowsum + q.n| against the lower bound; the product sits on lanes 16..31
+    auto denominators = [&](int c, float rowsum, float lower, float qn_scale, float eps_j) -> bool {
+      if (!mbar_wait(bar0 + 8u * BAR_SDN, (uint32_t)(c + 1) & 1u)) return false;
+      if (c >= 1 && !mbar_wait(bar0 + 8u * BAR_EGDONE, (uint32_t)(c - 1) & 1u)) return false;  // s_inv is free again
+      tc_fence_after();
+      uint32_t dn[8];
+      tmem_ld_x8(tS, dn);
+      tc_wait_ld();
+      const float dot = __shfl_down_sync(0xffffffffu, __uint_as_float(dn[0]) + __uint_as_float(dn[1]), 16);
+      if (lane < 16) s_inv[j] = __fdividef(1.f, fmaxf(fabsf(fmaf(dot, qn_scale, rowsum)), lower) + eps_j);
+      tc_fence_before();
+      mbar_arrive(bar0 + 8u * BAR_INV);
+      return true;
+    };
 #pragma unroll 1
-          for (int rep = 0; rep < 2; ++rep) {
-            CW_TL(4, 8 + rep);
+    for (int chunk = 0; chunk < nchunks; ++chunk) {
+      const int buf = chunk & 1;
+      const uint32_t par = (uint32_t)chunk & 1u;
+      const float* gb = gate_buf(buf);
+      CW_TL(0, 0);
+      CW_WAIT(BAR_GFULL0 + buf, (uint32_t)(chunk >> 1) & 1u);
+      CW_TL(0, 1);
+      const float yj = gb[G_Y + j];
+      const float lower = gb[G_LOWER + j];
+      const float eps_j = p.eps * gb[G_EPS + j];
+      const float mult = gb[G_MULT], qn_scale = gb[G_QN], cb_scale = gb[G_CB];
+      const bool exact = gb[G_EXACT] != 0.f;
+      if (chunk + 1 == nchunks) back_last = expf(gb[G_RHO]);
+      // ---- T -> bf16 copy, this group's blocks (the state group converts everything for the first chunk)
+      if (chunk >= 1) {
+        CW_WAIT(BAR_HC, par ^ 1u);  // T holds chunk-1; its UMMAs no longer read the bf16 copy or the P tile
+        tc_fence_after();
+        if (!(XL_ABL & 1)) convert_T(CB_SPLIT, DHQK / 64, cb_scale, mult);
+        tc_fence_before();
+      }
+      mbar_arrive(bar0 + 8u * BAR_A);
+      CW_TL(0, 2);
+      // ---- denominators of the previous chunk
+      if (chunk >= 1 && !denominators(chunk - 1, rowsum_prev, lower_prev, qn_scale_prev, eps_prev)) { ok = false; break; }
+      CW_TL(0, 3);
+      CW_WAIT(BAR_SDN, par);
+      CW_TL(0, 4);
+      tc_fence_after();
+      // ---- P from S (rows of this warp: j = 16 warp + lane for lanes 0..15)
+      // Rolled over 16-column pieces on purpose (small code): piece q holds columns 16q..16q+15; this warp's rows
+      // 16w..16w+15 need pieces 0..w (piece w straddles the diagonal), the others are zero.
+      float rs[4] = {0.f, 0.f, 0.f, 0.f};
+      unsigned char* prow = smem + LY::OFF_P + j * 128;
+#pragma unroll 1
+      for (int q = 0; q < ((XL_ABL & 2) ? 0 : 4); ++q) {
+        uint4 o0 = make_uint4(0u, 0u, 0u, 0u), o1 = o0;
+        if (q <= warp) {  // warp-uniform
+          uint32_t sv[16];
+          tmem_ld_x16(tS + 16 * q, sv);
+          float4 z4[4];
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-              const float t = __shfl_up_sync(0xffffffffu, inc2, o);
-              if (lane >= o) inc2 += t;
+          for (int i = 0; i < 4; ++i) z4[i] = *reinterpret_cast<const float4*>(gb + G_Z + 16 * q + 4 * i);
+          const float zv[16] = {z4[0].x, z4[0].y, z4[0].z, z4[0].w, z4[1].x, z4[1].y, z4[1].z, z4[1].w,
+                                z4[2].x, z4[2].y, z4[2].z, z4[2].w, z4[3].x, z4[3].y, z4[3].z, z4[3].w};
+          float e[16];
+          if (exact) {
+            float4 a4[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a4[i] = *reinterpret_cast<const float4*>(gb + G_X + 16 * q + 4 * i);
+            const float av[16] = {a4[0].x, a4[0].y, a4[0].z, a4[0].w, a4[1].x, a4[1].y, a4[1].z, a4[1].w,
+                                  a4[2].x, a4[2].y, a4[2].z, a4[2].w, a4[3].x, a4[3].y, a4[3].z, a4[3].w};
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float x = __uint_as_float(sv[i]) * qscale * ex2_approx(av[i] - yj);
+              e[i] = (16 * q + i <= j) ? x : 0.f;
             }
+          } else {
+            tc_wait_ld();
+            const int lim = (q < warp) ? 64 : j;  // pieces left of the diagonal piece need no mask
+#pragma unroll
+            for (int i = 0; i < 16; ++i) e[i] = (16 * q + i <= lim) ? __uint_as_float(sv[i]) * qscale : 0.f;
           }
-          CW_TL(4, 10);
-          if (inc2 == 123.456f) s_tmp[5] = inc2;
+          o0 = make_uint4(pack_bf16x2(e[0], e[1]), pack_bf16x2(e[2], e[3]), pack_bf16x2(e[4], e[5]), pack_bf16x2(e[6], e[7]));
+          o1 = make_uint4(pack_bf16x2(e[8], e[9]), pack_bf16x2(e[10], e[11]), pack_bf16x2(e[12], e[13]), pack_bf16x2(e[14], e[15]));
+          // (row sums from the unrounded values: the difference to the bf16 P is below the bf16 rounding of h)
+#pragma unroll
+          for (int i = 0; i < 16; ++i) rs[i & 3] = fmaf(e[i], zv[i], rs[i & 3]);
         }
-#endif
-        float prevmax = __shfl_up_sync(0xffffffffu, cmx, 1);
-        if (lane == 0) prevmax = -INFINITY;
-        const float mu0 = fmaxf(m_prev, fmaxf(prevmax, ap0));
-        const float mu1 = fmaxf(m_prev, cmx);
-        const float mu_star = __shfl_sync(0xffffffffu, mu1, 31);
-        const float gsum = __shfl_sync(0xffffffffu, b1, 31);
-        CW_TL(4, 5);
-        // lazy decay frame: C = exp(rho) T
-        const float cand = rho + (m_prev - mu_star);
-        const bool rescale = cand < CW_RESCALE_BELOW;
-        const float mult = rescale ? __expf(cand) : 1.f;
-        const float rho_new = rescale ? 0.f : cand;
-        *reinterpret_cast<float2*>(s_b + t0) = make_float2(b0, b1);
-        *reinterpret_cast<float2*>(s_apl + t0) = make_float2(ap0 * CW_LOG2E, ap1 * CW_LOG2E);
-        *reinterpret_cast<float2*>(s_mul + t0) = make_float2(mu0 * CW_LOG2E, mu1 * CW_LOG2E);
-        *reinterpret_cast<float2*>(s_r + t0) = make_float2(__expf(m_prev - mu0 + rho) * qscale, __expf(m_prev - mu1 + rho) * qscale);
-        CW_TL(4, 6);
-        const float w0 = __expf(ap0 - mu_star - rho_new), w1 = __expf(ap1 - mu_star - rho_new);
-        *reinterpret_cast<float2*>(s_w + buf * CW_L + t0) = make_float2(w0, w1);
-        {
-          const __nv_bfloat162 hi = __floats2bfloat162_rn(w0, w1);
-          const float2 hif = __bfloat1622float2(hi);
-          const __nv_bfloat162 lo = __floats2bfloat162_rn(w0 - hif.x, w1 - hif.y);
-          unsigned char* wm = smem + LY::OFF_WMAT + buf * 1024;
-          *reinterpret_cast<__nv_bfloat162*>(wm + sw128_off(0, t0)) = hi;
-          *reinterpret_cast<__nv_bfloat162*>(wm + sw128_off(1, t0)) = lo;
+        if (lane < 16) {
+          *reinterpret_cast<uint4*>(prow + (((2 * q) ^ (j & 7)) << 4)) = o0;
+          *reinterpret_cast<uint4*>(prow + (((2 * q + 1) ^ (j & 7)) << 4)) = o1;
         }
-        CW_TL(4, 7);
-        if (lane == 0) { s_scal[buf * 4 + 0] = mult; s_scal[buf * 4 + 1] = rho_new; }
-        {  // next chunk's gate values (clamped addresses; the tail mask is applied at use)
-          const long long tn = (long long)(chunk + 1) * CW_L + 2 * lane;
-          const long long ta = tn < len ? tn : len - 1, tb = tn + 1 < len ? tn + 1 : len - 1;
-          gi0 = ig[ta * p.g_st]; gf0 = fg[ta * p.g_st];
-          gi1 = ig[tb * p.g_st]; gf1 = fg[tb * p.g_st];
-        }
-        m_prev = gsum + mu_star;
-        rho = rho_new;
       }
       CW_TL(0, 12);
       fence_proxy_async_smem();
       CW_TL(0, 13);
-      gate_group_sync();
-      mbar_arrive(bar0 + 8u * BAR_GATES);
-      CW_TL(0, 1);
+      tc_fence_before();
+      mbar_arrive(bar0 + 8u * BAR_B);
+      CW_TL(0, 5);
+      const float rowsum = (rs[0] + rs[1]) + (rs[2] + rs[3]);
+      rowsum_prev = rowsum;
+      lower_prev = lower;
+      qn_scale_prev = qn_scale;
+      eps_prev = eps_j;
 
-      // ---- q <- r_j q IN PLACE in the stage tile (thread: row j = g/2, half of the row).  S of this chunk, the
-      // only consumer of the un-scaled q, has been issued one iteration ahead and must have completed.
-      CW_WAIT(BAR_FULL0 + st, par_full);
-      CW_WAIT(BAR_S, par);
-      CW_TL(0, 2);
+      // ---- n of this chunk: n = mult n + nu, published as the hi/lo operand of the next chunk.  The other operand
+      // buffer is still read by this chunk's normaliser product.
+      CW_WAIT(BAR_NU, par);
+      CW_TL(0, 6);
+      tc_fence_after();
       {
-        const int j = g >> 1, half = g & 1;
-        const __nv_bfloat162 rr = __float2bfloat162_rn(s_r[j]);
-        unsigned char* qt = smem + LY::OFF_STAGE + st * LY::STAGE_BYTES;
-        constexpr int CH = NKB * 4;              // 16-byte pieces per thread
-        constexpr int BATCH = CH < 8 ? CH : 8;   // loads first, then stores: the two tiles may not alias in the compiler's eyes
-#pragma unroll 1
-        for (int i0 = 0; i0 < (XL_ABL == 1 ? 0 : CH); i0 += BATCH) {
-          uint4 v[BATCH];
-          uint32_t off[BATCH];
-#pragma unroll
-          for (int i = 0; i < BATCH; ++i) {
-            const int cidx = half * CH + i0 + i;
-            const int box = cidx >> 3;
-            const int c = (NKB >= 2) ? ((cidx & 7) ^ (half << 2)) : (cidx & 7);
-            off[i] = box * CW_BOX_BYTES + j * 128 + ((c ^ (j & 7)) << 4);
-            v[i] = *reinterpret_cast<const uint4*>(qt + off[i]);
-          }
-#pragma unroll
-          for (int i = 0; i < BATCH; ++i) *reinterpret_cast<uint4*>(qt + off[i]) = scale_bf16x8(v[i], rr);
-        }
-      }
-      CW_TL(0, 14);
-      fence_proxy_async_smem();
-      mbar_arrive(bar0 + 8u * BAR_QS);
-      mbar_arrive(bar0 + 8u * (BAR_EMPTY0 + st));  // this thread is done reading the q tile of this stage
-      CW_TL(0, 3);
-
-      // ---- n of the previous chunk: n = mult n + nu, then the hi/lo operand for this chunk's normaliser product
-      if (chunk >= 1) {
-        CW_WAIT(BAR_C, par ^ 1u);
-        tc_fence_after();
         uint32_t r[32];
         tmem_ld_x32(tS + 8, r);
-        CW_TL(0, 4);
-        const float mult_last = s_scal[(buf ^ 1) * 4 + 0];
         tc_wait_ld();
         if (lane >= 16) {
 #pragma unroll
           for (int gq = 0; gq < NKB; ++gq) {
             const int d = 64 * gq + 16 * warp + (lane - 16);
-            const float nv = fmaf(s_n[d], mult_last, __uint_as_float(r[8 * gq]) + __uint_as_float(r[8 * gq + 1]));
+            const float nv = fmaf(s_n[d], mult, __uint_as_float(r[8 * gq]) + __uint_as_float(r[8 * gq + 1]));
             s_n[d] = nv;
-            publish_n(d, nv);
-          }
-        }
-        fence_proxy_async_smem();
-        tc_fence_before();
-        mbar_arrive(bar0 + 8u * BAR_NMAT);
-      }
-      CW_TL(0, 5);
-
-      // ---- P from S (rows of this warp: j = 16 warp + lane for lanes 0..15)
-      if (chunk >= 1) CW_WAIT(BAR_H, par ^ 1u);  // the UMMAs of chunk-1 no longer read the P tile
-      CW_TL(0, 6);
-      tc_fence_after();
-      const int j = warp * 16 + (lane & 15);
-      const float mulj = s_mul[j];
-      float rowsum = 0.f;
-#pragma unroll 1
-      for (int half = 0; half < (XL_ABL == 3 ? 0 : 2); ++half) {
-        if (32 * half > 16 * warp + 15) {  // warp-uniform: this half lies wholly above the diagonal
-          if (lane < 16) {
-#pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
-              const int c = half * 4 + c4;
-              *reinterpret_cast<uint4*>(smem + LY::OFF_P + j * 128 + ((c ^ (j & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
-            }
-          }
-          continue;
-        }
-        uint32_t sv[32];
-        tmem_ld_x32(tS + 32 * half, sv);
-        float4 a4[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) a4[i] = *reinterpret_cast<const float4*>(s_apl + 32 * half + 4 * i);
-        tc_wait_ld();
-        if (lane < 16) {
-          uint4 o[4];
-#pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) {
-            const int c = half * 4 + c4;
-            o[c4] = make_uint4(0u, 0u, 0u, 0u);
-            if (8 * c <= 16 * warp + 15) {  // warp-uniform: blocks wholly above the diagonal stay zero
-              const float av[8] = {a4[2 * c4].x, a4[2 * c4].y, a4[2 * c4].z, a4[2 * c4].w,
-                                   a4[2 * c4 + 1].x, a4[2 * c4 + 1].y, a4[2 * c4 + 1].z, a4[2 * c4 + 1].w};
-              float e[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const int l = c * 8 + i;
-                const float x = __uint_as_float(sv[c4 * 8 + i]) * qscale * ex2_approx(av[i] - mulj);
-                e[i] = (l <= j) ? x : 0.f;
-              }
-              o[c4].x = pack_bf16x2(e[0], e[1]);
-              o[c4].y = pack_bf16x2(e[2], e[3]);
-              o[c4].z = pack_bf16x2(e[4], e[5]);
-              o[c4].w = pack_bf16x2(e[6], e[7]);
-              const float2 f0 = unpack_bf16x2(o[c4].x), f1 = unpack_bf16x2(o[c4].y), f2 = unpack_bf16x2(o[c4].z),
-                           f3 = unpack_bf16x2(o[c4].w);
-              rowsum += (f0.x + f0.y) + (f1.x + f1.y) + (f2.x + f2.y) + (f3.x + f3.y);
-            }
-          }
-#pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) {
-            const int c = half * 4 + c4;
-            *reinterpret_cast<uint4*>(smem + LY::OFF_P + j * 128 + ((c ^ (j & 7)) << 4)) = o[c4];
+            publish_n(buf ^ 1, d, nv);
           }
         }
       }
-      CW_TL(0, 15);
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(bar0 + 8u * BAR_P);
+      mbar_arrive(bar0 + 8u * BAR_A);                 // n operand of the next chunk; nu columns free
+      mbar_arrive(bar0 + 8u * (BAR_GEMPTY0 + buf));  // done with this chunk's gate data (so is nu, which read w)
       CW_TL(0, 7);
-
-      // ---- denominators: the normaliser product sits on lanes 16..31, the row sums on lanes 0..15
-      const float lower = __expf(-(s_b[j] + mulj * (1.f / CW_LOG2E)));
-      CW_WAIT(BAR_DN, par);
-      CW_TL(0, 8);
-      tc_fence_after();
-      {
-        uint32_t dn[8];
-        tmem_ld_x8(tS, dn);
-        tc_wait_ld();
-        const float dot = __shfl_down_sync(0xffffffffu, __uint_as_float(dn[0]) + __uint_as_float(dn[1]), 16);
-        if (chunk >= 1) CW_WAIT(BAR_HFREE, par ^ 1u);  // the epilogue group is done with the previous chunk's s_inv
-        if (lane < 16) s_inv[buf * CW_L + j] = __fdividef(1.f, fmaxf(fabsf(rowsum + dot), lower) + p.eps);
-      }
-      tc_fence_before();
-      mbar_arrive(bar0 + 8u * BAR_INV);
-      CW_TL(0, 9);
     }
-    // ---- final n, m
-    if (ok) {
-      do {
-        CW_WAIT(BAR_C, (uint32_t)(nchunks - 1) & 1u);
-        tc_fence_after();
-        uint32_t r[32];
-        tmem_ld_x32(tS + 8, r);
-        tc_wait_ld();
-        const int lb = (nchunks - 1) & 1;
-        if (slice == 0 && lane >= 16) {
-          const float mult_last = s_scal[lb * 4 + 0], back = expf(s_scal[lb * 4 + 1]);
+    if (ok) ok = denominators(nchunks - 1, rowsum_prev, lower_prev, qn_scale_prev, eps_prev);
+    // ---- final n (back in the true frame)
+    if (ok && slice == 0 && lane >= 16) {
 #pragma unroll
-          for (int gq = 0; gq < NKB; ++gq) {
-            const int d = 64 * gq + 16 * warp + (lane - 16);
-            const float nv = fmaf(s_n[d], mult_last, __uint_as_float(r[8 * gq]) + __uint_as_float(r[8 * gq + 1]));
-            p.n_out[sidx * DHQK + d] = nv * back;
-          }
-        }
-        if (slice == 0 && g == CW_SCAN_WARP * 32) p.m_out[sidx] = m_prev;
-      } while (false);
+      for (int gq = 0; gq < NKB; ++gq) {
+        const int d = 64 * gq + 16 * warp + (lane - 16);
+        p.n_out[sidx * DHQK + d] = s_n[d] * back_last;
+      }
     }
-  } else if (warp < 8) {
+  } else if (warp < W_EPI_GROUP) {
     // =========================================================================================== state group
     const int t = tid - 128;
     const int dv = (warp & 3) * 32 + lane;  // tensor-memory lane = value column within the slice
@@ -537,45 +589,26 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     for (int chunk = 0; chunk < nchunks; ++chunk) {
       const int st = chunk & 1, buf = chunk & 1;
       const uint32_t par = (uint32_t)chunk & 1u, par_full = (uint32_t)(chunk >> 1) & 1u;
-      CW_WAIT(BAR_GATES, par);
+      const float* gb = gate_buf(buf);
       CW_TL(1, 1);
-      const float mult = s_scal[buf * 4 + 0];
-      rho_last = s_scal[buf * 4 + 1];
-      const __nv_bfloat162 ww = __float2bfloat162_rn(s_w[buf * CW_L + (t >> 1)]);
-      if (chunk >= 1) CW_WAIT(BAR_C, par ^ 1u);  // T holds chunk-1; its UMMAs no longer read Tb or the scaled-v tile
+      CW_WAIT(BAR_GFULL0 + buf, par_full);
+      const float mult = gb[G_MULT], cb_scale = gb[G_CB];
+      const bool exact = gb[G_EXACT] != 0.f;
+      rho_last = gb[G_RHO];
+      const __nv_bfloat162 rr = __float2bfloat162_rn(gb[G_R + (t >> 1)]);
+      const __nv_bfloat162 ww = __float2bfloat162_rn(gb[G_W + (t >> 1)]);
+      if (chunk >= 1) CW_WAIT(BAR_HC, par ^ 1u);  // T holds chunk-1; its UMMAs no longer read Tb or the scaled-v tile
       CW_TL(1, 2);
       tc_fence_after();
-      // ---- T -> bf16 copy (operand of the inter-chunk product); rescale T only when the frame ran out
-#pragma unroll 1
-      for (int cb = 0; cb < (XL_ABL == 2 ? 0 : DHQK / 64); ++cb) {
-        uint32_t r0[32], r1[32];
-        tmem_ld_x32(tC + cb * 64, r0);
-        tmem_ld_x32(tC + cb * 64 + 32, r1);
-        tc_wait_ld();
-        uint32_t pk[32];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          pk[i] = pack_bf16x2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
-          pk[16 + i] = pack_bf16x2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
-        }
-        tmem_st_x32(tCb + cb * 32, pk);
-        if (mult != 1.f) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            r0[i] = __float_as_uint(__uint_as_float(r0[i]) * mult);
-            r1[i] = __float_as_uint(__uint_as_float(r1[i]) * mult);
-          }
-          tmem_st_x32(tC + cb * 64, r0);
-          tmem_st_x32(tC + cb * 64 + 32, r1);
-        }
-      }
-      tc_wait_st();
+      // ---- T -> bf16 copy, this group's blocks (all of them for the first chunk: the gate group has not yet seen
+      // the initial state land in tensor memory)
+      if (!(XL_ABL & 1)) convert_T(0, chunk == 0 ? DHQK / 64 : CB_SPLIT, cb_scale, mult);
       tc_fence_before();
-      mbar_arrive(bar0 + 8u * BAR_CB);
+      mbar_arrive(bar0 + 8u * BAR_A);
+      if (!exact) mbar_arrive(bar0 + 8u * BAR_A);  // common frame: q is used as loaded
       CW_TL(1, 3);
       // ---- w-scaled v (thread: row l = t/2, box = t&1)
       CW_WAIT(BAR_FULL0 + st, par_full);
-      CW_TL(1, 4);
       {
         const int l = t >> 1, half = t & 1;
         const unsigned char* vt = smem + LY::OFF_STAGE + st * LY::STAGE_BYTES + 2 * LY::Q_BYTES;
@@ -588,17 +621,46 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
           v[i] = *reinterpret_cast<const uint4*>(vt + off[i]);
         }
 #pragma unroll
-        for (int i = 0; i < (XL_ABL == 6 ? 0 : 8); ++i) *reinterpret_cast<uint4*>(smem + LY::OFF_VH + off[i]) = scale_bf16x8(v[i], ww);
+        for (int i = 0; i < ((XL_ABL & 16) ? 0 : 8); ++i) *reinterpret_cast<uint4*>(smem + LY::OFF_VH + off[i]) = scale_bf16x8(v[i], ww);
       }
       fence_proxy_async_smem();
-      mbar_arrive(bar0 + 8u * BAR_VH);
-      mbar_arrive(bar0 + 8u * (BAR_EMPTY0 + st));
+      mbar_arrive(bar0 + 8u * BAR_B);
       CW_TL(1, 5);
+      // ---- exact frame only: q <- r_j q IN PLACE in the stage tile (thread: row j = t/2, half of the row).  S of
+      // this chunk, the only consumer of the un-scaled q, must have completed.
+      if (exact) {
+        CW_WAIT(BAR_SDN, par);
+        CW_TL(1, 4);
+        const int j = t >> 1, half = t & 1;
+        unsigned char* qt = smem + LY::OFF_STAGE + st * LY::STAGE_BYTES;
+        constexpr int CH = NKB * 4;              // 16-byte pieces per thread
+        constexpr int BATCH = CH < 8 ? CH : 8;   // loads first, then stores
+#pragma unroll 1
+        for (int i0 = 0; i0 < CH; i0 += BATCH) {
+          uint4 v[BATCH];
+          uint32_t off[BATCH];
+#pragma unroll
+          for (int i = 0; i < BATCH; ++i) {
+            const int cidx = half * CH + i0 + i;
+            const int box = cidx >> 3;
+            const int c = (NKB >= 2) ? ((cidx & 7) ^ (half << 2)) : (cidx & 7);
+            off[i] = box * CW_BOX_BYTES + j * 128 + ((c ^ (j & 7)) << 4);
+            v[i] = *reinterpret_cast<const uint4*>(qt + off[i]);
+          }
+#pragma unroll
+          for (int i = 0; i < BATCH; ++i) *reinterpret_cast<uint4*>(qt + off[i]) = scale_bf16x8(v[i], rr);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(bar0 + 8u * BAR_A);
+      }
+      mbar_arrive(bar0 + 8u * (BAR_EMPTY0 + st));
+      mbar_arrive(bar0 + 8u * (BAR_GEMPTY0 + buf));
+      CW_TL(1, 6);
     }
     // ---- final C = exp(rho) T
     if (ok) {
       do {
-        CW_WAIT(BAR_C, (uint32_t)(nchunks - 1) & 1u);
+        CW_WAIT(BAR_HC, (uint32_t)(nchunks - 1) & 1u);
         tc_fence_after();
         const float back = expf(rho_last);
 #pragma unroll 1
@@ -611,50 +673,48 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         }
       } while (false);
     }
-  } else if (warp < 12) {
+  } else if (warp < W_UMMA) {
     // =========================================================================================== epilogue group
-    // H^T sits in tensor memory with one value column per lane.  Each thread normalises its 64 tokens, writes them
-    // as bf16 into a [token][column] staging tile in shared memory, and the group then streams the tile out with
-    // 16-byte stores (a row of the tile is 256 contiguous bytes of h).
+    // H^T sits in tensor memory with one value column per lane.  Each thread pulls its 64 tokens into registers
+    // (which frees the accumulator for the next chunk at once), waits for the denominators, writes normalised bf16
+    // into a [token][column] staging tile in shared memory, and the group streams the tile out with 16-byte
+    // stores (a row of the tile is 256 contiguous bytes of h).
     const int t = tid - 256;
     const int dv = (warp & 3) * 32 + lane;
     unsigned char* hst = smem + LY::OFF_HST;
     __nv_bfloat16* hbase = reinterpret_cast<__nv_bfloat16*>(p.h) + b * p.h_sb + head * p.h_sh + tok0 * p.h_st + col0;
+    mbar_arrive(bar0 + 8u * BAR_A);  // the accumulator is free for chunk 0
 #pragma unroll 1
     for (int chunk = 0; chunk < nchunks; ++chunk) {
-      const int buf = chunk & 1;
       const uint32_t par = (uint32_t)chunk & 1u;
       const long long rem = len - (long long)chunk * CW_L;
       const int len_c = rem < CW_L ? (int)rem : CW_L;
-      CW_WAIT(BAR_H, par);
-      CW_WAIT(BAR_INV, par);
+      CW_WAIT(BAR_HC, par);
       CW_TL(2, 1);
       tc_fence_after();
-#pragma unroll 1
-      for (int half = (XL_ABL == 4 ? 1 : 0); half < 2; ++half) {
-        uint32_t hv[32];
-        tmem_ld_x32(tH + 32 * half, hv);
-        float4 iv[8];
+      uint32_t hv0[32], hv1[32];
+      tmem_ld_x32(tH, hv0);
+      tmem_ld_x32(tH + 32, hv1);
+      tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar0 + 8u * BAR_A);  // the accumulator is free for the next chunk
+      CW_WAIT(BAR_INV, par);
+      CW_TL(2, 2);
+      unsigned char* col = hst + dv * 2;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) iv[i] = *reinterpret_cast<const float4*>(s_inv + buf * CW_L + 32 * half + 4 * i);
-        tc_wait_ld();
-        if (half == 1) {  // the accumulator is in registers: release it before the stores go out
-          tc_fence_before();
-          mbar_arrive(bar0 + 8u * BAR_HFREE);
-        }
-        unsigned char* col = hst + (32 * half) * LY::HST_ROW + dv * 2;
+      for (int i = 0; i < ((XL_ABL & 4) ? 0 : 16); ++i) {
+        const float4 iv = *reinterpret_cast<const float4*>(s_inv + 4 * i);
+        const float sc[4] = {iv.x, iv.y, iv.z, iv.w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float sc[4] = {iv[i].x, iv[i].y, iv[i].z, iv[i].w};
-#pragma unroll
-          for (int u = 0; u < 4; ++u)
-            *reinterpret_cast<__nv_bfloat16*>(col + (4 * i + u) * LY::HST_ROW) = __float2bfloat16_rn(__uint_as_float(hv[4 * i + u]) * sc[u]);
-        }
+        for (int u = 0; u < 4; ++u)
+          *reinterpret_cast<__nv_bfloat16*>(col + (4 * i + u) * LY::HST_ROW) =
+              __float2bfloat16_rn(__uint_as_float(i < 8 ? hv0[4 * i + u] : hv1[4 * (i & 7) + u]) * sc[u]);
       }
+      mbar_arrive(bar0 + 8u * BAR_EGDONE);  // s_inv may be rewritten
       epilogue_group_sync();
       __nv_bfloat16* ho = hbase + (long long)chunk * CW_L * p.h_st;
 #pragma unroll
-      for (int i = 0; i < (XL_ABL == 4 ? 0 : 8); ++i) {
+      for (int i = 0; i < ((XL_ABL & 4) ? 0 : 8); ++i) {
         const int idx = i * 128 + t, row = idx >> 4, c = idx & 15;
         if (row < len_c)
           *reinterpret_cast<uint4*>(ho + (long long)row * p.h_st + c * 8) = *reinterpret_cast<const uint4*>(hst + row * LY::HST_ROW + c * 16);
@@ -662,13 +722,12 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       epilogue_group_sync();  // the tile is rewritten by the next chunk
       CW_TL(2, 3);
     }
-  } else if (warp == 12) {
+  } else if (warp == W_UMMA) {
     // =========================================================================================== UMMA issuer
     // The whole warp runs this code (warp-uniform control flow, waits never branch out of it); one elected lane
     // issues each instruction.  Every descriptor is formed from one runtime base plus compile-time constants so
-    // that the address arithmetic stays on the uniform datapath.  Iteration `it` finishes chunk it-1 (H^T, qn,
-    // T, nu) and starts chunk `it` (S) in between, so the P pass and the in-place q scaling of a chunk overlap
-    // the state update of the previous one.
+    // that the address arithmetic stays on the uniform datapath.  A chain of UMMAs accumulating into one tile runs
+    // at its latency (about 60 cycles a step), so every phase interleaves two independent products step by step.
     constexpr uint32_t IDESC_S = umma_idesc_bf16(64, 64, 0, 0);
     constexpr uint32_t IDESC_HI = umma_idesc_bf16(128, 64, 0, 0);
     constexpr uint32_t IDESC_HV = umma_idesc_bf16(128, 64, 1, 0);
@@ -685,80 +744,86 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     // MN-major tiles one 8 KiB box
     constexpr uint32_t LBO_K = (16u >> 4) << 16, LBO_MN = ((uint32_t)CW_BOX_BYTES >> 4) << 16;
     bool okm = true;
+    {  // S of chunk 0
+      const uint32_t s_q = sbase_u + LY::OFF_STAGE, s_k = s_q + LY::Q_BYTES;
+      okm &= MMA_WAIT_U(BAR_FULL0, 0u);
+      tc_fence_after();
 #pragma unroll 1
-    for (int it = 0; it <= nchunks_u; ++it) {
-      if (it >= 1) {
-        const int chunk = it - 1;
-        const uint32_t par = (uint32_t)chunk & 1u;
-        const uint32_t stg = sbase_u + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES;  // q | k | v of this chunk
-        const uint32_t s_k = stg + LY::Q_BYTES, s_v = s_k + LY::Q_BYTES;
-        const uint32_t wm = sbase_u + LY::OFF_WMAT + (chunk & 1) * 1024;
-        // H^T = Tb (r q~)^T
-        okm &= MMA_WAIT_U(BAR_CB, par);
-        okm &= MMA_WAIT_U(BAR_QS, par);
-        if (chunk >= 1) okm &= MMA_WAIT_U(BAR_HFREE, par ^ 1u);
-        CW_TL(3, 1);
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < DHQK / 16; ++ks)
-          umma_ts_lo(tmem_u + LY::T_H, tmem_u + LY::T_CB + ks * 8,
-                        (LBO_K + ((stg + (ks >> 2) * CW_BOX_BYTES + (ks & 3) * 32) >> 4)), IDESC_HI, ks != 0);
-        // qn = (r q~) [n_hi n_lo]^T
-        okm &= MMA_WAIT_U(BAR_NMAT, par);
-        CW_TL(3, 3);
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < (XL_ABL == 7 ? 1 : DHQK / 16); ++ks)
-          umma_ss_lo(t_odd, (LBO_K + ((stg + (ks >> 2) * CW_BOX_BYTES + (ks & 3) * 32) >> 4)),
-                        (LBO_K + ((sbase_u + LY::OFF_NMAT + (ks >> 2) * 1024 + (ks & 3) * 32) >> 4)), IDESC_DN, ks != 0);
-        umma_commit_elect(bar_u + 8u * BAR_DN);
-        // H^T += V^T P^T
-        okm &= MMA_WAIT_U(BAR_P, par);
-        CW_TL(3, 4);
-        tc_fence_after();
+      for (int kb = 0; kb < NKB; ++kb)
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ss_lo(tmem_u + LY::T_H, (LBO_MN + ((s_v >> 4) + ((kk * 2048) >> 4))),
-                        (LBO_K + ((sbase_u >> 4) + ((LY::OFF_P + kk * 32) >> 4))), IDESC_HV, 1);
-        umma_commit_elect(bar_u + 8u * BAR_H);
+          umma_ss_lo(tmem_u + LY::T_S, (LBO_K + ((s_q + kb * CW_BOX_BYTES + kk * 32) >> 4)),
+                     (LBO_K + ((s_k + kb * CW_BOX_BYTES + kk * 32) >> 4)), IDESC_S, (kb | kk) != 0);
+      umma_commit_elect(bar_u + 8u * BAR_SDN);
+    }
+#pragma unroll 1
+    for (int chunk = 0; chunk < nchunks_u; ++chunk) {
+      const uint32_t par = (uint32_t)chunk & 1u;
+      const uint32_t stg = sbase_u + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES;  // q | k | v of this chunk
+      const uint32_t s_k = stg + LY::Q_BYTES, s_v = s_k + LY::Q_BYTES;
+      const uint32_t wm = sbase_u + LY::OFF_WMAT + (chunk & 1) * 1024;
+      const uint32_t nm = sbase_u + LY::OFF_NMAT + (chunk & 1) * (NKB * 1024);
+      // ---- phase A:  H^T = Tb q^T   interleaved with   nu = K^T [w_hi w_lo]^T  (NKB chains)
+      okm &= MMA_WAIT_U(BAR_A, par);
+      CW_TL(3, 1);
+      tc_fence_after();
+      // (outer loops rolled, small code: the loops of all roles together have to stay in the instruction cache)
+#pragma unroll 1
+      for (int kb = 0; kb < NKB; ++kb) {
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const int ks = 4 * kb + kk;
+          umma_ts_lo(tmem_u + LY::T_H, tmem_u + LY::T_CB + ks * 8, (LBO_K + ((stg + kb * CW_BOX_BYTES + kk * 32) >> 4)),
+                     IDESC_HI, ks != 0);
+          // nu step (token slice, feature block) = (ks / NKB, ks % NKB): 4 x NKB = DHQK/16 steps as well
+          const int tsl = ks / NKB, gq = ks % NKB;
+          umma_ss_lo(t_odd + 8 + 8 * gq, (LBO_MN + ((s_k + gq * CW_BOX_BYTES + tsl * 2048) >> 4)),
+                     (LBO_K + ((wm + tsl * 32) >> 4)), IDESC_NU, tsl != 0);
+        }
       }
-      if (it < nchunks_u) {
-        const int chunk = it;
-        const uint32_t s_q = sbase_u + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES, s_k = s_q + LY::Q_BYTES;
-        okm &= MMA_WAIT_U(BAR_FULL0 + (chunk & 1), (uint32_t)(chunk >> 1) & 1u);
-        CW_TL(3, 7);
-        tc_fence_after();
+      CW_TL(3, 2);
+      umma_commit_elect(bar_u + 8u * BAR_NU);
+      // ---- phase B:  H^T += V^T P^T (exact frame) or (wV)^T P^T (common frame)   interleaved with   T += (wV)^T K
+      okm &= MMA_WAIT_U(BAR_B, par);
+      CW_TL(3, 3);
+      tc_fence_after();
+      {
+        const float exact_f = *reinterpret_cast<const float*>(smem + LY::OFF_F32 + ((chunk & 1) * LY::GATE_F32 + G_EXACT) * 4);
+        const bool exact_u = __shfl_sync(0xffffffffu, exact_f != 0.f ? 1 : 0, 0) != 0;
+        const uint32_t va = exact_u ? s_v : sbase_u + LY::OFF_VH;
 #pragma unroll
-        for (int kb = 0; kb < NKB; ++kb)
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_ss_lo(tmem_u + LY::T_S, (LBO_K + ((s_q >> 4) + ((kb * CW_BOX_BYTES + kk * 32) >> 4))),
-                          (LBO_K + ((s_k >> 4) + ((kb * CW_BOX_BYTES + kk * 32) >> 4))), IDESC_S, (kb | kk) != 0);
-        umma_commit_elect(bar_u + 8u * BAR_S);
-      }
-      if (it >= 1) {
-        const int chunk = it - 1;
-        const uint32_t par = (uint32_t)chunk & 1u;
-        const uint32_t s_k = sbase_u + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES + LY::Q_BYTES;
-        const uint32_t wm = sbase_u + LY::OFF_WMAT + (chunk & 1) * 1024;
-        // T += (w V)^T K ;  nu = K^T [w_hi w_lo]^T
-        okm &= MMA_WAIT_U(BAR_VH, par);
-        CW_TL(3, 5);
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
+        for (int kk = 0; kk < 4; ++kk) {
+          umma_ss_lo(tmem_u + LY::T_H, (LBO_MN + ((va >> 4) + ((kk * 2048) >> 4))),
+                     (LBO_K + ((sbase_u >> 4) + ((LY::OFF_P + kk * 32) >> 4))), IDESC_HV, 1);
           umma_ss_lo(tmem_u + LY::T_C, (LBO_MN + ((sbase_u >> 4) + ((LY::OFF_VH + kk * 2048) >> 4))),
-                        (LBO_MN + ((s_k >> 4) + ((kk * 2048) >> 4))), IDESC_C, 1);
-#pragma unroll
-        for (int kk = 0; kk < (XL_ABL == 7 ? 1 : 4); ++kk)
-#pragma unroll
-          for (int gq = 0; gq < (XL_ABL == 7 ? 1 : NKB); ++gq)
-            umma_ss_lo(t_odd + 8 + 8 * gq, (LBO_MN + ((s_k >> 4) + ((gq * CW_BOX_BYTES + kk * 2048) >> 4))),
-                          (LBO_K + ((wm >> 4) + ((kk * 32) >> 4))), IDESC_NU, kk != 0);
-        umma_commit_elect(bar_u + 8u * BAR_C);
-        umma_commit_elect(bar_u + 8u * (BAR_EMPTY0 + (chunk & 1)));
-        CW_TL(3, 6);
+                     (LBO_MN + ((s_k >> 4) + ((kk * 2048) >> 4))), IDESC_C, 1);
+        }
       }
+      CW_TL(3, 4);
+      umma_commit_elect(bar_u + 8u * BAR_HC);
+      // ---- phase C (while T is converted for the next chunk):  S of the next chunk   interleaved with
+      //      qn = q [n_hi n_lo]^T of this one
+      const bool more = chunk + 1 < nchunks_u;
+      const uint32_t nq = sbase_u + LY::OFF_STAGE + ((chunk + 1) & 1) * LY::STAGE_BYTES, nk = nq + LY::Q_BYTES;
+      if (more) okm &= MMA_WAIT_U(BAR_FULL0 + ((chunk + 1) & 1), (uint32_t)((chunk + 1) >> 1) & 1u);
+      // (the qn columns are free: the gate group read the previous product before it wrote this chunk's P)
+      CW_TL(3, 5);
+      tc_fence_after();
+      // No branch inside the issue loop (a uniform `if` around an UMMA costs ~40 cycles per instruction): behind the
+      // last chunk S is formed from the other stage's stale tiles and never read.
+#pragma unroll 1
+      for (int kb = 0; kb < NKB; ++kb) {
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          umma_ss_lo(tmem_u + LY::T_S, (LBO_K + ((nq + kb * CW_BOX_BYTES + kk * 32) >> 4)),
+                     (LBO_K + ((nk + kb * CW_BOX_BYTES + kk * 32) >> 4)), IDESC_S, (kb | kk) != 0);
+          umma_ss_lo(t_odd, (LBO_K + ((stg + kb * CW_BOX_BYTES + kk * 32) >> 4)),
+                     (LBO_K + ((nm + kb * 1024 + kk * 32) >> 4)), IDESC_DN, (kb | kk) != 0);
+        }
+      }
+      CW_TL(3, 6);
+      umma_commit_elect(bar_u + 8u * BAR_SDN);
+      umma_commit_elect(bar_u + 8u * (BAR_EMPTY0 + (chunk & 1)));
     }
     ok = okm;
   } else {
@@ -772,6 +837,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         const uint32_t bar = bar0 + 8u * (BAR_FULL0 + st);
         const uint32_t dst = sbase + LY::OFF_STAGE + st * LY::STAGE_BYTES;
         const int tk = (int)(tok0 + (long long)chunk * CW_L);
+        if ((XL_ABL & 8) && chunk >= 2) { mbar_arrive(bar); continue; }
         mbar_expect_tx(bar, LY::STAGE_BYTES);
         int cq[4], ck[4], cv[4];
         cq[maps.pos[0][0]] = tk; cq[maps.pos[0][1]] = head; cq[maps.pos[0][2]] = b;
@@ -800,7 +866,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   if (!ok && p.status) atomicExch(p.status, 1);
   tc_fence_before();
   __syncthreads();
-  if (warp == 12) tmem_dealloc(tmem, CW_TMEM_COLS);
+  if (warp == W_UMMA) tmem_dealloc(tmem, CW_TMEM_COLS);
 }
 
 // ---------------------------------------------------------------------------------------------
