@@ -86,11 +86,13 @@ enum CwBar {  // mbarrier indices.  Barriers whose producer may run two chunks a
   BAR_FULL0 = 0, BAR_FULL1, BAR_EMPTY0, BAR_EMPTY1,   // TMA stage of q,k,v: landed / consumed
   BAR_GFULL0, BAR_GFULL1, BAR_GEMPTY0, BAR_GEMPTY1,   // gate data of a chunk: published / consumed
   BAR_A,     // phase A may issue: bf16 copy of T (state + gate group), q final (state group), H^T drained
-             // (epilogue group), n operand published and nu columns read (gate group): 5 x 128 arrivals
+             // (epilogue group): 4 x 128 arrivals
   BAR_B,     // phase B may issue: P (gate group), w-scaled v (state group): 2 x 128 arrivals
-  BAR_NU,    // commit after phase A: nu complete
+  BAR_C2,    // phase C may issue (gate group): n operand of the next chunk published, nu and qn columns read,
+             // gate data of the next chunk visible.  Completion k+1 comes from the gate group's iteration k.
   BAR_HC,    // commit after phase B: H^T and T complete
-  BAR_SDN,   // commit after phase C: S of the next chunk and qn of this one complete (completion k = S(k), qn(k-1))
+  BAR_S,     // commit inside phase C: S of the next chunk complete (completion k = S(k))
+  BAR_NU,    // commit after phase C: nu and qn of the next chunk complete (completion k = nu(k), qn(k))
   BAR_INV,   // gate group -> epilogue group: 1/denominator published
   BAR_EGDONE,  // epilogue group -> gate group: 1/denominator consumed
   BAR_COUNT
@@ -279,11 +281,11 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   if (tid == 0) {
     for (int i = 0; i < BAR_COUNT; ++i) {
       uint32_t cnt = 128;                                                        // one 4-warp group arrives
-      if (i == BAR_FULL0 || i == BAR_FULL1 || i == BAR_NU || i == BAR_HC || i == BAR_SDN) cnt = 1;
+      if (i == BAR_FULL0 || i == BAR_FULL1 || i == BAR_NU || i == BAR_HC || i == BAR_S) cnt = 1;
       if (i == BAR_EMPTY0 || i == BAR_EMPTY1) cnt = 129;    // state group + UMMA commit
       if (i == BAR_GFULL0 || i == BAR_GFULL1) cnt = 32;     // the scan warp
       if (i == BAR_GEMPTY0 || i == BAR_GEMPTY1) cnt = 256;  // state group + gate group
-      if (i == BAR_A) cnt = 640;
+      if (i == BAR_A) cnt = 512;
       if (i == BAR_B) cnt = 256;
       mbar_init(bar0 + 8u * i, cnt);
     }
@@ -418,8 +420,8 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     if (ok && slice == 0 && lane == 0) p.m_out[sidx] = m_prev;
   } else if (warp < W_STATE_GROUP) {
     // =========================================================================================== gate group
-    // Iteration j: its half of the T -> bf16 conversion for chunk j; denominators of chunk j-1; P(j) from S(j);
-    // then, once nu of chunk j is complete, n(j) and its hi/lo operand for chunk j+1.
+    // Iteration j: its half of the T -> bf16 conversion for chunk j; P(j) from S(j); then, with nu(j) and qn(j)
+    // (issued one chunk ahead, behind S(j)): n(j) and its hi/lo operand for chunk j+1, and the denominators of chunk j.
     const int g = tid;  // 0..127
     for (int d = g; d < DHQK; d += 128) s_n[d] = p.n0 ? p.n0[sidx * DHQK + d] : 0.f;
     auto publish_n = [&](int nbuf, int d, float nv) {  // hi/lo bf16 split of n[d] into rows 0/1 of the N=8 operand
@@ -431,24 +433,10 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     };
     for (int d = g; d < DHQK; d += 128) publish_n(0, d, s_n[d]);
     fence_proxy_async_smem();
-    mbar_arrive(bar0 + 8u * BAR_A);  // n operand for chunk 0
+    if (mbar_wait(bar0 + 8u * BAR_GFULL0, 0u)) mbar_arrive(bar0 + 8u * BAR_C2);  // n operand and gate data of chunk 0
+    else ok = false;
     const int j = warp * 16 + (lane & 15);  // S row of this thread (lanes 0..15); lanes 16..31 see the N=8 products
-    float rowsum_prev = 0.f, lower_prev = 0.f, qn_scale_prev = 1.f, eps_prev = 0.f;
     float back_last = 1.f;
-    // denominators of chunk c: |rowsum + q.n| against the lower bound; the product sits on lanes 16..31
-    auto denominators = [&](int c, float rowsum, float lower, float qn_scale, float eps_j) -> bool {
-      if (!mbar_wait(bar0 + 8u * BAR_SDN, (uint32_t)(c + 1) & 1u)) return false;
-      if (c >= 1 && !mbar_wait(bar0 + 8u * BAR_EGDONE, (uint32_t)(c - 1) & 1u)) return false;  // s_inv is free again
-      tc_fence_after();
-      uint32_t dn[8];
-      tmem_ld_x8(tS, dn);
-      tc_wait_ld();
-      const float dot = __shfl_down_sync(0xffffffffu, __uint_as_float(dn[0]) + __uint_as_float(dn[1]), 16);
-      if (lane < 16) s_inv[j] = __fdividef(1.f, fmaxf(fabsf(fmaf(dot, qn_scale, rowsum)), lower) + eps_j);
-      tc_fence_before();
-      mbar_arrive(bar0 + 8u * BAR_INV);
-      return true;
-    };
 #pragma unroll 1
     for (int chunk = 0; chunk < nchunks; ++chunk) {
       const int buf = chunk & 1;
@@ -460,23 +448,26 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       const float yj = gb[G_Y + j];
       const float lower = gb[G_LOWER + j];
       const float eps_j = p.eps * gb[G_EPS + j];
-      const float mult = gb[G_MULT], qn_scale = gb[G_QN], cb_scale = gb[G_CB];
+      const float mult = gb[G_MULT], cb_scale = gb[G_CB];
       const bool exact = gb[G_EXACT] != 0.f;
+      // the normaliser product is formed from q as loaded: its scale is the row's r_j in the exact frame
+      const float qn_scale = exact ? gb[G_R + j] : gb[G_QN];
       if (chunk + 1 == nchunks) back_last = expf(gb[G_RHO]);
       // ---- T -> bf16 copy, this group's blocks (the state group converts everything for the first chunk)
       if (chunk >= 1) {
         CW_WAIT(BAR_HC, par ^ 1u);  // T holds chunk-1; its UMMAs no longer read the bf16 copy or the P tile
         tc_fence_after();
+        CW_TL(0, 10);
         if (!(XL_ABL & 1)) convert_T(CB_SPLIT, DHQK / 64, cb_scale, mult);
+        CW_TL(0, 11);
         tc_fence_before();
       }
       mbar_arrive(bar0 + 8u * BAR_A);
       CW_TL(0, 2);
-      // ---- denominators of the previous chunk
-      if (chunk >= 1 && !denominators(chunk - 1, rowsum_prev, lower_prev, qn_scale_prev, eps_prev)) { ok = false; break; }
-      CW_TL(0, 3);
-      CW_WAIT(BAR_SDN, par);
+      CW_TL(0, 14);
+      CW_WAIT(BAR_S, par);
       CW_TL(0, 4);
+      CW_TL(0, 15);
       tc_fence_after();
       // ---- P from S (rows of this warp: j = 16 warp + lane for lanes 0..15)
       // Rolled over 16-column pieces on purpose (small code): piece q holds columns 16q..16q+15; this warp's rows
@@ -531,20 +522,19 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       mbar_arrive(bar0 + 8u * BAR_B);
       CW_TL(0, 5);
       const float rowsum = (rs[0] + rs[1]) + (rs[2] + rs[3]);
-      rowsum_prev = rowsum;
-      lower_prev = lower;
-      qn_scale_prev = qn_scale;
-      eps_prev = eps_j;
 
-      // ---- n of this chunk: n = mult n + nu, published as the hi/lo operand of the next chunk.  The other operand
-      // buffer is still read by this chunk's normaliser product.
+      // ---- n of this chunk: n = mult n + nu, published as the hi/lo operand of the next chunk (the other operand
+      // buffer: this chunk's normaliser product has read its own long ago); and the normaliser product itself
       CW_WAIT(BAR_NU, par);
       CW_TL(0, 6);
       tc_fence_after();
+      float dot;
       {
-        uint32_t r[32];
+        uint32_t r[32], dn[8];
         tmem_ld_x32(tS + 8, r);
+        tmem_ld_x8(tS, dn);
         tc_wait_ld();
+        dot = __shfl_down_sync(0xffffffffu, __uint_as_float(dn[0]) + __uint_as_float(dn[1]), 16);
         if (lane >= 16) {
 #pragma unroll
           for (int gq = 0; gq < NKB; ++gq) {
@@ -557,11 +547,15 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       }
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(bar0 + 8u * BAR_A);                 // n operand of the next chunk; nu columns free
+      if (chunk + 1 < nchunks) CW_WAIT(BAR_GFULL0 + (buf ^ 1), (uint32_t)((chunk + 1) >> 1) & 1u);  // w operand of the next chunk
+      mbar_arrive(bar0 + 8u * BAR_C2);                // phase C of this chunk may issue
       mbar_arrive(bar0 + 8u * (BAR_GEMPTY0 + buf));  // done with this chunk's gate data (so is nu, which read w)
       CW_TL(0, 7);
+      // ---- denominators: |rowsum + q.n| against the lower bound (the product sits on lanes 16..31)
+      if (chunk >= 1) CW_WAIT(BAR_EGDONE, par ^ 1u);  // the epilogue group has consumed the previous ones
+      if (lane < 16) s_inv[j] = __fdividef(1.f, fmaxf(fabsf(fmaf(dot, qn_scale, rowsum)), lower) + eps_j);
+      mbar_arrive(bar0 + 8u * BAR_INV);
     }
-    if (ok) ok = denominators(nchunks - 1, rowsum_prev, lower_prev, qn_scale_prev, eps_prev);
     // ---- final n (back in the true frame)
     if (ok && slice == 0 && lane >= 16) {
 #pragma unroll
@@ -629,7 +623,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       // ---- exact frame only: q <- r_j q IN PLACE in the stage tile (thread: row j = t/2, half of the row).  S of
       // this chunk, the only consumer of the un-scaled q, must have completed.
       if (exact) {
-        CW_WAIT(BAR_SDN, par);
+        CW_WAIT(BAR_NU, par);  // S, nu and qn of this chunk (issued one chunk ahead) no longer read q as loaded
         CW_TL(1, 4);
         const int j = t >> 1, half = t & 1;
         unsigned char* qt = smem + LY::OFF_STAGE + st * LY::STAGE_BYTES;
@@ -744,45 +738,59 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     // MN-major tiles one 8 KiB box
     constexpr uint32_t LBO_K = (16u >> 4) << 16, LBO_MN = ((uint32_t)CW_BOX_BYTES >> 4) << 16;
     bool okm = true;
-    {  // S of chunk 0
-      const uint32_t s_q = sbase_u + LY::OFF_STAGE, s_k = s_q + LY::Q_BYTES;
-      okm &= MMA_WAIT_U(BAR_FULL0, 0u);
+    // Phase C of chunk k forms everything of chunk k+1 that does not depend on the state: S, nu and qn.  It runs
+    // while T is converted for chunk k+1, so the tensor pipe has work during the one long dependency of the loop.
+    auto phase_c = [&](int next) {  // S(next), then nu(next) interleaved with qn(next)
+      [[maybe_unused]] const int chunk = next;  // (time stamps of this phase are filed under the chunk it prepares)
+      const uint32_t nq = sbase_u + LY::OFF_STAGE + (next & 1) * LY::STAGE_BYTES, nk = nq + LY::Q_BYTES;
+      const uint32_t wm = sbase_u + LY::OFF_WMAT + (next & 1) * 1024;
+      const uint32_t nm = sbase_u + LY::OFF_NMAT + (next & 1) * (NKB * 1024);
+      okm &= MMA_WAIT_U(BAR_FULL0 + (next & 1), (uint32_t)(next >> 1) & 1u);
+      okm &= MMA_WAIT_U(BAR_C2, (uint32_t)next & 1u);
+      CW_TL(3, 5);
       tc_fence_after();
 #pragma unroll 1
       for (int kb = 0; kb < NKB; ++kb)
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ss_lo(tmem_u + LY::T_S, (LBO_K + ((s_q + kb * CW_BOX_BYTES + kk * 32) >> 4)),
-                     (LBO_K + ((s_k + kb * CW_BOX_BYTES + kk * 32) >> 4)), IDESC_S, (kb | kk) != 0);
-      umma_commit_elect(bar_u + 8u * BAR_SDN);
-    }
-#pragma unroll 1
-    for (int chunk = 0; chunk < nchunks_u; ++chunk) {
-      const uint32_t par = (uint32_t)chunk & 1u;
-      const uint32_t stg = sbase_u + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES;  // q | k | v of this chunk
-      const uint32_t s_k = stg + LY::Q_BYTES, s_v = s_k + LY::Q_BYTES;
-      const uint32_t wm = sbase_u + LY::OFF_WMAT + (chunk & 1) * 1024;
-      const uint32_t nm = sbase_u + LY::OFF_NMAT + (chunk & 1) * (NKB * 1024);
-      // ---- phase A:  H^T = Tb q^T   interleaved with   nu = K^T [w_hi w_lo]^T  (NKB chains)
-      okm &= MMA_WAIT_U(BAR_A, par);
-      CW_TL(3, 1);
-      tc_fence_after();
-      // (outer loops rolled, small code: the loops of all roles together have to stay in the instruction cache)
+          umma_ss_lo(tmem_u + LY::T_S, (LBO_K + ((nq + kb * CW_BOX_BYTES + kk * 32) >> 4)),
+                     (LBO_K + ((nk + kb * CW_BOX_BYTES + kk * 32) >> 4)), IDESC_S, (kb | kk) != 0);
+      umma_commit_elect(bar_u + 8u * BAR_S);
 #pragma unroll 1
       for (int kb = 0; kb < NKB; ++kb) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           const int ks = 4 * kb + kk;
-          umma_ts_lo(tmem_u + LY::T_H, tmem_u + LY::T_CB + ks * 8, (LBO_K + ((stg + kb * CW_BOX_BYTES + kk * 32) >> 4)),
-                     IDESC_HI, ks != 0);
           // nu step (token slice, feature block) = (ks / NKB, ks % NKB): 4 x NKB = DHQK/16 steps as well
           const int tsl = ks / NKB, gq = ks % NKB;
-          umma_ss_lo(t_odd + 8 + 8 * gq, (LBO_MN + ((s_k + gq * CW_BOX_BYTES + tsl * 2048) >> 4)),
-                     (LBO_K + ((wm + tsl * 32) >> 4)), IDESC_NU, tsl != 0);
+          if (!(XL_ABL & 32) || kk == 0) {
+            umma_ss_lo(t_odd + 8 + 8 * gq, (LBO_MN + ((nk + gq * CW_BOX_BYTES + tsl * 2048) >> 4)),
+                       (LBO_K + ((wm + tsl * 32) >> 4)), IDESC_NU, tsl != 0);
+            umma_ss_lo(t_odd, (LBO_K + ((nq + kb * CW_BOX_BYTES + kk * 32) >> 4)),
+                       (LBO_K + ((nm + kb * 1024 + kk * 32) >> 4)), IDESC_DN, ks != 0);
+          }
         }
       }
-      CW_TL(3, 2);
       umma_commit_elect(bar_u + 8u * BAR_NU);
+      CW_TL(3, 6);
+    };
+    phase_c(0);
+#pragma unroll 1
+    for (int chunk = 0; chunk < nchunks_u; ++chunk) {
+      const uint32_t par = (uint32_t)chunk & 1u;
+      const uint32_t stg = sbase_u + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES;  // q | k | v of this chunk
+      const uint32_t s_k = stg + LY::Q_BYTES, s_v = s_k + LY::Q_BYTES;
+      // ---- phase A:  H^T = Tb q^T
+      okm &= MMA_WAIT_U(BAR_A, par);
+      CW_TL(3, 1);
+      tc_fence_after();
+#pragma unroll 1
+      for (int kb = 0; kb < NKB; ++kb)
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ts_lo(tmem_u + LY::T_H, tmem_u + LY::T_CB + (4 * kb + kk) * 8,
+                     (LBO_K + ((stg + kb * CW_BOX_BYTES + kk * 32) >> 4)), IDESC_HI, (kb | kk) != 0);
+      CW_TL(3, 2);
       // ---- phase B:  H^T += V^T P^T (exact frame) or (wV)^T P^T (common frame)   interleaved with   T += (wV)^T K
       okm &= MMA_WAIT_U(BAR_B, par);
       CW_TL(3, 3);
@@ -801,29 +809,9 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       }
       CW_TL(3, 4);
       umma_commit_elect(bar_u + 8u * BAR_HC);
-      // ---- phase C (while T is converted for the next chunk):  S of the next chunk   interleaved with
-      //      qn = q [n_hi n_lo]^T of this one
-      const bool more = chunk + 1 < nchunks_u;
-      const uint32_t nq = sbase_u + LY::OFF_STAGE + ((chunk + 1) & 1) * LY::STAGE_BYTES, nk = nq + LY::Q_BYTES;
-      if (more) okm &= MMA_WAIT_U(BAR_FULL0 + ((chunk + 1) & 1), (uint32_t)((chunk + 1) >> 1) & 1u);
-      // (the qn columns are free: the gate group read the previous product before it wrote this chunk's P)
-      CW_TL(3, 5);
-      tc_fence_after();
-      // No branch inside the issue loop (a uniform `if` around an UMMA costs ~40 cycles per instruction): behind the
-      // last chunk S is formed from the other stage's stale tiles and never read.
-#pragma unroll 1
-      for (int kb = 0; kb < NKB; ++kb) {
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          umma_ss_lo(tmem_u + LY::T_S, (LBO_K + ((nq + kb * CW_BOX_BYTES + kk * 32) >> 4)),
-                     (LBO_K + ((nk + kb * CW_BOX_BYTES + kk * 32) >> 4)), IDESC_S, (kb | kk) != 0);
-          umma_ss_lo(t_odd, (LBO_K + ((stg + kb * CW_BOX_BYTES + kk * 32) >> 4)),
-                     (LBO_K + ((nm + kb * 1024 + kk * 32) >> 4)), IDESC_DN, (kb | kk) != 0);
-        }
-      }
-      CW_TL(3, 6);
-      umma_commit_elect(bar_u + 8u * BAR_SDN);
-      umma_commit_elect(bar_u + 8u * (BAR_EMPTY0 + (chunk & 1)));
+      umma_commit_elect(bar_u + 8u * (BAR_EMPTY0 + (chunk & 1)));  // the stage of this chunk is consumed
+      // ---- phase C for the next chunk (one branch around the whole phase, none inside the issue loops)
+      if (chunk + 1 < nchunks_u) phase_c(chunk + 1);
     }
     ok = okm;
   } else {
