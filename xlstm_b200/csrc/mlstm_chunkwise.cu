@@ -54,18 +54,18 @@ constexpr float CW_FAST_SPREAD = 30.f;     // largest in-chunk spread of the sta
 // Per-chunk gate data published by the scan warp (float offsets into one parity's slot).  Every row j of a chunk
 // is computed in a frame exp(-phi_j); h_j = H_j / den_j does not depend on the choice.
 //   exact frame  phi_j = mu_j        : q is scaled by r_j in place, P_jl = S_jl e^{a'_l - mu_j}, H^T += V^T P^T
-//   common frame phi_j = mu* + rho'  : q stays as loaded, the bf16 copy of T carries the scalar, P_jl = S_jl and
-//                                      H^T += (wV)^T P^T with the w-scaled v the state update needs anyway
+//   common frame phi_j = mu* + rho'  : q stays as loaded, the bf16 copy of T carries the scalar,
+//                                      P_jl = S_jl w_l (no exponential per element, no per-row factor)
 // The common frame is used whenever mu* - mu_0 <= CW_FAST_SPREAD (rows then differ by at most e^-30 in scale,
 // which fp32 accumulators and bf16 operands carry without loss); the exact frame covers chunks in which the
-// stabiliser jumps further.  Both produce P_jl = S_jl/sqrt(d) 2^(x_l - y_j) and rowsum_j = sum_l P_jl z_l.
+// stabiliser jumps further.  Exact: P_jl = S_jl/sqrt(d) 2^(x_l - y_j); common: P_jl = S_jl z_l; rowsum_j = sum_l P_jl.
 enum GateSlot {
   G_LOWER = 0 * CW_L,  // exp(-(b_j + phi_j)): lower bound of the denominator
   G_X = 1 * CW_L,      // x_l (log2 units; -inf for tokens past the end of the document)
   G_Y = 2 * CW_L,      // y_j (log2 units)
   G_R = 3 * CW_L,      // r_j exp(rho) / sqrt(d) (exact frame only)
   G_W = 4 * CW_L,      // w_l = exp(a'_l - mu* - rho')
-  G_Z = 5 * CW_L,      // z_l
+  G_Z = 5 * CW_L,      // z_l = w_l / sqrt(d) (common frame)
   G_EPS = 6 * CW_L,    // exp(mu_j - phi_j): eps of the denominator in the row's frame
   G_MULT = 7 * CW_L,   // rescale multiplier of T (1 unless the lazy frame ran out)
   G_RHO = G_MULT + 1,  // rho'
@@ -391,7 +391,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         *reinterpret_cast<float2*>(gb + G_LOWER + t0) = make_float2(__expf(-(b0 + phi)), __expf(-(b1 + phi)));
         *reinterpret_cast<float2*>(gb + G_X + t0) = make_float2(t0 < len_c ? 0.f : -INFINITY, t1 < len_c ? 0.f : -INFINITY);
         *reinterpret_cast<float2*>(gb + G_Y + t0) = make_float2(0.f, 0.f);
-        *reinterpret_cast<float2*>(gb + G_Z + t0) = make_float2(w0, w1);
+        *reinterpret_cast<float2*>(gb + G_Z + t0) = make_float2(w0 * qscale, w1 * qscale);
         *reinterpret_cast<float2*>(gb + G_EPS + t0) = make_float2(__expf(mu0 - phi), __expf(mu1 - phi));
       }
       {
@@ -502,13 +502,13 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
             tc_wait_ld();
             const int lim = (q < warp) ? 64 : j;  // pieces left of the diagonal piece need no mask
 #pragma unroll
-            for (int i = 0; i < 16; ++i) e[i] = (16 * q + i <= lim) ? __uint_as_float(sv[i]) * qscale : 0.f;
+            for (int i = 0; i < 16; ++i) e[i] = (16 * q + i <= lim) ? __uint_as_float(sv[i]) * zv[i] : 0.f;
           }
           o0 = make_uint4(pack_bf16x2(e[0], e[1]), pack_bf16x2(e[2], e[3]), pack_bf16x2(e[4], e[5]), pack_bf16x2(e[6], e[7]));
           o1 = make_uint4(pack_bf16x2(e[8], e[9]), pack_bf16x2(e[10], e[11]), pack_bf16x2(e[12], e[13]), pack_bf16x2(e[14], e[15]));
           // (row sums from the unrounded values: the difference to the bf16 P is below the bf16 rounding of h)
 #pragma unroll
-          for (int i = 0; i < 16; ++i) rs[i & 3] = fmaf(e[i], zv[i], rs[i & 3]);
+          for (int i = 0; i < 16; ++i) rs[i & 3] += e[i];
         }
         if (lane < 16) {
           *reinterpret_cast<uint4*>(prow + (((2 * q) ^ (j & 7)) << 4)) = o0;
@@ -791,17 +791,14 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
           umma_ts_lo(tmem_u + LY::T_H, tmem_u + LY::T_CB + (4 * kb + kk) * 8,
                      (LBO_K + ((stg + kb * CW_BOX_BYTES + kk * 32) >> 4)), IDESC_HI, (kb | kk) != 0);
       CW_TL(3, 2);
-      // ---- phase B:  H^T += V^T P^T (exact frame) or (wV)^T P^T (common frame)   interleaved with   T += (wV)^T K
+      // ---- phase B:  H^T += V^T P^T   interleaved with   T += (wV)^T K
       okm &= MMA_WAIT_U(BAR_B, par);
       CW_TL(3, 3);
       tc_fence_after();
       {
-        const float exact_f = *reinterpret_cast<const float*>(smem + LY::OFF_F32 + ((chunk & 1) * LY::GATE_F32 + G_EXACT) * 4);
-        const bool exact_u = __shfl_sync(0xffffffffu, exact_f != 0.f ? 1 : 0, 0) != 0;
-        const uint32_t va = exact_u ? s_v : sbase_u + LY::OFF_VH;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-          umma_ss_lo(tmem_u + LY::T_H, (LBO_MN + ((va >> 4) + ((kk * 2048) >> 4))),
+          umma_ss_lo(tmem_u + LY::T_H, (LBO_MN + ((s_v >> 4) + ((kk * 2048) >> 4))),
                      (LBO_K + ((sbase_u >> 4) + ((LY::OFF_P + kk * 32) >> 4))), IDESC_HV, 1);
           umma_ss_lo(tmem_u + LY::T_C, (LBO_MN + ((sbase_u >> 4) + ((LY::OFF_VH + kk * 2048) >> 4))),
                      (LBO_MN + ((s_k >> 4) + ((kk * 2048) >> 4))), IDESC_C, 1);
