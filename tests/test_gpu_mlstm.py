@@ -109,6 +109,8 @@ def test_recurrent_fp32_config1_shape():
     (1, 1, 64, 256, 512, False),
     (2, 3, 1000, 256, 512, True),
     (1, 2, 7, 64, 128, False),       # shorter than one chunk
+    (1, 2, 200, 256, 256, True),     # more feature blocks than value slices: no cluster split of the normaliser
+    (1, 1, 130, 128, 512, False),    # fewer feature blocks than value slices: likewise
 ])
 def test_chunkwise_matches_oracle(B, NH, S, DQ, DV, with_state):
     import xlstm_b200
@@ -118,6 +120,31 @@ def test_chunkwise_matches_oracle(B, NH, S, DQ, DV, with_state):
     h, st = xlstm_b200.mlstm_sequence(*_cuda(q, k, v, i, f), *_cuda(*init), kernel="chunkwise")
     xlstm_b200.check_device_status()
     _check(h, st, h_ref, st_ref, TOL_BF16)
+
+
+@pytest.mark.parametrize("cluster,DQ,DV", [(4, 256, 512), (2, 128, 256), (2, 256, 512)])
+def test_chunkwise_cluster_shared_normaliser_opt_in(cluster, DQ, DV):
+    """XL_CW_CLUSTER=2|4 lets the value slices of a head share the normaliser work through a thread-block cluster
+    (read once per process, hence the child process).  Same results as the default path."""
+    import os, subprocess, sys
+    code = (
+        "import sys, torch; sys.path.insert(0, %r); sys.path.insert(0, %r)\n"
+        "import xlstm_b200\n"
+        "from oracle import mlstm as O\n"
+        "from conftest import rel_l2\n"
+        "from test_gpu_mlstm import _inputs, _state\n"
+        "q, k, v, i, f = _inputs(31, 2, 2, 300, %d, %d, torch.bfloat16)\n"
+        "init = _state(32, 2, 2, %d, %d)\n"
+        "h_ref, st_ref = O.mlstm_inference(q, k, v, i, f, *init)\n"
+        "h, st = xlstm_b200.mlstm_sequence(*[t.cuda() for t in (q, k, v, i, f)], *[t.cuda() for t in init], kernel='chunkwise')\n"
+        "xlstm_b200.check_device_status()\n"
+        "errs = [rel_l2(h.float().cpu(), h_ref.float())] + [rel_l2(a.cpu(), b) for a, b in zip(st, st_ref)]\n"
+        "print('ERRS', errs)\n"
+        "assert max(errs) < 1e-2, errs\n"
+    ) % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))), os.path.dirname(os.path.abspath(__file__)), DQ, DV, DQ, DV)
+    env = dict(os.environ, XL_CW_CLUSTER=str(cluster))
+    res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
 
 
 def test_chunkwise_harsh_gates_stay_finite_and_match():
@@ -131,12 +158,13 @@ def test_chunkwise_harsh_gates_stay_finite_and_match():
     _check(h, st, h_ref, st_ref, TOL_BF16)
 
 
+@pytest.mark.parametrize("DQ,DV", [(64, 128), (256, 512)])
 @pytest.mark.parametrize("jump", [20.0, 40.0, 120.0])
-def test_chunkwise_stabiliser_jumps_inside_a_chunk(jump):
+def test_chunkwise_stabiliser_jumps_inside_a_chunk(jump, DQ, DV):
     """An input gate that leaps by `jump` nats in the middle of a chunk: the rows before the leap must keep their
     own scale (the kernel switches that chunk to its per-row frame), the rows after it forget the past."""
     import xlstm_b200
-    B, NH, S, DQ, DV = 1, 2, 256, 64, 128
+    B, NH, S = 1, 2, 256
     q, k, v, i, f = _inputs(21, B, NH, S, DQ, DV, torch.bfloat16)
     # a common component in q and k keeps q.n away from zero, so that h is well conditioned where only a few
     # tokens carry weight

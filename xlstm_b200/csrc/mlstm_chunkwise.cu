@@ -36,6 +36,7 @@
 // documents are chunked from their own first token, so a chunk never straddles a document boundary and the
 // tail chunk is masked (i = -inf, log f = 0) instead of padded.
 #include <cuda.h>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -43,7 +44,7 @@ namespace xl {
 
 constexpr int CW_L = 64;         // tokens per chunk
 constexpr int CW_DV = 128;       // value columns per CTA (UMMA M)
-constexpr int CW_THREADS = 480;  // 15 warps, see roles above
+constexpr int CW_THREADS = 512;  // 16 warps, see roles above
 constexpr int CW_STAGES = 2;
 constexpr int CW_BOX_BYTES = 64 * 128;  // one TMA box: 64 rows x 64 bf16
 constexpr uint32_t CW_TMEM_COLS = 512;
@@ -77,7 +78,7 @@ enum GateSlot {
 #define XL_ABL 0  // timing experiments: skip one phase (wrong results); 0 = product
 #endif
 
-enum CwWarp { W_GATE_GROUP = 0, W_STATE_GROUP = 4, W_EPI_GROUP = 8, W_UMMA = 12, W_TMA = 13, W_SCAN = 14 };
+enum CwWarp { W_GATE_GROUP = 0, W_STATE_GROUP = 4, W_EPI_GROUP = 8, W_UMMA = 12, W_TMA = 13, W_SCAN = 14, W_SEND = 15 };
 
 enum CwBar {  // mbarrier indices.  Barriers whose producer may run two chunks ahead of a waiter come in pairs
               // indexed by chunk parity (a parity wait is only meaningful one phase back).  A satisfied wait
@@ -95,6 +96,8 @@ enum CwBar {  // mbarrier indices.  Barriers whose producer may run two chunks a
   BAR_NU,    // commit after phase C: nu and qn of the next chunk complete (completion k = nu(k), qn(k))
   BAR_INV,   // gate group -> epilogue group: 1/denominator published
   BAR_EGDONE,  // epilogue group -> gate group: 1/denominator consumed
+  BAR_QN0, BAR_QN1,  // split mode: partial normaliser products of all CTAs of the cluster have arrived (by chunk parity)
+  BAR_PART,          // split mode: gate group -> sender warp: this CTA's partial product is in shared memory
   BAR_COUNT
 };
 
@@ -113,7 +116,7 @@ struct CwLayout {
   static constexpr int OFF_HST = OFF_WMAT + 2 * 1024;          // [64][HST_ROW] normalised h of one chunk
   static constexpr int OFF_F32 = OFF_HST + CW_L * HST_ROW;
   static constexpr int GATE_F32 = 7 * CW_L + 8;                // per parity: see GateSlot
-  static constexpr int N_F32 = 2 * GATE_F32 + CW_L + DHQK;     // + 1/denominator + n state
+  static constexpr int N_F32 = 2 * GATE_F32 + CW_L + DHQK + 2 * 4 * CW_L + 2 * 4 * CW_L + 2 * CW_L;  // + 1/denominator + n state + partial qn [2][<=4][64] + denominator terms [2][4][64] + own partial [2][64]
   static constexpr int OFF_BAR = OFF_F32 + N_F32 * 4;          // mbarriers (8-byte aligned)
   static constexpr int TOTAL = OFF_BAR + BAR_COUNT * 8 + 16;
   static constexpr int DYN_SMEM = TOTAL + 1024;                // slack to align the base to 1024 B
@@ -137,6 +140,46 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 __device__ __forceinline__ float fast_log_sigmoid(float x) { return fminf(x, 0.f) - __logf(1.f + __expf(-fabsf(x))); }
+// ---- thread-block cluster helpers (split mode)
+__device__ __forceinline__ uint32_t cw_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cw_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cw_map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cw_st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cw_arrive_cluster_relaxed(uint32_t remote_bar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ void cw_arrive_cluster(uint32_t remote_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+// bounded wait with cluster-scope acquire (the data the barrier guards was written by other CTAs)
+__device__ __forceinline__ bool cw_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t it = 0;
+  for (;;) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (++it > (1u << 22)) return false;
+    if (it > 64) __nanosleep(64);
+  }
+}
 __device__ __forceinline__ void gate_group_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ void epilogue_group_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
 
@@ -217,11 +260,18 @@ static __device__ __noinline__ void cw_convert_T(uint32_t tC, uint32_t tCb, int 
   tc_wait_st();
 }
 
-template <int DHQK>
+// CS > 1 (split mode): CS neighbouring CTAs of one (document, head) -- each owns a 128-column slice of DHV -- form a
+// thread-block cluster and share the normaliser state n: each carries NKB/CS of its 64-feature blocks (their nu,
+// their share of q.n) and the partial products are summed through distributed shared memory.  The N=8 UMMAs cost a
+// full issue slot of the tensor pipe each, so this takes up to a quarter of the pipe's work per chunk away.
+template <int DHQK, int CS>
 __global__ void __launch_bounds__(CW_THREADS, 1)
 mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_params p) {
   using LY = CwLayout<DHQK>;
   constexpr int NKB = LY::NKB;
+  constexpr bool SPLIT = CS > 1;
+  constexpr int NB = NKB / CS;  // 64-feature blocks of n this CTA carries
+  static_assert(NKB % CS == 0 && (NB == 1 || NB == 2 || NB == 4), "feature blocks per CTA");
   extern __shared__ unsigned char cw_smem_raw[];
   // 128-byte-swizzled tiles need 1024-byte aligned bases
   // (pointer arithmetic on the __shared__ array, not an integer round trip, so that every access below is
@@ -232,7 +282,10 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   // gate data of a chunk, double buffered by chunk parity (see GateSlot)
   auto gate_buf = [&](int parity) { return s_f + parity * LY::GATE_F32; };
   float* s_inv = s_f + 2 * LY::GATE_F32;  // 1 / denominator of the chunk in the epilogue
-  float* s_n = s_inv + CW_L;              // n state in the lazy frame, DHQK
+  float* s_n = s_inv + CW_L;              // n state in the lazy frame (DHQK, or this CTA's 64 in split mode)
+  float* s_qn = s_n + DHQK;               // split mode: partial q.n of every CTA of the cluster, [2][CS][64]
+  float* s_den = s_qn + 2 * 4 * CW_L;     // split mode: rowsum, lower bound, eps, q.n scale per row, [2][4][64]
+  float* s_part = s_den + 2 * 4 * CW_L;   // split mode: this CTA's partial q.n on its way to the cluster, [2][64]
   const uint32_t bar0 = sbase + LY::OFF_BAR;
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + LY::OFF_BAR + BAR_COUNT * 8);
 
@@ -287,6 +340,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       if (i == BAR_GEMPTY0 || i == BAR_GEMPTY1) cnt = 256;  // state group + gate group
       if (i == BAR_A) cnt = 512;
       if (i == BAR_B) cnt = 256;
+      if (i == BAR_QN0 || i == BAR_QN1) cnt = CS;           // one arrival from the sender warp of every CTA of the cluster
       mbar_init(bar0 + 8u * i, cnt);
     }
     fence_barrier_init();
@@ -303,8 +357,10 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   }
   tc_fence_before();
   __syncthreads();
+  if (SPLIT) cw_cluster_sync();  // every CTA's barriers exist before anybody arrives on them remotely
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
+  const int rank = SPLIT ? (int)cw_cluster_rank() : 0;  // which feature blocks of n this CTA carries in split mode
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;  // tcgen05.ld/st: a warp reaches lanes 32*(warp%4)..+31
   const uint32_t tC = tmem + LY::T_C + lane_base, tCb = tmem + LY::T_CB + lane_base;
   const uint32_t tH = tmem + LY::T_H + lane_base, tS = tmem + LY::T_S + lane_base;
@@ -423,15 +479,17 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     // Iteration j: its half of the T -> bf16 conversion for chunk j; P(j) from S(j); then, with nu(j) and qn(j)
     // (issued one chunk ahead, behind S(j)): n(j) and its hi/lo operand for chunk j+1, and the denominators of chunk j.
     const int g = tid;  // 0..127
-    for (int d = g; d < DHQK; d += 128) s_n[d] = p.n0 ? p.n0[sidx * DHQK + d] : 0.f;
+    // (d counts the features this CTA carries: all of DHQK, or block `rank` in split mode)
+    const int dfirst = 64 * NB * rank;
+    for (int d = g; d < 64 * NB; d += 128) s_n[d] = p.n0 ? p.n0[sidx * DHQK + dfirst + d] : 0.f;
     auto publish_n = [&](int nbuf, int d, float nv) {  // hi/lo bf16 split of n[d] into rows 0/1 of the N=8 operand
       const __nv_bfloat16 hi = __float2bfloat16_rn(nv);
       const __nv_bfloat16 lo = __float2bfloat16_rn(nv - __bfloat162float(hi));
-      unsigned char* box = smem + LY::OFF_NMAT + nbuf * (NKB * 1024) + (d >> 6) * 1024;
+      unsigned char* box = smem + LY::OFF_NMAT + nbuf * (NB * 1024) + (d >> 6) * 1024;
       *reinterpret_cast<__nv_bfloat16*>(box + sw128_off(0, d & 63)) = hi;
       *reinterpret_cast<__nv_bfloat16*>(box + sw128_off(1, d & 63)) = lo;
     };
-    for (int d = g; d < DHQK; d += 128) publish_n(0, d, s_n[d]);
+    for (int d = g; d < 64 * NB; d += 128) publish_n(0, d, s_n[d]);
     fence_proxy_async_smem();
     if (mbar_wait(bar0 + 8u * BAR_GFULL0, 0u)) mbar_arrive(bar0 + 8u * BAR_C2);  // n operand and gate data of chunk 0
     else ok = false;
@@ -530,14 +588,17 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       tc_fence_after();
       float dot;
       {
-        uint32_t r[32], dn[8];
-        tmem_ld_x32(tS + 8, r);
+        uint32_t r[8 * NB], dn[8];
+        if constexpr (NB == 1) tmem_ld_x8(tS + 8, r);
+        else if constexpr (NB == 2) tmem_ld_x16(tS + 8, r);
+        else tmem_ld_x32(tS + 8, r);
         tmem_ld_x8(tS, dn);
         tc_wait_ld();
-        dot = __shfl_down_sync(0xffffffffu, __uint_as_float(dn[0]) + __uint_as_float(dn[1]), 16);
+        dot = __uint_as_float(dn[0]) + __uint_as_float(dn[1]);  // lanes 16..31: row 16 warp + lane - 16
+        if constexpr (!SPLIT) dot = __shfl_down_sync(0xffffffffu, dot, 16);
         if (lane >= 16) {
 #pragma unroll
-          for (int gq = 0; gq < NKB; ++gq) {
+          for (int gq = 0; gq < NB; ++gq) {
             const int d = 64 * gq + 16 * warp + (lane - 16);
             const float nv = fmaf(s_n[d], mult, __uint_as_float(r[8 * gq]) + __uint_as_float(r[8 * gq + 1]));
             s_n[d] = nv;
@@ -553,15 +614,28 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       CW_TL(0, 7);
       // ---- denominators: |rowsum + q.n| against the lower bound (the product sits on lanes 16..31)
       if (chunk >= 1) CW_WAIT(BAR_EGDONE, par ^ 1u);  // the epilogue group has consumed the previous ones
-      if (lane < 16) s_inv[j] = __fdividef(1.f, fmaxf(fabsf(fmaf(dot, qn_scale, rowsum)), lower) + eps_j);
-      mbar_arrive(bar0 + 8u * BAR_INV);
+      if constexpr (SPLIT) {
+        // The terms this CTA knows go to the epilogue group, its share of q.n (through the sender warp) to every CTA
+        // of the cluster, itself included: the epilogue group, which has the slack, waits for the partial products --
+        // this group never waits on another CTA.
+        if (lane < 16) {
+          float* dd = s_den + buf * 4 * CW_L + j;
+          dd[0] = rowsum; dd[CW_L] = lower; dd[2 * CW_L] = eps_j; dd[3 * CW_L] = qn_scale;
+        }
+        else s_part[buf * CW_L + 16 * warp + (lane - 16)] = dot;
+        mbar_arrive(bar0 + 8u * BAR_INV);
+        mbar_arrive(bar0 + 8u * BAR_PART);  // the sender warp takes it from here (remote stores and their fence are slow)
+      } else {
+        if (lane < 16) s_inv[j] = __fdividef(1.f, fmaxf(fabsf(fmaf(dot, qn_scale, rowsum)), lower) + eps_j);
+        mbar_arrive(bar0 + 8u * BAR_INV);
+      }
     }
     // ---- final n (back in the true frame)
-    if (ok && slice == 0 && lane >= 16) {
+    if (ok && slice < CS && lane >= 16) {  // the first cluster of the head writes n: every CTA the blocks it carries
 #pragma unroll
-      for (int gq = 0; gq < NKB; ++gq) {
+      for (int gq = 0; gq < NB; ++gq) {
         const int d = 64 * gq + 16 * warp + (lane - 16);
-        p.n_out[sidx * DHQK + d] = s_n[d] * back_last;
+        p.n_out[sidx * DHQK + dfirst + d] = s_n[d] * back_last;
       }
     }
   } else if (warp < W_EPI_GROUP) {
@@ -678,36 +752,60 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     unsigned char* hst = smem + LY::OFF_HST;
     __nv_bfloat16* hbase = reinterpret_cast<__nv_bfloat16*>(p.h) + b * p.h_sb + head * p.h_sh + tok0 * p.h_st + col0;
     mbar_arrive(bar0 + 8u * BAR_A);  // the accumulator is free for chunk 0
+    // Denominators of chunk c, ready long before H^T(c) is (they depend on the previous phase of UMMAs only): taken
+    // one chunk ahead of the accumulator so that nothing stands between H^T landing and its drain.
+    auto denominators_ready = [&](int c) -> bool {
+      if (!mbar_wait(bar0 + 8u * BAR_INV, (uint32_t)c & 1u)) return false;
+      if constexpr (SPLIT) {
+        // from the gate group's terms and the partial normaliser products of the whole cluster
+        const int buf = c & 1, row = t & 63;
+        if (!cw_wait_cluster(bar0 + 8u * (BAR_QN0 + buf), (uint32_t)(c >> 1) & 1u)) return false;
+        float dsum = 0.f;
+#pragma unroll
+        for (int r2 = 0; r2 < CS; ++r2) dsum += s_qn[(buf * CS + r2) * CW_L + row];
+        const float* dd = s_den + buf * 4 * CW_L + row;
+        s_inv[row] = __fdividef(1.f, fmaxf(fabsf(fmaf(dsum, dd[3 * CW_L], dd[0])), dd[CW_L]) + dd[2 * CW_L]);
+        epilogue_group_sync();
+      }
+      return true;
+    };
+    if (!denominators_ready(0)) ok = false;
 #pragma unroll 1
-    for (int chunk = 0; chunk < nchunks; ++chunk) {
+    for (int chunk = 0; ok && chunk < nchunks; ++chunk) {
       const uint32_t par = (uint32_t)chunk & 1u;
       const long long rem = len - (long long)chunk * CW_L;
       const int len_c = rem < CW_L ? (int)rem : CW_L;
       CW_WAIT(BAR_HC, par);
       CW_TL(2, 1);
       tc_fence_after();
-      uint32_t hv0[32], hv1[32];
-      tmem_ld_x32(tH, hv0);
-      tmem_ld_x32(tH + 32, hv1);
-      tc_wait_ld();
-      tc_fence_before();
-      mbar_arrive(bar0 + 8u * BAR_A);  // the accumulator is free for the next chunk
-      CW_WAIT(BAR_INV, par);
-      CW_TL(2, 2);
+      // drain, normalise and stage in two rolled passes of 32 tokens (small code)
       unsigned char* col = hst + dv * 2;
+#pragma unroll 1
+      for (int q = 0; q < ((XL_ABL & 4) ? 0 : 2); ++q) {
+        uint32_t hv[32];
+        tmem_ld_x32(tH + 32 * q, hv);
+        float4 iv[8];
 #pragma unroll
-      for (int i = 0; i < ((XL_ABL & 4) ? 0 : 16); ++i) {
-        const float4 iv = *reinterpret_cast<const float4*>(s_inv + 4 * i);
-        const float sc[4] = {iv.x, iv.y, iv.z, iv.w};
+        for (int i = 0; i < 8; ++i) iv[i] = *reinterpret_cast<const float4*>(s_inv + 32 * q + 4 * i);
+        tc_wait_ld();
+        if (q == 1) {  // the accumulator is in registers: free for the next chunk
+          tc_fence_before();
+          mbar_arrive(bar0 + 8u * BAR_A);
+          CW_TL(2, 4);
+        }
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-          *reinterpret_cast<__nv_bfloat16*>(col + (4 * i + u) * LY::HST_ROW) =
-              __float2bfloat16_rn(__uint_as_float(i < 8 ? hv0[4 * i + u] : hv1[4 * (i & 7) + u]) * sc[u]);
+        for (int i = 0; i < 8; ++i) {
+          const float sc[4] = {iv[i].x, iv[i].y, iv[i].z, iv[i].w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            *reinterpret_cast<__nv_bfloat16*>(col + (32 * q + 4 * i + u) * LY::HST_ROW) =
+                __float2bfloat16_rn(__uint_as_float(hv[4 * i + u]) * sc[u]);
+        }
       }
-      mbar_arrive(bar0 + 8u * BAR_EGDONE);  // s_inv may be rewritten
+      mbar_arrive(bar0 + 8u * BAR_EGDONE);  // the denominators of this chunk are consumed
       epilogue_group_sync();
       __nv_bfloat16* ho = hbase + (long long)chunk * CW_L * p.h_st;
-#pragma unroll
+#pragma unroll 2
       for (int i = 0; i < ((XL_ABL & 4) ? 0 : 8); ++i) {
         const int idx = i * 128 + t, row = idx >> 4, c = idx & 15;
         if (row < len_c)
@@ -715,6 +813,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       }
       epilogue_group_sync();  // the tile is rewritten by the next chunk
       CW_TL(2, 3);
+      if (chunk + 1 < nchunks && !denominators_ready(chunk + 1)) ok = false;
     }
   } else if (warp == W_UMMA) {
     // =========================================================================================== UMMA issuer
@@ -730,9 +829,13 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     constexpr uint32_t IDESC_NU = umma_idesc_bf16(64, 8, 1, 0);
     // Values that are warp-uniform in fact but not provably so (read from shared or global memory) are broadcast
     // with a shuffle: that is what lets the compiler keep UMMA operands in uniform registers.
-    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0), sbase_u = __shfl_sync(0xffffffffu, sbase, 0);
+    // (shared-memory base for DESCRIPTORS only: the 18-bit offset inside this CTA's window.  In a cluster launch the
+    // shared address of every CTA but rank 0 carries the rank in its upper bits, which would spill into the
+    // descriptor's leading-offset field.)
+    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0), sbase_u = __shfl_sync(0xffffffffu, sbase, 0) & 0x3FFFFu;
     const uint32_t bar_u = __shfl_sync(0xffffffffu, bar0, 0);
     const int nchunks_u = __shfl_sync(0xffffffffu, nchunks, 0);
+    [[maybe_unused]] const uint32_t rank_u = (uint32_t)__shfl_sync(0xffffffffu, rank, 0);
     const uint32_t t_odd = tmem_u + LY::T_S + (16u << 16);  // odd 16-lane halves of the S columns
     // lower descriptor words (start address >> 4 | leading offset); K-major tiles use leading offset 16 B,
     // MN-major tiles one 8 KiB box
@@ -744,7 +847,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       [[maybe_unused]] const int chunk = next;  // (time stamps of this phase are filed under the chunk it prepares)
       const uint32_t nq = sbase_u + LY::OFF_STAGE + (next & 1) * LY::STAGE_BYTES, nk = nq + LY::Q_BYTES;
       const uint32_t wm = sbase_u + LY::OFF_WMAT + (next & 1) * 1024;
-      const uint32_t nm = sbase_u + LY::OFF_NMAT + (next & 1) * (NKB * 1024);
+      const uint32_t nm = sbase_u + LY::OFF_NMAT + (next & 1) * (NB * 1024);
       okm &= MMA_WAIT_U(BAR_FULL0 + (next & 1), (uint32_t)(next >> 1) & 1u);
       okm &= MMA_WAIT_U(BAR_C2, (uint32_t)next & 1u);
       CW_TL(3, 5);
@@ -756,17 +859,19 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
           umma_ss_lo(tmem_u + LY::T_S, (LBO_K + ((nq + kb * CW_BOX_BYTES + kk * 32) >> 4)),
                      (LBO_K + ((nk + kb * CW_BOX_BYTES + kk * 32) >> 4)), IDESC_S, (kb | kk) != 0);
       umma_commit_elect(bar_u + 8u * BAR_S);
+      // nu and q.n of the feature blocks this CTA carries (all of them unless the cluster shares the work), step by step
+      const uint32_t kblk = nk + rank_u * (NB * CW_BOX_BYTES), qblk = nq + rank_u * (NB * CW_BOX_BYTES);
 #pragma unroll 1
-      for (int kb = 0; kb < NKB; ++kb) {
+      for (int kb = 0; kb < NB; ++kb) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           const int ks = 4 * kb + kk;
-          // nu step (token slice, feature block) = (ks / NKB, ks % NKB): 4 x NKB = DHQK/16 steps as well
-          const int tsl = ks / NKB, gq = ks % NKB;
+          // nu step (token slice, feature block) = (ks / NB, ks % NB): 4 x NB steps, like q.n
+          const int tsl = ks / NB, gq = ks % NB;
           if (!(XL_ABL & 32) || kk == 0) {
-            umma_ss_lo(t_odd + 8 + 8 * gq, (LBO_MN + ((nk + gq * CW_BOX_BYTES + tsl * 2048) >> 4)),
+            umma_ss_lo(t_odd + 8 + 8 * gq, (LBO_MN + ((kblk + gq * CW_BOX_BYTES + tsl * 2048) >> 4)),
                        (LBO_K + ((wm + tsl * 32) >> 4)), IDESC_NU, tsl != 0);
-            umma_ss_lo(t_odd, (LBO_K + ((nq + kb * CW_BOX_BYTES + kk * 32) >> 4)),
+            umma_ss_lo(t_odd, (LBO_K + ((qblk + kb * CW_BOX_BYTES + kk * 32) >> 4)),
                        (LBO_K + ((nm + kb * 1024 + kk * 32) >> 4)), IDESC_DN, ks != 0);
           }
         }
@@ -811,6 +916,29 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       if (chunk + 1 < nchunks_u) phase_c(chunk + 1);
     }
     ok = okm;
+  } else if (warp == W_SEND) {
+    // =========================================================================================== sender (split mode)
+    // Ships this CTA's partial normaliser products to every CTA of the cluster: remote stores, ONE cluster-scope
+    // fence, then one relaxed arrival per destination.  (Done by the gate group itself, with a releasing arrival per
+    // destination, this cost it ~4000 cycles per chunk.)
+    if constexpr (SPLIT) {
+#pragma unroll 1
+      for (int chunk = 0; chunk < nchunks; ++chunk) {
+        const int buf = chunk & 1;
+        CW_WAIT(BAR_PART, (uint32_t)chunk & 1u);
+        const float v0 = s_part[buf * CW_L + lane], v1 = s_part[buf * CW_L + 32 + lane];
+        const uint32_t slot = smem_u32(s_qn + (buf * CS + rank) * CW_L + lane);
+#pragma unroll
+        for (int r2 = 0; r2 < CS; ++r2) {
+          const uint32_t dst = cw_map_to_cta(slot, (uint32_t)r2);
+          cw_st_cluster_f32(dst, v0);
+          cw_st_cluster_f32(dst + 32 * 4, v1);
+        }
+        asm volatile("fence.acq_rel.cluster;" ::: "memory");
+        __syncwarp();
+        if (lane < CS) cw_arrive_cluster_relaxed(cw_map_to_cta(bar0 + 8u * (BAR_QN0 + buf), (uint32_t)lane));
+      }
+    }
   } else {
     // =========================================================================================== TMA issuer
     if (lane == 0) {
@@ -852,6 +980,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   tc_fence_before();
   __syncthreads();
   if (warp == W_UMMA) tmem_dealloc(tmem, CW_TMEM_COLS);
+  if (SPLIT) cw_cluster_sync();  // nobody leaves while a peer may still write into its shared memory
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -919,15 +1048,41 @@ static int make_map(CUtensorMap* m, int pos[3], const void* base, int D, int S, 
 
 int validate_seq_common(const xl_mlstm_seq_params* p);
 
+template <int DHQK, int CS>
+static int launch_chunkwise_cs(const CwMaps& maps, const xl_mlstm_seq_params* p, cudaStream_t st, dim3 grid) {
+  using LY = CwLayout<DHQK>;
+  auto kern = mlstm_chunkwise_kernel<DHQK, CS>;
+  XL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LY::DYN_SMEM));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(CW_THREADS);
+  cfg.dynamicSmemBytes = LY::DYN_SMEM;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)CS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = CS > 1 ? 1 : 0;
+  XL_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, maps, *p));
+  return check_launch("xl_mlstm_chunkwise");
+}
+
 template <int DHQK>
 static int launch_chunkwise(const CwMaps& maps, const xl_mlstm_seq_params* p, cudaStream_t st) {
   using LY = CwLayout<DHQK>;
   static_assert(LY::DYN_SMEM <= 227 * 1024, "shared memory budget");
-  XL_CUDA_TRY(cudaFuncSetAttribute(mlstm_chunkwise_kernel<DHQK>, cudaFuncAttributeMaxDynamicSharedMemorySize, LY::DYN_SMEM));
   const int nd = p->cu_seqlens ? p->num_docs : p->B;
-  dim3 grid(p->DHV / CW_DV, p->NH, nd), block(CW_THREADS);
-  mlstm_chunkwise_kernel<DHQK><<<grid, block, LY::DYN_SMEM, st>>>(maps, *p);
-  return check_launch("xl_mlstm_chunkwise");
+  const int nslices = p->DHV / CW_DV;
+  dim3 grid(nslices, p->NH, nd);
+  // Cluster size: 1 unless XL_CW_CLUSTER asks for 2 or 4.  Sharing the normaliser work takes a quarter of the UMMAs
+  // away, but the CTAs of a cluster then advance in lock step (each needs every other's partial product every chunk)
+  // and on config 2 that costs more than it saves (measured 312 vs 283 us), so it stays an opt-in experiment.
+  static const int forced = [] { const char* e = getenv("XL_CW_CLUSTER"); return e ? atoi(e) : 1; }();
+  if (forced == 2 && LY::NKB % 2 == 0 && nslices % 2 == 0) return launch_chunkwise_cs<DHQK, (LY::NKB % 2 == 0 ? 2 : 1)>(maps, p, st, grid);
+  if (forced == 4 && LY::NKB % 4 == 0 && nslices % 4 == 0) return launch_chunkwise_cs<DHQK, (LY::NKB % 4 == 0 ? 4 : 1)>(maps, p, st, grid);
+  return launch_chunkwise_cs<DHQK, 1>(maps, p, st, grid);
 }
 
 }  // namespace xl
