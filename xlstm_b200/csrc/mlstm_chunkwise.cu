@@ -61,13 +61,13 @@ constexpr float CW_FAST_SPREAD = 30.f;     // largest in-chunk spread of the sta
 // which fp32 accumulators and bf16 operands carry without loss); the exact frame covers chunks in which the
 // stabiliser jumps further.  Exact: P_jl = S_jl/sqrt(d) 2^(x_l - y_j); common: P_jl = S_jl z_l; rowsum_j = sum_l P_jl.
 enum GateSlot {
-  G_LOWER = 0 * CW_L,  // exp(-(b_j + phi_j)): lower bound of the denominator
+  G_LOWER = 0 * CW_L,  // exp(-(b_j + phi_j)): lower bound of the denominator (x sqrt(d) in the common frame)
   G_X = 1 * CW_L,      // x_l (log2 units; -inf for tokens past the end of the document)
   G_Y = 2 * CW_L,      // y_j (log2 units)
   G_R = 3 * CW_L,      // r_j exp(rho) / sqrt(d) (exact frame only)
   G_W = 4 * CW_L,      // w_l = exp(a'_l - mu* - rho')
-  G_Z = 5 * CW_L,      // z_l = w_l / sqrt(d) (common frame)
-  G_EPS = 6 * CW_L,    // exp(mu_j - phi_j): eps of the denominator in the row's frame
+  G_Z = 5 * CW_L,      // z_l = w_l (common frame)
+  G_EPS = 6 * CW_L,    // exp(mu_j - phi_j): eps of the denominator in the row's frame (x sqrt(d) in the common frame)
   G_MULT = 7 * CW_L,   // rescale multiplier of T (1 unless the lazy frame ran out)
   G_RHO = G_MULT + 1,  // rho'
   G_EXACT = G_MULT + 2,  // 1.0 = exact frame
@@ -241,10 +241,18 @@ static __device__ __noinline__ void cw_convert_T(uint32_t tC, uint32_t tCb, int 
     tmem_ld_x32(tC + cb * 64 + 32, r1);
     tc_wait_ld();
     uint32_t pk[32];
+    if (cb_scale == 1.f) {  // the usual case: nothing but the conversion
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      pk[i] = pack_bf16x2(__uint_as_float(r0[2 * i]) * cb_scale, __uint_as_float(r0[2 * i + 1]) * cb_scale);
-      pk[16 + i] = pack_bf16x2(__uint_as_float(r1[2 * i]) * cb_scale, __uint_as_float(r1[2 * i + 1]) * cb_scale);
+      for (int i = 0; i < 16; ++i) {
+        pk[i] = pack_bf16x2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+        pk[16 + i] = pack_bf16x2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        pk[i] = pack_bf16x2(__uint_as_float(r0[2 * i]) * cb_scale, __uint_as_float(r0[2 * i + 1]) * cb_scale);
+        pk[16 + i] = pack_bf16x2(__uint_as_float(r1[2 * i]) * cb_scale, __uint_as_float(r1[2 * i + 1]) * cb_scale);
+      }
     }
     tmem_st_x32(tCb + cb * 32, pk);
     if (mult != 1.f) {
@@ -443,12 +451,14 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         *reinterpret_cast<float2*>(gb + G_Z + t0) = make_float2(1.f, 1.f);
         *reinterpret_cast<float2*>(gb + G_EPS + t0) = make_float2(1.f, 1.f);
       } else {
-        const float phi = mu_star + rho_new;
-        *reinterpret_cast<float2*>(gb + G_LOWER + t0) = make_float2(__expf(-(b0 + phi)), __expf(-(b1 + phi)));
+        // The common frame leaves the 1/sqrt(d) of q out of BOTH numerator and denominator (h is their ratio): the
+        // bf16 copy of T and P then need no multiplication at all; the lower bound and eps take sqrt(d) instead.
+        const float phi = mu_star + rho_new, sqrt_d = 1.f / qscale;
+        *reinterpret_cast<float2*>(gb + G_LOWER + t0) = make_float2(__expf(-(b0 + phi)) * sqrt_d, __expf(-(b1 + phi)) * sqrt_d);
         *reinterpret_cast<float2*>(gb + G_X + t0) = make_float2(t0 < len_c ? 0.f : -INFINITY, t1 < len_c ? 0.f : -INFINITY);
         *reinterpret_cast<float2*>(gb + G_Y + t0) = make_float2(0.f, 0.f);
-        *reinterpret_cast<float2*>(gb + G_Z + t0) = make_float2(w0 * qscale, w1 * qscale);
-        *reinterpret_cast<float2*>(gb + G_EPS + t0) = make_float2(__expf(mu0 - phi), __expf(mu1 - phi));
+        *reinterpret_cast<float2*>(gb + G_Z + t0) = make_float2(w0, w1);
+        *reinterpret_cast<float2*>(gb + G_EPS + t0) = make_float2(__expf(mu0 - phi) * sqrt_d, __expf(mu1 - phi) * sqrt_d);
       }
       {
         const __nv_bfloat162 hi = __floats2bfloat162_rn(w0, w1);
@@ -462,10 +472,10 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         gb[G_MULT] = mult;
         gb[G_RHO] = rho_new;
         gb[G_EXACT] = exact ? 1.f : 0.f;
-        // common frame: T q enters as exp(rho + m_prev - mu* - rho') T q / sqrt(d); that exponent is the rescale
-        // multiplier itself (1 whenever no rescale happens)
-        gb[G_CB] = exact ? 1.f : mult * qscale;
-        gb[G_QN] = exact ? 1.f : mult * qscale;
+        // common frame: T q enters as exp(rho + m_prev - mu* - rho') T q; that exponent is the rescale multiplier
+        // itself (1 whenever no rescale happens)
+        gb[G_CB] = exact ? 1.f : mult;
+        gb[G_QN] = exact ? 1.f : mult;
       }
       m_prev = gsum + mu_star;
       rho = rho_new;
