@@ -375,7 +375,10 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   const float qscale = rsqrtf((float)DHQK);
   bool ok = true;
   auto convert_T = [&](int b0, int b1, float cb_scale, float mult) { cw_convert_T(tC, tCb, b0, b1, cb_scale, mult); };
-  constexpr int CB_SPLIT = (DHQK / 64 + 1) / 2;  // blocks [0, CB_SPLIT) state group, [CB_SPLIT, DHQK/64) gate group
+  // blocks [0, CB_SPLIT) state group, [CB_SPLIT, DHQK/64) gate group.  The gate group takes one block only: the phase
+  // of UMMAs that runs meanwhile is longer than three blocks take, and the gate group's P pass -- next on the critical
+  // path, it gates phase B -- starts that much earlier.
+  constexpr int CB_SPLIT = DHQK / 64 >= 2 ? DHQK / 64 - 1 : 1;
 
   if (warp == W_SCAN) {
     // =========================================================================================== scan warp
