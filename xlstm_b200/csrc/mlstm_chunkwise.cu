@@ -15,22 +15,32 @@
 //
 // Tensor-core work per chunk (all operands bf16, fp32 accumulation in tensor memory):
 //   S    [64 x 64]     = Q K^T                  M=64  N=64   K=DHQK  A,B K-major TMA tiles
-//   H^T  [128 x 64]    = Tb (r q~)^T            M=128 N=64   K=DHQK  A = bf16 copy of T in tensor memory
+//   H^T  [128 x 64]    = Tb q^T                 M=128 N=64   K=DHQK  A = bf16 copy of T in tensor memory
 //   H^T               += V^T P^T                M=128 N=64   K=64    A = V tile used MN-major, B = P tile
 //   T    [128 x DHQK] += (w V)^T K              M=128 N=DHQK K=64    both MN-major
-//   qn   [64 x 8]      = (r q~) [n_hi n_lo]^T   M=64  N=8    K=DHQK  normaliser dot product, n split hi/lo
+//   qn   [64 x 8]      = q [n_hi n_lo]^T        M=64  N=8    K=DHQK  normaliser dot product, n split hi/lo
 //   nu   [DHQK x 8]    = K^T [w_hi w_lo]^T      M=64  N=8    K=64    n update, per 64-feature block
 // The two N=8 products land on the odd 16-lane halves of the S columns (an M=64 accumulator only occupies
 // the even halves), so the 512 tensor-memory columns are exactly: T 256 | Tb 128 | H^T 64 | S,qn,nu 64.
+// Every UMMA of these shapes costs the pipe ~33 cycles (the N=256 ones 132), whatever its N: 80 of them per chunk.
 //
-// Warp roles (480 threads): warp 14 carries the gate recurrence (scans, r, w, frame) one to two chunks ahead;
-// warps 0-3 gate group (P from S, denominators, n and its hi/lo operand); warps 4-7 state group (T -> bf16
-// copy / lazy rescale, r-scaled q in place in its TMA stage once S has consumed it, w-scaled v); warps 8-11
-// epilogue group (H^T -> registers -> normalised bf16 tile in shared memory -> 16-byte global stores); warp 12
-// issues every UMMA; warp 13 issues the TMA loads.  Per chunk the tensor pipe runs H^T (inter, intra), T and
-// nu, then S of the next chunk and the normaliser product of this one: the last two need neither T nor its
-// bf16 copy, so they fill the time the state group spends converting T.  Groups hand work to each other
+// Warp roles: warp 14 carries the gate recurrence (scans, r, w, frame) one to two chunks ahead; warps 0-3 gate
+// group (one block of the T -> bf16 conversion, P from S, the terms of the denominators, n and its hi/lo operand);
+// warps 4-7 state group (the rest of the conversion / lazy rescale, w-scaled v, in the exact frame r-scaled q in
+// place in its TMA stage); warps 8-11 epilogue group (1/denominator, H^T -> normalised bf16 tile in shared memory ->
+// 16-byte global stores); warp 12 issues every UMMA; warp 13 issues the TMA loads; warp 15 only works in the
+// opt-in cluster mode.  Per chunk the tensor pipe runs phase A (H^T inter), phase B (H^T intra interleaved with
+// the T update) and phase C: S, nu and qn of the NEXT chunk, which need neither T nor its bf16 copy and so fill
+// the time the conversion of T takes -- the one long dependency of the loop.  Groups hand work to each other
 // through mbarriers only; every wait is bounded, and no waiter is ever more than one phase behind its producer.
+//
+// Three things about code generation decide the speed of this kernel as much as the schedule does:
+//   * the compiler issues an UMMA as ~4 instructions only where it can PROVE warp-uniform control flow: the role
+//     dispatch uses a shuffled warp index, the issuing warp calls no non-inlined function (waits are inline) and
+//     has no branch inside an issue loop; otherwise every UMMA becomes ~35 instructions and the warp sets the pace;
+//   * all roles' per-chunk code together must stay small (rolled loops over pieces, one shared copy of the
+//     conversion): unrolled, every pass ran mostly on instruction-fetch misses;
+//   * polling warps take issue slots from working ones: waits back off at once.
 //
 // q, k, v tiles arrive by TMA (128-byte swizzle) straight from the caller's strided (B, NH, S, D) views;
 // documents are chunked from their own first token, so a chunk never straddles a document boundary and the
