@@ -12,7 +12,11 @@
 // the M=16 side of m16n8k16.  Each thread ends a step holding all four gate pre-activations of its four
 // (row, unit) pairs in its accumulators, so the pointwise update runs in registers with c, n, m kept in
 // fp32 registers for the whole sequence.  The new h (bf16) is pushed into the double-buffered h tile of
-// EVERY CTA of the cluster through distributed shared memory, then one cluster barrier ends the step.
+// EVERY CTA of the cluster with asynchronous distributed-shared-memory stores that count their bytes on the
+// destination's mbarrier: a CTA starts step t+1 the moment all of h_t has landed in ITS tile -- no cluster-wide
+// barrier and no release/acquire fence on the per-step chain (that barrier was 2/3 of the step time).  The data
+// dependency itself orders buffer reuse: whoever pushes h_{t+1} into a tile has consumed h_t, which every CTA
+// pushed only after its last read of h_{t-1}, the previous content of that buffer.
 // Wx is streamed through an 8-step cp.async ring so that HBM latency is off the dependency chain.
 // A document boundary (cu_seqlens) zeroes h, c, n, m of that batch row inside the kernel.
 #include "common.cuh"
@@ -45,8 +49,16 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ void st_cluster_u32(uint32_t addr, uint32_t v) {
-  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+// Bounded wait without back-off: this wait is the per-step latency chain, a sleep would land on it in full.
+__device__ __forceinline__ bool sl_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t it = 0; it < (1u << 26); ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+// 4-byte store into (another) CTA's shared memory that adds its 4 bytes to the transaction count of an mbarrier there
+__device__ __forceinline__ void st_async_u32(uint32_t addr, uint32_t v, uint32_t remote_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(addr), "r"(v), "r"(remote_bar)
+               : "memory");
 }
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -85,6 +97,8 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
   extern __shared__ __align__(16) unsigned char sl_smem[];
   __nv_bfloat16* s_h = reinterpret_cast<__nv_bfloat16*>(sl_smem);                    // 2 x 16 x H_STRIDE
   unsigned char* s_wx = sl_smem + 2 * SL_ROWS * H_STRIDE * sizeof(__nv_bfloat16);    // SL_RING x SL_WX_STEP_BYTES
+  const uint32_t s_bar = smem_u32(s_wx + SL_RING * SL_WX_STEP_BYTES);                // 2 mbarriers: h tile 0 / 1 complete
+  constexpr uint32_t H_TILE_BYTES = SL_ROWS * DH * 2;                                // what one step delivers to a CTA
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t rank = cluster_ctarank();       // which 32-unit slice of the head
@@ -161,6 +175,11 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
 
   // ---- h tile (both buffers) of this CTA: buffer 0 holds h_{-1}; every CTA fills its own copy completely
   for (int i = tid; i < 2 * SL_ROWS * H_STRIDE; i += SL_THREADS) s_h[i] = __float2bfloat16_rn(0.f);
+  if (tid == 0) {
+    mbar_init(s_bar, 1);      // one arrival per phase: the local expect_tx
+    mbar_init(s_bar + 8, 1);
+    fence_barrier_init();
+  }
   __syncthreads();
   if (p.state0) {
     for (int i = tid; i < SL_ROWS * DH; i += SL_THREADS) {
@@ -201,9 +220,15 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
 
   __nv_bfloat16* hout = reinterpret_cast<__nv_bfloat16*>(p.h_out);
 
+  bool ok = true;
   for (int t = 0; t < S; ++t) {
     issue_wx(t + SL_RING - 1);
     const int cur = t & 1, nxt = cur ^ 1;
+    // this step's h_t will land in tile `nxt` of this CTA: announce its size on that tile's barrier
+    if (tid == 0) mbar_expect_tx(s_bar + 8u * nxt, H_TILE_BYTES);
+    // h_{t-1} complete in tile `cur` (tile 0 holds the initial state at t = 0: nothing to wait for; its barrier's
+    // first phase therefore belongs to t = 2)
+    if (t >= 1 && !sl_wait(s_bar + 8u * cur, (uint32_t)((t >> 1) - (cur == 0 ? 1 : 0)) & 1u)) { ok = false; break; }
 
     // accumulators start from Wx + bias
     float acc[4][4];
@@ -244,12 +269,7 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
       m_[i] = mn;
       hn[i] = __fdividef(c_[i], n_[i]) * __fdividef(1.f, 1.f + __expf(-orr));
     }
-    // output h_t, (B, NH, S, DH)
     const uint32_t pa = pack_bf16x2(hn[0], hn[1]), pb = pack_bf16x2(hn[2], hn[3]);
-    if (ok_a) *reinterpret_cast<uint32_t*>(hout + (((size_t)gb_a * NH + head) * S + t) * DH + unit_h) = pa;
-    if (ok_b) *reinterpret_cast<uint32_t*>(hout + (((size_t)gb_b * NH + head) * S + t) * DH + unit_h) = pb;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) hlast[i] = hn[i];
     // a row whose next token opens a new document restarts from the zero state
     uint32_t push_a = pa, push_b = pb;
     if (reset_next_a) {
@@ -266,12 +286,20 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
     const uint32_t nb = s_h_u32 + nxt * (SL_ROWS * H_STRIDE * 2);
 #pragma unroll
     for (int r = 0; r < NCTA; ++r) {
-      st_cluster_u32(map_to_cta(nb + slot_a, r), push_a);
-      st_cluster_u32(map_to_cta(nb + slot_b, r), push_b);
+      const uint32_t rbar = map_to_cta(s_bar + 8u * nxt, r);
+      st_async_u32(map_to_cta(nb + slot_a, r), push_a, rbar);
+      st_async_u32(map_to_cta(nb + slot_b, r), push_b, rbar);
     }
+    // output h_t, (B, NH, S, DH) -- after the pushes: they are on the step-to-step chain, this store is not
+    if (ok_a) *reinterpret_cast<uint32_t*>(hout + (((size_t)gb_a * NH + head) * S + t) * DH + unit_h) = pa;
+    if (ok_b) *reinterpret_cast<uint32_t*>(hout + (((size_t)gb_b * NH + head) * S + t) * DH + unit_h) = pb;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) hlast[i] = hn[i];
     cp_async_wait<SL_RING - 2>();  // this thread's part of step t+1 has landed
-    cluster_barrier();
+    __syncthreads();               // ... and everybody else's (CTA-wide only)
   }
+  if (!ok && p.status) atomicExch(p.status, 1);
+  cluster_barrier();  // nobody leaves while a peer may still push into its tile
 
   // final state (4, B, H): h, c, n, m
 #pragma unroll
@@ -290,7 +318,7 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
 template <int DH>
 static int launch_slstm(const xl_slstm_params* p, cudaStream_t st) {
   constexpr int NCTA = DH / SL_UNITS;
-  const size_t smem = 2 * SL_ROWS * (DH + 8) * 2 + (size_t)SL_RING * SL_WX_STEP_BYTES;
+  const size_t smem = 2 * SL_ROWS * (DH + 8) * 2 + (size_t)SL_RING * SL_WX_STEP_BYTES + 16;  // + 2 mbarriers
   XL_CUDA_TRY(cudaFuncSetAttribute(slstm_forward_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(NCTA, p->NH, (p->B + SL_ROWS - 1) / SL_ROWS);

@@ -222,7 +222,10 @@ class LargeModel:
                 body()
         torch.cuda.current_stream(dev).wait_stream(side)
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        # With tensor parallelism the graph holds NCCL all-reduces: their communicator is warm (the warm-up runs above)
+        # and the capture must not be global, or the watchdog thread's event queries would invalidate it.
+        mode = "thread_local" if self.tp_world > 1 else "global"
+        with torch.cuda.graph(graph, capture_error_mode=mode):
             body()
         for i, st in snapshot.items():   # undo the state changes of the warm-up and capture runs
             for dst, src in zip(self._g_state[i], st):
