@@ -254,11 +254,14 @@ def build_case(name, dev, rank):
         tok_dev = tok_host.to(dev)
         out_host = torch.empty(B, GEN, dtype=torch.long).pin_memory()
 
+        # the decode loop replays a CUDA graph; with tensor parallelism (NCCL all-reduces inside the graph) only on request
+        graphed = world == 1 or os.environ.get("XL_TP_GRAPH", "0") == "1"
+
         def step():
-            return model.generate(tok_dev, GEN, use_cuda_graph=True)[0]
+            return model.generate(tok_dev, GEN, use_cuda_graph=graphed)[0]
 
         def e2e_step():
-            out_host.copy_(model.generate(tok_host.to(dev, non_blocking=True), GEN, use_cuda_graph=True)[0], non_blocking=True)
+            out_host.copy_(model.generate(tok_host.to(dev, non_blocking=True), GEN, use_cuda_graph=graphed)[0], non_blocking=True)
 
         cfg = dict(model="xLSTM-7B-shaped (random init)", embedding_dim=4096, num_heads=8, num_blocks=32, vocab_size=50304,
                    global_batch=B, seq_len=S, decode_tokens=GEN)
