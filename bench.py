@@ -254,8 +254,8 @@ def build_case(name, dev, rank):
         tok_dev = tok_host.to(dev)
         out_host = torch.empty(B, GEN, dtype=torch.long).pin_memory()
 
-        # the decode loop replays a CUDA graph; with tensor parallelism (NCCL all-reduces inside the graph) only on request
-        graphed = world == 1 or os.environ.get("XL_TP_GRAPH", "0") == "1"
+        # the decode loop replays a CUDA graph (with tensor parallelism the NCCL all-reduces are part of it)
+        graphed = os.environ.get("XL_DECODE_GRAPH", "1") == "1"
 
         def step():
             return model.generate(tok_dev, GEN, use_cuda_graph=graphed)[0]
@@ -265,7 +265,7 @@ def build_case(name, dev, rank):
 
         cfg = dict(model="xLSTM-7B-shaped (random init)", embedding_dim=4096, num_heads=8, num_blocks=32, vocab_size=50304,
                    global_batch=B, seq_len=S, decode_tokens=GEN)
-        return dict(step=step, e2e_step=e2e_step, units=B * (S + GEN), unit="tokens/s", metric="xlstm7b_prefill_decode_tokens_per_s",
+        return dict(step=step, e2e_step=e2e_step, teardown=model.release_graph, units=B * (S + GEN), unit="tokens/s", metric="xlstm7b_prefill_decode_tokens_per_s",
                     workload="xlstm7b_prefill8x8192_decode512", cfg=cfg, bytes=32 * (chunkwise_bytes(B, 8 // world, S, 256, 512)),
                     flops=0, kernel="mlstm_chunkwise_kernel<256> (32 launches per step)", h2d=tok_host.numel() * 8, d2h=out_host.numel() * 8,
                     l2="weights (13.7 GB) and activations exceed the 126 MB L2", launches=32 + 32 * GEN, scaling="strong",
@@ -328,7 +328,9 @@ def main():
     e2e_ms, e2e_steps = float("nan"), 0
     if not args.no_e2e:
         # the clock record needs a few hundred ms under load: keep the same step running, untimed, until it has samples
-        if rank == 0 and sampler.proc is not None:
+        # (not when the step holds collectives, as the tensor-parallel model step does: rank 0 alone would wait for
+        # its peers for ever -- and those steps run for seconds anyway, the record is long enough)
+        if rank == 0 and sampler.proc is not None and case.get("parallelism") != "tp":
             t_end = time.time() + 3.0
             base = sampler.count()
             while sampler.count() < base + 8 and time.time() < t_end:
@@ -384,7 +386,10 @@ def main():
             dt = cpu_chunkwise_seconds(threads)
             line["cpu_baseline"] = {"value": CFG["S"] / dt, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": CPU_SAMPLE}
         print(json.dumps(line))
+    if case.get("teardown"):
+        case["teardown"]()   # a live CUDA graph with NCCL kernels keeps the communicator from shutting down
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

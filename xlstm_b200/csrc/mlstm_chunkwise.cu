@@ -84,9 +84,6 @@ enum GateSlot {
   G_CB = G_MULT + 3,     // scale of the bf16 copy of T
   G_QN = G_MULT + 4,     // scale of the normaliser product
 };
-#ifndef XL_ABL
-#define XL_ABL 0  // timing experiments: skip one phase (wrong results); 0 = product
-#endif
 
 enum CwWarp { W_GATE_GROUP = 0, W_STATE_GROUP = 4, W_EPI_GROUP = 8, W_UMMA = 12, W_TMA = 13, W_SCAN = 14, W_SEND = 15 };
 
@@ -539,7 +536,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         CW_WAIT(BAR_HC, par ^ 1u);  // T holds chunk-1; its UMMAs no longer read the bf16 copy or the P tile
         tc_fence_after();
         CW_TL(0, 10);
-        if (!(XL_ABL & 1)) convert_T(CB_SPLIT, DHQK / 64, cb_scale, mult);
+        convert_T(CB_SPLIT, DHQK / 64, cb_scale, mult);
         CW_TL(0, 11);
         tc_fence_before();
       }
@@ -556,7 +553,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       float rs[4] = {0.f, 0.f, 0.f, 0.f};
       unsigned char* prow = smem + LY::OFF_P + j * 128;
 #pragma unroll 1
-      for (int q = 0; q < ((XL_ABL & 2) ? 0 : 4); ++q) {
+      for (int q = 0; q < 4; ++q) {
         uint4 o0 = make_uint4(0u, 0u, 0u, 0u), o1 = o0;
         if (q <= warp) {  // warp-uniform
           uint32_t sv[16];
@@ -693,7 +690,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       tc_fence_after();
       // ---- T -> bf16 copy, this group's blocks (all of them for the first chunk: the gate group has not yet seen
       // the initial state land in tensor memory)
-      if (!(XL_ABL & 1)) convert_T(0, chunk == 0 ? DHQK / 64 : CB_SPLIT, cb_scale, mult);
+      convert_T(0, chunk == 0 ? DHQK / 64 : CB_SPLIT, cb_scale, mult);
       tc_fence_before();
       mbar_arrive(bar0 + 8u * BAR_A);
       if (!exact) mbar_arrive(bar0 + 8u * BAR_A);  // common frame: q is used as loaded
@@ -712,7 +709,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
           v[i] = *reinterpret_cast<const uint4*>(vt + off[i]);
         }
 #pragma unroll
-        for (int i = 0; i < ((XL_ABL & 16) ? 0 : 8); ++i) *reinterpret_cast<uint4*>(smem + LY::OFF_VH + off[i]) = scale_bf16x8(v[i], ww);
+        for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(smem + LY::OFF_VH + off[i]) = scale_bf16x8(v[i], ww);
       }
       fence_proxy_async_smem();
       mbar_arrive(bar0 + 8u * BAR_B);
@@ -804,7 +801,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       // drain, normalise and stage in two rolled passes of 32 tokens (small code)
       unsigned char* col = hst + dv * 2;
 #pragma unroll 1
-      for (int q = 0; q < ((XL_ABL & 4) ? 0 : 2); ++q) {
+      for (int q = 0; q < 2; ++q) {
         uint32_t hv[32];
         tmem_ld_x32(tH + 32 * q, hv);
         float4 iv[8];
@@ -829,7 +826,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       epilogue_group_sync();
       __nv_bfloat16* ho = hbase + (long long)chunk * CW_L * p.h_st;
 #pragma unroll 2
-      for (int i = 0; i < ((XL_ABL & 4) ? 0 : 8); ++i) {
+      for (int i = 0; i < 8; ++i) {
         const int idx = i * 128 + t, row = idx >> 4, c = idx & 15;
         if (row < len_c)
           *reinterpret_cast<uint4*>(ho + (long long)row * p.h_st + c * 8) = *reinterpret_cast<const uint4*>(hst + row * LY::HST_ROW + c * 16);
@@ -891,12 +888,10 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
           const int ks = 4 * kb + kk;
           // nu step (token slice, feature block) = (ks / NB, ks % NB): 4 x NB steps, like q.n
           const int tsl = ks / NB, gq = ks % NB;
-          if (!(XL_ABL & 32) || kk == 0) {
-            umma_ss_lo(t_odd + 8 + 8 * gq, (LBO_MN + ((kblk + gq * CW_BOX_BYTES + tsl * 2048) >> 4)),
-                       (LBO_K + ((wm + tsl * 32) >> 4)), IDESC_NU, tsl != 0);
-            umma_ss_lo(t_odd, (LBO_K + ((qblk + kb * CW_BOX_BYTES + kk * 32) >> 4)),
-                       (LBO_K + ((nm + kb * 1024 + kk * 32) >> 4)), IDESC_DN, ks != 0);
-          }
+          umma_ss_lo(t_odd + 8 + 8 * gq, (LBO_MN + ((kblk + gq * CW_BOX_BYTES + tsl * 2048) >> 4)),
+                     (LBO_K + ((wm + tsl * 32) >> 4)), IDESC_NU, tsl != 0);
+          umma_ss_lo(t_odd, (LBO_K + ((qblk + kb * CW_BOX_BYTES + kk * 32) >> 4)),
+                     (LBO_K + ((nm + kb * 1024 + kk * 32) >> 4)), IDESC_DN, ks != 0);
         }
       }
       umma_commit_elect(bar_u + 8u * BAR_NU);
@@ -973,7 +968,6 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         const uint32_t bar = bar0 + 8u * (BAR_FULL0 + st);
         const uint32_t dst = sbase + LY::OFF_STAGE + st * LY::STAGE_BYTES;
         const int tk = (int)(tok0 + (long long)chunk * CW_L);
-        if ((XL_ABL & 8) && chunk >= 2) { mbar_arrive(bar); continue; }
         mbar_expect_tx(bar, LY::STAGE_BYTES);
         int cq[4], ck[4], cv[4];
         cq[maps.pos[0][0]] = tk; cq[maps.pos[0][1]] = head; cq[maps.pos[0][2]] = b;

@@ -232,6 +232,15 @@ class LargeModel:
                 dst.copy_(src)
         self._graph, self._graph_batch = graph, batch
 
+    def release_graph(self):
+        """Drop the captured decode graph and its static buffers.  With tensor parallelism call this before the process
+        group is destroyed: a live graph that holds NCCL kernels keeps the communicator from shutting down."""
+        self._graph = None
+        self._g_state = None
+        self._g_tok = None
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+
     @torch.no_grad()
     def generate(self, prefill_tokens, max_length: int, state=None, use_cuda_graph: bool = False):
         """Greedy decoding as ``generate_tokens`` does it (``generate.py:79-85``): the first iteration consumes the
