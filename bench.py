@@ -266,8 +266,12 @@ def build_case(name, dev, rank):
         cfg = dict(model="xLSTM-7B-shaped (random init)", embedding_dim=4096, num_heads=8, num_blocks=32, vocab_size=50304,
                    global_batch=B, seq_len=S, decode_tokens=GEN)
         return dict(step=step, e2e_step=e2e_step, teardown=model.release_graph, units=B * (S + GEN), unit="tokens/s", metric="xlstm7b_prefill_decode_tokens_per_s",
-                    workload="xlstm7b_prefill8x8192_decode512", cfg=cfg, bytes=32 * (chunkwise_bytes(B, 8 // world, S, 256, 512)),
-                    flops=0, kernel="mlstm_chunkwise_kernel<256> (32 launches per step)", h2d=tok_host.numel() * 8, d2h=out_host.numel() * 8,
+                    workload="xlstm7b_prefill8x8192_decode512", cfg=cfg,
+                    # algorithmic bytes of one step per rank: the weights once per decoded token (and once for the prefill)
+                    # plus the cell's prefill traffic; the decode loop is what the time goes to
+                    bytes=(GEN + 1) * sum(t.numel() * t.element_size() for t in model.parameters_on_device() if t is not model.embedding)
+                    + 32 * chunkwise_bytes(B, 8 // world, S, 256, 512),
+                    flops=0, kernel="whole step: prefill (32 chunkwise launches + library GEMMs) and 512 graph replays", h2d=tok_host.numel() * 8, d2h=out_host.numel() * 8,
                     l2="weights (13.7 GB) and activations exceed the 126 MB L2", launches=32 + 32 * GEN, scaling="strong",
                     parallelism="tp", heavy=True)
     raise SystemExit(f"unknown case {name}")

@@ -232,6 +232,13 @@ class LargeModel:
                 dst.copy_(src)
         self._graph, self._graph_batch = graph, batch
 
+    def parameters_on_device(self):
+        """Every weight tensor this rank holds (its share under tensor parallelism)."""
+        out = [self.embedding, self.out_norm, self.lm_head]
+        for blk in self.blocks:
+            out += [v for v in blk.values() if isinstance(v, torch.Tensor)]
+        return out
+
     def release_graph(self):
         """Drop the captured decode graph and its static buffers.  With tensor parallelism call this before the process
         group is destroyed: a live graph that holds NCCL kernels keeps the communicator from shutting down."""
