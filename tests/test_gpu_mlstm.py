@@ -241,3 +241,21 @@ def test_chunkwise_full_size_config2_properties():
     h2, st2 = xlstm_b200.mlstm_sequence(q[:1, :, half:], k[:1, :, half:], v[:1, :, half:], i[:1, :, half:], f[:1, :, half:], *st1, kernel="chunkwise")
     assert rel_l2(torch.cat([h1, h2], 2).float(), h[:1].float()) < TOL_BF16
     assert rel_l2(st2[0], c[:1]) < TOL_BF16
+
+
+def test_prefill_from_pinned_host_buffers_equals_device_call():
+    """The host-buffer entry (pieces over three streams, uploads / kernels / downloads overlapped) returns what the
+    device-resident call returns."""
+    import xlstm_b200
+    B, NH, S, DQ, DV = 3, 4, 200, 64, 128
+    q, k, v, i, f = _inputs(41, B, NH, S, DQ, DV, torch.bfloat16)
+    host = [t.pin_memory() for t in (q, k, v, i, f)]
+    h_host = torch.empty(B, NH, S, DV, dtype=torch.bfloat16).pin_memory()
+    c_host = torch.empty(B, NH, DQ, DV).pin_memory()
+    n_host = torch.empty(B, NH, DQ).pin_memory()
+    m_host = torch.empty(B, NH, 1).pin_memory()
+    xlstm_b200.mlstm_sequence_from_host(*host, h_host, c_host, n_host, m_host)
+    torch.cuda.synchronize()
+    h, (c, n, m) = xlstm_b200.mlstm_sequence(*_cuda(q, k, v, i, f), kernel="chunkwise")
+    assert torch.equal(h_host, h.cpu()) and torch.equal(c_host, c.cpu())
+    assert torch.equal(n_host, n.cpu()) and torch.equal(m_host, m.cpu())

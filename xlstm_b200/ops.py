@@ -143,6 +143,53 @@ def mlstm_sequence(q, k, v, i, f, c_initial=None, n_initial=None, m_initial=None
     return h, (c, n, m)
 
 
+_host_streams: dict[int, list] = {}
+
+
+def mlstm_sequence_from_host(q, k, v, i, f, h_out, c_out, n_out=None, m_out=None, device=None, head_groups: int = 2,
+                             eps: float = 1e-6):
+    """Prefill whose inputs and outputs live in pinned HOST memory: q, k ``(B,NH,S,DHQK)``, v ``(B,NH,S,DHV)``, gates
+    ``(B,NH,S)`` in, ``h_out (B,NH,S,DHV)``, ``c_out (B,NH,DHQK,DHV)`` (optionally n, m) out, zero initial state.
+
+    Heads and batch rows are independent, so the call is cut into ``B x head_groups`` contiguous pieces that go round
+    three streams: the upload of one piece overlaps the kernel and the download of the pieces before it (the link is
+    full duplex), and the whole call takes about as long as its uploads alone.  Returns when everything is enqueued;
+    the caller's current stream waits for the last piece."""
+    dev = torch.device(device if device is not None else "cuda")
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    dev = torch.device("cuda", idx)
+    B, NH = q.shape[0], q.shape[1]
+    if NH % head_groups:
+        raise ValueError(f"num_heads={NH} is not divisible by head_groups={head_groups}")
+    for t in (q, k, v, i, f, h_out, c_out):
+        if t.device.type != "cpu" or not t.is_pinned():
+            raise ValueError("mlstm_sequence_from_host wants pinned host tensors")
+    streams = _host_streams.setdefault(idx, [torch.cuda.Stream(device=dev) for _ in range(3)])
+    cur = torch.cuda.current_stream(dev)
+    for st in streams:
+        st.wait_stream(cur)
+    hg = NH // head_groups
+    piece = 0
+    for b in range(B):
+        for g in range(head_groups):
+            sl = (slice(b, b + 1), slice(g * hg, (g + 1) * hg))
+            st = streams[piece % len(streams)]
+            piece += 1
+            with torch.cuda.stream(st):
+                dq, dk, dv, di, df = [t[sl].to(dev, non_blocking=True) for t in (q, k, v, i, f)]
+                h, (c, n, m) = mlstm_sequence(dq, dk, dv, di, df, kernel="chunkwise", eps=eps)
+                h_out[sl].copy_(h, non_blocking=True)
+                c_out[sl].copy_(c, non_blocking=True)
+                if n_out is not None:
+                    n_out[sl].copy_(n, non_blocking=True)
+                if m_out is not None:
+                    m_out[sl].copy_(m, non_blocking=True)
+                for t in (dq, dk, dv, di, df, h, c, n, m):
+                    t.record_stream(st)
+    for st in streams:
+        cur.wait_stream(st)
+
+
 def mlstm_step(q, k, v, i, f, c, n, m, slot=None, eps: float = 1e-6, inplace: bool = True):
     """One decode step.  q,k (B,NH,DHQK), v (B,NH,DHV), i,f (B,NH[,1]); state pool c (N,NH,DHQK,DHV),
     n (N,NH,DHQK), m (N,NH[,1]) fp32; ``slot`` (B,) int32 selects each stream's pool row (default: row b).
