@@ -235,6 +235,34 @@ def build_case(name, dev, rank):
                     kernel="slstm_forward_kernel<256>", h2d=wx_h.numel() * 2, d2h=o_host.numel() * 2,
                     l2="inputs (%d MB) exceed the 126 MB L2" % (slstm_bytes(**cfg) // 10 ** 6), launches=1,
                     traffic=323.9e6)  # profiles/slstm_forward_config3.md
+    if name == "layer_ops":
+        # the two fused operators next to the cell, at the 7B layer's prefill shapes (8 x 8192 tokens, D = 4096)
+        B, S, NH, DH = 8, 8192, 8, 512
+        D = NH * DH
+        g = torch.Generator(device=dev).manual_seed(7 + rank)
+        x = torch.randn(B, S, D, device=dev, generator=g).bfloat16()
+        y = torch.randn(B, S, D, device=dev, generator=g).bfloat16()
+        h = torch.randn(B, NH, S, DH, device=dev, generator=g).bfloat16()
+        o = torch.randn(B, S, D, device=dev, generator=g).bfloat16()
+        w = torch.ones(D, device=dev).bfloat16()
+        x_host = x[:1].cpu().pin_memory()
+        out_host = torch.empty(1, S, D, dtype=torch.bfloat16).pin_memory()
+
+        def step():
+            xlstm_b200.add_rmsnorm(x, w, y)
+            return xlstm_b200.headnorm_gate(h, o, w)
+
+        def e2e_step():
+            xd = x_host.to(dev, non_blocking=True)
+            out_host.copy_(xlstm_b200.add_rmsnorm(xd, w)[1], non_blocking=True)
+
+        cfg = dict(B=B, S=S, NH=NH, DH=DH, D=D)
+        # add+norm reads x, y and writes x_new, normed; norm+gate reads h, o and writes out (the weights stay in L2)
+        return dict(step=step, e2e_step=e2e_step, units=B * S, unit="tokens/s", metric="layer_adjacent_ops_tokens_per_s",
+                    workload="xlstm7b_layer_add_rmsnorm_plus_headnorm_gate", cfg=cfg, bytes=7 * B * S * D * 2, flops=0,
+                    kernel="add_rmsnorm_kernel<bf16> + headnorm_gate_kernel<bf16>", h2d=x_host.numel() * 2,
+                    d2h=out_host.numel() * 2, l2="operands (7 x 537 MB per step) exceed the 126 MB L2", launches=2,
+                    traffic=None)
     if name == "model7b":
         # BASELINE config 4: xLSTM-7B-shaped model, random-init bf16, prefill 8 x 8192 tokens then 512 greedy tokens.
         # Heads are tensor-parallel over the ranks (strong scaling): dense layers are library GEMMs, the cell is ours.
@@ -243,7 +271,8 @@ def build_case(name, dev, rank):
         world = dist.get_world_size() if dist.is_initialized() else 1
         mcfg = LargeConfig(embedding_dim=4096, num_heads=8, num_blocks=32, vocab_size=50304)
         sd = procedural_state_dict(mcfg, seed=0, dtype=torch.bfloat16, device=dev, gen_device=dev)
-        model = LargeModel(mcfg, sd, dev, torch.bfloat16, tp_rank=rank if world > 1 else 0, tp_world=world)
+        model = LargeModel(mcfg, sd, dev, torch.bfloat16, tp_rank=rank if world > 1 else 0, tp_world=world,
+                           fused_adjacent=os.environ.get("XL_FUSED_ADJACENT", "1") != "0")
         del sd
         torch.cuda.empty_cache()
         B, S, GEN = 8, 8192, 512
@@ -280,7 +309,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--case", default="chunkwise", choices=["chunkwise", "chunkwise_b1", "step", "slstm", "model7b"])
+    ap.add_argument("--case", default="chunkwise", choices=["chunkwise", "chunkwise_b1", "step", "slstm", "layer_ops", "model7b"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="profiling runs: device-resident loop only")
     args = ap.parse_args()

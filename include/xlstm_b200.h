@@ -137,6 +137,48 @@ typedef struct xl_slstm_params {
 /* Requires DH in {64,128,256} and B <= 32. */
 int xl_slstm_forward(const xl_slstm_params* p, void* cuda_stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Operators next to the mLSTM cell in the reference's layer (xlstm/xlstm_large/model.py:379-452), each one pass
+ * over its data.  Rounding follows the reference's eager sequence: reductions in fp32, the normalised value is
+ * rounded to `dtype`, multiplied by the weight and rounded again (components.py:58-63, 86-97, 171-185); the gate is rounded after
+ * the sigmoid and after the product (model.py:445-449).
+ * ---------------------------------------------------------------------------------------------- */
+
+/* x_out = x + y (rounded to dtype; skipped when y is NULL), normed = RMSNorm(x_out) * weight.
+ * Replaces `x = x + block_out` followed by RMSNorm.forward (components.py:70-97; model.py:499-510). */
+typedef struct xl_add_rmsnorm_params {
+  const void* x;       /* (rows, D), row stride x_sr elements */
+  const void* y;       /* (rows, D) contiguous rows with stride y_sr, or NULL */
+  const void* weight;  /* (D) */
+  void* x_out;         /* (rows, D) stride xo_sr; may alias x; NULL allowed when y is NULL */
+  void* normed;        /* (rows, D) stride n_sr */
+  int64_t rows; int32_t D;
+  int64_t x_sr, y_sr, xo_sr, n_sr;
+  float eps;
+  int32_t dtype;
+} xl_add_rmsnorm_params;
+
+/* Requires D a multiple of the 16-byte vector (8 bf16 / 4 fp32) and D <= 8192 (bf16) / 4096 (fp32). */
+int xl_add_rmsnorm(const xl_add_rmsnorm_params* p, void* cuda_stream);
+
+/* out[b, s, head*DH + d] = sigmoid(o[b, s, head*DH + d]) * (LayerNorm_d(h[b, head, s, :]) * weight[head*DH + d]).
+ * Replaces MultiHeadLayerNorm.forward on the transposed cell output (components.py:188-242; model.py:435-444) and the
+ * output gate (model.py:445-449); h is read through its strides, so the cell's (B, NH, S, DH) output needs no
+ * transpose copy. */
+typedef struct xl_headnorm_gate_params {
+  const void* h;       /* (B, NH, S, DH) through h_sb, h_sh, h_st (elements); DH contiguous */
+  const void* o;       /* gate pre-activations (B, S, NH*DH) through o_sb, o_st; NH*DH contiguous */
+  const void* weight;  /* (NH*DH) */
+  void* out;           /* (B, S, NH*DH) contiguous */
+  int32_t B, NH, S, DH;
+  int64_t h_sb, h_sh, h_st, o_sb, o_st;
+  float eps;
+  int32_t dtype;
+} xl_headnorm_gate_params;
+
+/* Requires DH a multiple of the 16-byte vector and DH <= 1024 (bf16) / 512 (fp32). */
+int xl_headnorm_gate(const xl_headnorm_gate_params* p, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

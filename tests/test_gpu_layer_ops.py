@@ -1,0 +1,96 @@
+"""Parity of the cell-adjacent kernels (through the C ABI) with the CPU oracle and the reference-module fixtures.
+
+Tolerances: the kernels round where the reference's eager operators round, so bf16 results may differ from the
+oracle only where the fp32 reduction order moves a value across a rounding boundary: at most one bf16 step
+(relative 2^-7) on under 1 % of the elements.  fp32 results agree to 2e-6 relative to the row scale."""
+import pytest
+import torch
+
+from conftest import load_golden
+from oracle import layer_ops as O
+
+pytestmark = pytest.mark.gpu
+DT = {"f32": torch.float32, "bf16": torch.bfloat16}
+
+
+def _close(got, want, dt):
+    got, want = got.float().cpu(), want.float().cpu()
+    diff = (got - want).abs()
+    if dt == torch.bfloat16:
+        assert (diff <= want.abs() * 2.0 ** -7 + 1e-30).all(), float(diff.max())
+        assert (diff == 0).float().mean().item() > 0.99
+    else:
+        assert float(diff.max()) <= 2e-6 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("tag", ["f32", "bf16"])
+def test_kernels_match_reference_module_fixtures(tag):
+    import xlstm_b200
+    g, dt = load_golden("layer_ops"), DT[tag]
+    x, y, w = (g[f"rms_{tag}_{k}"].to(dt).cuda() for k in ("x", "y", "w"))
+    x_new, normed = xlstm_b200.add_rmsnorm(x, w, y, eps=1e-6)
+    assert torch.equal(x_new.float().cpu(), g[f"rms_{tag}_xnew"])
+    _close(normed, g[f"rms_{tag}_normed"], dt)
+    h, o, w2 = (g[f"hng_{tag}_{k}"].to(dt).cuda() for k in ("h", "o", "w"))
+    _close(xlstm_b200.headnorm_gate(h, o, w2, eps=1e-6), g[f"hng_{tag}_out"], dt)
+
+
+@pytest.mark.parametrize("tag,rows,D", [("bf16", 37, 4096), ("bf16", 5, 8192), ("bf16", 64, 512), ("f32", 9, 512),
+                                        ("f32", 3, 4096), ("bf16", 1, 8)])
+@pytest.mark.parametrize("residual", [False, True])
+def test_add_rmsnorm_matches_oracle(tag, rows, D, residual):
+    import xlstm_b200
+    dt = DT[tag]
+    g = torch.Generator().manual_seed(rows * 131 + D)
+    x = (3.0 * torch.randn(rows, D, generator=g)).to(dt)
+    y = torch.randn(rows, D, generator=g).to(dt) if residual else None
+    w = (1.0 + 0.2 * torch.randn(D, generator=g)).to(dt)
+    want_x, want_n = O.add_rmsnorm(x, w, y, eps=1e-6)
+    got_x, got_n = xlstm_b200.add_rmsnorm(x.cuda(), w.cuda(), None if y is None else y.cuda(), eps=1e-6)
+    assert torch.equal(got_x.cpu(), want_x)
+    _close(got_n, want_n, dt)
+
+
+def test_add_rmsnorm_in_place_and_batched_shape():
+    import xlstm_b200
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(2, 7, 1024, generator=g).bfloat16()
+    y = torch.randn(2, 7, 1024, generator=g).bfloat16()
+    w = torch.ones(1024).bfloat16()
+    want_x, want_n = O.add_rmsnorm(x, w, y)
+    xd = x.cuda()
+    got_x, got_n = xlstm_b200.add_rmsnorm(xd, w.cuda(), y.cuda(), inplace=True)
+    assert got_x.data_ptr() == xd.data_ptr() and got_n.shape == x.shape
+    assert torch.equal(xd.cpu(), want_x)
+    _close(got_n, want_n, torch.bfloat16)
+
+
+@pytest.mark.parametrize("tag,B,NH,S,DH", [("bf16", 2, 8, 33, 512), ("bf16", 1, 4, 1, 512), ("f32", 3, 4, 17, 128),
+                                           ("bf16", 2, 2, 5, 1024), ("f32", 1, 2, 3, 512), ("bf16", 1, 3, 7, 64)])
+def test_headnorm_gate_matches_oracle_on_strided_views(tag, B, NH, S, DH):
+    import xlstm_b200
+    dt = DT[tag]
+    g = torch.Generator().manual_seed(B * 1000 + S * 10 + NH)
+    h = (2.0 * torch.randn(B, NH, S, DH, generator=g) + 0.3).to(dt)
+    wide = (2.0 * torch.randn(B, S, 3 * NH * DH, generator=g)).to(dt)   # the gate is a column slice of a wider projection
+    w = (1.0 + 0.2 * torch.randn(NH * DH, generator=g)).to(dt)
+    o = wide[..., 2 * NH * DH:]
+    want = O.headnorm_gate(h, o, w, eps=1e-6)
+    got = xlstm_b200.headnorm_gate(h.cuda(), wide.cuda()[..., 2 * NH * DH:], w.cuda(), eps=1e-6)
+    _close(got, want, dt)
+    # the same values through a token-major buffer viewed as (B, NH, S, DH), as the decode step produces them
+    hs = h.transpose(1, 2).contiguous().cuda().transpose(1, 2)
+    _close(xlstm_b200.headnorm_gate(hs, o.cuda(), w.cuda(), eps=1e-6), want, dt)
+
+
+def test_unsupported_widths_are_refused_before_launch():
+    import xlstm_b200
+    from xlstm_b200._lib import XlError
+    with pytest.raises(XlError):
+        xlstm_b200.add_rmsnorm(torch.zeros(2, 12, device="cuda", dtype=torch.bfloat16), torch.ones(12, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(XlError):
+        xlstm_b200.add_rmsnorm(torch.zeros(2, 16384, device="cuda", dtype=torch.bfloat16), torch.ones(16384, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(XlError):
+        xlstm_b200.headnorm_gate(torch.zeros(1, 1, 1, 2048, device="cuda", dtype=torch.bfloat16),
+                                 torch.zeros(1, 1, 2048, device="cuda", dtype=torch.bfloat16),
+                                 torch.ones(2048, device="cuda", dtype=torch.bfloat16))

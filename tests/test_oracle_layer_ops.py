@@ -1,0 +1,35 @@
+"""The CPU oracle of the cell-adjacent operators against fixtures produced by the reference's own norm modules."""
+import pytest
+import torch
+
+from conftest import load_golden
+from oracle import layer_ops as O
+
+DT = {"f32": torch.float32, "bf16": torch.bfloat16}
+
+
+@pytest.mark.parametrize("tag", ["f32", "bf16"])
+def test_add_rmsnorm_matches_reference_modules(tag):
+    g, dt = load_golden("layer_ops"), DT[tag]
+    x, y, w = (g[f"rms_{tag}_{k}"].to(dt) for k in ("x", "y", "w"))
+    x_new, normed = O.add_rmsnorm(x, w, y, eps=1e-6)
+    # the same rounding points as the eager reference: bit-exact in bf16, reduction order only in fp32
+    assert torch.equal(x_new.float(), g[f"rms_{tag}_xnew"])
+    tol = 0.0 if tag == "bf16" else 1e-6
+    assert (normed.float() - g[f"rms_{tag}_normed"]).abs().max().item() <= tol
+
+
+@pytest.mark.parametrize("tag", ["f32", "bf16"])
+def test_headnorm_gate_matches_reference_modules(tag):
+    g, dt = load_golden("layer_ops"), DT[tag]
+    h, o, w = (g[f"hng_{tag}_{k}"].to(dt) for k in ("h", "o", "w"))
+    out = O.headnorm_gate(h, o, w, eps=1e-6)
+    tol = 0.0 if tag == "bf16" else 1e-6
+    assert (out.float() - g[f"hng_{tag}_out"]).abs().max().item() <= tol
+
+
+def test_add_rmsnorm_without_residual_returns_input():
+    x = torch.randn(3, 64)
+    x_new, normed = O.add_rmsnorm(x, torch.ones(64))
+    assert x_new is x
+    assert torch.allclose(normed.pow(2).mean(-1), torch.ones(3), atol=1e-4)

@@ -16,6 +16,7 @@ XL_F32, XL_BF16 = 0, 1
 EXPORTS = (
     "xl_strerror", "xl_last_cuda_error", "xl_abi_version",
     "xl_mlstm_chunkwise", "xl_mlstm_recurrent", "xl_mlstm_step", "xl_slstm_forward",
+    "xl_add_rmsnorm", "xl_headnorm_gate",
 )
 
 
@@ -61,6 +62,24 @@ class SlstmParams(C.Structure):
     ]
 
 
+class AddRmsnormParams(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("y", C.c_void_p), ("weight", C.c_void_p), ("x_out", C.c_void_p), ("normed", C.c_void_p),
+        ("rows", C.c_int64), ("D", C.c_int32),
+        ("x_sr", C.c_int64), ("y_sr", C.c_int64), ("xo_sr", C.c_int64), ("n_sr", C.c_int64),
+        ("eps", C.c_float), ("dtype", C.c_int32),
+    ]
+
+
+class HeadnormGateParams(C.Structure):
+    _fields_ = [
+        ("h", C.c_void_p), ("o", C.c_void_p), ("weight", C.c_void_p), ("out", C.c_void_p),
+        ("B", C.c_int32), ("NH", C.c_int32), ("S", C.c_int32), ("DH", C.c_int32),
+        ("h_sb", C.c_int64), ("h_sh", C.c_int64), ("h_st", C.c_int64), ("o_sb", C.c_int64), ("o_st", C.c_int64),
+        ("eps", C.c_float), ("dtype", C.c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -78,7 +97,8 @@ def lib() -> C.CDLL:
         l.xl_last_cuda_error.restype = C.c_char_p
         l.xl_abi_version.restype = C.c_int
         for name, ptype in (("xl_mlstm_chunkwise", MlstmSeqParams), ("xl_mlstm_recurrent", MlstmSeqParams),
-                            ("xl_mlstm_step", MlstmStepParams), ("xl_slstm_forward", SlstmParams)):
+                            ("xl_mlstm_step", MlstmStepParams), ("xl_slstm_forward", SlstmParams),
+                            ("xl_add_rmsnorm", AddRmsnormParams), ("xl_headnorm_gate", HeadnormGateParams)):
             fn = getattr(l, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(ptype), C.c_void_p]

@@ -1,0 +1,205 @@
+// Operators next to the mLSTM cell in the reference's layer, each fused into one pass over its data:
+//   xl_add_rmsnorm    residual add + RMSNorm                      (xlstm/xlstm_large/model.py:499-510, components.py:70-97)
+//   xl_headnorm_gate  per-head LayerNorm of the cell output read through its (B,NH,S,DH) strides, weight, output gate
+//                     (xlstm/xlstm_large/model.py:435-449, components.py:171-242)
+// Both are bound by HBM traffic: every element is read once with 16-byte loads, kept in registers across the
+// reduction, and written once.  Rounding points are those of the reference's eager operator sequence (fp32
+// reductions; the normalised value rounded to the model dtype, then the weight product rounded, then the gate).
+#include "common.cuh"
+
+namespace xl {
+
+constexpr int ADJ_MAXC = 4;  // 16-byte vectors per thread
+
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  float v[4];
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __nv_bfloat16 v[8];
+};
+
+template <typename T>
+__device__ __forceinline__ Vec16<T> load16(const T* p) {
+  Vec16<T> r;
+  *reinterpret_cast<uint4*>(r.v) = *reinterpret_cast<const uint4*>(p);
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ void store16(T* p, const Vec16<T>& r) {
+  *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(r.v);
+}
+
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// residual add + RMSNorm: one CTA of 256 threads per row
+// ------------------------------------------------------------------------------------------------------------
+constexpr int RMS_THREADS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(RMS_THREADS) add_rmsnorm_kernel(const xl_add_rmsnorm_params p) {
+  constexpr int V = Vec16<T>::N;
+  __shared__ float s_part[RMS_THREADS / 32];
+  const long long row = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const T* x = static_cast<const T*>(p.x) + row * p.x_sr;
+  const T* y = p.y ? static_cast<const T*>(p.y) + row * p.y_sr : nullptr;
+  const T* w = static_cast<const T*>(p.weight);
+  T* xo = p.x_out ? static_cast<T*>(p.x_out) + row * p.xo_sr : nullptr;
+  T* nd = static_cast<T*>(p.normed) + row * p.n_sr;
+
+  Vec16<T> xv[ADJ_MAXC];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < ADJ_MAXC; ++c) {
+    const int e = (c * RMS_THREADS + tid) * V;
+    if (e < p.D) {
+      xv[c] = load16(x + e);
+      if (y) {
+        const Vec16<T> yv = load16(y + e);
+#pragma unroll
+        for (int i = 0; i < V; ++i) xv[c].v[i] = from_float<T>(to_float(xv[c].v[i]) + to_float(yv.v[i]));
+        store16(xo + e, xv[c]);
+      }
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const float f = to_float(xv[c].v[i]);
+        ss = fmaf(f, f, ss);
+      }
+    }
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) s_part[warp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < RMS_THREADS / 32; ++i) tot += s_part[i];
+  const float r = rsqrtf(tot / (float)p.D + p.eps);
+#pragma unroll
+  for (int c = 0; c < ADJ_MAXC; ++c) {
+    const int e = (c * RMS_THREADS + tid) * V;
+    if (e < p.D) {
+      const Vec16<T> wv = load16(w + e);
+      Vec16<T> o;
+#pragma unroll
+      for (int i = 0; i < V; ++i)
+        o.v[i] = from_float<T>(to_float(from_float<T>(to_float(xv[c].v[i]) * r)) * to_float(wv.v[i]));
+      store16(nd + e, o);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// per-head LayerNorm + weight + output gate: one warp per (batch, token, head)
+// ------------------------------------------------------------------------------------------------------------
+constexpr int HNG_WARPS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(HNG_WARPS * 32) headnorm_gate_kernel(const xl_headnorm_gate_params p) {
+  constexpr int V = Vec16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * HNG_WARPS + (threadIdx.x >> 5);
+  const long long units = (long long)p.B * p.S * p.NH;
+  if (unit >= units) return;
+  const int head = (int)(unit % p.NH);
+  const long long bs = unit / p.NH;
+  const int s = (int)(bs % p.S), b = (int)(bs / p.S);
+  const T* h = static_cast<const T*>(p.h) + b * p.h_sb + head * p.h_sh + s * p.h_st;
+  const T* o = static_cast<const T*>(p.o) + b * p.o_sb + s * p.o_st + (long long)head * p.DH;
+  const T* w = static_cast<const T*>(p.weight) + (long long)head * p.DH;
+  T* out = static_cast<T*>(p.out) + (bs * p.NH + head) * p.DH;
+
+  Vec16<T> hv[ADJ_MAXC];
+  float sum = 0.f;
+#pragma unroll
+  for (int c = 0; c < ADJ_MAXC; ++c) {
+    const int e = (c * 32 + lane) * V;
+    if (e < p.DH) {
+      hv[c] = load16(h + e);
+#pragma unroll
+      for (int i = 0; i < V; ++i) sum += to_float(hv[c].v[i]);
+    }
+  }
+  const float mean = warp_sum(sum) / (float)p.DH;
+  float sq = 0.f;
+#pragma unroll
+  for (int c = 0; c < ADJ_MAXC; ++c) {
+    const int e = (c * 32 + lane) * V;
+    if (e < p.DH) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const float d = to_float(hv[c].v[i]) - mean;
+        sq = fmaf(d, d, sq);
+      }
+    }
+  }
+  const float r = rsqrtf(warp_sum(sq) / (float)p.DH + p.eps);
+#pragma unroll
+  for (int c = 0; c < ADJ_MAXC; ++c) {
+    const int e = (c * 32 + lane) * V;
+    if (e < p.DH) {
+      const Vec16<T> ov = load16(o + e), wv = load16(w + e);
+      Vec16<T> y;
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const T nrm = from_float<T>((to_float(hv[c].v[i]) - mean) * r);
+        const T nw = from_float<T>(to_float(nrm) * to_float(wv.v[i]));
+        const T g = from_float<T>(1.f / (1.f + expf(-to_float(ov.v[i]))));
+        y.v[i] = from_float<T>(to_float(g) * to_float(nw));
+      }
+      store16(out + e, y);
+    }
+  }
+}
+
+}  // namespace xl
+
+extern "C" int xl_add_rmsnorm(const xl_add_rmsnorm_params* p, void* cuda_stream) {
+  using namespace xl;
+  if (!p || !p->x || !p->weight || !p->normed) return XL_ERR_NULL_POINTER;
+  if (p->y && !p->x_out) return XL_ERR_NULL_POINTER;
+  if (p->dtype != XL_F32 && p->dtype != XL_BF16) return XL_ERR_BAD_DTYPE;
+  const int V = p->dtype == XL_F32 ? 4 : 8;
+  if (p->rows < 0 || p->D <= 0 || p->D % V != 0) return XL_ERR_BAD_SHAPE;
+  if (p->D > RMS_THREADS * ADJ_MAXC * V) return XL_ERR_TOO_LARGE;
+  if (p->rows > 0x7fffffffLL) return XL_ERR_TOO_LARGE;
+  if (p->x_sr % V || p->n_sr % V || (p->y && (p->y_sr % V || p->xo_sr % V))) return XL_ERR_BAD_STRIDE;
+  if (!aligned16(p->x) || !aligned16(p->weight) || !aligned16(p->normed) || (p->y && (!aligned16(p->y) || !aligned16(p->x_out))))
+    return XL_ERR_BAD_ALIGNMENT;
+  if (p->normed == p->x || (p->y && p->normed == p->x_out)) return XL_ERR_ALIASING;
+  if (p->rows == 0) return XL_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  if (p->dtype == XL_F32)
+    add_rmsnorm_kernel<float><<<(unsigned)p->rows, RMS_THREADS, 0, st>>>(*p);
+  else
+    add_rmsnorm_kernel<__nv_bfloat16><<<(unsigned)p->rows, RMS_THREADS, 0, st>>>(*p);
+  return check_launch("xl_add_rmsnorm");
+}
+
+extern "C" int xl_headnorm_gate(const xl_headnorm_gate_params* p, void* cuda_stream) {
+  using namespace xl;
+  if (!p || !p->h || !p->o || !p->weight || !p->out) return XL_ERR_NULL_POINTER;
+  if (p->dtype != XL_F32 && p->dtype != XL_BF16) return XL_ERR_BAD_DTYPE;
+  const int V = p->dtype == XL_F32 ? 4 : 8;
+  if (p->B <= 0 || p->NH <= 0 || p->S <= 0 || p->DH <= 0 || p->DH % V != 0) return XL_ERR_BAD_SHAPE;
+  if (p->DH > 32 * ADJ_MAXC * V) return XL_ERR_TOO_LARGE;
+  if (p->h_sb % V || p->h_sh % V || p->h_st % V || p->o_sb % V || p->o_st % V) return XL_ERR_BAD_STRIDE;
+  if (!aligned16(p->h) || !aligned16(p->o) || !aligned16(p->weight) || !aligned16(p->out)) return XL_ERR_BAD_ALIGNMENT;
+  if (p->out == p->h || p->out == p->o) return XL_ERR_ALIASING;
+  const long long units = (long long)p->B * p->S * p->NH;
+  const long long blocks = (units + HNG_WARPS - 1) / HNG_WARPS;
+  if (blocks > 0x7fffffffLL) return XL_ERR_TOO_LARGE;
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  if (p->dtype == XL_F32)
+    headnorm_gate_kernel<float><<<(unsigned)blocks, HNG_WARPS * 32, 0, st>>>(*p);
+  else
+    headnorm_gate_kernel<__nv_bfloat16><<<(unsigned)blocks, HNG_WARPS * 32, 0, st>>>(*p);
+  return check_launch("xl_headnorm_gate");
+}

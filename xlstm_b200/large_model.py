@@ -112,10 +112,12 @@ class LargeModel:
     the two partial sums per block are all-reduced over ``group``."""
 
     def __init__(self, cfg: LargeConfig, state_dict: dict, device, dtype=torch.bfloat16, tp_rank: int = 0,
-                 tp_world: int = 1, group=None, cell_ops=ops):
+                 tp_world: int = 1, group=None, cell_ops=ops, fused_adjacent: bool = True):
         # `cell_ops` provides mlstm_sequence / mlstm_step; the default is this package's CUDA kernels (the test
         # suite substitutes the CPU oracle to check the dense part of this mirror against the reference on a CPU)
         self.cell = cell_ops
+        # residual add + RMSNorm and per-head norm + output gate as single kernels of this package (CUDA only)
+        self.fused = bool(fused_adjacent) and torch.device(device).type == "cuda" and cell_ops is ops
         if cfg.num_heads % tp_world or cfg.ffn_dim % tp_world:
             raise ValueError("num_heads and the FFN width must be divisible by the tensor-parallel world size")
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
@@ -170,6 +172,9 @@ class LargeModel:
         else:
             c, n, m = state if state is not None else (None, None, None)
             h, new_state = self.cell.mlstm_sequence(q, k, v, ig, fg, c, n, m, cu_seqlens=cu_seqlens, eps=cfg.eps)
+        if self.fused:
+            hg = ops.headnorm_gate(h, o, blk["mh_norm"], eps=cfg.norm_eps)
+            return self._all_reduce(F.linear(hg, blk["out_proj"])), new_state
         h = h.transpose(1, 2)                            # (B,S,NHl,dv)
         hf = h.float()
         hn = (hf - hf.mean(-1, keepdim=True)) * torch.rsqrt(hf.var(-1, keepdim=True, unbiased=False) + cfg.norm_eps)
@@ -177,23 +182,33 @@ class LargeModel:
         y = F.linear(torch.sigmoid(o) * hn, blk["out_proj"])
         return self._all_reduce(y), new_state
 
+    def _add_norm(self, x, y, w):
+        """x + y (y may be None) and its RMSNorm, as the reference's block does with two operators (model.py:499-510)."""
+        if self.fused:
+            return ops.add_rmsnorm(x, w, y, eps=self.cfg.norm_eps, inplace=True)
+        if y is not None:
+            x = x + y
+        return x, _rms_norm(x, w, self.cfg.norm_eps)
+
     def forward(self, tokens, state: Optional[dict] = None, cu_seqlens=None, slot=None, last_only: bool = False):
         """tokens (B,S) int64 -> logits (B,S,V) (or (B,1,V) with ``last_only``) and the per-block state dict
         ``{i: (c,n,m)}`` exactly as ``xLSTMLarge.forward`` returns it (``model.py:126-153``)."""
         cfg = self.cfg
         x = self.embedding[tokens]
         new_state = {}
+        pending = None   # output of the previous sub-block, added to the residual stream by the next norm call
         for i, blk in enumerate(self.blocks):
-            y, st = self._mlstm_layer(blk, _rms_norm(x, blk["norm_mlstm"], cfg.norm_eps), None if state is None else state[i],
-                                      cu_seqlens, slot)
-            x = x + y
+            x, xn = self._add_norm(x, pending, blk["norm_mlstm"])
+            y, st = self._mlstm_layer(blk, xn, None if state is None else state[i], cu_seqlens, slot)
             new_state[i] = st
-            u = F.linear(_rms_norm(x, blk["norm_ffn"], cfg.norm_eps), blk["up"])
-            g, z = u.chunk(2, dim=-1)
-            x = x + self._all_reduce(F.linear(F.silu(g) * z, blk["down"]))
+            x, xn = self._add_norm(x, y, blk["norm_ffn"])
+            g, z = F.linear(xn, blk["up"]).chunk(2, dim=-1)
+            pending = self._all_reduce(F.linear(F.silu(g) * z, blk["down"]))
         if last_only:
             x = x[:, -1:]
-        logits = F.linear(_rms_norm(x, self.out_norm, cfg.norm_eps), self.lm_head)
+            pending = None if pending is None else pending[:, -1:]
+        x, xn = self._add_norm(x, pending, self.out_norm)
+        logits = F.linear(xn, self.lm_head)
         return _soft_cap(logits, cfg.output_logit_soft_cap), new_state
 
     # ------------------------------------------------------------------------------------------------

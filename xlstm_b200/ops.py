@@ -12,7 +12,8 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
-from ._lib import MlstmSeqParams, MlstmStepParams, SlstmParams, XL_BF16, XL_F32, check, lib
+from ._lib import (AddRmsnormParams, HeadnormGateParams, MlstmSeqParams, MlstmStepParams, SlstmParams, XL_BF16, XL_F32,
+                   check, lib)
 
 _DTYPES = {torch.float32: XL_F32, torch.bfloat16: XL_BF16}
 _status_words: dict[int, torch.Tensor] = {}
@@ -279,3 +280,67 @@ def slstm_forward(wx, R, bias, state0=None, cu_seqlens=None):
     with torch.cuda.device(dev):
         check(lib().xl_slstm_forward(C.byref(p), _stream_ptr(dev)), "xl_slstm_forward")
     return out, st
+
+
+def add_rmsnorm(x, weight, y=None, eps: float = 1e-6, inplace: bool = False):
+    """``x_new = x + y`` (when ``y`` is given) and ``RMSNorm(x_new) * weight`` in one pass; returns
+    ``(x_new, normed)``.  This is the residual add of one sub-block fused with the pre-norm of the next
+    (xlstm/xlstm_large/model.py:499-510; RMSNorm: components.py:70-97), with the reference's rounding points.
+    ``x`` is (..., D) with contiguous rows; ``inplace`` writes ``x_new`` over ``x``."""
+    _require_cuda(x, weight, y)
+    if x.dtype not in _DTYPES or weight.dtype != x.dtype or (y is not None and (y.dtype != x.dtype or y.shape != x.shape)):
+        raise ValueError("add_rmsnorm: x, y and weight must share one dtype (float32 or bfloat16) and x, y one shape")
+    D = x.shape[-1]
+    if weight.shape != (D,):
+        raise ValueError("add_rmsnorm: weight must have shape (D,)")
+    x2 = x.reshape(-1, D)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    y2 = None
+    if y is not None:
+        y2 = y.reshape(-1, D)
+        if y2.stride(-1) != 1:
+            y2 = y2.contiguous()
+    normed = torch.empty((x2.shape[0], D), dtype=x.dtype, device=x.device)
+    xo = None
+    if y2 is not None:
+        xo = x2 if (inplace and x2.data_ptr() == x.data_ptr()) else torch.empty((x2.shape[0], D), dtype=x.dtype, device=x.device)
+    p = AddRmsnormParams()
+    p.x, p.weight, p.normed = x2.data_ptr(), weight.contiguous().data_ptr(), normed.data_ptr()
+    p.y = y2.data_ptr() if y2 is not None else None
+    p.x_out = xo.data_ptr() if xo is not None else None
+    p.rows, p.D = x2.shape[0], D
+    p.x_sr, p.n_sr = x2.stride(0), D
+    p.y_sr = y2.stride(0) if y2 is not None else 0
+    p.xo_sr = xo.stride(0) if xo is not None else 0
+    p.eps, p.dtype = eps, _DTYPES[x.dtype]
+    with torch.cuda.device(x.device):
+        check(lib().xl_add_rmsnorm(C.byref(p), _stream_ptr(x.device)), "xl_add_rmsnorm")
+    x_new = x if xo is None else xo.reshape(x.shape)
+    return x_new, normed.reshape(x.shape)
+
+
+def headnorm_gate(h, o_preact, weight, eps: float = 1e-6):
+    """``sigmoid(o_preact) * (LayerNorm over DH of h, per head) * weight`` -> (B, S, NH*DH).
+
+    ``h`` is the cell output (B, NH, S, DH), read through its strides (no transpose copy); ``o_preact`` is
+    (B, S, NH*DH), possibly a column slice of a wider projection output.  Follows MultiHeadLayerNorm.forward
+    and the output gate of the reference layer (components.py:188-242, xlstm_large/model.py:445-449)."""
+    _require_cuda(h, o_preact, weight)
+    if h.dim() != 4 or h.dtype not in _DTYPES or o_preact.dtype != h.dtype or weight.dtype != h.dtype:
+        raise ValueError("headnorm_gate: h must be (B,NH,S,DH); h, o_preact and weight must share float32 or bfloat16")
+    B, NH, S, DH = h.shape
+    if o_preact.shape != (B, S, NH * DH) or weight.shape != (NH * DH,):
+        raise ValueError("headnorm_gate: o_preact must be (B,S,NH*DH) and weight (NH*DH,)")
+    h = _last_contig(h)
+    o = _last_contig(o_preact)
+    out = torch.empty((B, S, NH * DH), dtype=h.dtype, device=h.device)
+    p = HeadnormGateParams()
+    p.h, p.o, p.weight, p.out = h.data_ptr(), o.data_ptr(), weight.contiguous().data_ptr(), out.data_ptr()
+    p.B, p.NH, p.S, p.DH = B, NH, S, DH
+    p.h_sb, p.h_sh, p.h_st = h.stride()[:3]
+    p.o_sb, p.o_st = o.stride()[:2]
+    p.eps, p.dtype = eps, _DTYPES[h.dtype]
+    with torch.cuda.device(h.device):
+        check(lib().xl_headnorm_gate(C.byref(p), _stream_ptr(h.device)), "xl_headnorm_gate")
+    return out
