@@ -237,7 +237,7 @@ def build_case(name, dev, rank):
                     traffic=323.9e6)  # profiles/slstm_forward_config3.md
     if name == "layer_ops":
         # the two fused operators next to the cell, at the 7B layer's prefill shapes (8 x 8192 tokens, D = 4096)
-        B, S, NH, DH = 8, 8192, 8, 512
+        B, S, NH, DH = int(os.environ.get("XL_LAYER_OPS_B", "8")), 8192, 8, 512   # (a smaller B for profiler captures)
         D = NH * DH
         g = torch.Generator(device=dev).manual_seed(7 + rank)
         x = torch.randn(B, S, D, device=dev, generator=g).bfloat16()
@@ -245,23 +245,24 @@ def build_case(name, dev, rank):
         h = torch.randn(B, NH, S, DH, device=dev, generator=g).bfloat16()
         o = torch.randn(B, S, D, device=dev, generator=g).bfloat16()
         w = torch.ones(D, device=dev).bfloat16()
-        x_host = x[:1].cpu().pin_memory()
-        out_host = torch.empty(1, S, D, dtype=torch.bfloat16).pin_memory()
+        host = [t.cpu().pin_memory() for t in (x, y, h, o)]
+        out_host = [torch.empty(B, S, D, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
 
         def step():
             xlstm_b200.add_rmsnorm(x, w, y)
             return xlstm_b200.headnorm_gate(h, o, w)
 
         def e2e_step():
-            xd = x_host.to(dev, non_blocking=True)
-            out_host.copy_(xlstm_b200.add_rmsnorm(xd, w)[1], non_blocking=True)
+            xd, yd, hd, od = [t.to(dev, non_blocking=True) for t in host]
+            out_host[0].copy_(xlstm_b200.add_rmsnorm(xd, w, yd)[1], non_blocking=True)
+            out_host[1].copy_(xlstm_b200.headnorm_gate(hd, od, w), non_blocking=True)
 
         cfg = dict(B=B, S=S, NH=NH, DH=DH, D=D)
         # add+norm reads x, y and writes x_new, normed; norm+gate reads h, o and writes out (the weights stay in L2)
         return dict(step=step, e2e_step=e2e_step, units=B * S, unit="tokens/s", metric="layer_adjacent_ops_tokens_per_s",
                     workload="xlstm7b_layer_add_rmsnorm_plus_headnorm_gate", cfg=cfg, bytes=7 * B * S * D * 2, flops=0,
-                    kernel="add_rmsnorm_kernel<bf16> + headnorm_gate_kernel<bf16>", h2d=x_host.numel() * 2,
-                    d2h=out_host.numel() * 2, l2="operands (7 x 537 MB per step) exceed the 126 MB L2", launches=2,
+                    kernel="add_rmsnorm_kernel<bf16> + headnorm_gate_kernel<bf16>", h2d=4 * B * S * D * 2,
+                    d2h=2 * B * S * D * 2, l2="operands (7 x %d MB per step) exceed the 126 MB L2" % (B * S * D * 2 // 10 ** 6), launches=2,
                     traffic=None)
     if name == "model7b":
         # BASELINE config 4: xLSTM-7B-shaped model, random-init bf16, prefill 8 x 8192 tokens then 512 greedy tokens.

@@ -179,6 +179,21 @@ typedef struct xl_headnorm_gate_params {
 /* Requires DH a multiple of the 16-byte vector and DH <= 1024 (bf16) / 512 (fp32). */
 int xl_headnorm_gate(const xl_headnorm_gate_params* p, void* cuda_stream);
 
+/* out[i] = cap * tanh(x[i] / cap) with the quotient, the tanh and the product each rounded to `dtype`, as the
+ * reference's eager soft_cap does (xlstm/xlstm_large/components.py:5-22; gate pre-activations model.py:389-394,
+ * 407-409, logits model.py:149-151).  `out_f32` != 0 writes the (dtype-rounded) result as fp32, which is what the
+ * cell kernels take for the gates. */
+typedef struct xl_soft_cap_params {
+  const void* x;   /* n elements, contiguous */
+  void* out;       /* n elements of `dtype`, or of fp32 when out_f32 != 0; may alias x when the types agree */
+  int64_t n;
+  float cap;
+  int32_t dtype;
+  int32_t out_f32;
+} xl_soft_cap_params;
+
+int xl_soft_cap(const xl_soft_cap_params* p, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

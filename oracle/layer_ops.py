@@ -11,8 +11,10 @@ Restates, with explicit rounding points, what the reference computes eagerly:
   229-242``: fp32 mean / biased variance, cast, reshape, ``* weight``) and the output gate
   ``sigmoid(o_preact) * h_norm`` (``model.py:445-449``).
 
+* ``soft_cap``: ``cap * tanh(values / cap)`` (``components.py:5-22``), every operator in the input dtype.
+
 Pinning: ``tests/golden/make_golden_layer.py`` ran the reference's own ``RMSNorm`` and ``MultiHeadLayerNorm``
-modules in this container and committed inputs and outputs; ``tests/test_oracle_layer_ops.py`` checks this
+modules and its ``soft_cap`` function in this container and committed inputs and outputs; ``tests/test_oracle_layer_ops.py`` checks this
 restatement against them.
 """
 from __future__ import annotations
@@ -40,3 +42,11 @@ def headnorm_gate(h: torch.Tensor, o_preact: torch.Tensor, weight: torch.Tensor,
     nw = (n.reshape(B, S, NH * DH).float() * weight.float()).to(dt)
     g = torch.sigmoid(o_preact.float()).to(dt)
     return (g.float() * nw.float()).to(dt)
+
+
+def soft_cap(x: torch.Tensor, cap: float, out_float32: bool = False):
+    dt = x.dtype
+    q = (x.float() / cap).to(dt)
+    t = torch.tanh(q.float()).to(dt)
+    y = (cap * t.float()).to(dt)
+    return y.float() if out_float32 else y

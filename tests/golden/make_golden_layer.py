@@ -4,7 +4,7 @@ Run once, in a container where the reference checkout is available:
 
     python tests/golden/make_golden_layer.py /path/to/reference
 
-It imports ``xlstm/xlstm_large/components.py`` (RMSNorm, MultiHeadLayerNorm), feeds seeded inputs in fp32 and
+It imports ``xlstm/xlstm_large/components.py`` (RMSNorm, MultiHeadLayerNorm, soft_cap), feeds seeded inputs in fp32 and
 bf16 and stores inputs and outputs (bf16 tensors as their fp32 images, which is exact).  The residual add and the
 output gate are the eager expressions of ``xlstm/xlstm_large/model.py:445-449, 499-510``.
 """
@@ -54,6 +54,10 @@ def main(ref_root):
             gated = torch.sigmoid(o) * h_norm
         out.update({f"hng_{tag}_h": h.float().numpy(), f"hng_{tag}_o": o.float().numpy(), f"hng_{tag}_w": w2.float().numpy(),
                     f"hng_{tag}_out": gated.float().numpy()})
+        # soft cap (gate pre-activations use 15, logits 30)
+        v = (20.0 * torch.randn(4, 333, generator=g)).to(dt)
+        out.update({f"cap_{tag}_x": v.float().numpy(), f"cap_{tag}_15": comp.soft_cap(v, 15.0).float().numpy(),
+                    f"cap_{tag}_30": comp.soft_cap(v, 30.0).float().numpy()})
     np.savez_compressed(os.path.join(HERE, "layer_ops.npz"), **out)
     print("wrote layer_ops.npz with", len(out), "arrays")
 

@@ -94,3 +94,23 @@ def test_unsupported_widths_are_refused_before_launch():
         xlstm_b200.headnorm_gate(torch.zeros(1, 1, 1, 2048, device="cuda", dtype=torch.bfloat16),
                                  torch.zeros(1, 1, 2048, device="cuda", dtype=torch.bfloat16),
                                  torch.ones(2048, device="cuda", dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("tag", ["f32", "bf16"])
+def test_soft_cap_matches_oracle_and_reference_fixture(tag):
+    import xlstm_b200
+    g, dt = load_golden("layer_ops"), DT[tag]
+    x = g[f"cap_{tag}_x"].to(dt)
+    for cap in (15.0, 30.0):
+        got = xlstm_b200.soft_cap(x.cuda(), cap)
+        got32 = xlstm_b200.soft_cap(x.cuda(), cap, out_float32=True)
+        assert got.dtype == dt and got32.dtype == torch.float32
+        assert torch.equal(got32.cpu(), got.float().cpu())
+        want = g[f"cap_{tag}_{int(cap)}"]
+        diff = (got.float().cpu() - want).abs()
+        if tag == "bf16":   # tanhf on the device and on the host may differ in the last fp32 bit before the bf16 rounding
+            assert (diff <= want.abs() * 2.0 ** -7).all() and (diff == 0).float().mean().item() > 0.99
+        else:
+            assert float(diff.max()) <= 1e-5
+    big = torch.randn(3, 1000003, generator=torch.Generator().manual_seed(1)) * 40
+    _close(xlstm_b200.soft_cap(big.cuda(), 30.0), O.soft_cap(big, 30.0), torch.float32)

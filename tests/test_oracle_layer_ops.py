@@ -33,3 +33,15 @@ def test_add_rmsnorm_without_residual_returns_input():
     x_new, normed = O.add_rmsnorm(x, torch.ones(64))
     assert x_new is x
     assert torch.allclose(normed.pow(2).mean(-1), torch.ones(3), atol=1e-4)
+
+
+@pytest.mark.parametrize("tag", ["f32", "bf16"])
+def test_soft_cap_matches_reference_function(tag):
+    g, dt = load_golden("layer_ops"), DT[tag]
+    x = g[f"cap_{tag}_x"].to(dt)
+    for cap in (15.0, 30.0):
+        want = g[f"cap_{tag}_{int(cap)}"]
+        got = O.soft_cap(x, cap)
+        tol = 0.0 if tag == "bf16" else 4e-6
+        assert (got.float() - want).abs().max().item() <= tol
+        assert torch.equal(O.soft_cap(x, cap, out_float32=True), got.float())

@@ -16,7 +16,7 @@ XL_F32, XL_BF16 = 0, 1
 EXPORTS = (
     "xl_strerror", "xl_last_cuda_error", "xl_abi_version",
     "xl_mlstm_chunkwise", "xl_mlstm_recurrent", "xl_mlstm_step", "xl_slstm_forward",
-    "xl_add_rmsnorm", "xl_headnorm_gate",
+    "xl_add_rmsnorm", "xl_headnorm_gate", "xl_soft_cap",
 )
 
 
@@ -80,6 +80,11 @@ class HeadnormGateParams(C.Structure):
     ]
 
 
+class SoftCapParams(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("out", C.c_void_p), ("n", C.c_int64), ("cap", C.c_float), ("dtype", C.c_int32),
+                ("out_f32", C.c_int32)]
+
+
 _lib = None
 
 
@@ -98,7 +103,8 @@ def lib() -> C.CDLL:
         l.xl_abi_version.restype = C.c_int
         for name, ptype in (("xl_mlstm_chunkwise", MlstmSeqParams), ("xl_mlstm_recurrent", MlstmSeqParams),
                             ("xl_mlstm_step", MlstmStepParams), ("xl_slstm_forward", SlstmParams),
-                            ("xl_add_rmsnorm", AddRmsnormParams), ("xl_headnorm_gate", HeadnormGateParams)):
+                            ("xl_add_rmsnorm", AddRmsnormParams), ("xl_headnorm_gate", HeadnormGateParams),
+                            ("xl_soft_cap", SoftCapParams)):
             fn = getattr(l, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(ptype), C.c_void_p]

@@ -1,5 +1,6 @@
 // Operators next to the mLSTM cell in the reference's layer, each fused into one pass over its data:
 //   xl_add_rmsnorm    residual add + RMSNorm                      (xlstm/xlstm_large/model.py:499-510, components.py:70-97)
+//   xl_soft_cap       cap * tanh(x / cap) of gate pre-activations and logits  (components.py:5-22)
 //   xl_headnorm_gate  per-head LayerNorm of the cell output read through its (B,NH,S,DH) strides, weight, output gate
 //                     (xlstm/xlstm_large/model.py:435-449, components.py:171-242)
 // Both are bound by HBM traffic: every element is read once with 16-byte loads, kept in registers across the
@@ -9,7 +10,7 @@
 
 namespace xl {
 
-constexpr int ADJ_MAXC = 4;  // 16-byte vectors per thread
+constexpr int ADJ_MAXC = 4;  // most 16-byte vectors per thread (kernels are instantiated for 1, 2 and 4)
 
 template <typename T> struct Vec16;
 template <> struct Vec16<float> {
@@ -32,6 +33,41 @@ __device__ __forceinline__ void store16(T* p, const Vec16<T>& r) {
   *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(r.v);
 }
 
+// The gate is rounded to T right away: for bf16 the hardware exponential and reciprocal (a few fp32 ulp) are far
+// inside the rounding step and keep the kernel on the memory roofline (with expf and an IEEE division the kernel
+// was bound by instruction issue: 0.49 ms against 0.25 ms of traffic at the 7B shapes); fp32 keeps the exact forms.
+template <typename T> __device__ __forceinline__ float sigmoid_for(float x);
+template <> __device__ __forceinline__ float sigmoid_for<float>(float x) { return 1.f / (1.f + expf(-x)); }
+template <> __device__ __forceinline__ float sigmoid_for<__nv_bfloat16>(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+
+// out = round(round(sigmoid(o)) * round(round((h - mean) * r) * w)), the eager reference's rounding sequence.
+__device__ __forceinline__ Vec16<float> normalise_weight_gate(const Vec16<float>& h, const Vec16<float>& o,
+                                                              const Vec16<float>& w, float mean, float r) {
+  Vec16<float> y;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) y.v[i] = sigmoid_for<float>(o.v[i]) * (((h.v[i] - mean) * r) * w.v[i]);
+  return y;
+}
+// bf16: two elements per instruction where the hardware has it -- one packed conversion per rounding point and
+// packed bf16 multiplies (the product of two bf16 values rounded once, which is what "multiply in fp32, round to
+// bf16" gives).  Element by element, with a conversion per rounding, the kernel was bound by instruction issue.
+__device__ __forceinline__ Vec16<__nv_bfloat16> normalise_weight_gate(const Vec16<__nv_bfloat16>& h, const Vec16<__nv_bfloat16>& o,
+                                                                      const Vec16<__nv_bfloat16>& w, float mean, float r) {
+  Vec16<__nv_bfloat16> y;
+  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(h.v);
+  const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(o.v);
+  const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(w.v);
+  __nv_bfloat162* y2 = reinterpret_cast<__nv_bfloat162*>(y.v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 hf = __bfloat1622float2(h2[i]), of = __bfloat1622float2(o2[i]);
+    const __nv_bfloat162 nw = __hmul2(__floats2bfloat162_rn((hf.x - mean) * r, (hf.y - mean) * r), w2[i]);
+    const __nv_bfloat162 g = __floats2bfloat162_rn(sigmoid_for<__nv_bfloat16>(of.x), sigmoid_for<__nv_bfloat16>(of.y));
+    y2[i] = __hmul2(g, nw);
+  }
+  return y;
+}
+
 __device__ __forceinline__ float warp_sum(float x) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
@@ -43,7 +79,7 @@ __device__ __forceinline__ float warp_sum(float x) {
 // ------------------------------------------------------------------------------------------------------------
 constexpr int RMS_THREADS = 256;
 
-template <typename T>
+template <typename T, int NC>
 __global__ void __launch_bounds__(RMS_THREADS) add_rmsnorm_kernel(const xl_add_rmsnorm_params p) {
   constexpr int V = Vec16<T>::N;
   __shared__ float s_part[RMS_THREADS / 32];
@@ -55,17 +91,29 @@ __global__ void __launch_bounds__(RMS_THREADS) add_rmsnorm_kernel(const xl_add_r
   T* xo = p.x_out ? static_cast<T*>(p.x_out) + row * p.xo_sr : nullptr;
   T* nd = static_cast<T*>(p.normed) + row * p.n_sr;
 
-  Vec16<T> xv[ADJ_MAXC];
-  float ss = 0.f;
+  // every load of the row is issued before the first use (x, y and the weights: up to 12 vectors in flight per thread)
+  Vec16<T> xv[NC], yv[NC], wv[NC];
 #pragma unroll
-  for (int c = 0; c < ADJ_MAXC; ++c) {
+  for (int c = 0; c < NC; ++c) {
     const int e = (c * RMS_THREADS + tid) * V;
     if (e < p.D) {
       xv[c] = load16(x + e);
-      if (y) {
-        const Vec16<T> yv = load16(y + e);
+      if (y) yv[c] = load16(y + e);
+    }
+  }
 #pragma unroll
-        for (int i = 0; i < V; ++i) xv[c].v[i] = from_float<T>(to_float(xv[c].v[i]) + to_float(yv.v[i]));
+  for (int c = 0; c < NC; ++c) {
+    const int e = (c * RMS_THREADS + tid) * V;
+    if (e < p.D) wv[c] = load16(w + e);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    const int e = (c * RMS_THREADS + tid) * V;
+    if (e < p.D) {
+      if (y) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) xv[c].v[i] = from_float<T>(to_float(xv[c].v[i]) + to_float(yv[c].v[i]));
         store16(xo + e, xv[c]);
       }
 #pragma unroll
@@ -83,14 +131,13 @@ __global__ void __launch_bounds__(RMS_THREADS) add_rmsnorm_kernel(const xl_add_r
   for (int i = 0; i < RMS_THREADS / 32; ++i) tot += s_part[i];
   const float r = rsqrtf(tot / (float)p.D + p.eps);
 #pragma unroll
-  for (int c = 0; c < ADJ_MAXC; ++c) {
+  for (int c = 0; c < NC; ++c) {
     const int e = (c * RMS_THREADS + tid) * V;
     if (e < p.D) {
-      const Vec16<T> wv = load16(w + e);
       Vec16<T> o;
 #pragma unroll
       for (int i = 0; i < V; ++i)
-        o.v[i] = from_float<T>(to_float(from_float<T>(to_float(xv[c].v[i]) * r)) * to_float(wv.v[i]));
+        o.v[i] = from_float<T>(to_float(from_float<T>(to_float(xv[c].v[i]) * r)) * to_float(wv[c].v[i]));
       store16(nd + e, o);
     }
   }
@@ -101,7 +148,7 @@ __global__ void __launch_bounds__(RMS_THREADS) add_rmsnorm_kernel(const xl_add_r
 // ------------------------------------------------------------------------------------------------------------
 constexpr int HNG_WARPS = 8;
 
-template <typename T>
+template <typename T, int NC>
 __global__ void __launch_bounds__(HNG_WARPS * 32) headnorm_gate_kernel(const xl_headnorm_gate_params p) {
   constexpr int V = Vec16<T>::N;
   const int lane = threadIdx.x & 31;
@@ -116,13 +163,22 @@ __global__ void __launch_bounds__(HNG_WARPS * 32) headnorm_gate_kernel(const xl_
   const T* w = static_cast<const T*>(p.weight) + (long long)head * p.DH;
   T* out = static_cast<T*>(p.out) + (bs * p.NH + head) * p.DH;
 
-  Vec16<T> hv[ADJ_MAXC];
-  float sum = 0.f;
+  // every load of the row is issued before the first use
+  Vec16<T> hv[NC], ov[NC], wv[NC];
 #pragma unroll
-  for (int c = 0; c < ADJ_MAXC; ++c) {
+  for (int c = 0; c < NC; ++c) {
     const int e = (c * 32 + lane) * V;
     if (e < p.DH) {
       hv[c] = load16(h + e);
+      ov[c] = load16(o + e);
+      wv[c] = load16(w + e);
+    }
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    const int e = (c * 32 + lane) * V;
+    if (e < p.DH) {
 #pragma unroll
       for (int i = 0; i < V; ++i) sum += to_float(hv[c].v[i]);
     }
@@ -130,7 +186,7 @@ __global__ void __launch_bounds__(HNG_WARPS * 32) headnorm_gate_kernel(const xl_
   const float mean = warp_sum(sum) / (float)p.DH;
   float sq = 0.f;
 #pragma unroll
-  for (int c = 0; c < ADJ_MAXC; ++c) {
+  for (int c = 0; c < NC; ++c) {
     const int e = (c * 32 + lane) * V;
     if (e < p.DH) {
 #pragma unroll
@@ -142,20 +198,24 @@ __global__ void __launch_bounds__(HNG_WARPS * 32) headnorm_gate_kernel(const xl_
   }
   const float r = rsqrtf(warp_sum(sq) / (float)p.DH + p.eps);
 #pragma unroll
-  for (int c = 0; c < ADJ_MAXC; ++c) {
+  for (int c = 0; c < NC; ++c) {
     const int e = (c * 32 + lane) * V;
     if (e < p.DH) {
-      const Vec16<T> ov = load16(o + e), wv = load16(w + e);
-      Vec16<T> y;
-#pragma unroll
-      for (int i = 0; i < V; ++i) {
-        const T nrm = from_float<T>((to_float(hv[c].v[i]) - mean) * r);
-        const T nw = from_float<T>(to_float(nrm) * to_float(wv.v[i]));
-        const T g = from_float<T>(1.f / (1.f + expf(-to_float(ov.v[i]))));
-        y.v[i] = from_float<T>(to_float(g) * to_float(nw));
-      }
-      store16(out + e, y);
+      store16(out + e, normalise_weight_gate(hv[c], ov[c], wv[c], mean, r));
     }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// soft cap: cap * tanh(x / cap), each operator's result rounded to T
+// ------------------------------------------------------------------------------------------------------------
+template <typename T, typename O>
+__global__ void __launch_bounds__(256) soft_cap_kernel(const T* __restrict__ x, O* __restrict__ out, long long n, float cap) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const T q = from_float<T>(to_float(x[i]) / cap);
+    const T t = from_float<T>(tanhf(to_float(q)));
+    out[i] = from_float<O>(to_float(from_float<T>(cap * to_float(t))));
   }
 }
 
@@ -176,10 +236,17 @@ extern "C" int xl_add_rmsnorm(const xl_add_rmsnorm_params* p, void* cuda_stream)
   if (p->normed == p->x || (p->y && p->normed == p->x_out)) return XL_ERR_ALIASING;
   if (p->rows == 0) return XL_OK;
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
-  if (p->dtype == XL_F32)
-    add_rmsnorm_kernel<float><<<(unsigned)p->rows, RMS_THREADS, 0, st>>>(*p);
-  else
-    add_rmsnorm_kernel<__nv_bfloat16><<<(unsigned)p->rows, RMS_THREADS, 0, st>>>(*p);
+  const int nc = (p->D + RMS_THREADS * V - 1) / (RMS_THREADS * V);
+  const unsigned grid = (unsigned)p->rows;
+#define XL_RMS_LAUNCH(T)                                                              \
+  do {                                                                                \
+    if (nc <= 1) add_rmsnorm_kernel<T, 1><<<grid, RMS_THREADS, 0, st>>>(*p);          \
+    else if (nc <= 2) add_rmsnorm_kernel<T, 2><<<grid, RMS_THREADS, 0, st>>>(*p);     \
+    else add_rmsnorm_kernel<T, 4><<<grid, RMS_THREADS, 0, st>>>(*p);                  \
+  } while (0)
+  if (p->dtype == XL_F32) XL_RMS_LAUNCH(float);
+  else XL_RMS_LAUNCH(__nv_bfloat16);
+#undef XL_RMS_LAUNCH
   return check_launch("xl_add_rmsnorm");
 }
 
@@ -197,9 +264,34 @@ extern "C" int xl_headnorm_gate(const xl_headnorm_gate_params* p, void* cuda_str
   const long long blocks = (units + HNG_WARPS - 1) / HNG_WARPS;
   if (blocks > 0x7fffffffLL) return XL_ERR_TOO_LARGE;
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
-  if (p->dtype == XL_F32)
-    headnorm_gate_kernel<float><<<(unsigned)blocks, HNG_WARPS * 32, 0, st>>>(*p);
-  else
-    headnorm_gate_kernel<__nv_bfloat16><<<(unsigned)blocks, HNG_WARPS * 32, 0, st>>>(*p);
+  const int nc = (p->DH + 32 * V - 1) / (32 * V);
+#define XL_HNG_LAUNCH(T)                                                                              \
+  do {                                                                                                \
+    if (nc <= 1) headnorm_gate_kernel<T, 1><<<(unsigned)blocks, HNG_WARPS * 32, 0, st>>>(*p);         \
+    else if (nc <= 2) headnorm_gate_kernel<T, 2><<<(unsigned)blocks, HNG_WARPS * 32, 0, st>>>(*p);    \
+    else headnorm_gate_kernel<T, 4><<<(unsigned)blocks, HNG_WARPS * 32, 0, st>>>(*p);                 \
+  } while (0)
+  if (p->dtype == XL_F32) XL_HNG_LAUNCH(float);
+  else XL_HNG_LAUNCH(__nv_bfloat16);
+#undef XL_HNG_LAUNCH
   return check_launch("xl_headnorm_gate");
+}
+
+extern "C" int xl_soft_cap(const xl_soft_cap_params* p, void* cuda_stream) {
+  using namespace xl;
+  if (!p || !p->x || !p->out) return XL_ERR_NULL_POINTER;
+  if (p->dtype != XL_F32 && p->dtype != XL_BF16) return XL_ERR_BAD_DTYPE;
+  if (p->n < 0 || !(p->cap > 0.f)) return XL_ERR_BAD_SHAPE;
+  if (p->n == 0) return XL_OK;
+  if (p->out == p->x && p->dtype == XL_BF16 && p->out_f32) return XL_ERR_ALIASING;
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  const long long want = (p->n + 255) / 256;
+  const unsigned grid = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+  if (p->dtype == XL_F32)
+    soft_cap_kernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float*>(p->x), static_cast<float*>(p->out), p->n, p->cap);
+  else if (p->out_f32)
+    soft_cap_kernel<__nv_bfloat16, float><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(p->x), static_cast<float*>(p->out), p->n, p->cap);
+  else
+    soft_cap_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(p->x), static_cast<__nv_bfloat16*>(p->out), p->n, p->cap);
+  return check_launch("xl_soft_cap");
 }

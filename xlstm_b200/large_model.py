@@ -116,7 +116,7 @@ class LargeModel:
         # `cell_ops` provides mlstm_sequence / mlstm_step; the default is this package's CUDA kernels (the test
         # suite substitutes the CPU oracle to check the dense part of this mirror against the reference on a CPU)
         self.cell = cell_ops
-        # residual add + RMSNorm and per-head norm + output gate as single kernels of this package (CUDA only)
+        # residual add + RMSNorm, per-head norm + output gate and the soft caps as single kernels of this package (CUDA only)
         self.fused = bool(fused_adjacent) and torch.device(device).type == "cuda" and cell_ops is ops
         if cfg.num_heads % tp_world or cfg.ffn_dim % tp_world:
             raise ValueError("num_heads and the FFN width must be divisible by the tensor-parallel world size")
@@ -160,7 +160,10 @@ class LargeModel:
         B, S, _ = x.shape
         qkvo = F.linear(x, blk["qkvo"])
         q, k, v, o = torch.split(qkvo, [NHl * dq, NHl * dq, NHl * dv, NHl * dv], dim=-1)
-        gates = _soft_cap(F.linear(x, blk["if_w"], blk["if_b"]).float(), cfg.gate_soft_cap)   # (B,S,2*NHl) fp32
+        if self.fused:   # capped in the model dtype as the reference does, handed to the cell as fp32
+            gates = ops.soft_cap(F.linear(x, blk["if_w"], blk["if_b"]), cfg.gate_soft_cap, out_float32=True)
+        else:
+            gates = _soft_cap(F.linear(x, blk["if_w"], blk["if_b"]).float(), cfg.gate_soft_cap)   # (B,S,2*NHl) fp32
         ig, fg = gates[..., :NHl].transpose(1, 2), gates[..., NHl:].transpose(1, 2)          # (B,NHl,S) views
         q = q.reshape(B, S, NHl, dq).transpose(1, 2)     # strided views, no copies (model.py:415-417)
         k = k.reshape(B, S, NHl, dq).transpose(1, 2)
@@ -209,6 +212,8 @@ class LargeModel:
             pending = None if pending is None else pending[:, -1:]
         x, xn = self._add_norm(x, pending, self.out_norm)
         logits = F.linear(xn, self.lm_head)
+        if self.fused:
+            return ops.soft_cap(logits, cfg.output_logit_soft_cap), new_state
         return _soft_cap(logits, cfg.output_logit_soft_cap), new_state
 
     # ------------------------------------------------------------------------------------------------

@@ -12,7 +12,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
-from ._lib import (AddRmsnormParams, HeadnormGateParams, MlstmSeqParams, MlstmStepParams, SlstmParams, XL_BF16, XL_F32,
+from ._lib import (AddRmsnormParams, HeadnormGateParams, MlstmSeqParams, MlstmStepParams, SlstmParams, SoftCapParams, XL_BF16, XL_F32,
                    check, lib)
 
 _DTYPES = {torch.float32: XL_F32, torch.bfloat16: XL_BF16}
@@ -343,4 +343,21 @@ def headnorm_gate(h, o_preact, weight, eps: float = 1e-6):
     p.eps, p.dtype = eps, _DTYPES[h.dtype]
     with torch.cuda.device(h.device):
         check(lib().xl_headnorm_gate(C.byref(p), _stream_ptr(h.device)), "xl_headnorm_gate")
+    return out
+
+
+def soft_cap(x, cap: float, out_float32: bool = False):
+    """``cap * tanh(x / cap)`` in one kernel with the rounding of the reference's eager ``soft_cap``
+    (xlstm/xlstm_large/components.py:5-22).  ``out_float32`` returns the result (rounded to ``x.dtype``) as
+    float32, the type the cell kernels take for gate pre-activations."""
+    _require_cuda(x)
+    if x.dtype not in _DTYPES:
+        raise ValueError("soft_cap: float32 or bfloat16 only")
+    xc = x.contiguous()
+    out = torch.empty(xc.shape, dtype=torch.float32 if out_float32 else x.dtype, device=x.device)
+    p = SoftCapParams()
+    p.x, p.out, p.n, p.cap = xc.data_ptr(), out.data_ptr(), xc.numel(), float(cap)
+    p.dtype, p.out_f32 = _DTYPES[x.dtype], int(out_float32)
+    with torch.cuda.device(x.device):
+        check(lib().xl_soft_cap(C.byref(p), _stream_ptr(x.device)), "xl_soft_cap")
     return out
