@@ -181,11 +181,12 @@ int xl_headnorm_gate(const xl_headnorm_gate_params* p, void* cuda_stream);
 
 /* out[i] = cap * tanh(x[i] / cap) with the quotient, the tanh and the product each rounded to `dtype`, as the
  * reference's eager soft_cap does (xlstm/xlstm_large/components.py:5-22; gate pre-activations model.py:389-394,
- * 407-409, logits model.py:149-151).  `out_f32` != 0 writes the (dtype-rounded) result as fp32, which is what the
- * cell kernels take for the gates. */
+ * 407-409, logits model.py:149-151).  out_f32 = 1 writes the (dtype-rounded) result as fp32, which is what the
+ * cell kernels take for the gates; out_f32 = 2 writes fp32 computed in fp32 from the `dtype` input without the
+ * intermediate roundings (for callers that keep the gates in fp32 although the model runs in bf16). */
 typedef struct xl_soft_cap_params {
   const void* x;   /* n elements, contiguous */
-  void* out;       /* n elements of `dtype`, or of fp32 when out_f32 != 0; may alias x when the types agree */
+  void* out;       /* n elements of `dtype`, or of fp32 when out_f32 is 1 or 2; may alias x when the types agree */
   int64_t n;
   float cap;
   int32_t dtype;

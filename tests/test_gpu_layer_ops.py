@@ -112,5 +112,8 @@ def test_soft_cap_matches_oracle_and_reference_fixture(tag):
             assert (diff <= want.abs() * 2.0 ** -7).all() and (diff == 0).float().mean().item() > 0.99
         else:
             assert float(diff.max()) <= 1e-5
+    if tag == "bf16":   # fp32 arithmetic on bf16 inputs
+        got = xlstm_b200.soft_cap(x.cuda(), 15.0, out_float32=True, float32_math=True)
+        _close(got, O.soft_cap(x.float(), 15.0), torch.float32)
     big = torch.randn(3, 1000003, generator=torch.Generator().manual_seed(1)) * 40
     _close(xlstm_b200.soft_cap(big.cuda(), 30.0), O.soft_cap(big, 30.0), torch.float32)

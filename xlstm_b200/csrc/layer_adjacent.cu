@@ -209,13 +209,17 @@ __global__ void __launch_bounds__(HNG_WARPS * 32) headnorm_gate_kernel(const xl_
 // ------------------------------------------------------------------------------------------------------------
 // soft cap: cap * tanh(x / cap), each operator's result rounded to T
 // ------------------------------------------------------------------------------------------------------------
-template <typename T, typename O>
+template <typename T, typename O, bool ROUND_EACH>
 __global__ void __launch_bounds__(256) soft_cap_kernel(const T* __restrict__ x, O* __restrict__ out, long long n, float cap) {
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-    const T q = from_float<T>(to_float(x[i]) / cap);
-    const T t = from_float<T>(tanhf(to_float(q)));
-    out[i] = from_float<O>(to_float(from_float<T>(cap * to_float(t))));
+    if (ROUND_EACH) {
+      const T q = from_float<T>(to_float(x[i]) / cap);
+      const T t = from_float<T>(tanhf(to_float(q)));
+      out[i] = from_float<O>(to_float(from_float<T>(cap * to_float(t))));
+    } else {
+      out[i] = from_float<O>(cap * tanhf(to_float(x[i]) / cap));
+    }
   }
 }
 
@@ -281,17 +285,19 @@ extern "C" int xl_soft_cap(const xl_soft_cap_params* p, void* cuda_stream) {
   using namespace xl;
   if (!p || !p->x || !p->out) return XL_ERR_NULL_POINTER;
   if (p->dtype != XL_F32 && p->dtype != XL_BF16) return XL_ERR_BAD_DTYPE;
-  if (p->n < 0 || !(p->cap > 0.f)) return XL_ERR_BAD_SHAPE;
+  if (p->n < 0 || !(p->cap > 0.f) || p->out_f32 < 0 || p->out_f32 > 2) return XL_ERR_BAD_SHAPE;
   if (p->n == 0) return XL_OK;
   if (p->out == p->x && p->dtype == XL_BF16 && p->out_f32) return XL_ERR_ALIASING;
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
   const long long want = (p->n + 255) / 256;
   const unsigned grid = (unsigned)(want < 148 * 16 ? want : 148 * 16);
   if (p->dtype == XL_F32)
-    soft_cap_kernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float*>(p->x), static_cast<float*>(p->out), p->n, p->cap);
+    soft_cap_kernel<float, float, false><<<grid, 256, 0, st>>>(static_cast<const float*>(p->x), static_cast<float*>(p->out), p->n, p->cap);
+  else if (p->out_f32 == 2)
+    soft_cap_kernel<__nv_bfloat16, float, false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(p->x), static_cast<float*>(p->out), p->n, p->cap);
   else if (p->out_f32)
-    soft_cap_kernel<__nv_bfloat16, float><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(p->x), static_cast<float*>(p->out), p->n, p->cap);
+    soft_cap_kernel<__nv_bfloat16, float, true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(p->x), static_cast<float*>(p->out), p->n, p->cap);
   else
-    soft_cap_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(p->x), static_cast<__nv_bfloat16*>(p->out), p->n, p->cap);
+    soft_cap_kernel<__nv_bfloat16, __nv_bfloat16, true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(p->x), static_cast<__nv_bfloat16*>(p->out), p->n, p->cap);
   return check_launch("xl_soft_cap");
 }

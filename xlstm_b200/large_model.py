@@ -160,8 +160,8 @@ class LargeModel:
         B, S, _ = x.shape
         qkvo = F.linear(x, blk["qkvo"])
         q, k, v, o = torch.split(qkvo, [NHl * dq, NHl * dq, NHl * dv, NHl * dv], dim=-1)
-        if self.fused:   # capped in the model dtype as the reference does, handed to the cell as fp32
-            gates = ops.soft_cap(F.linear(x, blk["if_w"], blk["if_b"]), cfg.gate_soft_cap, out_float32=True)
+        if self.fused:   # capped in fp32 like the eager path below: the gates enter exponentials in the cell
+            gates = ops.soft_cap(F.linear(x, blk["if_w"], blk["if_b"]), cfg.gate_soft_cap, out_float32=True, float32_math=True)
         else:
             gates = _soft_cap(F.linear(x, blk["if_w"], blk["if_b"]).float(), cfg.gate_soft_cap)   # (B,S,2*NHl) fp32
         ig, fg = gates[..., :NHl].transpose(1, 2), gates[..., NHl:].transpose(1, 2)          # (B,NHl,S) views

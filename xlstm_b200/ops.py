@@ -346,10 +346,13 @@ def headnorm_gate(h, o_preact, weight, eps: float = 1e-6):
     return out
 
 
-def soft_cap(x, cap: float, out_float32: bool = False):
+def soft_cap(x, cap: float, out_float32: bool = False, float32_math: bool = False):
     """``cap * tanh(x / cap)`` in one kernel with the rounding of the reference's eager ``soft_cap``
     (xlstm/xlstm_large/components.py:5-22).  ``out_float32`` returns the result (rounded to ``x.dtype``) as
-    float32, the type the cell kernels take for gate pre-activations."""
+    float32, the type the cell kernels take for gate pre-activations; with ``float32_math`` as well the
+    quotient, tanh and product are not rounded to ``x.dtype`` in between (gates kept in fp32 in a bf16 model)."""
+    if float32_math and not out_float32:
+        raise ValueError("soft_cap: float32_math needs out_float32")
     _require_cuda(x)
     if x.dtype not in _DTYPES:
         raise ValueError("soft_cap: float32 or bfloat16 only")
@@ -357,7 +360,7 @@ def soft_cap(x, cap: float, out_float32: bool = False):
     out = torch.empty(xc.shape, dtype=torch.float32 if out_float32 else x.dtype, device=x.device)
     p = SoftCapParams()
     p.x, p.out, p.n, p.cap = xc.data_ptr(), out.data_ptr(), xc.numel(), float(cap)
-    p.dtype, p.out_f32 = _DTYPES[x.dtype], int(out_float32)
+    p.dtype, p.out_f32 = _DTYPES[x.dtype], (2 if float32_math else int(out_float32))
     with torch.cuda.device(x.device):
         check(lib().xl_soft_cap(C.byref(p), _stream_ptr(x.device)), "xl_soft_cap")
     return out
