@@ -263,7 +263,8 @@ def build_case(name, dev, rank):
                     workload="xlstm7b_layer_add_rmsnorm_plus_headnorm_gate", cfg=cfg, bytes=7 * B * S * D * 2, flops=0,
                     kernel="add_rmsnorm_kernel<bf16> + headnorm_gate_kernel<bf16>", h2d=4 * B * S * D * 2,
                     d2h=2 * B * S * D * 2, l2="operands (7 x %d MB per step) exceed the 126 MB L2" % (B * S * D * 2 // 10 ** 6), launches=2,
-                    traffic=None)
+                    # dram read+write of both kernels captured at B=2 (profiles/layer_adjacent_ops.md), scaled by B
+                    traffic=863.3e6 * B / 2)
     if name == "model7b":
         # BASELINE config 4: xLSTM-7B-shaped model, random-init bf16, prefill 8 x 8192 tokens then 512 greedy tokens.
         # Heads are tensor-parallel over the ranks (strong scaling): dense layers are library GEMMs, the cell is ours.

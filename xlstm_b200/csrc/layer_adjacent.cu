@@ -152,16 +152,16 @@ template <typename T, int NC>
 __global__ void __launch_bounds__(HNG_WARPS * 32) headnorm_gate_kernel(const xl_headnorm_gate_params p) {
   constexpr int V = Vec16<T>::N;
   const int lane = threadIdx.x & 31;
-  const long long unit = (long long)blockIdx.x * HNG_WARPS + (threadIdx.x >> 5);
-  const long long units = (long long)p.B * p.S * p.NH;
-  if (unit >= units) return;
-  const int head = (int)(unit % p.NH);
-  const long long bs = unit / p.NH;
-  const int s = (int)(bs % p.S), b = (int)(bs / p.S);
+  // 32-bit index arithmetic on purpose (grid.y = batch row): with 64-bit divisions for (batch, token, head) the index
+  // computation alone was more than half of the warp's instructions
+  const unsigned unit = blockIdx.x * HNG_WARPS + (threadIdx.x >> 5);   // (token, head) within the batch row
+  if (unit >= (unsigned)p.S * (unsigned)p.NH) return;
+  const unsigned s = unit / (unsigned)p.NH, head = unit - s * (unsigned)p.NH;
+  const long long b = blockIdx.y;
   const T* h = static_cast<const T*>(p.h) + b * p.h_sb + head * p.h_sh + s * p.h_st;
   const T* o = static_cast<const T*>(p.o) + b * p.o_sb + s * p.o_st + (long long)head * p.DH;
   const T* w = static_cast<const T*>(p.weight) + (long long)head * p.DH;
-  T* out = static_cast<T*>(p.out) + (bs * p.NH + head) * p.DH;
+  T* out = static_cast<T*>(p.out) + ((b * p.S + s) * p.NH + head) * p.DH;
 
   // every load of the row is issued before the first use
   Vec16<T> hv[NC], ov[NC], wv[NC];
@@ -264,16 +264,16 @@ extern "C" int xl_headnorm_gate(const xl_headnorm_gate_params* p, void* cuda_str
   if (p->h_sb % V || p->h_sh % V || p->h_st % V || p->o_sb % V || p->o_st % V) return XL_ERR_BAD_STRIDE;
   if (!aligned16(p->h) || !aligned16(p->o) || !aligned16(p->weight) || !aligned16(p->out)) return XL_ERR_BAD_ALIGNMENT;
   if (p->out == p->h || p->out == p->o) return XL_ERR_ALIASING;
-  const long long units = (long long)p->B * p->S * p->NH;
-  const long long blocks = (units + HNG_WARPS - 1) / HNG_WARPS;
-  if (blocks > 0x7fffffffLL) return XL_ERR_TOO_LARGE;
+  const long long per_row = (long long)p->S * p->NH;
+  if (per_row > 0x7fffffffLL || p->B > 65535) return XL_ERR_TOO_LARGE;
+  const dim3 blocks((unsigned)((per_row + HNG_WARPS - 1) / HNG_WARPS), (unsigned)p->B);
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
   const int nc = (p->DH + 32 * V - 1) / (32 * V);
 #define XL_HNG_LAUNCH(T)                                                                              \
   do {                                                                                                \
-    if (nc <= 1) headnorm_gate_kernel<T, 1><<<(unsigned)blocks, HNG_WARPS * 32, 0, st>>>(*p);         \
-    else if (nc <= 2) headnorm_gate_kernel<T, 2><<<(unsigned)blocks, HNG_WARPS * 32, 0, st>>>(*p);    \
-    else headnorm_gate_kernel<T, 4><<<(unsigned)blocks, HNG_WARPS * 32, 0, st>>>(*p);                 \
+    if (nc <= 1) headnorm_gate_kernel<T, 1><<<blocks, HNG_WARPS * 32, 0, st>>>(*p);         \
+    else if (nc <= 2) headnorm_gate_kernel<T, 2><<<blocks, HNG_WARPS * 32, 0, st>>>(*p);    \
+    else headnorm_gate_kernel<T, 4><<<blocks, HNG_WARPS * 32, 0, st>>>(*p);                 \
   } while (0)
   if (p->dtype == XL_F32) XL_HNG_LAUNCH(float);
   else XL_HNG_LAUNCH(__nv_bfloat16);
