@@ -228,10 +228,12 @@ class LargeModel:
 
         def body():
             logits, st = self.forward(self._g_tok, self._g_state, last_only=True)
+            dsts, srcs = [], []
             for i, (c, n, m) in st.items():
                 assert c is self._g_state[i][0]
-                self._g_state[i][1].copy_(n)
-                self._g_state[i][2].copy_(m.reshape(self._g_state[i][2].shape))
+                dsts += [self._g_state[i][1], self._g_state[i][2]]
+                srcs += [n, m.reshape(self._g_state[i][2].shape)]
+            torch._foreach_copy_(dsts, srcs)   # one multi-tensor launch instead of two small copies per block
             self._g_tok.copy_(torch.argmax(logits[:, -1:], dim=-1))
 
         snapshot = {i: tuple(t.clone() for t in st) for i, st in self._g_state.items()}
