@@ -13,7 +13,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from conftest import load_golden, rel_l2
-from xlstm_b200.large_model import LargeConfig, LargeModel, procedural_state_dict
+from xlstm_b200.large_model import ContinuousDecoder, LargeConfig, LargeModel, procedural_state_dict
 
 CFG1 = LargeConfig(embedding_dim=512, num_heads=4, num_blocks=6, vocab_size=2048)
 
@@ -147,7 +147,7 @@ def test_tensor_parallel_nccl_decode_on_two_gpus(tmp_path):
     script.write_text(
         "import os, sys, torch, torch.distributed as dist\n"
         f"sys.path.insert(0, {root!r})\n"
-        "from xlstm_b200.large_model import LargeConfig, LargeModel, procedural_state_dict\n"
+        "from xlstm_b200.large_model import ContinuousDecoder, LargeConfig, LargeModel, procedural_state_dict\n"
         "rank, world = int(os.environ['RANK']), int(os.environ['WORLD_SIZE'])\n"
         "dev = torch.device('cuda', int(os.environ['LOCAL_RANK'])); torch.cuda.set_device(dev)\n"
         "dist.init_process_group('nccl', device_id=dev)\n"
@@ -169,3 +169,41 @@ def test_tensor_parallel_nccl_decode_on_two_gpus(tmp_path):
            "--master-port", "29541", str(script)]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
     assert res.returncode == 0 and res.stdout.count("TP_OK") == 2, res.stdout[-2000:] + res.stderr[-3000:]
+
+
+def _continuous_case():
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 64, (int(n),), generator=g) for n in (5, 70, 13, 64, 9, 33, 21)]
+    return prompts, [4, 7, 1, 5, 9, 3, 6]
+
+
+def test_continuous_batching_equals_per_document_decoding_on_cpu():
+    """Seven documents through three state slots with refill: every stream's tokens equal what the plain greedy loop
+    gives for that document alone (host logic of the driver; the CPU oracle is the cell)."""
+    cfg = LargeConfig(embedding_dim=128, num_heads=2, num_blocks=2, vocab_size=64)
+    model = LargeModel(cfg, procedural_state_dict(cfg, 4), "cpu", torch.float32, cell_ops=_oracle_cell())
+    prompts, counts = _continuous_case()
+    dec = ContinuousDecoder(model, 3)
+    outs = dec.run(prompts, counts)
+    assert len(dec.slots.free) == 3 and not dec.slots.owner
+    for p, c, o in zip(prompts, counts, outs):
+        assert torch.equal(model.generate(p[None], c)[0][0], o)
+    with pytest.raises(ValueError):
+        dec.run(prompts, [1, 2])
+
+
+@pytest.mark.gpu
+def test_continuous_batching_graph_replay_with_refill_on_gpu():
+    """The same on the GPU: the decode step is a replayed CUDA graph whose static state buffers are the slot pool;
+    refills write prefill states into single rows between replays."""
+    import xlstm_b200
+    cfg = LargeConfig(embedding_dim=128, num_heads=2, num_blocks=2, vocab_size=64)
+    model = LargeModel(cfg, procedural_state_dict(cfg, 4), "cuda", torch.float32)
+    prompts, counts = _continuous_case()
+    dec = ContinuousDecoder(model, 3)
+    assert dec.graphed
+    outs = dec.run(prompts, counts)
+    xlstm_b200.check_device_status()
+    for p, c, o in zip(prompts, counts, outs):
+        assert torch.equal(model.generate(p[None].cuda(), c)[0][0].cpu(), o)
+    model.release_graph()

@@ -297,3 +297,79 @@ class LargeModel:
         if use_cuda_graph and max_length > 1:
             state = self._g_state
         return out, state
+
+
+class ContinuousDecoder:
+    """Continuous-batch greedy decoding over a fixed pool of state slots (BASELINE config 5: decode slots with refill).
+
+    Every stream owns one row of the per-block state pool; a decode step advances ALL rows at once (on CUDA by
+    replaying the captured graph of ``LargeModel``, whose static state buffers ARE the pool).  When a stream has its
+    tokens the host frees the slot (``sharding.SlotPool``) and the next queued document takes it over: its prompt is
+    prefilled as a batch of one, the resulting (C, n, m) are written into the slot's rows and its first generated
+    token into the slot's token cell.  The reference's loop (``generate.py:27-90``) has no refill: it decodes one
+    fixed batch to the end.  Token by token a stream computes what ``LargeModel.generate`` computes for it alone.
+    Rows of free slots keep stepping on stale data; nothing reads them."""
+
+    def __init__(self, model: LargeModel, num_slots: int, use_cuda_graph: Optional[bool] = None):
+        from .sharding import SlotPool
+        self.model, self.num_slots = model, num_slots
+        cfg, dev = model.cfg, model.device
+        self.graphed = (dev.type == "cuda") if use_cuda_graph is None else use_cuda_graph
+        self.state = {i: (torch.zeros(num_slots, model.nh_local, model.dq, model.dv, device=dev),
+                          torch.zeros(num_slots, model.nh_local, model.dq, device=dev),
+                          torch.zeros(num_slots, model.nh_local, 1, device=dev)) for i in range(cfg.num_blocks)}
+        self.tok = torch.zeros(num_slots, 1, dtype=torch.long, device=dev)
+        self.slots = SlotPool(num_slots)
+        if self.graphed:
+            model._capture_decode_graph(self.state, num_slots)   # the graph's static buffers are this pool
+            self.state, self.tok = model._g_state, model._g_tok
+
+    @torch.no_grad()
+    def _admit(self, slot: int, prompt: torch.Tensor) -> None:
+        logits, st = self.model.forward(prompt.reshape(1, -1).to(self.model.device), last_only=True)
+        for i, (c, n, m) in st.items():
+            self.state[i][0][slot].copy_(c[0])
+            self.state[i][1][slot].copy_(n[0])
+            self.state[i][2][slot].copy_(m[0].reshape(self.state[i][2][slot].shape))
+        self.tok[slot].copy_(torch.argmax(logits[0, -1:], dim=-1))
+
+    @torch.no_grad()
+    def _step(self) -> None:
+        if self.graphed:
+            self.model._graph.replay()
+            return
+        logits, st = self.model.forward(self.tok, self.state, last_only=True)
+        for i, (c, n, m) in st.items():
+            for dst, src in zip(self.state[i], (c, n, m)):
+                if dst is not src:
+                    dst.copy_(src.reshape(dst.shape))
+        self.tok.copy_(torch.argmax(logits[:, -1:], dim=-1))
+
+    @torch.no_grad()
+    def run(self, prompts, new_tokens):
+        """prompts: sequence of 1-D int64 tensors; new_tokens: int or per-document counts (>= 1).  Returns the list of
+        generated token tensors in the order of ``prompts``."""
+        counts = [int(new_tokens)] * len(prompts) if isinstance(new_tokens, int) else [int(x) for x in new_tokens]
+        if len(counts) != len(prompts) or any(c < 1 for c in counts):
+            raise ValueError("one positive token count per prompt")
+        queue = list(range(len(prompts)))[::-1]
+        active = {}          # slot -> [document, tokens still to produce, position of its first token in `hist`]
+        hist = []            # token column of every step (device tensors; read back once at the end)
+        spans = {}           # document -> (slot, first, count)
+        while queue or active:
+            while queue and self.slots.free:
+                d = queue.pop()
+                s = self.slots.acquire(d)
+                self._admit(s, prompts[d])
+                active[s] = [d, counts[d], len(hist)]
+            hist.append(self.tok[:, 0].clone())      # the token every active slot has just produced
+            for s in list(active):
+                active[s][1] -= 1
+                if active[s][1] == 0:
+                    d, _, first = active.pop(s)
+                    spans[d] = (s, first, counts[d])
+                    self.slots.release(s)
+            if active:
+                self._step()
+        cols = torch.stack(hist, dim=1).cpu()          # (slots, steps)
+        return [cols[spans[d][0], spans[d][1]:spans[d][1] + spans[d][2]].clone() for d in range(len(prompts))]
