@@ -265,6 +265,37 @@ def build_case(name, dev, rank):
                     d2h=2 * B * S * D * 2, l2="operands (7 x %d MB per step) exceed the 126 MB L2" % (B * S * D * 2 // 10 ** 6), launches=2,
                     # dram read+write of both kernels captured at B=2 (profiles/layer_adjacent_ops.md), scaled by B
                     traffic=863.3e6 * B / 2)
+    if name == "continuous7b":
+        # BASELINE config 5 in small: documents of log-normal length through a pool of decode slots with refill
+        # (xLSTM-7B-shaped mirror, random init; 128 documents, 64 slots, 64 greedy tokens each)
+        from xlstm_b200.large_model import ContinuousDecoder, LargeConfig, LargeModel, procedural_state_dict
+        mcfg = LargeConfig(embedding_dim=4096, num_heads=8, num_blocks=32, vocab_size=50304)
+        sd = procedural_state_dict(mcfg, seed=0, dtype=torch.bfloat16, device=dev, gen_device=dev)
+        model = LargeModel(mcfg, sd, dev, torch.bfloat16)
+        del sd
+        torch.cuda.empty_cache()
+        NDOC, NSLOT, GEN = 128, 64, 64
+        g = torch.Generator().manual_seed(11)
+        lens = torch.exp(torch.randn(NDOC, generator=g) + 6.0).clamp(16, 2048).long().tolist()
+        prompts_host = [torch.randint(0, mcfg.vocab_size, (n,), generator=g).pin_memory() for n in lens]
+        prompts = [t.to(dev) for t in prompts_host]
+        dec = ContinuousDecoder(model, NSLOT)
+
+        def step():
+            return dec.run(prompts, GEN)
+
+        def e2e_step():   # prompts from pinned host memory; run() reads the generated tokens back to the host
+            return dec.run([t.to(dev, non_blocking=True) for t in prompts_host], GEN)
+
+        cfg = dict(model="xLSTM-7B-shaped (random init)", documents=NDOC, slots=NSLOT, new_tokens=GEN,
+                   prompt_tokens=sum(lens), lengths="exp(N(6,1)) clipped to [16,2048]")
+        steps_est = NDOC * GEN // NSLOT
+        return dict(step=step, e2e_step=e2e_step, teardown=model.release_graph, units=sum(lens) + NDOC * GEN, unit="tokens/s",
+                    metric="xlstm7b_continuous_decode_tokens_per_s", workload="xlstm7b_128docs_64slots_refill", cfg=cfg,
+                    bytes=(steps_est + NDOC) * sum(t.numel() * t.element_size() for t in model.parameters_on_device() if t is not model.embedding),
+                    flops=0, kernel="whole run: single-document prefills and graph-replayed decode steps over the slot pool",
+                    h2d=sum(lens) * 8, d2h=NSLOT * steps_est * 8, l2="weights (13.7 GB) exceed the 126 MB L2",
+                    launches=steps_est + 32 * NDOC, heavy=True)
     if name == "model7b":
         # BASELINE config 4: xLSTM-7B-shaped model, random-init bf16, prefill 8 x 8192 tokens then 512 greedy tokens.
         # Heads are tensor-parallel over the ranks (strong scaling): dense layers are library GEMMs, the cell is ours.
@@ -311,7 +342,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--case", default="chunkwise", choices=["chunkwise", "chunkwise_b1", "step", "slstm", "layer_ops", "model7b"])
+    ap.add_argument("--case", default="chunkwise", choices=["chunkwise", "chunkwise_b1", "step", "slstm", "layer_ops", "model7b", "continuous7b"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="profiling runs: device-resident loop only")
     args = ap.parse_args()
