@@ -17,7 +17,10 @@
  *     m (N, NH); an absent initial state means C = 0, n = 0, m = 0
  *     (xlstm/blocks/mlstm/backends.py:185-194).
  *   - the 1/sqrt(DHQK) factor is applied to q; C and n hold un-scaled keys
- *     (xlstm/blocks/mlstm/backends.py:168).
+ *     (xlstm/blocks/mlstm/backends.py:168).  This is the convention of the third-party mlstm_kernels package
+ *     the reference's xLSTM-Large model calls; the older step function recurrent_step_stabilized_simple
+ *     (xlstm/blocks/mlstm/backends.py:134-137) scales k instead, so its C and n differ from these by sqrt(DHQK)
+ *     and states are NOT interchangeable with xlstm.blocks.mlstm step states.
  *   - packed ragged batches: cu_seqlens (device, int32, num_docs + 1 entries)
  *     lists document boundaries on the flattened (B * S) token axis; a
  *     document must not straddle two rows.  Every document starts from the
@@ -105,8 +108,13 @@ typedef struct xl_mlstm_step_params {
   const float* c_in; const float* n_in; const float* m_in;  /* state pool (NSLOT, NH, ...) */
   float* c_out; float* n_out; float* m_out;     /* c_out may alias c_in (in-place update of the large state);
                                                    n_out/m_out must not alias n_in/m_in */
-  const int32_t* slot;                          /* device (B) row of the pool per stream, or NULL = identity */
+  const int32_t* slot;                          /* device (B) row of the pool per stream, or NULL = identity.
+                                                   slot[b] < 0: stream b is inactive (its pool rows are not touched, its
+                                                   h is zero).  slot[b] >= n_slots: skipped likewise and *status = 2.
+                                                   Two active streams must not name the same row (they would race). */
+  int32_t* status;                              /* device word or NULL */
   int32_t B, NH, DHQK, DHV;
+  int32_t n_slots;                              /* rows of the state pool; used only with `slot` */
   int64_t q_sb, q_sh, k_sb, k_sh, v_sb, v_sh, h_sb, h_sh, g_sb, g_sh;
   float eps;
   int32_t dtype;
@@ -115,8 +123,9 @@ typedef struct xl_mlstm_step_params {
 int xl_mlstm_step(const xl_mlstm_step_params* p, void* cuda_stream);
 
 /* ------------------------------------------------------------------------------------------------
- * sLSTM forward over a sequence, one persistent kernel (recurrent matrix resident in shared memory,
- * one thread-block cluster per head, one cluster barrier per time step).
+ * sLSTM forward over a sequence, one persistent kernel: one thread-block cluster per (head, group of 16 batch
+ * rows), each CTA's slice of the recurrent matrix resident in registers as tensor-core fragments, the new h
+ * exchanged every time step through asynchronous distributed-shared-memory stores that complete on mbarriers.
  * Replaces sLSTMFunc.forward (xlstm/blocks/slstm/src/cuda/slstm.cc:53-135), i.e. the host loop
  * ForwardPass::Run (slstm_forward.cu:217-267) + SLSTMPointwiseForward (slstm_pointwise.cu:24-116).
  * ---------------------------------------------------------------------------------------------- */
@@ -134,7 +143,7 @@ typedef struct xl_slstm_params {
   int32_t dtype;
 } xl_slstm_params;
 
-/* Requires DH in {64,128,256} and B <= 32. */
+/* Requires DH in {64,128,256}; any B (batch rows are tiled into groups of 16), dtype XL_BF16. */
 int xl_slstm_forward(const xl_slstm_params* p, void* cuda_stream);
 
 /* ------------------------------------------------------------------------------------------------

@@ -44,8 +44,8 @@ class MlstmStepParams(C.Structure):
         ("igate", C.c_void_p), ("fgate", C.c_void_p),
         ("c_in", C.c_void_p), ("n_in", C.c_void_p), ("m_in", C.c_void_p),
         ("c_out", C.c_void_p), ("n_out", C.c_void_p), ("m_out", C.c_void_p),
-        ("slot", C.c_void_p),
-        ("B", C.c_int32), ("NH", C.c_int32), ("DHQK", C.c_int32), ("DHV", C.c_int32),
+        ("slot", C.c_void_p), ("status", C.c_void_p),
+        ("B", C.c_int32), ("NH", C.c_int32), ("DHQK", C.c_int32), ("DHV", C.c_int32), ("n_slots", C.c_int32),
         ("q_sb", C.c_int64), ("q_sh", C.c_int64), ("k_sb", C.c_int64), ("k_sh", C.c_int64),
         ("v_sb", C.c_int64), ("v_sh", C.c_int64), ("h_sb", C.c_int64), ("h_sh", C.c_int64),
         ("g_sb", C.c_int64), ("g_sh", C.c_int64),

@@ -140,6 +140,9 @@ register_kernel("step", "b200", _b200_step)
 # ------------------------------------------------------------------------------------------------
 @dataclass
 class mLSTMBackendConfig:
+    """Same fields as the upstream config.  The b200 kernels are FORWARD ONLY: the modes 'train' and
+    'train_with_padding' run them without an autograd graph, and ``mLSTMBackend.forward`` raises if an input
+    requires a gradient while gradients are enabled."""
     chunkwise_kernel: ChunkwiseKernelType = "chunkwise--b200"
     sequence_kernel: SequenceKernelType = "native_sequence__b200"
     step_kernel: StepKernelType = "b200"
@@ -193,6 +196,12 @@ class mLSTMBackend(nn.Module):
             return_last_states = self.config.return_last_states
         S = q.shape[2]
         L = self.config.chunk_size
+        if mode != "inference" and torch.is_grad_enabled() and any(
+                t is not None and t.requires_grad for t in (q, k, v, i, f, c_initial, n_initial, m_initial)):
+            if not getattr(self.chunkwise_kernel_fn, "differentiable", False):
+                raise RuntimeError(
+                    f"mLSTM kernel {self.config.chunkwise_kernel!r} is forward only (no backward kernel): run it under "
+                    "torch.no_grad() or detach the inputs; training needs a differentiable kernel")
         if mode == "train":
             if S % L != 0 and not getattr(self.chunkwise_kernel_fn, "handles_any_length", False):
                 raise ValueError(f"sequence length {S} is not a multiple of chunk_size {L}; use train_with_padding")

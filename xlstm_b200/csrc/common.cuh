@@ -34,7 +34,6 @@ __device__ __forceinline__ float log_sigmoid(float x) {
   // min(x,0) - log1p(exp(-|x|))
   return fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
 }
-__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
 
 __device__ __forceinline__ float to_float(float x) { return x; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
@@ -59,9 +58,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
-__device__ __forceinline__ void mbar_inval(uint32_t bar) {
-  asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
@@ -72,11 +68,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-#ifdef XL_WAIT_TEST
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#endif
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -93,11 +85,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if (++it > (1u << 22)) return false;
     // back off at once: warps that poll take issue slots from the warps that work (measured: 2 % of the chunkwise
     // kernel's time against polling flat out for the first 64 probes)
-#ifdef XL_WAIT_SLEEP_NS
-    __nanosleep(XL_WAIT_SLEEP_NS);
-#else
     __nanosleep(40);
-#endif
   }
   return true;
 }
@@ -138,45 +126,10 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// D[tmem] (+)= A[smem] * B[smem]; single-thread issue.
-__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Warp-uniform variants: the whole warp executes the call, one elected lane issues.  Keeping the issuing
-// code warp-uniform lets descriptor arithmetic stay on the uniform datapath, which makes back-to-back
-// UMMA issue an order of magnitude cheaper than issuing from inside a divergent `if (lane == 0)` block.
-__device__ __forceinline__ void umma_ss_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "elect.sync _|q, 0xffffffff;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_ts_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "elect.sync _|q, 0xffffffff;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
+// The UMMA wrappers are warp-uniform: the whole warp executes the call, one elected lane issues.  Keeping the issuing
+// code warp-uniform lets descriptor arithmetic stay on the uniform datapath, which makes back-to-back UMMA issue an
+// order of magnitude cheaper than issuing from inside a divergent `if (lane == 0)` block.
+// The mbarrier arrives (count 1) when all UMMAs issued before by this thread have completed.
 __device__ __forceinline__ void umma_commit_elect(uint32_t bar) {
   asm volatile(
       "{\n\t.reg .pred q;\n\t"
@@ -184,9 +137,13 @@ __device__ __forceinline__ void umma_commit_elect(uint32_t bar) {
       "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar)
       : "memory");
 }
-// Cheapest issue path: every descriptor used by the kernels has the same upper word (stride offset 1024 B,
-// version 1, 128-byte swizzle); only the lower word (start address and leading offset) varies, so it is
-// passed as a 32-bit value and advancing a tile is one 32-bit add of (bytes >> 4).
+// Shared-memory matrix descriptors, 128-byte swizzle, operand tiles built from [rows x 128 B] boxes:
+//   K-major : rows are MN indices, 8-row groups 1024 B apart (stride offset); leading offset unused.
+//   MN-major: rows are K indices (8-row groups 1024 B apart = stride offset), 64-element MN blocks one box apart
+//             (leading offset).
+// Every descriptor used by the kernels has the same upper word (stride offset 1024 B, version 1, 128-byte
+// swizzle); only the lower word (start address and leading offset) varies, so it is passed as a 32-bit value and
+// advancing a tile is one 32-bit add of (bytes >> 4).
 constexpr uint32_t UMMA_DESC_HI_SW128 = (1024u >> 4) | (1u << 14) | (2u << 29);
 __device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr, uint32_t leading_bytes) {
   return ((smem_addr & 0x3FFFFu) >> 4) | ((leading_bytes >> 4) << 16);
@@ -213,14 +170,6 @@ __device__ __forceinline__ void umma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uin
       : "memory");
 }
 
-// Descriptor of the same tile `bytes` further on (bytes must be a multiple of 16 and stay inside shared memory).
-__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t bytes) { return desc + (uint64_t)(bytes >> 4); }
-
-// mbarrier arrives (count 1) when all previously issued UMMAs of this thread have completed.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
 // Instruction descriptor for kind::f16 with bf16 operands and fp32 accumulation.
 // a_mn / b_mn: operand is MN-major (1) or K-major (0) in shared memory.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, int a_mn, int b_mn) {
@@ -228,20 +177,6 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, int a_mn, i
          | (1u << 7)                   // A format: bf16
          | (1u << 10)                  // B format: bf16
          | (uint32_t(a_mn) << 15) | (uint32_t(b_mn) << 16) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
-}
-
-// Shared-memory matrix descriptor, 128-byte swizzle, operand tiles built from [rows x 128 B] boxes.
-//   K-major : rows are MN indices, 8-row groups 1024 B apart (stride offset); leading offset unused.
-//   MN-major: rows are K indices (8-row groups 1024 B apart = stride offset), 64-element MN blocks
-//             `mn_block_bytes` apart (leading offset).
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t leading_bytes, uint32_t stride_bytes) {
-  uint64_t d = 0;
-  d |= uint64_t((smem_addr & 0x3FFFFu) >> 4);
-  d |= uint64_t((leading_bytes >> 4) & 0x3FFFu) << 16;
-  d |= uint64_t((stride_bytes >> 4) & 0x3FFFu) << 32;
-  d |= uint64_t(1) << 46;  // descriptor version (Blackwell)
-  d |= uint64_t(2) << 61;  // SWIZZLE_128B
-  return d;
 }
 
 // tcgen05.ld / st, shape 32x32b: thread i of the warp owns lane (quarter*32 + i), N consecutive columns.
@@ -269,13 +204,6 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[32]) {

@@ -28,8 +28,7 @@
 // group (one block of the T -> bf16 conversion, P from S, the terms of the denominators, n and its hi/lo operand);
 // warps 4-7 state group (the rest of the conversion / lazy rescale, w-scaled v, in the exact frame r-scaled q in
 // place in its TMA stage); warps 8-11 epilogue group (1/denominator, H^T -> normalised bf16 tile in shared memory ->
-// 16-byte global stores); warp 12 issues every UMMA; warp 13 issues the TMA loads; warp 15 only works in the
-// opt-in cluster mode.  Per chunk the tensor pipe runs phase A (H^T inter), phase B (H^T intra interleaved with
+// 16-byte global stores); warp 12 issues every UMMA; warp 13 issues the TMA loads.  Per chunk the tensor pipe runs phase A (H^T inter), phase B (H^T intra interleaved with
 // the T update) and phase C: S, nu and qn of the NEXT chunk, which need neither T nor its bf16 copy and so fill
 // the time the conversion of T takes -- the one long dependency of the loop.  Groups hand work to each other
 // through mbarriers only; every wait is bounded, and no waiter is ever more than one phase behind its producer.
@@ -46,7 +45,6 @@
 // documents are chunked from their own first token, so a chunk never straddles a document boundary and the
 // tail chunk is masked (i = -inf, log f = 0) instead of padded.
 #include <cuda.h>
-#include <cstdlib>
 
 #include "common.cuh"
 
@@ -54,7 +52,7 @@ namespace xl {
 
 constexpr int CW_L = 64;         // tokens per chunk
 constexpr int CW_DV = 128;       // value columns per CTA (UMMA M)
-constexpr int CW_THREADS = 512;  // 16 warps, see roles above
+constexpr int CW_THREADS = 480;  // 15 warps, see roles above
 constexpr int CW_STAGES = 2;
 constexpr int CW_BOX_BYTES = 64 * 128;  // one TMA box: 64 rows x 64 bf16
 constexpr uint32_t CW_TMEM_COLS = 512;
@@ -85,7 +83,7 @@ enum GateSlot {
   G_QN = G_MULT + 4,     // scale of the normaliser product
 };
 
-enum CwWarp { W_GATE_GROUP = 0, W_STATE_GROUP = 4, W_EPI_GROUP = 8, W_UMMA = 12, W_TMA = 13, W_SCAN = 14, W_SEND = 15 };
+enum CwWarp { W_GATE_GROUP = 0, W_STATE_GROUP = 4, W_EPI_GROUP = 8, W_UMMA = 12, W_TMA = 13, W_SCAN = 14 };
 
 enum CwBar {  // mbarrier indices.  Barriers whose producer may run two chunks ahead of a waiter come in pairs
               // indexed by chunk parity (a parity wait is only meaningful one phase back).  A satisfied wait
@@ -103,8 +101,6 @@ enum CwBar {  // mbarrier indices.  Barriers whose producer may run two chunks a
   BAR_NU,    // commit after phase C: nu and qn of the next chunk complete (completion k = nu(k), qn(k))
   BAR_INV,   // gate group -> epilogue group: 1/denominator published
   BAR_EGDONE,  // epilogue group -> gate group: 1/denominator consumed
-  BAR_QN0, BAR_QN1,  // split mode: partial normaliser products of all CTAs of the cluster have arrived (by chunk parity)
-  BAR_PART,          // split mode: gate group -> sender warp: this CTA's partial product is in shared memory
   BAR_COUNT
 };
 
@@ -123,7 +119,7 @@ struct CwLayout {
   static constexpr int OFF_HST = OFF_WMAT + 2 * 1024;          // [64][HST_ROW] normalised h of one chunk
   static constexpr int OFF_F32 = OFF_HST + CW_L * HST_ROW;
   static constexpr int GATE_F32 = 7 * CW_L + 8;                // per parity: see GateSlot
-  static constexpr int N_F32 = 2 * GATE_F32 + CW_L + DHQK + 2 * 4 * CW_L + 2 * 4 * CW_L + 2 * CW_L;  // + 1/denominator + n state + partial qn [2][<=4][64] + denominator terms [2][4][64] + own partial [2][64]
+  static constexpr int N_F32 = 2 * GATE_F32 + CW_L + DHQK;     // + 1/denominator + n state
   static constexpr int OFF_BAR = OFF_F32 + N_F32 * 4;          // mbarriers (8-byte aligned)
   static constexpr int TOTAL = OFF_BAR + BAR_COUNT * 8 + 16;
   static constexpr int DYN_SMEM = TOTAL + 1024;                // slack to align the base to 1024 B
@@ -147,46 +143,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 __device__ __forceinline__ float fast_log_sigmoid(float x) { return fminf(x, 0.f) - __logf(1.f + __expf(-fabsf(x))); }
-// ---- thread-block cluster helpers (split mode)
-__device__ __forceinline__ uint32_t cw_cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cw_cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t cw_map_to_cta(uint32_t smem_addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void cw_st_cluster_f32(uint32_t addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
-__device__ __forceinline__ void cw_arrive_cluster_relaxed(uint32_t remote_bar) {
-  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
-}
-__device__ __forceinline__ void cw_arrive_cluster(uint32_t remote_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
-}
-// bounded wait with cluster-scope acquire (the data the barrier guards was written by other CTAs)
-__device__ __forceinline__ bool cw_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t it = 0;
-  for (;;) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    if (++it > (1u << 22)) return false;
-    if (it > 64) __nanosleep(64);
-  }
-}
 __device__ __forceinline__ void gate_group_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ void epilogue_group_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
 
@@ -205,27 +161,7 @@ __device__ __forceinline__ uint32_t sw128_off(int row, int col) {
   return (uint32_t)(row * 128 + ((((col >> 3) ^ (row & 7)) << 4) | ((col & 7) << 1)));
 }
 
-// Optional per-role timestamps of one CTA (debug builds only; compiled out otherwise).
-#ifdef XL_CW_TIMELINE
-#ifndef XL_TL_SMSP
-#define XL_TL_SMSP 0
-#endif
-__device__ unsigned long long g_cw_timeline[5][256][16];
-__device__ unsigned long long g_cw_cta[4096][4];
-#define CW_TL(role, ev)                                                                                         \
-  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && chunk < 256 && (threadIdx.x & 31) == 0 && (warp & 3) == XL_TL_SMSP) \
-    g_cw_timeline[role][chunk][ev] = clock64();
-#define CW_TLS(role, ev)                                                                                        \
-  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && chunk < 256 && (threadIdx.x & 31) == 0) \
-    g_cw_timeline[role][chunk][ev] = clock64();
-#else
-#define CW_TL(role, ev)
-#define CW_TLS(role, ev)
-#endif
-
 // Wait used by the UMMA-issuing warp: after a first expired wait the later ones return at once.
-#define MMA_WAIT(idx, parity) (okm ? mbar_wait(bar0 + 8u * (uint32_t)(idx), (uint32_t)(parity)) : false)
-
 #define MMA_WAIT_U(idx, parity) (okm ? mbar_wait(bar_u + 8u * (uint32_t)(idx), (uint32_t)(parity)) : false)
 
 #define CW_WAIT(idx, parity)                                   \
@@ -275,18 +211,13 @@ static __device__ __noinline__ void cw_convert_T(uint32_t tC, uint32_t tCb, int 
   tc_wait_st();
 }
 
-// CS > 1 (split mode): CS neighbouring CTAs of one (document, head) -- each owns a 128-column slice of DHV -- form a
-// thread-block cluster and share the normaliser state n: each carries NKB/CS of its 64-feature blocks (their nu,
-// their share of q.n) and the partial products are summed through distributed shared memory.  The N=8 UMMAs cost a
-// full issue slot of the tensor pipe each, so this takes up to a quarter of the pipe's work per chunk away.
-template <int DHQK, int CS>
+template <int DHQK>
 __global__ void __launch_bounds__(CW_THREADS, 1)
 mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_params p) {
   using LY = CwLayout<DHQK>;
   constexpr int NKB = LY::NKB;
-  constexpr bool SPLIT = CS > 1;
-  constexpr int NB = NKB / CS;  // 64-feature blocks of n this CTA carries
-  static_assert(NKB % CS == 0 && (NB == 1 || NB == 2 || NB == 4), "feature blocks per CTA");
+  constexpr int NB = NKB;  // 64-feature blocks of the normaliser state n
+  static_assert(NB == 1 || NB == 2 || NB == 4, "feature blocks");
   extern __shared__ unsigned char cw_smem_raw[];
   // 128-byte-swizzled tiles need 1024-byte aligned bases
   // (pointer arithmetic on the __shared__ array, not an integer round trip, so that every access below is
@@ -297,10 +228,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   // gate data of a chunk, double buffered by chunk parity (see GateSlot)
   auto gate_buf = [&](int parity) { return s_f + parity * LY::GATE_F32; };
   float* s_inv = s_f + 2 * LY::GATE_F32;  // 1 / denominator of the chunk in the epilogue
-  float* s_n = s_inv + CW_L;              // n state in the lazy frame (DHQK, or this CTA's 64 in split mode)
-  float* s_qn = s_n + DHQK;               // split mode: partial q.n of every CTA of the cluster, [2][CS][64]
-  float* s_den = s_qn + 2 * 4 * CW_L;     // split mode: rowsum, lower bound, eps, q.n scale per row, [2][4][64]
-  float* s_part = s_den + 2 * 4 * CW_L;   // split mode: this CTA's partial q.n on its way to the cluster, [2][64]
+  float* s_n = s_inv + CW_L;              // n state in the lazy frame (DHQK)
   const uint32_t bar0 = sbase + LY::OFF_BAR;
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + LY::OFF_BAR + BAR_COUNT * 8);
 
@@ -310,10 +238,6 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   // plain `threadIdx.x >> 5` every UMMA becomes a ~35-instruction sequence and the issuing warp, not the tensor
   // pipe, sets the pace.
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
-#ifdef XL_CW_TIMELINE
-  const unsigned long long cta_t0 = clock64();
-  unsigned long long cta_g0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(cta_g0));
-#endif
   const int slice = blockIdx.x, head = blockIdx.y, doc = blockIdx.z;
   const int col0 = slice * CW_DV;
   const int DHV = p.DHV;
@@ -355,7 +279,6 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       if (i == BAR_GEMPTY0 || i == BAR_GEMPTY1) cnt = 256;  // state group + gate group
       if (i == BAR_A) cnt = 512;
       if (i == BAR_B) cnt = 256;
-      if (i == BAR_QN0 || i == BAR_QN1) cnt = CS;           // one arrival from the sender warp of every CTA of the cluster
       mbar_init(bar0 + 8u * i, cnt);
     }
     fence_barrier_init();
@@ -372,10 +295,8 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   }
   tc_fence_before();
   __syncthreads();
-  if (SPLIT) cw_cluster_sync();  // every CTA's barriers exist before anybody arrives on them remotely
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
-  const int rank = SPLIT ? (int)cw_cluster_rank() : 0;  // which feature blocks of n this CTA carries in split mode
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;  // tcgen05.ld/st: a warp reaches lanes 32*(warp%4)..+31
   const uint32_t tC = tmem + LY::T_C + lane_base, tCb = tmem + LY::T_CB + lane_base;
   const uint32_t tH = tmem + LY::T_H + lane_base, tS = tmem + LY::T_S + lane_base;
@@ -408,9 +329,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       const long long rem = len - (long long)chunk * CW_L;
       const int len_c = rem < CW_L ? (int)rem : CW_L;
       float* gb = gate_buf(buf);
-      CW_TLS(4, 0);
       CW_WAIT(BAR_GEMPTY0 + buf, ((uint32_t)(chunk >> 1) & 1u) ^ 1u);  // consumers of chunk-2 are done with this buffer
-      CW_TLS(4, 1);
       const float ci0 = gi0, ci1 = gi1, cf0 = gf0, cf1 = gf1;
       {
         const long long tn = (long long)(chunk + 1) * CW_L + 2 * lane;
@@ -442,7 +361,6 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       const float mu1 = fmaxf(m_prev, cmx);
       const float mu_star = __shfl_sync(0xffffffffu, mu1, 31);
       const float gsum = __shfl_sync(0xffffffffu, b1, 31);
-      CW_TLS(4, 2);
       // lazy decay frame: C = exp(rho) T
       const float cand = rho + (m_prev - mu_star);
       const bool rescale = cand < CW_RESCALE_BELOW;
@@ -491,7 +409,6 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       rho = rho_new;
       fence_proxy_async_smem();
       mbar_arrive(bar0 + 8u * (BAR_GFULL0 + buf));
-      CW_TLS(4, 3);
     }
     if (ok && slice == 0 && lane == 0) p.m_out[sidx] = m_prev;
   } else if (warp < W_STATE_GROUP) {
@@ -499,9 +416,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     // Iteration j: its half of the T -> bf16 conversion for chunk j; P(j) from S(j); then, with nu(j) and qn(j)
     // (issued one chunk ahead, behind S(j)): n(j) and its hi/lo operand for chunk j+1, and the denominators of chunk j.
     const int g = tid;  // 0..127
-    // (d counts the features this CTA carries: all of DHQK, or block `rank` in split mode)
-    const int dfirst = 64 * NB * rank;
-    for (int d = g; d < 64 * NB; d += 128) s_n[d] = p.n0 ? p.n0[sidx * DHQK + dfirst + d] : 0.f;
+    for (int d = g; d < DHQK; d += 128) s_n[d] = p.n0 ? p.n0[sidx * DHQK + d] : 0.f;
     auto publish_n = [&](int nbuf, int d, float nv) {  // hi/lo bf16 split of n[d] into rows 0/1 of the N=8 operand
       const __nv_bfloat16 hi = __float2bfloat16_rn(nv);
       const __nv_bfloat16 lo = __float2bfloat16_rn(nv - __bfloat162float(hi));
@@ -509,7 +424,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       *reinterpret_cast<__nv_bfloat16*>(box + sw128_off(0, d & 63)) = hi;
       *reinterpret_cast<__nv_bfloat16*>(box + sw128_off(1, d & 63)) = lo;
     };
-    for (int d = g; d < 64 * NB; d += 128) publish_n(0, d, s_n[d]);
+    for (int d = g; d < DHQK; d += 128) publish_n(0, d, s_n[d]);
     fence_proxy_async_smem();
     if (mbar_wait(bar0 + 8u * BAR_GFULL0, 0u)) mbar_arrive(bar0 + 8u * BAR_C2);  // n operand and gate data of chunk 0
     else ok = false;
@@ -520,9 +435,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       const int buf = chunk & 1;
       const uint32_t par = (uint32_t)chunk & 1u;
       const float* gb = gate_buf(buf);
-      CW_TL(0, 0);
       CW_WAIT(BAR_GFULL0 + buf, (uint32_t)(chunk >> 1) & 1u);
-      CW_TL(0, 1);
       const float yj = gb[G_Y + j];
       const float lower = gb[G_LOWER + j];
       const float eps_j = p.eps * gb[G_EPS + j];
@@ -535,17 +448,11 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       if (chunk >= 1) {
         CW_WAIT(BAR_HC, par ^ 1u);  // T holds chunk-1; its UMMAs no longer read the bf16 copy or the P tile
         tc_fence_after();
-        CW_TL(0, 10);
         convert_T(CB_SPLIT, DHQK / 64, cb_scale, mult);
-        CW_TL(0, 11);
         tc_fence_before();
       }
       mbar_arrive(bar0 + 8u * BAR_A);
-      CW_TL(0, 2);
-      CW_TL(0, 14);
       CW_WAIT(BAR_S, par);
-      CW_TL(0, 4);
-      CW_TL(0, 15);
       tc_fence_after();
       // ---- P from S (rows of this warp: j = 16 warp + lane for lanes 0..15)
       // Rolled over 16-column pieces on purpose (small code): piece q holds columns 16q..16q+15; this warp's rows
@@ -593,18 +500,14 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
           *reinterpret_cast<uint4*>(prow + (((2 * q + 1) ^ (j & 7)) << 4)) = o1;
         }
       }
-      CW_TL(0, 12);
       fence_proxy_async_smem();
-      CW_TL(0, 13);
       tc_fence_before();
       mbar_arrive(bar0 + 8u * BAR_B);
-      CW_TL(0, 5);
       const float rowsum = (rs[0] + rs[1]) + (rs[2] + rs[3]);
 
       // ---- n of this chunk: n = mult n + nu, published as the hi/lo operand of the next chunk (the other operand
       // buffer: this chunk's normaliser product has read its own long ago); and the normaliser product itself
       CW_WAIT(BAR_NU, par);
-      CW_TL(0, 6);
       tc_fence_after();
       float dot;
       {
@@ -615,7 +518,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         tmem_ld_x8(tS, dn);
         tc_wait_ld();
         dot = __uint_as_float(dn[0]) + __uint_as_float(dn[1]);  // lanes 16..31: row 16 warp + lane - 16
-        if constexpr (!SPLIT) dot = __shfl_down_sync(0xffffffffu, dot, 16);
+        dot = __shfl_down_sync(0xffffffffu, dot, 16);
         if (lane >= 16) {
 #pragma unroll
           for (int gq = 0; gq < NB; ++gq) {
@@ -631,31 +534,17 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       if (chunk + 1 < nchunks) CW_WAIT(BAR_GFULL0 + (buf ^ 1), (uint32_t)((chunk + 1) >> 1) & 1u);  // w operand of the next chunk
       mbar_arrive(bar0 + 8u * BAR_C2);                // phase C of this chunk may issue
       mbar_arrive(bar0 + 8u * (BAR_GEMPTY0 + buf));  // done with this chunk's gate data (so is nu, which read w)
-      CW_TL(0, 7);
       // ---- denominators: |rowsum + q.n| against the lower bound (the product sits on lanes 16..31)
       if (chunk >= 1) CW_WAIT(BAR_EGDONE, par ^ 1u);  // the epilogue group has consumed the previous ones
-      if constexpr (SPLIT) {
-        // The terms this CTA knows go to the epilogue group, its share of q.n (through the sender warp) to every CTA
-        // of the cluster, itself included: the epilogue group, which has the slack, waits for the partial products --
-        // this group never waits on another CTA.
-        if (lane < 16) {
-          float* dd = s_den + buf * 4 * CW_L + j;
-          dd[0] = rowsum; dd[CW_L] = lower; dd[2 * CW_L] = eps_j; dd[3 * CW_L] = qn_scale;
-        }
-        else s_part[buf * CW_L + 16 * warp + (lane - 16)] = dot;
-        mbar_arrive(bar0 + 8u * BAR_INV);
-        mbar_arrive(bar0 + 8u * BAR_PART);  // the sender warp takes it from here (remote stores and their fence are slow)
-      } else {
-        if (lane < 16) s_inv[j] = __fdividef(1.f, fmaxf(fabsf(fmaf(dot, qn_scale, rowsum)), lower) + eps_j);
-        mbar_arrive(bar0 + 8u * BAR_INV);
-      }
+      if (lane < 16) s_inv[j] = __fdividef(1.f, fmaxf(fabsf(fmaf(dot, qn_scale, rowsum)), lower) + eps_j);
+      mbar_arrive(bar0 + 8u * BAR_INV);
     }
     // ---- final n (back in the true frame)
-    if (ok && slice < CS && lane >= 16) {  // the first cluster of the head writes n: every CTA the blocks it carries
+    if (ok && slice == 0 && lane >= 16) {  // the first slice of the head writes n
 #pragma unroll
       for (int gq = 0; gq < NB; ++gq) {
         const int d = 64 * gq + 16 * warp + (lane - 16);
-        p.n_out[sidx * DHQK + dfirst + d] = s_n[d] * back_last;
+        p.n_out[sidx * DHQK + d] = s_n[d] * back_last;
       }
     }
   } else if (warp < W_EPI_GROUP) {
@@ -678,7 +567,6 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       const int st = chunk & 1, buf = chunk & 1;
       const uint32_t par = (uint32_t)chunk & 1u, par_full = (uint32_t)(chunk >> 1) & 1u;
       const float* gb = gate_buf(buf);
-      CW_TL(1, 1);
       CW_WAIT(BAR_GFULL0 + buf, par_full);
       const float mult = gb[G_MULT], cb_scale = gb[G_CB];
       const bool exact = gb[G_EXACT] != 0.f;
@@ -686,7 +574,6 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       const __nv_bfloat162 rr = __float2bfloat162_rn(gb[G_R + (t >> 1)]);
       const __nv_bfloat162 ww = __float2bfloat162_rn(gb[G_W + (t >> 1)]);
       if (chunk >= 1) CW_WAIT(BAR_HC, par ^ 1u);  // T holds chunk-1; its UMMAs no longer read Tb or the scaled-v tile
-      CW_TL(1, 2);
       tc_fence_after();
       // ---- T -> bf16 copy, this group's blocks (all of them for the first chunk: the gate group has not yet seen
       // the initial state land in tensor memory)
@@ -694,7 +581,6 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       tc_fence_before();
       mbar_arrive(bar0 + 8u * BAR_A);
       if (!exact) mbar_arrive(bar0 + 8u * BAR_A);  // common frame: q is used as loaded
-      CW_TL(1, 3);
       // ---- w-scaled v (thread: row l = t/2, box = t&1)
       CW_WAIT(BAR_FULL0 + st, par_full);
       {
@@ -713,12 +599,10 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       }
       fence_proxy_async_smem();
       mbar_arrive(bar0 + 8u * BAR_B);
-      CW_TL(1, 5);
       // ---- exact frame only: q <- r_j q IN PLACE in the stage tile (thread: row j = t/2, half of the row).  S of
       // this chunk, the only consumer of the un-scaled q, must have completed.
       if (exact) {
         CW_WAIT(BAR_NU, par);  // S, nu and qn of this chunk (issued one chunk ahead) no longer read q as loaded
-        CW_TL(1, 4);
         const int j = t >> 1, half = t & 1;
         unsigned char* qt = smem + LY::OFF_STAGE + st * LY::STAGE_BYTES;
         constexpr int CH = NKB * 4;              // 16-byte pieces per thread
@@ -743,7 +627,6 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       }
       mbar_arrive(bar0 + 8u * (BAR_EMPTY0 + st));
       mbar_arrive(bar0 + 8u * (BAR_GEMPTY0 + buf));
-      CW_TL(1, 6);
     }
     // ---- final C = exp(rho) T
     if (ok) {
@@ -776,17 +659,6 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     // one chunk ahead of the accumulator so that nothing stands between H^T landing and its drain.
     auto denominators_ready = [&](int c) -> bool {
       if (!mbar_wait(bar0 + 8u * BAR_INV, (uint32_t)c & 1u)) return false;
-      if constexpr (SPLIT) {
-        // from the gate group's terms and the partial normaliser products of the whole cluster
-        const int buf = c & 1, row = t & 63;
-        if (!cw_wait_cluster(bar0 + 8u * (BAR_QN0 + buf), (uint32_t)(c >> 1) & 1u)) return false;
-        float dsum = 0.f;
-#pragma unroll
-        for (int r2 = 0; r2 < CS; ++r2) dsum += s_qn[(buf * CS + r2) * CW_L + row];
-        const float* dd = s_den + buf * 4 * CW_L + row;
-        s_inv[row] = __fdividef(1.f, fmaxf(fabsf(fmaf(dsum, dd[3 * CW_L], dd[0])), dd[CW_L]) + dd[2 * CW_L]);
-        epilogue_group_sync();
-      }
       return true;
     };
     if (!denominators_ready(0)) ok = false;
@@ -796,7 +668,6 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       const long long rem = len - (long long)chunk * CW_L;
       const int len_c = rem < CW_L ? (int)rem : CW_L;
       CW_WAIT(BAR_HC, par);
-      CW_TL(2, 1);
       tc_fence_after();
       // drain, normalise and stage in two rolled passes of 32 tokens (small code)
       unsigned char* col = hst + dv * 2;
@@ -811,7 +682,6 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         if (q == 1) {  // the accumulator is in registers: free for the next chunk
           tc_fence_before();
           mbar_arrive(bar0 + 8u * BAR_A);
-          CW_TL(2, 4);
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -832,7 +702,6 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
           *reinterpret_cast<uint4*>(ho + (long long)row * p.h_st + c * 8) = *reinterpret_cast<const uint4*>(hst + row * LY::HST_ROW + c * 16);
       }
       epilogue_group_sync();  // the tile is rewritten by the next chunk
-      CW_TL(2, 3);
       if (chunk + 1 < nchunks && !denominators_ready(chunk + 1)) ok = false;
     }
   } else if (warp == W_UMMA) {
@@ -849,13 +718,10 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     constexpr uint32_t IDESC_NU = umma_idesc_bf16(64, 8, 1, 0);
     // Values that are warp-uniform in fact but not provably so (read from shared or global memory) are broadcast
     // with a shuffle: that is what lets the compiler keep UMMA operands in uniform registers.
-    // (shared-memory base for DESCRIPTORS only: the 18-bit offset inside this CTA's window.  In a cluster launch the
-    // shared address of every CTA but rank 0 carries the rank in its upper bits, which would spill into the
-    // descriptor's leading-offset field.)
+    // (shared-memory base for DESCRIPTORS only: the 18-bit offset inside this CTA's window)
     const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0), sbase_u = __shfl_sync(0xffffffffu, sbase, 0) & 0x3FFFFu;
     const uint32_t bar_u = __shfl_sync(0xffffffffu, bar0, 0);
     const int nchunks_u = __shfl_sync(0xffffffffu, nchunks, 0);
-    [[maybe_unused]] const uint32_t rank_u = (uint32_t)__shfl_sync(0xffffffffu, rank, 0);
     const uint32_t t_odd = tmem_u + LY::T_S + (16u << 16);  // odd 16-lane halves of the S columns
     // lower descriptor words (start address >> 4 | leading offset); K-major tiles use leading offset 16 B,
     // MN-major tiles one 8 KiB box
@@ -864,13 +730,11 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     // Phase C of chunk k forms everything of chunk k+1 that does not depend on the state: S, nu and qn.  It runs
     // while T is converted for chunk k+1, so the tensor pipe has work during the one long dependency of the loop.
     auto phase_c = [&](int next) {  // S(next), then nu(next) interleaved with qn(next)
-      [[maybe_unused]] const int chunk = next;  // (time stamps of this phase are filed under the chunk it prepares)
       const uint32_t nq = sbase_u + LY::OFF_STAGE + (next & 1) * LY::STAGE_BYTES, nk = nq + LY::Q_BYTES;
       const uint32_t wm = sbase_u + LY::OFF_WMAT + (next & 1) * 1024;
       const uint32_t nm = sbase_u + LY::OFF_NMAT + (next & 1) * (NB * 1024);
       okm &= MMA_WAIT_U(BAR_FULL0 + (next & 1), (uint32_t)(next >> 1) & 1u);
       okm &= MMA_WAIT_U(BAR_C2, (uint32_t)next & 1u);
-      CW_TL(3, 5);
       tc_fence_after();
 #pragma unroll 1
       for (int kb = 0; kb < NKB; ++kb)
@@ -879,8 +743,8 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
           umma_ss_lo(tmem_u + LY::T_S, (LBO_K + ((nq + kb * CW_BOX_BYTES + kk * 32) >> 4)),
                      (LBO_K + ((nk + kb * CW_BOX_BYTES + kk * 32) >> 4)), IDESC_S, (kb | kk) != 0);
       umma_commit_elect(bar_u + 8u * BAR_S);
-      // nu and q.n of the feature blocks this CTA carries (all of them unless the cluster shares the work), step by step
-      const uint32_t kblk = nk + rank_u * (NB * CW_BOX_BYTES), qblk = nq + rank_u * (NB * CW_BOX_BYTES);
+      // nu and q.n of all feature blocks, step by step
+      const uint32_t kblk = nk, qblk = nq;
 #pragma unroll 1
       for (int kb = 0; kb < NB; ++kb) {
 #pragma unroll
@@ -895,7 +759,6 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         }
       }
       umma_commit_elect(bar_u + 8u * BAR_NU);
-      CW_TL(3, 6);
     };
     phase_c(0);
 #pragma unroll 1
@@ -905,7 +768,6 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       const uint32_t s_k = stg + LY::Q_BYTES, s_v = s_k + LY::Q_BYTES;
       // ---- phase A:  H^T = Tb q^T
       okm &= MMA_WAIT_U(BAR_A, par);
-      CW_TL(3, 1);
       tc_fence_after();
 #pragma unroll 1
       for (int kb = 0; kb < NKB; ++kb)
@@ -913,10 +775,8 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         for (int kk = 0; kk < 4; ++kk)
           umma_ts_lo(tmem_u + LY::T_H, tmem_u + LY::T_CB + (4 * kb + kk) * 8,
                      (LBO_K + ((stg + kb * CW_BOX_BYTES + kk * 32) >> 4)), IDESC_HI, (kb | kk) != 0);
-      CW_TL(3, 2);
       // ---- phase B:  H^T += V^T P^T   interleaved with   T += (wV)^T K
       okm &= MMA_WAIT_U(BAR_B, par);
-      CW_TL(3, 3);
       tc_fence_after();
       {
 #pragma unroll
@@ -927,36 +787,12 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
                      (LBO_MN + ((s_k >> 4) + ((kk * 2048) >> 4))), IDESC_C, 1);
         }
       }
-      CW_TL(3, 4);
       umma_commit_elect(bar_u + 8u * BAR_HC);
       umma_commit_elect(bar_u + 8u * (BAR_EMPTY0 + (chunk & 1)));  // the stage of this chunk is consumed
       // ---- phase C for the next chunk (one branch around the whole phase, none inside the issue loops)
       if (chunk + 1 < nchunks_u) phase_c(chunk + 1);
     }
     ok = okm;
-  } else if (warp == W_SEND) {
-    // =========================================================================================== sender (split mode)
-    // Ships this CTA's partial normaliser products to every CTA of the cluster: remote stores, ONE cluster-scope
-    // fence, then one relaxed arrival per destination.  (Done by the gate group itself, with a releasing arrival per
-    // destination, this cost it ~4000 cycles per chunk.)
-    if constexpr (SPLIT) {
-#pragma unroll 1
-      for (int chunk = 0; chunk < nchunks; ++chunk) {
-        const int buf = chunk & 1;
-        CW_WAIT(BAR_PART, (uint32_t)chunk & 1u);
-        const float v0 = s_part[buf * CW_L + lane], v1 = s_part[buf * CW_L + 32 + lane];
-        const uint32_t slot = smem_u32(s_qn + (buf * CS + rank) * CW_L + lane);
-#pragma unroll
-        for (int r2 = 0; r2 < CS; ++r2) {
-          const uint32_t dst = cw_map_to_cta(slot, (uint32_t)r2);
-          cw_st_cluster_f32(dst, v0);
-          cw_st_cluster_f32(dst + 32 * 4, v1);
-        }
-        asm volatile("fence.acq_rel.cluster;" ::: "memory");
-        __syncwarp();
-        if (lane < CS) cw_arrive_cluster_relaxed(cw_map_to_cta(bar0 + 8u * (BAR_QN0 + buf), (uint32_t)lane));
-      }
-    }
   } else {
     // =========================================================================================== TMA issuer
     if (lane == 0) {
@@ -986,18 +822,10 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     __syncwarp();
   }
 
-#ifdef XL_CW_TIMELINE
-  if (tid == 0) {
-    const int lin = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-    unsigned smid; asm("mov.u32 %0, %%smid;" : "=r"(smid));
-    if (lin < 4096) { g_cw_cta[lin][0] = clock64() - cta_t0; g_cw_cta[lin][1] = smid; g_cw_cta[lin][2] = cta_t0; unsigned long long g1; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1)); g_cw_cta[lin][3] = g1 - cta_g0; }
-  }
-#endif
   if (!ok && p.status) atomicExch(p.status, 1);
   tc_fence_before();
   __syncthreads();
   if (warp == W_UMMA) tmem_dealloc(tmem, CW_TMEM_COLS);
-  if (SPLIT) cw_cluster_sync();  // nobody leaves while a peer may still write into its shared memory
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1065,53 +893,19 @@ static int make_map(CUtensorMap* m, int pos[3], const void* base, int D, int S, 
 
 int validate_seq_common(const xl_mlstm_seq_params* p);
 
-template <int DHQK, int CS>
-static int launch_chunkwise_cs(const CwMaps& maps, const xl_mlstm_seq_params* p, cudaStream_t st, dim3 grid) {
-  using LY = CwLayout<DHQK>;
-  auto kern = mlstm_chunkwise_kernel<DHQK, CS>;
-  XL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LY::DYN_SMEM));
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(CW_THREADS);
-  cfg.dynamicSmemBytes = LY::DYN_SMEM;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)CS;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = CS > 1 ? 1 : 0;
-  XL_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, maps, *p));
-  return check_launch("xl_mlstm_chunkwise");
-}
-
 template <int DHQK>
 static int launch_chunkwise(const CwMaps& maps, const xl_mlstm_seq_params* p, cudaStream_t st) {
   using LY = CwLayout<DHQK>;
   static_assert(LY::DYN_SMEM <= 227 * 1024, "shared memory budget");
   const int nd = p->cu_seqlens ? p->num_docs : p->B;
-  const int nslices = p->DHV / CW_DV;
-  dim3 grid(nslices, p->NH, nd);
-  // Cluster size: 1 unless XL_CW_CLUSTER asks for 2 or 4.  Sharing the normaliser work takes a quarter of the UMMAs
-  // away, but the CTAs of a cluster then advance in lock step (each needs every other's partial product every chunk)
-  // and on config 2 that costs more than it saves (measured 312 vs 283 us), so it stays an opt-in experiment.
-  static const int forced = [] { const char* e = getenv("XL_CW_CLUSTER"); return e ? atoi(e) : 1; }();
-  if (forced == 2 && LY::NKB % 2 == 0 && nslices % 2 == 0) return launch_chunkwise_cs<DHQK, (LY::NKB % 2 == 0 ? 2 : 1)>(maps, p, st, grid);
-  if (forced == 4 && LY::NKB % 4 == 0 && nslices % 4 == 0) return launch_chunkwise_cs<DHQK, (LY::NKB % 4 == 0 ? 4 : 1)>(maps, p, st, grid);
-  return launch_chunkwise_cs<DHQK, 1>(maps, p, st, grid);
+  dim3 grid(p->DHV / CW_DV, p->NH, nd);
+  auto kern = mlstm_chunkwise_kernel<DHQK>;
+  XL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LY::DYN_SMEM));
+  kern<<<grid, CW_THREADS, LY::DYN_SMEM, st>>>(maps, *p);
+  return check_launch("xl_mlstm_chunkwise");
 }
 
 }  // namespace xl
-
-#ifdef XL_CW_TIMELINE
-extern "C" int xl_debug_copy_cta(void* dst) {
-  return (int)cudaMemcpyFromSymbol(dst, xl::g_cw_cta, sizeof(xl::g_cw_cta));
-}
-extern "C" int xl_debug_copy_timeline(void* dst) {
-  return (int)cudaMemcpyFromSymbol(dst, xl::g_cw_timeline, sizeof(xl::g_cw_timeline));
-}
-#endif
 
 extern "C" int xl_mlstm_chunkwise(const xl_mlstm_seq_params* p, void* cuda_stream) {
   using namespace xl;

@@ -29,6 +29,14 @@ __global__ void __launch_bounds__(STEP_THREADS) mlstm_step_kernel(const xl_mlstm
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int DHQK = p.DHQK, DHV = p.DHV;
   const int64_t row = p.slot ? (int64_t)p.slot[b] : (int64_t)b;
+  if (p.slot && (row < 0 || row >= p.n_slots)) {
+    // a negative slot marks an inactive stream: nothing of the pool is touched, h is zero.  A slot beyond the pool is
+    // an error of the caller: the row is skipped all the same and the status word says so.
+    T* hz = reinterpret_cast<T*>(p.h) + b * p.h_sb + head * p.h_sh;
+    if (tid < STEP_COLS && col0 + tid < p.DHV) hz[col0 + tid] = from_float<T>(0.f);
+    if (row >= p.n_slots && tid == 0 && p.status) atomicExch(p.status, 2);
+    return;
+  }
   const int64_t sidx = row * p.NH + head;
 
   const T* q = reinterpret_cast<const T*>(p.q) + b * p.q_sb + head * p.q_sh;
@@ -132,6 +140,7 @@ extern "C" int xl_mlstm_step(const xl_mlstm_step_params* p, void* cuda_stream) {
   if (any_in && !all_in) return XL_ERR_NULL_POINTER;
   if (all_in && (p->n_in == p->n_out || p->m_in == p->m_out)) return XL_ERR_ALIASING;
   if (p->B <= 0 || p->NH <= 0 || p->DHQK <= 0 || p->DHV <= 0) return XL_ERR_BAD_SHAPE;
+  if (p->slot && p->n_slots <= 0) return XL_ERR_BAD_SHAPE;
   if (p->DHV % 4 != 0 || p->DHQK > 4096 || p->NH > 65535 || p->B > 65535) return XL_ERR_BAD_SHAPE;
   if (p->dtype != XL_F32 && p->dtype != XL_BF16) return XL_ERR_BAD_DTYPE;
   const int esz = p->dtype == XL_F32 ? 4 : 2;

@@ -228,7 +228,9 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
     if (tid == 0) mbar_expect_tx(s_bar + 8u * nxt, H_TILE_BYTES);
     // h_{t-1} complete in tile `cur` (tile 0 holds the initial state at t = 0: nothing to wait for; its barrier's
     // first phase therefore belongs to t = 2)
-    if (t >= 1 && !sl_wait(s_bar + 8u * cur, (uint32_t)((t >> 1) - (cur == 0 ? 1 : 0)) & 1u)) { ok = false; break; }
+    // (an expired wait does not leave the loop here: the decision to stop is taken by the whole CTA at the end of
+    // the step, so that no thread is left behind in the barrier there)
+    if (t >= 1 && !sl_wait(s_bar + 8u * cur, (uint32_t)((t >> 1) - (cur == 0 ? 1 : 0)) & 1u)) ok = false;
 
     // accumulators start from Wx + bias
     float acc[4][4];
@@ -296,7 +298,15 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
 #pragma unroll
     for (int i = 0; i < 4; ++i) hlast[i] = hn[i];
     cp_async_wait<SL_RING - 2>();  // this thread's part of step t+1 has landed
-    __syncthreads();               // ... and everybody else's (CTA-wide only)
+    // ... and everybody else's (CTA-wide only); the same barrier tells every thread whether any wait expired
+    if (__syncthreads_or(ok ? 0 : 1)) { ok = false; break; }
+  }
+  // The pushes of h_{S-1} are still on their way into tile S & 1 of every CTA; their completion is signalled on that
+  // tile's mbarrier only, so it is waited for (bounded) before anybody may leave: a CTA that exits while a peer's
+  // asynchronous store into its shared memory is in flight is undefined behaviour.
+  if (ok) {
+    const int last = S & 1;
+    if (!sl_wait(s_bar + 8u * last, (uint32_t)((S >> 1) - (last == 0 ? 1 : 0)) & 1u)) ok = false;
   }
   if (!ok && p.status) atomicExch(p.status, 1);
   cluster_barrier();  // nobody leaves while a peer may still push into its tile

@@ -30,6 +30,9 @@ def install_mlstm_backend() -> str:
     if existing is backend_module:
         return "shim"
     if existing is None and importlib.util.find_spec("mlstm_kernels") is not None:
+        # The upstream package is installed.  Its registries are keyed differently (module and function name split on
+        # "--"), so the b200 names are only reported as registered once they resolve through upstream's own
+        # config validation; otherwise this package's module takes the place of upstream's backend module.
         try:
             up = importlib.import_module("mlstm_kernels.torch")
             for attr, kind in (("_mlstm_chunkwise_kernel_registry", "chunkwise"), ("_mlstm_sequence_kernel_registry", "sequence"),
@@ -37,9 +40,12 @@ def install_mlstm_backend() -> str:
                 reg = getattr(up, attr, None)
                 if isinstance(reg, dict):
                     reg.update({n: f for n, f in backend_module._registry[kind].items() if "b200" in n})
+            upbm = importlib.import_module("mlstm_kernels.torch.backend_module")
+            upbm.mLSTMBackend(upbm.mLSTMBackendConfig(chunkwise_kernel="chunkwise--b200", sequence_kernel="native_sequence__b200",
+                                                      step_kernel="b200", mode="inference"))
             return "registered"
         except Exception:
-            pass
+            sys.modules.pop("mlstm_kernels.torch.backend_module", None)
     pkg = types.ModuleType("mlstm_kernels")
     pkg.__path__ = []  # mark as package
     sub = types.ModuleType("mlstm_kernels.torch")

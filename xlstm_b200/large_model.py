@@ -3,7 +3,7 @@
 The reference drives the cell kernels from ``xlstm/xlstm_large/model.py`` (embedding -> blocks of
 [RMSNorm, mLSTM layer, residual, RMSNorm, SwiGLU FFN, residual] -> RMSNorm -> lm_head -> soft cap,
 ``model.py:126-153, 379-452, 499-510``) and ``generate.py:27-90``.  That file runs unchanged on the
-kernels of this package; this mirror exists because benchmarks and GPU tests must
+kernels of this package (through ``xlstm_b200.integration``); this mirror exists because benchmarks and GPU tests must
 run where the reference checkout is not available, and because it adds what the reference has no code
 for: head-parallel execution over several GPUs (one process per GPU, NCCL all-reduce after the
 row-parallel projections) and slot-indexed states.
@@ -296,6 +296,8 @@ class LargeModel:
             out[:, i:i + 1] = last
         if use_cuda_graph and max_length > 1:
             state = self._g_state
+        if self.device.type == "cuda" and self.cell is ops:
+            ops.check_device_status(self.device)   # synchronises; surfaces a kernel whose bounded wait expired
         return out, state
 
 
@@ -372,4 +374,6 @@ class ContinuousDecoder:
             if active:
                 self._step()
         cols = torch.stack(hist, dim=1).cpu()          # (slots, steps)
+        if self.model.device.type == "cuda" and self.model.cell is ops:
+            ops.check_device_status(self.model.device)
         return [cols[spans[d][0], spans[d][1]:spans[d][1] + spans[d][2]].clone() for d in range(len(prompts))]

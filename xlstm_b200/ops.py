@@ -191,9 +191,34 @@ def mlstm_sequence_from_host(q, k, v, i, f, h_out, c_out, n_out=None, m_out=None
         cur.wait_stream(st)
 
 
+def prepare_slots(slot, B: int, n_slots: int, device) -> torch.Tensor:
+    """Pool rows of the B decode streams as the int32 device vector the step kernel reads.
+
+    A host tensor or list is checked here: one entry per stream, every entry below ``n_slots``, no row named by two
+    active streams (negative entries mark inactive streams and may repeat).  A tensor that already lives on the device
+    must be a (B,) integer vector; its values cannot be inspected without a synchronisation, so the kernel itself
+    skips entries outside the pool and reports them through the status word (``check_device_status``)."""
+    if torch.is_tensor(slot) and slot.is_cuda:
+        if slot.dim() != 1 or slot.numel() != B or slot.dtype not in (torch.int32, torch.int64):
+            raise ValueError(f"slot must be a ({B},) int32 (or int64) vector, got {tuple(slot.shape)} {slot.dtype}")
+        if slot.device != torch.device(device):
+            raise ValueError("slot lives on another device than the inputs")
+        return slot.to(torch.int32).contiguous()
+    vals = [int(x) for x in (slot.tolist() if torch.is_tensor(slot) else slot)]
+    if len(vals) != B:
+        raise ValueError(f"slot must have one entry per stream ({B}), got {len(vals)}")
+    active = [x for x in vals if x >= 0]
+    if any(x >= n_slots for x in active):
+        raise ValueError(f"slot entries must be below the pool size {n_slots}")
+    if len(set(active)) != len(active):
+        raise ValueError("two active streams name the same pool row")
+    return torch.tensor(vals, dtype=torch.int32, device=device)
+
+
 def mlstm_step(q, k, v, i, f, c, n, m, slot=None, eps: float = 1e-6, inplace: bool = True):
     """One decode step.  q,k (B,NH,DHQK), v (B,NH,DHV), i,f (B,NH[,1]); state pool c (N,NH,DHQK,DHV),
-    n (N,NH,DHQK), m (N,NH[,1]) fp32; ``slot`` (B,) int32 selects each stream's pool row (default: row b).
+    n (N,NH,DHQK), m (N,NH[,1]) fp32; ``slot`` (B,) selects each stream's pool row (default: row b; a negative
+    entry marks an inactive stream whose pool rows stay untouched; see :func:`prepare_slots`).
 
     With ``inplace`` the large C state is updated where it lives and the SAME tensor object is returned,
     so a caller that copies the returned state back into its own buffers (xlstm_large/model.py:221-225)
@@ -204,6 +229,10 @@ def mlstm_step(q, k, v, i, f, c, n, m, slot=None, eps: float = 1e-6, inplace: bo
     B, NH, DHQK = q.shape
     DHV = v.shape[-1]
     dev = q.device
+    if slot is not None:
+        if c is None:
+            raise ValueError("`slot` addresses rows of a state pool: pass c, n, m")
+        slot = prepare_slots(slot, B, c.shape[0], dev)
     q, k, v = _last_contig(q), _last_contig(k), _last_contig(v)
     i, f = _gate(i).reshape(B, NH), _gate(f).reshape(B, NH)
     if i.stride() != f.stride():
@@ -234,7 +263,8 @@ def mlstm_step(q, k, v, i, f, c, n, m, slot=None, eps: float = 1e-6, inplace: bo
         p.c_in, p.n_in, p.m_in = c.data_ptr(), n.data_ptr(), m.data_ptr()
     p.c_out, p.n_out, p.m_out = c_out.data_ptr(), n_out.data_ptr(), m_out.data_ptr()
     p.slot = slot.data_ptr() if slot is not None else None
-    p.B, p.NH, p.DHQK, p.DHV = B, NH, DHQK, DHV
+    p.status = status_word(dev).data_ptr()
+    p.B, p.NH, p.DHQK, p.DHV, p.n_slots = B, NH, DHQK, DHV, N
     p.q_sb, p.q_sh = q.stride()[:2]
     p.k_sb, p.k_sh = k.stride()[:2]
     p.v_sb, p.v_sh = v.stride()[:2]
