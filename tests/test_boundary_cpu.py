@@ -8,10 +8,7 @@ import sys
 import pytest
 import torch
 
-from conftest import ROOT, rel_l2
-
-REF = "/root/reference"
-has_ref = os.path.isdir(os.path.join(REF, "xlstm"))
+from conftest import ROOT, import_reference, rel_l2
 
 
 def test_library_exports_every_declared_symbol():
@@ -109,15 +106,11 @@ def _register_native_oracle():
     bm.register_kernel("step", "native", step)
 
 
-@pytest.mark.skipif(not has_ref, reason="reference checkout not present")
 def test_reference_model_runs_unchanged_on_the_shim():
-    """BASELINE config 1 shape, shortened: the reference's xlstm_large/model.py imports the shim, builds with
+    """The reference's small test model: its xlstm_large/model.py imports the shim, builds with
     the native triple (served by the oracle) and with the b200 names, and chunkwise == step-by-step."""
-    from xlstm_b200.integration import install_mlstm_backend
-    assert install_mlstm_backend() in ("shim", "registered")
+    import_reference()
     _register_native_oracle()
-    if REF not in sys.path:
-        sys.path.insert(0, REF)
     from xlstm.xlstm_large.model import xLSTMLarge, xLSTMLargeConfig
     torch.manual_seed(0)
     cfg = xLSTMLargeConfig(embedding_dim=128, num_heads=4, num_blocks=2, vocab_size=256, return_last_states=True,
@@ -143,10 +136,8 @@ def test_reference_model_runs_unchanged_on_the_shim():
         xLSTMLarge(xLSTMLargeConfig(embedding_dim=128, num_heads=4, num_blocks=1, vocab_size=64, step_kernel="nope"))
 
 
-@pytest.mark.skipif(not has_ref, reason="reference checkout not present")
 def test_reference_slstm_switch_accepts_b200():
-    if REF not in sys.path:
-        sys.path.insert(0, REF)
+    import_reference()
     from xlstm_b200.integration import install_slstm_backend
     cls = install_slstm_backend()
     from xlstm.blocks.slstm.cell import sLSTMCell, sLSTMCellConfig

@@ -1,6 +1,6 @@
 """Parity of the CUDA mLSTM kernels (through the C ABI) with the CPU oracle on identical seeded inputs.
 
-Tolerances (relative L2): bf16 outputs and states <= 1e-2, fp32 mode <= 1e-4 -- the bar BASELINE.json states.
+Tolerances (relative L2): bf16 outputs and states <= 1e-2, fp32 mode <= 1e-4.
 The bf16 oracle is "inputs rounded to bf16, arithmetic in fp32".
 """
 import math
@@ -94,7 +94,7 @@ def test_recurrent_fp32_matches_reference_fixtures(name):
 
 
 def test_recurrent_fp32_config1_shape():
-    """B=3, NH=4, S=256, DHQK=64, DHV=128, fp32: the cell shape of BASELINE config 1."""
+    """B=3, NH=4, S=256, DHQK=64, DHV=128, fp32: the cell shape of the small reference model (embedding 512, 4 heads)."""
     import xlstm_b200
     q, k, v, i, f = _inputs(5, 3, 4, 256, 64, 128, torch.float32)
     h_ref, st_ref = O.mlstm_chunkwise(q, k, v, i, f)
@@ -214,10 +214,11 @@ def test_packed_documents_reset_state_in_kernel(kernel, dtype, tol):
 
 
 def test_chunkwise_full_size_config2_properties():
-    """BASELINE config 2 at full size (B=4, NH=8, S=8192, DHQK=256, DHV=512, bf16).  Size-independent checks:
+    """The benchmark shape at full size (B=4, NH=8, S=8192, DHQK=256, DHV=512, bf16: xLSTM-7B heads).  Checks:
     (1) the tensor-core kernel agrees with the on-device fp32 recurrence for one (batch, head) pair,
     (2) splitting the sequence in two calls that hand the state over gives the same result,
-    (3) batch rows / heads are independent (same inputs in two rows -> identical outputs)."""
+    (3) batch rows / heads are independent (same inputs in two rows -> identical outputs),
+    (4) two full rows against the CPU oracle (h, C, n, m)."""
     import xlstm_b200
     B, NH, S, DQ, DV = 4, 8, 8192, 256, 512
     g = torch.Generator(device="cuda").manual_seed(0)
@@ -241,6 +242,13 @@ def test_chunkwise_full_size_config2_properties():
     h2, st2 = xlstm_b200.mlstm_sequence(q[:1, :, half:], k[:1, :, half:], v[:1, :, half:], i[:1, :, half:], f[:1, :, half:], *st1, kernel="chunkwise")
     assert rel_l2(torch.cat([h1, h2], 2).float(), h[:1].float()) < TOL_BF16
     assert rel_l2(st2[0], c[:1]) < TOL_BF16
+    # (4) against the CPU oracle directly: two full rows (all 8 heads, all 8192 tokens) of h and of the final C, n, m
+    for row in (1, 2):
+        h_ref, (c_ref, n_ref, m_ref) = O.mlstm_inference(q[row:row + 1].cpu(), k[row:row + 1].cpu(), v[row:row + 1].cpu(),
+                                                         i[row:row + 1].cpu(), f[row:row + 1].cpu())
+        _check(h[row:row + 1], (c[row:row + 1], n[row:row + 1], m[row:row + 1]), h_ref, (c_ref, n_ref, m_ref), TOL_BF16)
+        # no drift along the sequence: the last 512 tokens are as close as the whole row
+        assert rel_l2(h[row, :, -512:].float().cpu(), h_ref[0, :, -512:]) < TOL_BF16
 
 
 def test_prefill_from_pinned_host_buffers_equals_device_call():

@@ -68,3 +68,16 @@ def test_long_sequence_stays_in_tolerance():
     out_ref, last_ref = O.slstm_forward(wx, R, bias)
     out, last = _run(wx, R, bias)
     assert rel_l2(out, out_ref) < TOL and rel_l2(last[1], last_ref[1]) < TOL
+
+
+def test_full_length_sequence_2048_steps_against_the_oracle():
+    """The block-stack benchmark's cell shape at its full length: B=16, NH=4, DH=256, S=2048.  The kernel uses the
+    hardware exponential, logarithm and reciprocal throughout; 2048 steps must not accumulate their error."""
+    wx, R, bias, _ = _case(8, 16, 2048, 4, 256)
+    out_ref, last_ref = O.slstm_forward(wx, R, bias)
+    out, last = _run(wx, R, bias)
+    assert torch.isfinite(out).all()
+    assert rel_l2(out, out_ref) < TOL, rel_l2(out, out_ref)
+    assert rel_l2(out[:, :, -256:], out_ref[:, :, -256:]) < TOL
+    for idx in range(4):
+        assert rel_l2(last[idx], last_ref[idx]) < TOL, (idx, rel_l2(last[idx], last_ref[idx]))
