@@ -162,7 +162,11 @@ __device__ __forceinline__ uint32_t sw128_off(int row, int col) {
 }
 
 // Wait used by the UMMA-issuing warp: after a first expired wait the later ones return at once.
+#ifdef CW_MMA_SPIN
+#define MMA_WAIT_U(idx, parity) (okm ? mbar_wait_spin(bar_u + 8u * (uint32_t)(idx), (uint32_t)(parity)) : false)
+#else
 #define MMA_WAIT_U(idx, parity) (okm ? mbar_wait(bar_u + 8u * (uint32_t)(idx), (uint32_t)(parity)) : false)
+#endif
 
 #define CW_WAIT(idx, parity)                                   \
   if (!mbar_wait(bar0 + 8u * (uint32_t)(idx), (uint32_t)(parity))) { \
@@ -286,8 +290,9 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     tma_prefetch_desc(&maps.k);
     tma_prefetch_desc(&maps.v);
   }
-  for (int i = tid; i < (2 * NKB * 1024 + 2 * 1024) / 16; i += CW_THREADS)
-    reinterpret_cast<uint4*>(smem + LY::OFF_NMAT)[i] = make_uint4(0u, 0u, 0u, 0u);
+  // OFF_P .. OFF_HST: the P tile (its blocks right of the diagonal stay zero for ever) and the N=8 operands
+  for (int i = tid; i < (LY::OFF_HST - LY::OFF_P) / 16; i += CW_THREADS)
+    reinterpret_cast<uint4*>(smem + LY::OFF_P)[i] = make_uint4(0u, 0u, 0u, 0u);
   if (warp == W_UMMA) {
     __syncwarp();
     tmem_alloc(smem_u32(s_tmem), CW_TMEM_COLS);
@@ -303,9 +308,8 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
   const float qscale = rsqrtf((float)DHQK);
   bool ok = true;
   auto convert_T = [&](int b0, int b1, float cb_scale, float mult) { cw_convert_T(tC, tCb, b0, b1, cb_scale, mult); };
-  // blocks [0, CB_SPLIT) state group, [CB_SPLIT, DHQK/64) gate group.  The gate group takes one block only: the phase
-  // of UMMAs that runs meanwhile is longer than three blocks take, and the gate group's P pass -- next on the critical
-  // path, it gates phase B -- starts that much earlier.
+  // blocks [0, CB_SPLIT) state group, [CB_SPLIT, DHQK/64) epilogue group (one block: it has the slack; the gate
+  // group, whose P pass gates phase B, converts nothing).
   constexpr int CB_SPLIT = DHQK / 64 >= 2 ? DHQK / 64 - 1 : 1;
 
   if (warp == W_SCAN) {
@@ -428,7 +432,9 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     fence_proxy_async_smem();
     if (mbar_wait(bar0 + 8u * BAR_GFULL0, 0u)) mbar_arrive(bar0 + 8u * BAR_C2);  // n operand and gate data of chunk 0
     else ok = false;
-    const int j = warp * 16 + (lane & 15);  // S row of this thread (lanes 0..15); lanes 16..31 see the N=8 products
+    // S fragment of this thread: rows j0 and j0 + 8, column pair cq of every 8-column group; the N=8 products sit on
+    // lanes 16..31 of the plain (lane = thread) view
+    const int j0 = warp * 16 + (lane >> 2), cq = 2 * (lane & 3);
     float back_last = 1.f;
 #pragma unroll 1
     for (int chunk = 0; chunk < nchunks; ++chunk) {
@@ -436,74 +442,71 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       const uint32_t par = (uint32_t)chunk & 1u;
       const float* gb = gate_buf(buf);
       CW_WAIT(BAR_GFULL0 + buf, (uint32_t)(chunk >> 1) & 1u);
-      const float yj = gb[G_Y + j];
-      const float lower = gb[G_LOWER + j];
-      const float eps_j = p.eps * gb[G_EPS + j];
-      const float mult = gb[G_MULT], cb_scale = gb[G_CB];
+      const float y0 = gb[G_Y + j0], y1 = gb[G_Y + j0 + 8];
+      const float mult = gb[G_MULT];
       const bool exact = gb[G_EXACT] != 0.f;
       // the normaliser product is formed from q as loaded: its scale is the row's r_j in the exact frame
-      const float qn_scale = exact ? gb[G_R + j] : gb[G_QN];
+      const int jd = j0 + 8 * (lane & 1);  // the row whose denominator this thread writes (lanes 4i and 4i + 1)
+      const float lower = gb[G_LOWER + jd];
+      const float eps_j = p.eps * gb[G_EPS + jd];
+      const float qn_scale = exact ? gb[G_R + jd] : gb[G_QN];
       if (chunk + 1 == nchunks) back_last = expf(gb[G_RHO]);
-      // ---- T -> bf16 copy, this group's blocks (the state group converts everything for the first chunk)
-      if (chunk >= 1) {
-        CW_WAIT(BAR_HC, par ^ 1u);  // T holds chunk-1; its UMMAs no longer read the bf16 copy or the P tile
-        tc_fence_after();
-        convert_T(CB_SPLIT, DHQK / 64, cb_scale, mult);
-        tc_fence_before();
-      }
-      mbar_arrive(bar0 + 8u * BAR_A);
+      // S of this chunk complete.  The tensor pipe completes in order, so phase B of the previous chunk is complete as
+      // well: its UMMAs no longer read the P tile.
       CW_WAIT(BAR_S, par);
       tc_fence_after();
-      // ---- P from S (rows of this warp: j = 16 warp + lane for lanes 0..15)
-      // Rolled over 16-column pieces on purpose (small code): piece q holds columns 16q..16q+15; this warp's rows
-      // 16w..16w+15 need pieces 0..w (piece w straddles the diagonal), the others are zero.
-      float rs[4] = {0.f, 0.f, 0.f, 0.f};
-      unsigned char* prow = smem + LY::OFF_P + j * 128;
-#pragma unroll 1
-      for (int q = 0; q < 4; ++q) {
-        uint4 o0 = make_uint4(0u, 0u, 0u, 0u), o1 = o0;
-        if (q <= warp) {  // warp-uniform
-          uint32_t sv[16];
-          tmem_ld_x16(tS + 16 * q, sv);
-          float4 z4[4];
+      // ---- P from S.  One fragment load brings this warp's 16 rows x 64 columns of S to all 32 lanes (shape 16x256b:
+      // thread t holds rows j0 = 16 warp + t/4 and j0 + 8, columns 8g + 2 (t%4) + {0,1} of every 8-column group g), so
+      // the pass is one tensor-memory round trip instead of one per 16-column piece and no lane idles.  Rows 16w..16w+15
+      // need groups 0..2w+1 (the last two straddle the diagonal); the groups to their right are zero for ever
+      // (written once at set-up).
+      float rs0 = 0.f, rs1 = 0.f;
+      {
+        uint32_t sv[32];
+        tmem_ld_16x256b_x8(tS, sv);
+        unsigned char* prow0 = smem + LY::OFF_P + j0 * 128 + 2 * cq;
+        unsigned char* prow1 = prow0 + 8 * 128;
+        tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 4; ++i) z4[i] = *reinterpret_cast<const float4*>(gb + G_Z + 16 * q + 4 * i);
-          const float zv[16] = {z4[0].x, z4[0].y, z4[0].z, z4[0].w, z4[1].x, z4[1].y, z4[1].z, z4[1].w,
-                                z4[2].x, z4[2].y, z4[2].z, z4[2].w, z4[3].x, z4[3].y, z4[3].z, z4[3].w};
-          float e[16];
-          if (exact) {
-            float4 a4[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) a4[i] = *reinterpret_cast<const float4*>(gb + G_X + 16 * q + 4 * i);
-            const float av[16] = {a4[0].x, a4[0].y, a4[0].z, a4[0].w, a4[1].x, a4[1].y, a4[1].z, a4[1].w,
-                                  a4[2].x, a4[2].y, a4[2].z, a4[2].w, a4[3].x, a4[3].y, a4[3].z, a4[3].w};
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float x = __uint_as_float(sv[i]) * qscale * ex2_approx(av[i] - yj);
-              e[i] = (16 * q + i <= j) ? x : 0.f;
+        for (int g = 0; g < 8; ++g) {
+          if (g <= 2 * warp + 1) {  // warp-uniform
+            float e00, e01, e10, e11;
+            if (exact) {
+              const float2 a = *reinterpret_cast<const float2*>(gb + G_X + 8 * g + cq);
+              e00 = __uint_as_float(sv[4 * g + 0]) * qscale * ex2_approx(a.x - y0);
+              e01 = __uint_as_float(sv[4 * g + 1]) * qscale * ex2_approx(a.y - y0);
+              e10 = __uint_as_float(sv[4 * g + 2]) * qscale * ex2_approx(a.x - y1);
+              e11 = __uint_as_float(sv[4 * g + 3]) * qscale * ex2_approx(a.y - y1);
+            } else {
+              const float2 z = *reinterpret_cast<const float2*>(gb + G_Z + 8 * g + cq);
+              e00 = __uint_as_float(sv[4 * g + 0]) * z.x;
+              e01 = __uint_as_float(sv[4 * g + 1]) * z.y;
+              e10 = __uint_as_float(sv[4 * g + 2]) * z.x;
+              e11 = __uint_as_float(sv[4 * g + 3]) * z.y;
             }
-          } else {
-            tc_wait_ld();
-            const int lim = (q < warp) ? 64 : j;  // pieces left of the diagonal piece need no mask
-#pragma unroll
-            for (int i = 0; i < 16; ++i) e[i] = (16 * q + i <= lim) ? __uint_as_float(sv[i]) * zv[i] : 0.f;
+            if (g >= 2 * warp) {  // the 16 x 16 block on the diagonal: causal mask
+              const int c = 8 * g + cq;
+              e00 = (c <= j0) ? e00 : 0.f;
+              e01 = (c + 1 <= j0) ? e01 : 0.f;
+              e10 = (c <= j0 + 8) ? e10 : 0.f;
+              e11 = (c + 1 <= j0 + 8) ? e11 : 0.f;
+            }
+            // (row sums from the unrounded values: the difference to the bf16 P is below the bf16 rounding of h)
+            rs0 += e00 + e01;
+            rs1 += e10 + e11;
+            const uint32_t sw = (uint32_t)((g ^ (j0 & 7)) << 4);  // (j0 + 8) & 7 == j0 & 7
+            *reinterpret_cast<uint32_t*>(prow0 + sw) = pack_bf16x2(e00, e01);
+            *reinterpret_cast<uint32_t*>(prow1 + sw) = pack_bf16x2(e10, e11);
           }
-          o0 = make_uint4(pack_bf16x2(e[0], e[1]), pack_bf16x2(e[2], e[3]), pack_bf16x2(e[4], e[5]), pack_bf16x2(e[6], e[7]));
-          o1 = make_uint4(pack_bf16x2(e[8], e[9]), pack_bf16x2(e[10], e[11]), pack_bf16x2(e[12], e[13]), pack_bf16x2(e[14], e[15]));
-          // (row sums from the unrounded values: the difference to the bf16 P is below the bf16 rounding of h)
-#pragma unroll
-          for (int i = 0; i < 16; ++i) rs[i & 3] += e[i];
-        }
-        if (lane < 16) {
-          *reinterpret_cast<uint4*>(prow + (((2 * q) ^ (j & 7)) << 4)) = o0;
-          *reinterpret_cast<uint4*>(prow + (((2 * q + 1) ^ (j & 7)) << 4)) = o1;
         }
       }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(bar0 + 8u * BAR_B);
-      const float rowsum = (rs[0] + rs[1]) + (rs[2] + rs[3]);
+      rs0 += __shfl_xor_sync(0xffffffffu, rs0, 1);
+      rs0 += __shfl_xor_sync(0xffffffffu, rs0, 2);
+      rs1 += __shfl_xor_sync(0xffffffffu, rs1, 1);
+      rs1 += __shfl_xor_sync(0xffffffffu, rs1, 2);
 
       // ---- n of this chunk: n = mult n + nu, published as the hi/lo operand of the next chunk (the other operand
       // buffer: this chunk's normaliser product has read its own long ago); and the normaliser product itself
@@ -518,7 +521,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         tmem_ld_x8(tS, dn);
         tc_wait_ld();
         dot = __uint_as_float(dn[0]) + __uint_as_float(dn[1]);  // lanes 16..31: row 16 warp + lane - 16
-        dot = __shfl_down_sync(0xffffffffu, dot, 16);
+        dot = __shfl_sync(0xffffffffu, dot, 16 + (lane >> 2) + 8 * (lane & 1));  // ... to the thread that owns row jd
         if (lane >= 16) {
 #pragma unroll
           for (int gq = 0; gq < NB; ++gq) {
@@ -536,7 +539,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       mbar_arrive(bar0 + 8u * (BAR_GEMPTY0 + buf));  // done with this chunk's gate data (so is nu, which read w)
       // ---- denominators: |rowsum + q.n| against the lower bound (the product sits on lanes 16..31)
       if (chunk >= 1) CW_WAIT(BAR_EGDONE, par ^ 1u);  // the epilogue group has consumed the previous ones
-      if (lane < 16) s_inv[j] = __fdividef(1.f, fmaxf(fabsf(fmaf(dot, qn_scale, rowsum)), lower) + eps_j);
+      if ((lane & 2) == 0) s_inv[jd] = __fdividef(1.f, fmaxf(fabsf(fmaf(dot, qn_scale, (lane & 1) ? rs1 : rs0)), lower) + eps_j);
       mbar_arrive(bar0 + 8u * BAR_INV);
     }
     // ---- final n (back in the true frame)
@@ -655,6 +658,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     unsigned char* hst = smem + LY::OFF_HST;
     __nv_bfloat16* hbase = reinterpret_cast<__nv_bfloat16*>(p.h) + b * p.h_sb + head * p.h_sh + tok0 * p.h_st + col0;
     mbar_arrive(bar0 + 8u * BAR_A);  // the accumulator is free for chunk 0
+    mbar_arrive(bar0 + 8u * BAR_A);  // (this group's share of the T -> bf16 copy: the state group converts all of it for chunk 0)
     // Denominators of chunk c, ready long before H^T(c) is (they depend on the previous phase of UMMAs only): taken
     // one chunk ahead of the accumulator so that nothing stands between H^T landing and its drain.
     auto denominators_ready = [&](int c) -> bool {
@@ -669,6 +673,14 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       const int len_c = rem < CW_L ? (int)rem : CW_L;
       CW_WAIT(BAR_HC, par);
       tc_fence_after();
+      // ---- this group's block of the T -> bf16 copy for the NEXT chunk (T holds this chunk now)
+      if (chunk + 1 < nchunks) {
+        CW_WAIT(BAR_GFULL0 + ((chunk + 1) & 1), (uint32_t)((chunk + 1) >> 1) & 1u);
+        const float* gbn = gate_buf((chunk + 1) & 1);
+        convert_T(CB_SPLIT, DHQK / 64, gbn[G_CB], gbn[G_MULT]);
+        tc_fence_before();
+        mbar_arrive(bar0 + 8u * BAR_A);
+      }
       // drain, normalise and stage in two rolled passes of 32 tokens (small code)
       unsigned char* col = hst + dv * 2;
 #pragma unroll 1
