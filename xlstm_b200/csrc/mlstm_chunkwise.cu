@@ -92,7 +92,7 @@ enum CwBar {  // mbarrier indices.  Barriers whose producer may run two chunks a
   BAR_FULL0 = 0, BAR_FULL1, BAR_EMPTY0, BAR_EMPTY1,   // TMA stage of q,k,v: landed / consumed
   BAR_GFULL0, BAR_GFULL1, BAR_GEMPTY0, BAR_GEMPTY1,   // gate data of a chunk: published / consumed
   BAR_A,     // phase A may issue: bf16 copy of T (state + gate group), q final (state group), H^T drained
-             // (epilogue group): 4 x 128 arrivals
+             // (epilogue group), its block of the bf16 copy (epilogue group): 4 x 128 arrivals
   BAR_B,     // phase B may issue: P (gate group), w-scaled v (state group): 2 x 128 arrivals
   BAR_C2,    // phase C may issue (gate group): n operand of the next chunk published, nu and qn columns read,
              // gate data of the next chunk visible.  Completion k+1 comes from the gate group's iteration k.
@@ -101,6 +101,8 @@ enum CwBar {  // mbarrier indices.  Barriers whose producer may run two chunks a
   BAR_NU,    // commit after phase C: nu and qn of the next chunk complete (completion k = nu(k), qn(k))
   BAR_INV,   // gate group -> epilogue group: 1/denominator published
   BAR_EGDONE,  // epilogue group -> gate group: 1/denominator consumed
+  BAR_QNREAD,  // gate group -> epilogue group: q.n of a chunk is in registers (its columns may take the bf16 copy again)
+  BAR_TINIT,   // state group -> epilogue group: the initial state is in tensor memory
   BAR_COUNT
 };
 
@@ -108,13 +110,19 @@ template <int DHQK>
 struct CwLayout {
   static constexpr int NKB = DHQK / 64;                       // 64-wide boxes along DHQK
   static constexpr int Q_BYTES = NKB * CW_BOX_BYTES;
+  // k: 1 KiB in FRONT of every 64-feature box holds eight more rows for the S product, [n_hi; n_lo; 0 x 6] of that
+  // feature block: S and the normaliser product q.n come out of ONE UMMA with N = 72 (an N = 8 UMMA of its own costs
+  // the pipe as much as the N = 64 one)
+  static constexpr int K_STRIDE = CW_BOX_BYTES + 1024;
+  static constexpr int K_BYTES = NKB * K_STRIDE;
   static constexpr int V_BYTES = 2 * CW_BOX_BYTES;
-  static constexpr int STAGE_BYTES = 2 * Q_BYTES + V_BYTES;    // q, k, v of one chunk
+  static constexpr int OFF_K = Q_BYTES, OFF_V = Q_BYTES + K_BYTES;   // within a stage
+  static constexpr int STAGE_BYTES = Q_BYTES + K_BYTES + V_BYTES;    // q, k (+ n rows), v of one chunk
+  static constexpr int TX_BYTES = 2 * Q_BYTES + V_BYTES;             // what TMA delivers per stage
   static constexpr int OFF_STAGE = 0;
   static constexpr int OFF_VH = CW_STAGES * STAGE_BYTES;       // w_l-scaled v
   static constexpr int OFF_P = OFF_VH + V_BYTES;               // P tile
-  static constexpr int OFF_NMAT = OFF_P + CW_BOX_BYTES;        // 2 x [8 x DHQK] bf16: rows n_hi, n_lo, zeros
-  static constexpr int OFF_WMAT = OFF_NMAT + 2 * NKB * 1024;      // 2 x [8 x 64] bf16: rows w_hi, w_lo, zeros
+  static constexpr int OFF_WMAT = OFF_P + CW_BOX_BYTES;        // 2 x [8 x 64] bf16: rows w_hi, w_lo, zeros
   static constexpr int HST_ROW = CW_DV * 2 + 16;               // staged h row: 128 bf16 + 16 B pad
   static constexpr int OFF_HST = OFF_WMAT + 2 * 1024;          // [64][HST_ROW] normalised h of one chunk
   static constexpr int OFF_F32 = OFF_HST + CW_L * HST_ROW;
@@ -123,11 +131,17 @@ struct CwLayout {
   static constexpr int OFF_BAR = OFF_F32 + N_F32 * 4;          // mbarriers (8-byte aligned)
   static constexpr int TOTAL = OFF_BAR + BAR_COUNT * 8 + 16;
   static constexpr int DYN_SMEM = TOTAL + 1024;                // slack to align the base to 1024 B
-  // tensor-memory column map
+  // tensor-memory column map (512 columns, all used at DHQK = 256)
   static constexpr uint32_t T_C = 0;            // T (C^T in the lazy frame), fp32   DHQK columns
-  static constexpr uint32_t T_CB = 256;         // bf16 copy of T                    DHQK/2 columns
-  static constexpr uint32_t T_H = 384;          // H^T accumulator                   64 columns
-  static constexpr uint32_t T_S = 448;          // S (even 16-lane halves); qn, nu (odd halves)
+  static constexpr uint32_t T_H = 256;          // H^T accumulator                   64 columns
+  static constexpr uint32_t T_CB = 320;         // bf16 copy of T                    DHQK/2 columns
+  static constexpr uint32_t T_S = 448;          // S (even 16-lane halves); nu (odd halves)
+  // The S product is 72 columns wide, [q.n | S], and starts eight columns BEFORE T_S.  At DHQK = 256 those eight
+  // columns are the last eight of the bf16 copy (features 240..255).  The two uses alternate in time: the copy is read
+  // by phase A of a chunk, [q.n | S] of the NEXT chunk is issued behind that phase, the gate group takes q.n out as
+  // soon as it is complete, and only then does the epilogue group store the last eight columns of the next copy.
+  static constexpr uint32_t T_SX = T_S - 8;
+  static constexpr bool TAIL_SHARED = (T_CB + DHQK / 2 > T_SX);
 };
 
 struct CwMaps {
@@ -290,9 +304,15 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     tma_prefetch_desc(&maps.k);
     tma_prefetch_desc(&maps.v);
   }
-  // OFF_P .. OFF_HST: the P tile (its blocks right of the diagonal stay zero for ever) and the N=8 operands
+  // OFF_P .. OFF_HST: the P tile (its blocks right of the diagonal stay zero for ever) and the w operand of nu
   for (int i = tid; i < (LY::OFF_HST - LY::OFF_P) / 16; i += CW_THREADS)
     reinterpret_cast<uint4*>(smem + LY::OFF_P)[i] = make_uint4(0u, 0u, 0u, 0u);
+  // the eight extra B rows in front of every k box (rows 2..7 stay zero)
+  for (int i = tid; i < CW_STAGES * NKB * (1024 / 16); i += CW_THREADS) {
+    const int g = i / (1024 / 16);
+    reinterpret_cast<uint4*>(smem + LY::OFF_STAGE + (g / NKB) * LY::STAGE_BYTES + LY::OFF_K + (g % NKB) * LY::K_STRIDE)[i % (1024 / 16)] =
+        make_uint4(0u, 0u, 0u, 0u);
+  }
   if (warp == W_UMMA) {
     __syncwarp();
     tmem_alloc(smem_u32(s_tmem), CW_TMEM_COLS);
@@ -417,23 +437,26 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     if (ok && slice == 0 && lane == 0) p.m_out[sidx] = m_prev;
   } else if (warp < W_STATE_GROUP) {
     // =========================================================================================== gate group
-    // Iteration j: its half of the T -> bf16 conversion for chunk j; P(j) from S(j); then, with nu(j) and qn(j)
-    // (issued one chunk ahead, behind S(j)): n(j) and its hi/lo operand for chunk j+1, and the denominators of chunk j.
+    // Iteration j: q.n(j) and S(j) out of tensor memory, P(j); then, with nu(j) (issued one chunk ahead, behind S(j)):
+    // n(j) and its hi/lo rows for the S product of chunk j+1, and the denominators of chunk j.
     const int g = tid;  // 0..127
     for (int d = g; d < DHQK; d += 128) s_n[d] = p.n0 ? p.n0[sidx * DHQK + d] : 0.f;
-    auto publish_n = [&](int nbuf, int d, float nv) {  // hi/lo bf16 split of n[d] into rows 0/1 of the N=8 operand
+    // hi/lo bf16 split of n[d] into rows 0/1 in front of the k box of feature block d/64 in stage `nbuf`, where the S
+    // product of that stage's chunk picks them up as eight more B rows
+    auto publish_n = [&](int nbuf, int d, float nv) {
       const __nv_bfloat16 hi = __float2bfloat16_rn(nv);
       const __nv_bfloat16 lo = __float2bfloat16_rn(nv - __bfloat162float(hi));
-      unsigned char* box = smem + LY::OFF_NMAT + nbuf * (NB * 1024) + (d >> 6) * 1024;
+      unsigned char* box = smem + LY::OFF_STAGE + nbuf * LY::STAGE_BYTES + LY::OFF_K + (d >> 6) * LY::K_STRIDE;
       *reinterpret_cast<__nv_bfloat16*>(box + sw128_off(0, d & 63)) = hi;
       *reinterpret_cast<__nv_bfloat16*>(box + sw128_off(1, d & 63)) = lo;
     };
     for (int d = g; d < DHQK; d += 128) publish_n(0, d, s_n[d]);
     fence_proxy_async_smem();
-    if (mbar_wait(bar0 + 8u * BAR_GFULL0, 0u)) mbar_arrive(bar0 + 8u * BAR_C2);  // n operand and gate data of chunk 0
+    if (mbar_wait(bar0 + 8u * BAR_GFULL0, 0u)) mbar_arrive(bar0 + 8u * BAR_C2);  // n rows and gate data of chunk 0
     else ok = false;
-    // S fragment of this thread: rows j0 and j0 + 8, column pair cq of every 8-column group; the N=8 products sit on
-    // lanes 16..31 of the plain (lane = thread) view
+    // S fragment of this thread: rows j0 and j0 + 8, column pair cq of every 8-column group (q.n is the group in front
+    // of S: the threads with cq == 0 hold its hi and lo part); the nu products sit on lanes 16..31 of the plain
+    // (lane = thread) view
     const int j0 = warp * 16 + (lane >> 2), cq = 2 * (lane & 3);
     float back_last = 1.f;
 #pragma unroll 1
@@ -460,37 +483,47 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       // the pass is one tensor-memory round trip instead of one per 16-column piece and no lane idles.  Rows 16w..16w+15
       // need groups 0..2w+1 (the last two straddle the diagonal); the groups to their right are zero for ever
       // (written once at set-up).
-      float rs0 = 0.f, rs1 = 0.f;
+      float rs0 = 0.f, rs1 = 0.f, dot;
       {
-        uint32_t sv[32];
+        uint32_t sv[32], dn[4];
+        tmem_ld_16x256b_x1(tS - 8, dn);
         tmem_ld_16x256b_x8(tS, sv);
+        // the per-column factors of all eight groups are fetched up front, outside any branch: inside the branches below
+        // every load would wait out its shared-memory latency on its own, eight times in a row
+        float2 zz[8];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) zz[g] = *reinterpret_cast<const float2*>(gb + (exact ? G_X : G_Z) + 8 * g + cq);
         unsigned char* prow0 = smem + LY::OFF_P + j0 * 128 + 2 * cq;
         unsigned char* prow1 = prow0 + 8 * 128;
         tc_wait_ld();
+        tc_fence_before();
+        mbar_arrive(bar0 + 8u * BAR_QNREAD);  // the q.n columns may take the tail of the bf16 copy again
+        // q.n of rows j0 (registers 0, 1) and j0 + 8 (registers 2, 3) in the threads with cq == 0; the thread next to it
+        // takes the second row (jd)
+        const float d0 = __uint_as_float(dn[0]) + __uint_as_float(dn[1]), d1 = __uint_as_float(dn[2]) + __uint_as_float(dn[3]);
+        const float d1n = __shfl_sync(0xffffffffu, d1, lane & ~3);
+        dot = (lane & 1) ? d1n : d0;
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
           if (g <= 2 * warp + 1) {  // warp-uniform
             float e00, e01, e10, e11;
             if (exact) {
-              const float2 a = *reinterpret_cast<const float2*>(gb + G_X + 8 * g + cq);
-              e00 = __uint_as_float(sv[4 * g + 0]) * qscale * ex2_approx(a.x - y0);
-              e01 = __uint_as_float(sv[4 * g + 1]) * qscale * ex2_approx(a.y - y0);
-              e10 = __uint_as_float(sv[4 * g + 2]) * qscale * ex2_approx(a.x - y1);
-              e11 = __uint_as_float(sv[4 * g + 3]) * qscale * ex2_approx(a.y - y1);
+              e00 = __uint_as_float(sv[4 * g + 0]) * qscale * ex2_approx(zz[g].x - y0);
+              e01 = __uint_as_float(sv[4 * g + 1]) * qscale * ex2_approx(zz[g].y - y0);
+              e10 = __uint_as_float(sv[4 * g + 2]) * qscale * ex2_approx(zz[g].x - y1);
+              e11 = __uint_as_float(sv[4 * g + 3]) * qscale * ex2_approx(zz[g].y - y1);
             } else {
-              const float2 z = *reinterpret_cast<const float2*>(gb + G_Z + 8 * g + cq);
-              e00 = __uint_as_float(sv[4 * g + 0]) * z.x;
-              e01 = __uint_as_float(sv[4 * g + 1]) * z.y;
-              e10 = __uint_as_float(sv[4 * g + 2]) * z.x;
-              e11 = __uint_as_float(sv[4 * g + 3]) * z.y;
+              e00 = __uint_as_float(sv[4 * g + 0]) * zz[g].x;
+              e01 = __uint_as_float(sv[4 * g + 1]) * zz[g].y;
+              e10 = __uint_as_float(sv[4 * g + 2]) * zz[g].x;
+              e11 = __uint_as_float(sv[4 * g + 3]) * zz[g].y;
             }
-            if (g >= 2 * warp) {  // the 16 x 16 block on the diagonal: causal mask
-              const int c = 8 * g + cq;
-              e00 = (c <= j0) ? e00 : 0.f;
-              e01 = (c + 1 <= j0) ? e01 : 0.f;
-              e10 = (c <= j0 + 8) ? e10 : 0.f;
-              e11 = (c + 1 <= j0 + 8) ? e11 : 0.f;
-            }
+            // causal mask (only the two groups on the diagonal lose anything to it)
+            const int c = 8 * g + cq;
+            e00 = (c <= j0) ? e00 : 0.f;
+            e01 = (c + 1 <= j0) ? e01 : 0.f;
+            e10 = (c <= j0 + 8) ? e10 : 0.f;
+            e11 = (c + 1 <= j0 + 8) ? e11 : 0.f;
             // (row sums from the unrounded values: the difference to the bf16 P is below the bf16 rounding of h)
             rs0 += e00 + e01;
             rs1 += e10 + e11;
@@ -508,20 +541,16 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       rs1 += __shfl_xor_sync(0xffffffffu, rs1, 1);
       rs1 += __shfl_xor_sync(0xffffffffu, rs1, 2);
 
-      // ---- n of this chunk: n = mult n + nu, published as the hi/lo operand of the next chunk (the other operand
-      // buffer: this chunk's normaliser product has read its own long ago); and the normaliser product itself
+      // ---- n of this chunk: n = mult n + nu, published as the hi/lo rows of the next chunk's stage (the S product of
+      // the chunk that used that stage before has read its own long ago)
       CW_WAIT(BAR_NU, par);
       tc_fence_after();
-      float dot;
       {
-        uint32_t r[8 * NB], dn[8];
+        uint32_t r[8 * NB];
         if constexpr (NB == 1) tmem_ld_x8(tS + 8, r);
         else if constexpr (NB == 2) tmem_ld_x16(tS + 8, r);
         else tmem_ld_x32(tS + 8, r);
-        tmem_ld_x8(tS, dn);
         tc_wait_ld();
-        dot = __uint_as_float(dn[0]) + __uint_as_float(dn[1]);  // lanes 16..31: row 16 warp + lane - 16
-        dot = __shfl_sync(0xffffffffu, dot, 16 + (lane >> 2) + 8 * (lane & 1));  // ... to the thread that owns row jd
         if (lane >= 16) {
 #pragma unroll
           for (int gq = 0; gq < NB; ++gq) {
@@ -564,6 +593,8 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       tmem_st_x32(tC + cb * 32, r);
     }
     tc_wait_st();
+    tc_fence_before();
+    mbar_arrive(bar0 + 8u * BAR_TINIT);  // the epilogue group converts its block of the initial state
     float rho_last = 0.f;
 #pragma unroll 1
     for (int chunk = 0; chunk < nchunks; ++chunk) {
@@ -578,9 +609,8 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       const __nv_bfloat162 ww = __float2bfloat162_rn(gb[G_W + (t >> 1)]);
       if (chunk >= 1) CW_WAIT(BAR_HC, par ^ 1u);  // T holds chunk-1; its UMMAs no longer read Tb or the scaled-v tile
       tc_fence_after();
-      // ---- T -> bf16 copy, this group's blocks (all of them for the first chunk: the gate group has not yet seen
-      // the initial state land in tensor memory)
-      convert_T(0, chunk == 0 ? DHQK / 64 : CB_SPLIT, cb_scale, mult);
+      // ---- T -> bf16 copy, this group's blocks
+      convert_T(0, CB_SPLIT, cb_scale, mult);
       tc_fence_before();
       mbar_arrive(bar0 + 8u * BAR_A);
       if (!exact) mbar_arrive(bar0 + 8u * BAR_A);  // common frame: q is used as loaded
@@ -588,7 +618,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       CW_WAIT(BAR_FULL0 + st, par_full);
       {
         const int l = t >> 1, half = t & 1;
-        const unsigned char* vt = smem + LY::OFF_STAGE + st * LY::STAGE_BYTES + 2 * LY::Q_BYTES;
+        const unsigned char* vt = smem + LY::OFF_STAGE + st * LY::STAGE_BYTES + LY::OFF_V;
         uint4 v[8];
         uint32_t off[8];
 #pragma unroll
@@ -649,23 +679,81 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     }
   } else if (warp < W_UMMA) {
     // =========================================================================================== epilogue group
-    // H^T sits in tensor memory with one value column per lane.  Each thread pulls its 64 tokens into registers
-    // (which frees the accumulator for the next chunk at once), waits for the denominators, writes normalised bf16
-    // into a [token][column] staging tile in shared memory, and the group streams the tile out with 16-byte
-    // stores (a row of the tile is 256 contiguous bytes of h).
+    // H^T sits in tensor memory with one value column per lane.  The group pulls it into registers (which frees the
+    // accumulator for the next chunk at once), scales by 1/denominator, writes bf16 into a [token][column] staging tile
+    // in shared memory and streams the tile out with 16-byte stores (a row of the tile is 256 contiguous bytes of h).
     const int t = tid - 256;
-    const int dv = (warp & 3) * 32 + lane;
+    const int cq = 2 * (lane & 3);
     unsigned char* hst = smem + LY::OFF_HST;
+    const uint32_t hst_u = smem_u32(hst);
     __nv_bfloat16* hbase = reinterpret_cast<__nv_bfloat16*>(p.h) + b * p.h_sb + head * p.h_sh + tok0 * p.h_st + col0;
+    // This group's block of the T -> bf16 copy for chunk `next` (T holds chunk next - 1 or the initial state).  The block
+    // is read and converted at once; where its last eight columns double as the q.n columns of [q.n | S](next) they
+    // stay in registers (`tail`) until the gate group has taken q.n(next) out (finish_block).
+    constexpr bool EG_CONVERTS = DHQK / 64 >= 2;  // with one block only, the state group converts it
+    uint32_t tail[8];
+    auto convert_block = [&](int next) -> bool {
+      if constexpr (EG_CONVERTS) {
+        if (!mbar_wait(bar0 + 8u * (BAR_GFULL0 + (next & 1)), (uint32_t)(next >> 1) & 1u)) return false;
+        const float* gbn = gate_buf(next & 1);
+        const float cb_scale = gbn[G_CB], mult = gbn[G_MULT];
+        constexpr int cb = DHQK / 64 - 1;
+        uint32_t r0[32], r1[32];
+        tmem_ld_x32(tC + cb * 64, r0);
+        tmem_ld_x32(tC + cb * 64 + 32, r1);
+        tc_wait_ld();
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          pk[i] = pack_bf16x2(__uint_as_float(r0[2 * i]) * cb_scale, __uint_as_float(r0[2 * i + 1]) * cb_scale);
+          pk[16 + i] = pack_bf16x2(__uint_as_float(r1[2 * i]) * cb_scale, __uint_as_float(r1[2 * i + 1]) * cb_scale);
+        }
+        if constexpr (LY::TAIL_SHARED) {
+          uint32_t lo16[16], mid8[8];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) lo16[i] = pk[i];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { mid8[i] = pk[16 + i]; tail[i] = pk[24 + i]; }
+          tmem_st_x16(tCb + cb * 32, lo16);
+          tmem_st_x8(tCb + cb * 32 + 16, mid8);
+        } else {
+          tmem_st_x32(tCb + cb * 32, pk);
+        }
+        if (mult != 1.f) {  // the lazy frame ran out: rescale T itself
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            r0[i] = __float_as_uint(__uint_as_float(r0[i]) * mult);
+            r1[i] = __float_as_uint(__uint_as_float(r1[i]) * mult);
+          }
+          tmem_st_x32(tC + cb * 64, r0);
+          tmem_st_x32(tC + cb * 64 + 32, r1);
+        }
+      }
+      return true;
+    };
+    auto finish_block = [&](int next) -> bool {
+      if constexpr (EG_CONVERTS && LY::TAIL_SHARED) {
+        if (!mbar_wait(bar0 + 8u * BAR_QNREAD, (uint32_t)next & 1u)) return false;
+        tc_fence_after();
+        tmem_st_x8(tCb + DHQK / 2 - 8, tail);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar0 + 8u * BAR_A);  // this group's share of the bf16 copy for chunk `next`
+      return true;
+    };
+    if constexpr (EG_CONVERTS) {
+      if (!mbar_wait(bar0 + 8u * BAR_TINIT, 0u)) ok = false;
+      tc_fence_after();
+    }
+    if (ok && !convert_block(0)) ok = false;
     mbar_arrive(bar0 + 8u * BAR_A);  // the accumulator is free for chunk 0
-    mbar_arrive(bar0 + 8u * BAR_A);  // (this group's share of the T -> bf16 copy: the state group converts all of it for chunk 0)
-    // Denominators of chunk c, ready long before H^T(c) is (they depend on the previous phase of UMMAs only): taken
-    // one chunk ahead of the accumulator so that nothing stands between H^T landing and its drain.
+    if (ok && !finish_block(0)) ok = false;
+    // Denominators of chunk c: ready long before H^T(c) is (they depend on the previous phase of UMMAs only).
     auto denominators_ready = [&](int c) -> bool {
       if (!mbar_wait(bar0 + 8u * BAR_INV, (uint32_t)c & 1u)) return false;
       return true;
     };
-    if (!denominators_ready(0)) ok = false;
 #pragma unroll 1
     for (int chunk = 0; ok && chunk < nchunks; ++chunk) {
       const uint32_t par = (uint32_t)chunk & 1u;
@@ -674,47 +762,52 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       CW_WAIT(BAR_HC, par);
       tc_fence_after();
       // ---- this group's block of the T -> bf16 copy for the NEXT chunk (T holds this chunk now)
-      if (chunk + 1 < nchunks) {
-        CW_WAIT(BAR_GFULL0 + ((chunk + 1) & 1), (uint32_t)((chunk + 1) >> 1) & 1u);
-        const float* gbn = gate_buf((chunk + 1) & 1);
-        convert_T(CB_SPLIT, DHQK / 64, gbn[G_CB], gbn[G_MULT]);
-        tc_fence_before();
-        mbar_arrive(bar0 + 8u * BAR_A);
-      }
-      // drain, normalise and stage in two rolled passes of 32 tokens (small code)
-      unsigned char* col = hst + dv * 2;
+      const bool have_next = chunk + 1 < nchunks;
+      if (have_next && !convert_block(chunk + 1)) { ok = false; break; }
+      // the denominators of this chunk: published by the gate group about a chunk ago (waited for here and not at the
+      // end of the previous iteration, where the wait would hold up the conversion above)
+      if (!denominators_ready(chunk)) { ok = false; break; }
+      // drain, normalise and stage.  The accumulator comes out as two fragments of 16 value columns x 64 tokens
+      // (shape 16x256b: thread t holds columns t/4 and t/4 + 8, tokens 8g + 2 (t%4) + {0,1} of every group g); a pair of
+      // tokens packs into one register and stmatrix.trans writes 8 x 8 blocks transposed, so that a token's eight value
+      // columns land as 16 contiguous bytes of its row of the staging tile.
 #pragma unroll 1
-      for (int q = 0; q < 2; ++q) {
+      for (int half = 0; half < 2; ++half) {
         uint32_t hv[32];
-        tmem_ld_x32(tH + 32 * q, hv);
-        float4 iv[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) iv[i] = *reinterpret_cast<const float4*>(s_inv + 32 * q + 4 * i);
+        tmem_ld_16x256b_x8(tH + ((uint32_t)(half * 16) << 16), hv);
+        // lanes 8m .. 8m+7 address the rows of matrix m: token group (m >> 1), value columns + 8 (m & 1)
+        const uint32_t srow = hst_u + (uint32_t)((8 * (lane >> 4) + (lane & 7)) * LY::HST_ROW + ((warp & 3) * 32 + half * 16 + 8 * ((lane >> 3) & 1)) * 2);
         tc_wait_ld();
-        if (q == 1) {  // the accumulator is in registers: free for the next chunk
+        if (half == 1) {  // the accumulator is in registers: free for the next chunk
           tc_fence_before();
           mbar_arrive(bar0 + 8u * BAR_A);
+          if (have_next && !finish_block(chunk + 1)) ok = false;  // (the loop ends at its top)
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float sc[4] = {iv[i].x, iv[i].y, iv[i].z, iv[i].w};
-#pragma unroll
-          for (int u = 0; u < 4; ++u)
-            *reinterpret_cast<__nv_bfloat16*>(col + (32 * q + 4 * i + u) * LY::HST_ROW) =
-                __float2bfloat16_rn(__uint_as_float(hv[4 * i + u]) * sc[u]);
+        for (int gp = 0; gp < 4; ++gp) {
+          const float2 i0 = *reinterpret_cast<const float2*>(s_inv + 16 * gp + cq);
+          const float2 i1 = *reinterpret_cast<const float2*>(s_inv + 16 * gp + 8 + cq);
+          const uint32_t m0 = pack_bf16x2(__uint_as_float(hv[8 * gp + 0]) * i0.x, __uint_as_float(hv[8 * gp + 1]) * i0.y);
+          const uint32_t m1 = pack_bf16x2(__uint_as_float(hv[8 * gp + 2]) * i0.x, __uint_as_float(hv[8 * gp + 3]) * i0.y);
+          const uint32_t m2 = pack_bf16x2(__uint_as_float(hv[8 * gp + 4]) * i1.x, __uint_as_float(hv[8 * gp + 5]) * i1.y);
+          const uint32_t m3 = pack_bf16x2(__uint_as_float(hv[8 * gp + 6]) * i1.x, __uint_as_float(hv[8 * gp + 7]) * i1.y);
+          stmatrix_x4_trans(srow + (uint32_t)(16 * gp * LY::HST_ROW), m0, m1, m2, m3);
         }
       }
       mbar_arrive(bar0 + 8u * BAR_EGDONE);  // the denominators of this chunk are consumed
       epilogue_group_sync();
       __nv_bfloat16* ho = hbase + (long long)chunk * CW_L * p.h_st;
-#pragma unroll 2
-      for (int i = 0; i < 8; ++i) {
-        const int idx = i * 128 + t, row = idx >> 4, c = idx & 15;
-        if (row < len_c)
-          *reinterpret_cast<uint4*>(ho + (long long)row * p.h_st + c * 8) = *reinterpret_cast<const uint4*>(hst + row * LY::HST_ROW + c * 16);
+      {  // 64 rows of 256 bytes leave as 16-byte pieces, a row per 16 threads: all loads first, then the stores
+        uint4 piece[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) piece[i] = *reinterpret_cast<const uint4*>(hst + (i * 8 + (t >> 4)) * LY::HST_ROW + (t & 15) * 16);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int row = i * 8 + (t >> 4);
+          if (row < len_c) *reinterpret_cast<uint4*>(ho + (long long)row * p.h_st + (t & 15) * 8) = piece[i];
+        }
       }
       epilogue_group_sync();  // the tile is rewritten by the next chunk
-      if (chunk + 1 < nchunks && !denominators_ready(chunk + 1)) ok = false;
     }
   } else if (warp == W_UMMA) {
     // =========================================================================================== UMMA issuer
@@ -722,11 +815,10 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     // issues each instruction.  Every descriptor is formed from one runtime base plus compile-time constants so
     // that the address arithmetic stays on the uniform datapath.  A chain of UMMAs accumulating into one tile runs
     // at its latency (about 60 cycles a step), so every phase interleaves two independent products step by step.
-    constexpr uint32_t IDESC_S = umma_idesc_bf16(64, 64, 0, 0);
+    constexpr uint32_t IDESC_S = umma_idesc_bf16(64, 72, 0, 0);  // S and, from eight more B rows, q.n
     constexpr uint32_t IDESC_HI = umma_idesc_bf16(128, 64, 0, 0);
     constexpr uint32_t IDESC_HV = umma_idesc_bf16(128, 64, 1, 0);
     constexpr uint32_t IDESC_C = umma_idesc_bf16(128, DHQK, 1, 1);
-    constexpr uint32_t IDESC_DN = umma_idesc_bf16(64, 8, 0, 0);
     constexpr uint32_t IDESC_NU = umma_idesc_bf16(64, 8, 1, 0);
     // Values that are warp-uniform in fact but not provably so (read from shared or global memory) are broadcast
     // with a shuffle: that is what lets the compiler keep UMMA operands in uniform registers.
@@ -735,16 +827,17 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     const uint32_t bar_u = __shfl_sync(0xffffffffu, bar0, 0);
     const int nchunks_u = __shfl_sync(0xffffffffu, nchunks, 0);
     const uint32_t t_odd = tmem_u + LY::T_S + (16u << 16);  // odd 16-lane halves of the S columns
-    // lower descriptor words (start address >> 4 | leading offset); K-major tiles use leading offset 16 B,
-    // MN-major tiles one 8 KiB box
+    // lower descriptor words (start address >> 4 | leading offset); K-major tiles use leading offset 16 B, MN-major
+    // tiles the distance between their 64-wide boxes (8 KiB; 9 KiB for k, whose boxes have the n rows in front)
     constexpr uint32_t LBO_K = (16u >> 4) << 16, LBO_MN = ((uint32_t)CW_BOX_BYTES >> 4) << 16;
+    constexpr uint32_t LBO_MN_K = ((uint32_t)LY::K_STRIDE >> 4) << 16;
     bool okm = true;
-    // Phase C of chunk k forms everything of chunk k+1 that does not depend on the state: S, nu and qn.  It runs
+    // Phase C of chunk k forms everything of chunk k+1 that does not depend on the state: [q.n | S] and nu.  It runs
     // while T is converted for chunk k+1, so the tensor pipe has work during the one long dependency of the loop.
-    auto phase_c = [&](int next) {  // S(next), then nu(next) interleaved with qn(next)
-      const uint32_t nq = sbase_u + LY::OFF_STAGE + (next & 1) * LY::STAGE_BYTES, nk = nq + LY::Q_BYTES;
+    auto phase_c = [&](int next) {  // [q.n | S](next), then nu(next)
+      const uint32_t nq = sbase_u + LY::OFF_STAGE + (next & 1) * LY::STAGE_BYTES;
+      const uint32_t nrow = nq + LY::OFF_K, nk = nrow + 1024;  // n rows in front of the first k box | the k data
       const uint32_t wm = sbase_u + LY::OFF_WMAT + (next & 1) * 1024;
-      const uint32_t nm = sbase_u + LY::OFF_NMAT + (next & 1) * (NB * 1024);
       okm &= MMA_WAIT_U(BAR_FULL0 + (next & 1), (uint32_t)(next >> 1) & 1u);
       okm &= MMA_WAIT_U(BAR_C2, (uint32_t)next & 1u);
       tc_fence_after();
@@ -752,24 +845,16 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       for (int kb = 0; kb < NKB; ++kb)
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ss_lo(tmem_u + LY::T_S, (LBO_K + ((nq + kb * CW_BOX_BYTES + kk * 32) >> 4)),
-                     (LBO_K + ((nk + kb * CW_BOX_BYTES + kk * 32) >> 4)), IDESC_S, (kb | kk) != 0);
+          umma_ss_lo(tmem_u + LY::T_SX, (LBO_K + ((nq + kb * CW_BOX_BYTES + kk * 32) >> 4)),
+                     (LBO_K + ((nrow + kb * LY::K_STRIDE + kk * 32) >> 4)), IDESC_S, (kb | kk) != 0);
       umma_commit_elect(bar_u + 8u * BAR_S);
-      // nu and q.n of all feature blocks, step by step
-      const uint32_t kblk = nk, qblk = nq;
+      // nu of all feature blocks: step (token slice tsl, feature block gq), four independent accumulators in turn
 #pragma unroll 1
-      for (int kb = 0; kb < NB; ++kb) {
+      for (int tsl = 0; tsl < 4; ++tsl)
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const int ks = 4 * kb + kk;
-          // nu step (token slice, feature block) = (ks / NB, ks % NB): 4 x NB steps, like q.n
-          const int tsl = ks / NB, gq = ks % NB;
-          umma_ss_lo(t_odd + 8 + 8 * gq, (LBO_MN + ((kblk + gq * CW_BOX_BYTES + tsl * 2048) >> 4)),
+        for (int gq = 0; gq < NB; ++gq)
+          umma_ss_lo(t_odd + 8 + 8 * gq, (LBO_MN_K + ((nk + gq * LY::K_STRIDE + tsl * 2048) >> 4)),
                      (LBO_K + ((wm + tsl * 32) >> 4)), IDESC_NU, tsl != 0);
-          umma_ss_lo(t_odd, (LBO_K + ((qblk + kb * CW_BOX_BYTES + kk * 32) >> 4)),
-                     (LBO_K + ((nm + kb * 1024 + kk * 32) >> 4)), IDESC_DN, ks != 0);
-        }
-      }
       umma_commit_elect(bar_u + 8u * BAR_NU);
     };
     phase_c(0);
@@ -777,7 +862,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
     for (int chunk = 0; chunk < nchunks_u; ++chunk) {
       const uint32_t par = (uint32_t)chunk & 1u;
       const uint32_t stg = sbase_u + LY::OFF_STAGE + (chunk & 1) * LY::STAGE_BYTES;  // q | k | v of this chunk
-      const uint32_t s_k = stg + LY::Q_BYTES, s_v = s_k + LY::Q_BYTES;
+      const uint32_t s_k = stg + LY::OFF_K + 1024, s_v = stg + LY::OFF_V;
       // ---- phase A:  H^T = Tb q^T
       okm &= MMA_WAIT_U(BAR_A, par);
       tc_fence_after();
@@ -796,7 +881,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
           umma_ss_lo(tmem_u + LY::T_H, (LBO_MN + ((s_v >> 4) + ((kk * 2048) >> 4))),
                      (LBO_K + ((sbase_u >> 4) + ((LY::OFF_P + kk * 32) >> 4))), IDESC_HV, 1);
           umma_ss_lo(tmem_u + LY::T_C, (LBO_MN + ((sbase_u >> 4) + ((LY::OFF_VH + kk * 2048) >> 4))),
-                     (LBO_MN + ((s_k >> 4) + ((kk * 2048) >> 4))), IDESC_C, 1);
+                     (LBO_MN_K + ((s_k >> 4) + ((kk * 2048) >> 4))), IDESC_C, 1);
         }
       }
       umma_commit_elect(bar_u + 8u * BAR_HC);
@@ -816,7 +901,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
         const uint32_t bar = bar0 + 8u * (BAR_FULL0 + st);
         const uint32_t dst = sbase + LY::OFF_STAGE + st * LY::STAGE_BYTES;
         const int tk = (int)(tok0 + (long long)chunk * CW_L);
-        mbar_expect_tx(bar, LY::STAGE_BYTES);
+        mbar_expect_tx(bar, LY::TX_BYTES);
         int cq[4], ck[4], cv[4];
         cq[maps.pos[0][0]] = tk; cq[maps.pos[0][1]] = head; cq[maps.pos[0][2]] = b;
         ck[maps.pos[1][0]] = tk; ck[maps.pos[1][1]] = head; ck[maps.pos[1][2]] = b;
@@ -824,11 +909,11 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
 #pragma unroll
         for (int kb = 0; kb < NKB; ++kb) {
           tma_load_4d(dst + kb * CW_BOX_BYTES, &maps.q, bar, kb * 64, cq[1], cq[2], cq[3]);
-          tma_load_4d(dst + LY::Q_BYTES + kb * CW_BOX_BYTES, &maps.k, bar, kb * 64, ck[1], ck[2], ck[3]);
+          tma_load_4d(dst + LY::OFF_K + kb * LY::K_STRIDE + 1024, &maps.k, bar, kb * 64, ck[1], ck[2], ck[3]);
         }
 #pragma unroll
         for (int vb = 0; vb < 2; ++vb)
-          tma_load_4d(dst + 2 * LY::Q_BYTES + vb * CW_BOX_BYTES, &maps.v, bar, col0 + vb * 64, cv[1], cv[2], cv[3]);
+          tma_load_4d(dst + LY::OFF_V + vb * CW_BOX_BYTES, &maps.v, bar, col0 + vb * 64, cv[1], cv[2], cv[3]);
       }
     }
     __syncwarp();
