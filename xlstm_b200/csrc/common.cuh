@@ -90,14 +90,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   return true;
 }
 
-// The same without back-off, for a single warp whose wake-up time is on the critical path.
-__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity) {
-  uint32_t it = 0;
-  while (!mbar_try_wait(bar, parity))
-    if (++it > (1u << 24)) return false;
-  return true;
-}
-
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA, tcgen05.mma operands)
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }

@@ -14,24 +14,26 @@
 // and is folded into r_j and w_l, and T is rescaled in place only when rho drops below -30.
 //
 // Tensor-core work per chunk (all operands bf16, fp32 accumulation in tensor memory):
-//   S    [64 x 64]     = Q K^T                  M=64  N=64   K=DHQK  A,B K-major TMA tiles
+//   [qn|S] [64 x 72]   = Q [n_hi n_lo 0.. | K]^T    M=64  N=72   K=DHQK  S and the normaliser product q.n in one product:
+//                                                                        eight more B rows in front of every k box
 //   H^T  [128 x 64]    = Tb q^T                 M=128 N=64   K=DHQK  A = bf16 copy of T in tensor memory
 //   H^T               += V^T P^T                M=128 N=64   K=64    A = V tile used MN-major, B = P tile
 //   T    [128 x DHQK] += (w V)^T K              M=128 N=DHQK K=64    both MN-major
-//   qn   [64 x 8]      = q [n_hi n_lo]^T        M=64  N=8    K=DHQK  normaliser dot product, n split hi/lo
 //   nu   [DHQK x 8]    = K^T [w_hi w_lo]^T      M=64  N=8    K=64    n update, per 64-feature block
-// The two N=8 products land on the odd 16-lane halves of the S columns (an M=64 accumulator only occupies
-// the even halves), so the 512 tensor-memory columns are exactly: T 256 | Tb 128 | H^T 64 | S,qn,nu 64.
-// Every UMMA of these shapes costs the pipe ~33 cycles (the N=256 ones 132), whatever its N: 80 of them per chunk.
+// nu lands on the odd 16-lane halves of the S columns (an M=64 accumulator only occupies the even halves).  The 512
+// tensor-memory columns are: T 256 | H^T 64 | Tb 128 | S 64, and the eight q.n columns in front of S are the last eight
+// columns of Tb, which the two take in turns (see CwLayout).  Every UMMA of these shapes costs the pipe 33-40 cycles
+// whatever its N (the four N=256 ones 132): 64 of them per chunk.
 //
-// Warp roles: warp 14 carries the gate recurrence (scans, r, w, frame) one to two chunks ahead; warps 0-3 gate
-// group (one block of the T -> bf16 conversion, P from S, the terms of the denominators, n and its hi/lo operand);
-// warps 4-7 state group (the rest of the conversion / lazy rescale, w-scaled v, in the exact frame r-scaled q in
-// place in its TMA stage); warps 8-11 epilogue group (1/denominator, H^T -> normalised bf16 tile in shared memory ->
-// 16-byte global stores); warp 12 issues every UMMA; warp 13 issues the TMA loads.  Per chunk the tensor pipe runs phase A (H^T inter), phase B (H^T intra interleaved with
-// the T update) and phase C: S, nu and qn of the NEXT chunk, which need neither T nor its bf16 copy and so fill
-// the time the conversion of T takes -- the one long dependency of the loop.  Groups hand work to each other
-// through mbarriers only; every wait is bounded, and no waiter is ever more than one phase behind its producer.
+// Warp roles: warp 14 carries the gate recurrence (scans, r, w, frame) one to two chunks ahead; warps 0-3 gate group
+// (q.n and S out of tensor memory with one 16x256b fragment load, P, n and its hi/lo rows, the denominators); warps 4-7
+// state group (all but the last block of the T -> bf16 conversion / lazy rescale, w-scaled v, in the exact frame
+// r-scaled q in place in its TMA stage); warps 8-11 epilogue group (the last block of the conversion, H^T out as 16x256b
+// fragments -> scaled by 1/denominator -> stmatrix.trans into a [token][column] tile -> 16-byte global stores); warp 12
+// issues every UMMA; warp 13 issues the TMA loads.  Per chunk the tensor pipe runs phase A (H^T inter), phase B (H^T
+// intra interleaved with the T update) and phase C: [qn|S] and nu of the NEXT chunk, which need neither T nor its bf16
+// copy and so fill the time the conversion of T takes -- the one long dependency of the loop.  Groups hand work to each
+// other through mbarriers only; every wait is bounded, and no waiter is ever more than one phase behind its producer.
 //
 // Three things about code generation decide the speed of this kernel as much as the schedule does:
 //   * the compiler issues an UMMA as ~4 instructions only where it can PROVE warp-uniform control flow: the role
@@ -39,7 +41,11 @@
 //     has no branch inside an issue loop; otherwise every UMMA becomes ~35 instructions and the warp sets the pace;
 //   * all roles' per-chunk code together must stay small (rolled loops over pieces, one shared copy of the
 //     conversion): unrolled, every pass ran mostly on instruction-fetch misses;
-//   * polling warps take issue slots from working ones: waits back off at once.
+//   * polling warps take issue slots from working ones: waits back off at once;
+//   * a load inside a branch waits out its latency there: operands of unrolled, branchy code are fetched up front.
+// What the kernel is bound by at the xLSTM-7B head shape is the shared-memory data pipe, which UMMA operand fetches
+// (~200 KB per chunk), TMA writes (80 KB) and the groups' own loads and stores share; every step that took bytes off it
+// (q.n folded into S, stmatrix instead of 2-byte stores) showed in the time, moving work between groups did not.
 //
 // q, k, v tiles arrive by TMA (128-byte swizzle) straight from the caller's strided (B, NH, S, D) views;
 // documents are chunked from their own first token, so a chunk never straddles a document boundary and the
@@ -91,14 +97,14 @@ enum CwBar {  // mbarrier indices.  Barriers whose producer may run two chunks a
               // arrives on ONE barrier, whatever group it comes from.
   BAR_FULL0 = 0, BAR_FULL1, BAR_EMPTY0, BAR_EMPTY1,   // TMA stage of q,k,v: landed / consumed
   BAR_GFULL0, BAR_GFULL1, BAR_GEMPTY0, BAR_GEMPTY1,   // gate data of a chunk: published / consumed
-  BAR_A,     // phase A may issue: bf16 copy of T (state + gate group), q final (state group), H^T drained
-             // (epilogue group), its block of the bf16 copy (epilogue group): 4 x 128 arrivals
+  BAR_A,     // phase A may issue: bf16 copy of T (state group's blocks), q final (state group), H^T drained
+             // (epilogue group), the last block of the bf16 copy (epilogue group): 4 x 128 arrivals
   BAR_B,     // phase B may issue: P (gate group), w-scaled v (state group): 2 x 128 arrivals
-  BAR_C2,    // phase C may issue (gate group): n operand of the next chunk published, nu and qn columns read,
-             // gate data of the next chunk visible.  Completion k+1 comes from the gate group's iteration k.
+  BAR_C2,    // phase C may issue (gate group): n rows of the next chunk published, nu columns read, gate data of the
+             // next chunk visible.  Completion k+1 comes from the gate group's iteration k.
   BAR_HC,    // commit after phase B: H^T and T complete
-  BAR_S,     // commit inside phase C: S of the next chunk complete (completion k = S(k))
-  BAR_NU,    // commit after phase C: nu and qn of the next chunk complete (completion k = nu(k), qn(k))
+  BAR_S,     // commit inside phase C: [qn|S] of the next chunk complete (completion k = S(k))
+  BAR_NU,    // commit after phase C: nu of the next chunk complete (completion k = nu(k))
   BAR_INV,   // gate group -> epilogue group: 1/denominator published
   BAR_EGDONE,  // epilogue group -> gate group: 1/denominator consumed
   BAR_QNREAD,  // gate group -> epilogue group: q.n of a chunk is in registers (its columns may take the bf16 copy again)
@@ -176,11 +182,7 @@ __device__ __forceinline__ uint32_t sw128_off(int row, int col) {
 }
 
 // Wait used by the UMMA-issuing warp: after a first expired wait the later ones return at once.
-#ifdef CW_MMA_SPIN
-#define MMA_WAIT_U(idx, parity) (okm ? mbar_wait_spin(bar_u + 8u * (uint32_t)(idx), (uint32_t)(parity)) : false)
-#else
 #define MMA_WAIT_U(idx, parity) (okm ? mbar_wait(bar_u + 8u * (uint32_t)(idx), (uint32_t)(parity)) : false)
-#endif
 
 #define CW_WAIT(idx, parity)                                   \
   if (!mbar_wait(bar0 + 8u * (uint32_t)(idx), (uint32_t)(parity))) { \
@@ -566,7 +568,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       if (chunk + 1 < nchunks) CW_WAIT(BAR_GFULL0 + (buf ^ 1), (uint32_t)((chunk + 1) >> 1) & 1u);  // w operand of the next chunk
       mbar_arrive(bar0 + 8u * BAR_C2);                // phase C of this chunk may issue
       mbar_arrive(bar0 + 8u * (BAR_GEMPTY0 + buf));  // done with this chunk's gate data (so is nu, which read w)
-      // ---- denominators: |rowsum + q.n| against the lower bound (the product sits on lanes 16..31)
+      // ---- denominators: |rowsum + q.n| against the lower bound (lanes 4i and 4i + 1 write rows j0 and j0 + 8)
       if (chunk >= 1) CW_WAIT(BAR_EGDONE, par ^ 1u);  // the epilogue group has consumed the previous ones
       if ((lane & 2) == 0) s_inv[jd] = __fdividef(1.f, fmaxf(fabsf(fmaf(dot, qn_scale, (lane & 1) ? rs1 : rs0)), lower) + eps_j);
       mbar_arrive(bar0 + 8u * BAR_INV);
@@ -635,7 +637,7 @@ mlstm_chunkwise_kernel(const __grid_constant__ CwMaps maps, const xl_mlstm_seq_p
       // ---- exact frame only: q <- r_j q IN PLACE in the stage tile (thread: row j = t/2, half of the row).  S of
       // this chunk, the only consumer of the un-scaled q, must have completed.
       if (exact) {
-        CW_WAIT(BAR_NU, par);  // S, nu and qn of this chunk (issued one chunk ahead) no longer read q as loaded
+        CW_WAIT(BAR_NU, par);  // [qn|S] and nu of this chunk (issued one chunk ahead) no longer read q as loaded
         const int j = t >> 1, half = t & 1;
         unsigned char* qt = smem + LY::OFF_STAGE + st * LY::STAGE_BYTES;
         constexpr int CH = NKB * 4;              // 16-byte pieces per thread
