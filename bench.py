@@ -2,18 +2,24 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--case NAME]
 
-Headline case (default, "chunkwise"): BASELINE config 2 -- one step = one forward of the mLSTM cell over
-B=4 sequences x NH=8 heads x S=8192 tokens, DHQK=256, DHV=512, bf16 inputs, fp32 state, zero initial state;
-seeded synthetic inputs with the distributions BASELINE.json states.  The metric counts B*S tokens per step
-(one token = all 8 heads of one xLSTM-7B layer).  At N > 1 every rank runs its own batch of sequences
-(documents are data-parallel, no collective on the data path): weak scaling.
+Headline case (default, "chunkwise"): one step = one forward of the mLSTM cell over B=4 sequences x NH=8 heads x
+S=8192 tokens, DHQK=256, DHV=512 (the head shapes of xLSTM-7B), bf16 inputs, fp32 state, zero initial state; seeded
+synthetic inputs: q, k ~ N(0,1)/sqrt(256), v ~ N(0,1), input-gate pre-activations ~ N(0,1), forget-gate
+pre-activations ~ N(3,1).  The metric counts B*S tokens per step (one token = all 8 heads of one xLSTM-7B layer).  At
+N > 1 every rank runs its own batch of sequences (documents are data-parallel, no collective on the data path): weak
+scaling.
 
-Other cases print the same kind of line for the other kernels of the path:
+The default run adds, in the same JSON line under "sub", the other measurements of the path, each taken in the same
+process: the xLSTM-7B-shaped model (prefill 8 x 8192 tokens + 512 greedy tokens, heads tensor-parallel over the N
+ranks), and at N = 1 the decode-step kernel, the sLSTM kernel and the fused operators next to the cell.  `--case NAME`
+prints one of them as a line of its own:
   step          mLSTM decode step, 256 streams x 8 heads (xLSTM-7B head shapes), state resident in HBM
-  slstm         sLSTM forward, BASELINE config 3 cell shape (B=16, S=2048, NH=4, DH=256)
+  slstm         sLSTM forward at the block-stack benchmark's cell shape (B=16, S=2048, NH=4, DH=256), next to the
+                reference's own CUDA backend when the reference package is present
+  layer_ops     residual add + RMSNorm and per-head norm + output gate at the 7B prefill shapes
   chunkwise_b1  the headline kernel on one sequence (B=1): the size used for profiler captures
-  model7b       BASELINE config 4: xLSTM-7B-shaped model (random init, bf16), prefill 8 x 8192 tokens + 512 greedy
-                tokens; heads tensor-parallel over the ranks (strong scaling); use e.g. --steps 2 --warmup 3
+  model7b       the xLSTM-7B-shaped model (random init, bf16): prefill 8 x 8192 + 512 greedy tokens, strong scaling
+  continuous7b  continuous batching: packed prefill of log-normal documents into a pool of decode slots with refill
 
 `--impl reference` times the reference's native CPU formulation (the oracle port) on the host cores.
 """
@@ -21,6 +27,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -137,6 +144,12 @@ def cpu_chunkwise_seconds(threads):
 CPU_SAMPLE = "one sequence (B=1 of 4, all 8 heads, S=8192) per step; native chunkwise formulation in fp32 torch"
 
 
+def headline_config(world):
+    """The `config` object of the headline line: the same for both arms."""
+    return {"workload": "mlstm_chunkwise_7b_heads", **CFG, "parallelism": f"dp{world}",
+            "l2": "inputs (%d MB per step) exceed the 126 MB L2" % (chunkwise_bytes(**CFG) // 10 ** 6)}
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
@@ -152,9 +165,51 @@ def run_reference(args, rank):
         "impl": "reference", "metric": "mlstm_chunkwise_prefill_tokens_per_s", "value": val, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "mlstm_chunkwise_7b_heads", **CFG, "sample": "B=1 of 4 per step"},
+        "config": headline_config(args.gpus),
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": CPU_SAMPLE},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+# ---------------------------------------------------------------------------------------------- the reference's own sLSTM CUDA backend
+def reference_root():
+    for cand in (os.environ.get("XLSTM_REFERENCE"), os.path.join(ROOT, "baseline", "_ref")):
+        if cand and os.path.isdir(os.path.join(cand, "xlstm")):
+            return cand
+    return None
+
+
+def slstm_reference_cuda(cfg, dev, our_ms):
+    """Times the reference's sLSTM cell with backend="cuda" (xlstm/blocks/slstm/src/cuda/slstm_forward.cu:217-267: a host
+    loop of one cuBLAS call and one pointwise kernel per time step, JIT-compiled as compute_80 PTX) at the same cell
+    shape on this GPU.  Needs the reference package and a working nvcc on the machine; reports why when it cannot."""
+    root = reference_root()
+    if root is None:
+        return {"reference_cuda_unavailable": "reference package not found (XLSTM_REFERENCE or baseline/_ref)"}
+    try:
+        if root not in sys.path:
+            sys.path.insert(0, root)
+        os.environ.setdefault("TORCH_EXTENSIONS_DIR", os.path.join(ROOT, "baseline", "_ref_ext"))
+        from xlstm.blocks.slstm.cell import sLSTMCell, sLSTMCellConfig
+        B, S, NH, DH = cfg["B"], cfg["S"], cfg["NH"], cfg["DH"]
+        torch.manual_seed(0)
+        cell = sLSTMCell(sLSTMCellConfig(hidden_size=NH * DH, num_heads=NH, backend="cuda", dtype="bfloat16", batch_size=B,
+                                         recurrent_weight_init="standard")).to(dev).eval()
+        x = torch.randn(B, S, 4 * NH * DH, device=dev).bfloat16()
+        with torch.no_grad():
+            for _ in range(2):
+                cell(x)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                cell(x)
+            e1.record()
+            torch.cuda.synchronize()
+        ref_ms = e0.elapsed_time(e1) / 3
+        return {"reference_cuda_ms": ref_ms, "speedup_vs_reference_cuda": ref_ms / our_ms,
+                "reference_cuda": "sLSTMCell(backend='cuda') forward through the reference's own cell class, same shape"}
+    except Exception as e:   # no compiler, no reference sources, ...
+        return {"reference_cuda_unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
 
 
 # ---------------------------------------------------------------------------------------------- GPU cases
@@ -180,8 +235,8 @@ def build_case(name, dev, rank):
                     bytes=chunkwise_bytes(**cfg), flops=chunkwise_flops(**cfg), kernel="mlstm_chunkwise_kernel<256>",
                     h2d=sum(t.numel() * t.element_size() for t in host), d2h=h_host.numel() * 2 + c_host.numel() * 4,
                     l2="inputs (%d MB per step) exceed the 126 MB L2" % (chunkwise_bytes(**cfg) // 10 ** 6), launches=1,
-                    # dram read+write of one captured launch at B=1 (profiles/mlstm_chunkwise_config2.md), scaled by B
-                    traffic=178.2e6 * cfg["B"])
+                    traffic=178.2e6 * cfg["B"],
+                    traffic_source="constant: ncu dram__bytes_read.sum + dram__bytes_write.sum of ONE captured launch at B=1, scaled by the number of sequences, not measured in this run")
     if name == "step":
         cfg = dict(STEP_CFG)
         B, NH, DQ, DV = cfg["B"], cfg["NH"], cfg["DHQK"], cfg["DHV"]
@@ -210,7 +265,7 @@ def build_case(name, dev, rank):
                     flops=B * NH * 4 * DQ * DV, kernel="mlstm_step_kernel<bf16>",
                     h2d=sum(t.numel() * t.element_size() for t in host), d2h=h_host.numel() * 2,
                     l2="state pool (%d MB) exceeds the 126 MB L2" % (B * NH * DQ * DV * 4 // 10 ** 6), launches=1,
-                    traffic=2.101e9)  # profiles/mlstm_step_256streams.md
+                    traffic=2.101e9, traffic_source="constant: ncu dram__bytes_read.sum + dram__bytes_write.sum of ONE captured launch of this workload, not measured in this run")
     if name == "slstm":
         cfg = dict(SLSTM_CFG)
         B, S, NH, DH = cfg["B"], cfg["S"], cfg["NH"], cfg["DH"]
@@ -234,10 +289,11 @@ def build_case(name, dev, rank):
                     workload="slstm_cell_config3", cfg=cfg, bytes=slstm_bytes(**cfg), flops=S * B * NH * 2 * DH * 4 * DH,
                     kernel="slstm_forward_kernel<256>", h2d=wx_h.numel() * 2, d2h=o_host.numel() * 2,
                     l2="inputs (%d MB) exceed the 126 MB L2" % (slstm_bytes(**cfg) // 10 ** 6), launches=1,
-                    traffic=323.9e6)  # profiles/slstm_forward_config3.md
+                    traffic=323.9e6, traffic_source="constant: ncu dram__bytes_read.sum + dram__bytes_write.sum of ONE captured launch of this workload, not measured in this run",
+                    extra=lambda m: slstm_reference_cuda(cfg, dev, m["kernel_ms"]))
     if name == "layer_ops":
         # the two fused operators next to the cell, at the 7B layer's prefill shapes (8 x 8192 tokens, D = 4096)
-        B, S, NH, DH = int(os.environ.get("XL_LAYER_OPS_B", "8")), 8192, 8, 512   # (a smaller B for profiler captures)
+        B, S, NH, DH = 8, 8192, 8, 512
         D = NH * DH
         g = torch.Generator(device=dev).manual_seed(7 + rank)
         x = torch.randn(B, S, D, device=dev, generator=g).bfloat16()
@@ -263,23 +319,30 @@ def build_case(name, dev, rank):
                     workload="xlstm7b_layer_add_rmsnorm_plus_headnorm_gate", cfg=cfg, bytes=7 * B * S * D * 2, flops=0,
                     kernel="add_rmsnorm_kernel<bf16> + headnorm_gate_kernel<bf16>", h2d=4 * B * S * D * 2,
                     d2h=2 * B * S * D * 2, l2="operands (7 x %d MB per step) exceed the 126 MB L2" % (B * S * D * 2 // 10 ** 6), launches=2,
-                    # dram read+write of both kernels captured at B=2 (profiles/layer_adjacent_ops.md), scaled by B
-                    traffic=863.3e6 * B / 2)
+                    traffic=863.3e6 * B / 2, traffic_source="constant: ncu dram__bytes_read.sum + dram__bytes_write.sum of ONE captured launch of both kernels at B=2, scaled by B, not measured in this run")
     if name == "continuous7b":
-        # BASELINE config 5 in small: documents of log-normal length through a pool of decode slots with refill
-        # (xLSTM-7B-shaped mirror, random init; 128 documents, 64 slots, 64 greedy tokens each)
+        # Continuous batching on the xLSTM-7B-shaped model (random init): 512 documents of log-normal length (median 1024,
+        # sigma 1.0, clipped to [16, 16384]) are prefilled PACKED into rows of 32768 tokens (cu_seqlens, state reset inside
+        # the kernels) and decoded in 256 state slots for 256 greedy tokens each; finished streams hand their slot to the
+        # next queued document.  Documents are data-parallel: every rank takes its share (longest-first balancing) and
+        # 256 / world slots; no collective on the data path.
         from xlstm_b200.large_model import ContinuousDecoder, LargeConfig, LargeModel, procedural_state_dict
+        from xlstm_b200.sharding import shard_documents
+        import torch.distributed as dist
+        world = dist.get_world_size() if dist.is_initialized() else 1
         mcfg = LargeConfig(embedding_dim=4096, num_heads=8, num_blocks=32, vocab_size=50304)
         sd = procedural_state_dict(mcfg, seed=0, dtype=torch.bfloat16, device=dev, gen_device=dev)
         model = LargeModel(mcfg, sd, dev, torch.bfloat16)
         del sd
         torch.cuda.empty_cache()
-        NDOC, NSLOT, GEN = 128, 64, 64
+        NDOC, NSLOT, GEN = 512, 256, 256
         g = torch.Generator().manual_seed(11)
-        lens = torch.exp(torch.randn(NDOC, generator=g) + 6.0).clamp(16, 2048).long().tolist()
+        lens_all = torch.exp(torch.randn(NDOC, generator=g) + math.log(1024.0)).clamp(16, 16384).long().tolist()
+        mine = shard_documents(lens_all, world)[rank if world > 1 else 0]
+        lens = [lens_all[d] for d in mine]
         prompts_host = [torch.randint(0, mcfg.vocab_size, (n,), generator=g).pin_memory() for n in lens]
         prompts = [t.to(dev) for t in prompts_host]
-        dec = ContinuousDecoder(model, NSLOT)
+        dec = ContinuousDecoder(model, NSLOT // world, row_len=32768, max_rows_per_prefill=2)
 
         def step():
             return dec.run(prompts, GEN)
@@ -288,24 +351,26 @@ def build_case(name, dev, rank):
             return dec.run([t.to(dev, non_blocking=True) for t in prompts_host], GEN)
 
         cfg = dict(model="xLSTM-7B-shaped (random init)", documents=NDOC, slots=NSLOT, new_tokens=GEN,
-                   prompt_tokens=sum(lens), lengths="exp(N(6,1)) clipped to [16,2048]")
-        steps_est = NDOC * GEN // NSLOT
-        return dict(step=step, e2e_step=e2e_step, teardown=model.release_graph, units=sum(lens) + NDOC * GEN, unit="tokens/s",
-                    metric="xlstm7b_continuous_decode_tokens_per_s", workload="xlstm7b_128docs_64slots_refill", cfg=cfg,
-                    bytes=(steps_est + NDOC) * sum(t.numel() * t.element_size() for t in model.parameters_on_device() if t is not model.embedding),
-                    flops=0, kernel="whole run: single-document prefills and graph-replayed decode steps over the slot pool",
-                    h2d=sum(lens) * 8, d2h=NSLOT * steps_est * 8, l2="weights (13.7 GB) exceed the 126 MB L2",
-                    launches=steps_est + 32 * NDOC, heavy=True)
+                   prompt_tokens=sum(lens_all), lengths="exp(N(ln 1024, 1)) clipped to [16,16384]", row_len=32768,
+                   admission="packed prefill with cu_seqlens, per-document final states scattered into the slots")
+        steps_est = len(mine) * GEN // max(NSLOT // world, 1)
+        weight_bytes = sum(t.numel() * t.element_size() for t in model.parameters_on_device() if t is not model.embedding)
+        return dict(step=step, e2e_step=e2e_step, teardown=model.release_graph, units=sum(lens) + len(mine) * GEN, unit="tokens/s",
+                    metric="xlstm7b_continuous_decode_tokens_per_s", workload="xlstm7b_512docs_256slots_refill", cfg=cfg,
+                    bytes=steps_est * (weight_bytes + 32 * step_bytes(NSLOT // world, 8, 256, 512)) + 32 * chunkwise_bytes(1, 8, sum(lens), 256, 512),
+                    flops=0, kernel="whole run: packed prefills and graph-replayed decode steps over the slot pool",
+                    h2d=sum(lens) * 8, d2h=(NSLOT // world) * steps_est * 8, l2="weights (13.7 GB) exceed the 126 MB L2",
+                    launches=steps_est + 32 * 8, heavy=True,
+                    extra=lambda m: {"prefill_calls_per_run": dec.prefill_calls // max(m["steps"] + m["warmup"] + m["e2e_steps"], 1)})
     if name == "model7b":
-        # BASELINE config 4: xLSTM-7B-shaped model, random-init bf16, prefill 8 x 8192 tokens then 512 greedy tokens.
-        # Heads are tensor-parallel over the ranks (strong scaling): dense layers are library GEMMs, the cell is ours.
+        # xLSTM-7B-shaped model, random-init bf16: prefill 8 x 8192 tokens, then 512 greedy tokens.  Heads are
+        # tensor-parallel over the ranks (strong scaling): dense layers are library GEMMs, the cell is ours.
         from xlstm_b200.large_model import LargeConfig, LargeModel, procedural_state_dict
         import torch.distributed as dist
         world = dist.get_world_size() if dist.is_initialized() else 1
         mcfg = LargeConfig(embedding_dim=4096, num_heads=8, num_blocks=32, vocab_size=50304)
         sd = procedural_state_dict(mcfg, seed=0, dtype=torch.bfloat16, device=dev, gen_device=dev)
-        model = LargeModel(mcfg, sd, dev, torch.bfloat16, tp_rank=rank if world > 1 else 0, tp_world=world,
-                           fused_adjacent=os.environ.get("XL_FUSED_ADJACENT", "1") != "0")
+        model = LargeModel(mcfg, sd, dev, torch.bfloat16, tp_rank=rank if world > 1 else 0, tp_world=world)
         del sd
         torch.cuda.empty_cache()
         B, S, GEN = 8, 8192, 512
@@ -313,27 +378,164 @@ def build_case(name, dev, rank):
         tok_dev = tok_host.to(dev)
         out_host = torch.empty(B, GEN, dtype=torch.long).pin_memory()
 
-        # the decode loop replays a CUDA graph (with tensor parallelism the NCCL all-reduces are part of it)
-        graphed = os.environ.get("XL_DECODE_GRAPH", "1") == "1"
-
-        def step():
-            return model.generate(tok_dev, GEN, use_cuda_graph=graphed)[0]
+        def step():   # the decode loop replays a CUDA graph (with tensor parallelism the NCCL all-reduces are part of it)
+            return model.generate(tok_dev, GEN, use_cuda_graph=True)[0]
 
         def e2e_step():
-            out_host.copy_(model.generate(tok_host.to(dev, non_blocking=True), GEN, use_cuda_graph=graphed)[0], non_blocking=True)
+            out_host.copy_(model.generate(tok_host.to(dev, non_blocking=True), GEN, use_cuda_graph=True)[0], non_blocking=True)
+
+        streamed = [t for blk in model.blocks for k_, t in blk.items() if not k_.endswith("_full")] + [model.out_norm, model.lm_head]
+        weight_bytes = sum(t.numel() * t.element_size() for t in streamed)            # what one decode step streams per rank
+        flops_per_token = 2 * (32 * (4096 * (2 * 2048 + 2 * 4096) + 4096 * 16 + 4096 * 4096 + 3 * 4096 * 10944)) + 32 * 8 * 623616
+
+        def extra(m):
+            """Prefill and decode timed apart, the collectives of the prefill, and both against their bounds."""
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            ev[0].record()
+            model.forward(tok_dev, last_only=True)
+            ev[1].record()
+            model.forward(tok_dev, last_only=True, time_collectives=world > 1)
+            ev[2].record()
+            torch.cuda.synchronize()
+            prefill_ms = ev[0].elapsed_time(ev[1])
+            decode_ms = (m["kernel_ms"] - prefill_ms) / (GEN - 1)
+            try:
+                with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+                    pk = json.load(fh)
+                tflops, hbm = float(pk["bf16_tflops_sustained"]), float(pk["hbm_gbs"])
+            except Exception:
+                tflops, hbm = 1400.0, 6650.0
+            prefill_bound_ms = B * S * flops_per_token / (tflops * 1e12 * world) * 1e3
+            decode_bound_ms = (weight_bytes + 32 * step_bytes(B, 8 // world, 256, 512)) / (hbm * 1e9) * 1e3
+            out = {"prefill_ms": prefill_ms, "prefill_tokens_per_s": B * S / (prefill_ms * 1e-3), "decode_ms_per_step": decode_ms,
+                   "prefill_frac_of_tensor_bound": prefill_bound_ms / prefill_ms, "decode_frac_of_weight_streaming_bound": decode_bound_ms / decode_ms,
+                   "bounds": "prefill: %.1f GFLOP per token over the sustained bf16 peak of all ranks; decode: the rank's weights and "
+                             "states streamed once per step over the measured HBM peak" % (flops_per_token / 1e9)}
+            if world > 1:
+                out["prefill_collectives"] = {
+                    "scheme": "per block one all-gather (normed activations) + one reduce-scatter (out_proj partial sums) over the "
+                              "token axis, two batch pieces on two streams; decode: two all-reduces per block inside the step graph",
+                    "calls": model.comm_calls, "bytes_per_call": model.comm_bytes // max(model.comm_calls, 1),
+                    "event_ms_sum": model.comm_ms,
+                    "note": "CUDA-event time around each collective on its own stream, summed; the two streams overlap, so the sum "
+                            "can exceed the share of the prefill the collectives expose",
+                    "decode_all_reduce_bytes": B * 4096 * 2, "decode_all_reduces_per_step": 64}
+            return out
 
         cfg = dict(model="xLSTM-7B-shaped (random init)", embedding_dim=4096, num_heads=8, num_blocks=32, vocab_size=50304,
                    global_batch=B, seq_len=S, decode_tokens=GEN)
-        return dict(step=step, e2e_step=e2e_step, teardown=model.release_graph, units=B * (S + GEN), unit="tokens/s", metric="xlstm7b_prefill_decode_tokens_per_s",
-                    workload="xlstm7b_prefill8x8192_decode512", cfg=cfg,
+        return dict(step=step, e2e_step=e2e_step, teardown=model.release_graph, extra=extra, units=B * (S + GEN), unit="tokens/s",
+                    metric="xlstm7b_prefill_decode_tokens_per_s", workload="xlstm7b_prefill8x8192_decode512", cfg=cfg,
                     # algorithmic bytes of one step per rank: the weights once per decoded token (and once for the prefill)
                     # plus the cell's prefill traffic; the decode loop is what the time goes to
-                    bytes=(GEN + 1) * sum(t.numel() * t.element_size() for t in model.parameters_on_device() if t is not model.embedding)
-                    + 32 * chunkwise_bytes(B, 8 // world, S, 256, 512),
-                    flops=0, kernel="whole step: prefill (32 chunkwise launches + library GEMMs) and 512 graph replays", h2d=tok_host.numel() * 8, d2h=out_host.numel() * 8,
+                    bytes=(GEN + 1) * weight_bytes + 32 * chunkwise_bytes(B, 8 // world, S, 256, 512),
+                    flops=B * S * flops_per_token / world, kernel="whole step: prefill (32 chunkwise launches + library GEMMs) and 511 graph replays",
+                    h2d=tok_host.numel() * 8, d2h=out_host.numel() * 8,
                     l2="weights (13.7 GB) and activations exceed the 126 MB L2", launches=32 + 32 * GEN, scaling="strong",
                     parallelism="tp", heavy=True)
     raise SystemExit(f"unknown case {name}")
+
+
+def measure(case, steps, warmup, world, rank, dev, e2e=True, sampler=None, hold_clocks=False):
+    """Times `case` on the device (exactly `steps` steps between barriers, CUDA events on the launching stream, max over
+    ranks) and end to end from host buffers.  Returns a dict of raw numbers."""
+    import torch.distributed as dist
+    import xlstm_b200
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    step = case["step"]
+    for _ in range(warmup):
+        step()
+    xlstm_b200.check_device_status(dev)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    barrier()
+    ev[0].record()
+    for i in range(steps):
+        step()
+        ev[i + 1].record()
+    barrier()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    kernel_ms = sum(ev[i].elapsed_time(ev[i + 1]) for i in range(steps)) / steps
+    clocks = None
+    e2e_ms, e2e_steps = float("nan"), 0
+    if e2e:
+        # the clock record needs a few hundred ms under load: keep the same step running, untimed, until it has samples
+        # (not when the step holds collectives: rank 0 alone would wait for its peers for ever)
+        if hold_clocks and rank == 0 and sampler is not None and sampler.proc is not None and case.get("parallelism") != "tp":
+            t_end = time.time() + 3.0
+            base = sampler.count()
+            while sampler.count() < base + 8 and time.time() < t_end:
+                for _ in range(1 if case.get("heavy") else 20):
+                    step()
+                torch.cuda.synchronize()
+        if sampler is not None and rank == 0:
+            clocks = sampler.stop()
+        e2e_steps = 1 if case.get("heavy") else max(3, min(steps, 10))
+        for _ in range(0 if case.get("heavy") else 2):
+            case["e2e_step"]()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(e2e_steps):
+            case["e2e_step"]()
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1)
+    t = torch.tensor([total_ms, e2e_ms, kernel_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms, kernel_ms = t.tolist()
+    xlstm_b200.check_device_status(dev)
+    return dict(total_ms=total_ms, kernel_ms=kernel_ms, e2e_ms=e2e_ms, e2e_steps=e2e_steps, clocks=clocks, steps=steps, warmup=warmup)
+
+
+def record(case, m, world):
+    """The JSON fields of one measured case."""
+    strong = case.get("scaling") == "strong"
+    nrep = 1 if strong else world   # weak scaling: every rank processes its own units
+    peak, peak_kind = measured_peak_hbm()
+    achieved = case["bytes"] / (m["kernel_ms"] * 1e-3) / 1e9
+    out = {
+        "metric": case["metric"], "value": nrep * case["units"] * m["steps"] / (m["total_ms"] * 1e-3), "unit": case["unit"],
+        "n_gpus": world, "steps": m["steps"], "warmup": m["warmup"], "ms_per_step": m["total_ms"] / m["steps"],
+        "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": case["workload"], **case["cfg"], "parallelism": f"{case.get('parallelism', 'dp')}{world}", "l2": case["l2"]},
+        "gpu_launches": m["steps"] * case["launches"],
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": case.get("traffic"),
+                     "traffic_source": case.get("traffic_source", "not captured"),
+                     "peak_source": peak_kind, "kernel": case["kernel"], "kernel_ms": m["kernel_ms"],
+                     "algorithmic_bytes": case["bytes"], "tensor_tflops": case["flops"] / (m["kernel_ms"] * 1e-3) / 1e12},
+    }
+    if m["e2e_steps"]:
+        out["e2e"] = {"value": nrep * case["units"] * m["e2e_steps"] / (m["e2e_ms"] * 1e-3), "unit": case["unit"],
+                      "h2d_bytes_per_step": case["h2d"], "d2h_bytes_per_step": case["d2h"], "steps": m["e2e_steps"]}
+    return out
+
+
+def sub_record(name, dev, rank, world, steps, warmup):
+    """One of the secondary measurements, reduced to what the headline line carries under "sub"."""
+    case = build_case(name, dev, rank)
+    m = measure(case, steps, warmup, world, rank, dev, e2e=True)
+    r = record(case, m, world)
+    out = {k: r[k] for k in ("metric", "value", "unit", "ms_per_step", "scaling", "gpu_launches", "e2e")}
+    out["config"] = r["config"]
+    out["roofline"] = {k: r["roofline"][k] for k in ("bound", "achieved", "peak", "unit", "frac", "traffic", "traffic_source", "kernel", "kernel_ms")}
+    if case.get("extra"):
+        out.update(case["extra"](m))
+    if case.get("teardown"):
+        case["teardown"]()
+    del case
+    torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -342,7 +544,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--case", default="chunkwise", choices=["chunkwise", "chunkwise_b1", "step", "slstm", "layer_ops", "model7b", "continuous7b"])
+    ap.add_argument("--case", default="all", choices=["all", "chunkwise", "chunkwise_b1", "step", "slstm", "layer_ops", "model7b", "continuous7b"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="profiling runs: device-resident loop only")
     args = ap.parse_args()
@@ -356,101 +558,44 @@ def main():
     args.warmup = max(args.warmup, 3)
 
     import torch.distributed as dist
-    import xlstm_b200
+    import xlstm_b200  # noqa: F401
 
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    case = build_case(args.case, dev, rank)
-    step = case["step"]
+    headline = "chunkwise" if args.case == "all" else args.case
+    case = build_case(headline, dev, rank)
     sampler = ClockSampler(local)
     if rank == 0 and not args.no_e2e:
         sampler.start()
-    for _ in range(args.warmup):
-        step()
-    xlstm_b200.check_device_status(dev)
-
-    # ---- device-resident throughput: exactly K steps between barriers, one CUDA event per step
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    barrier()
-    ev[0].record()
-    for s in range(args.steps):
-        step()
-        ev[s + 1].record()
-    barrier()
-    total_ms = ev[0].elapsed_time(ev[-1])
-    kernel_ms = sum(ev[s].elapsed_time(ev[s + 1]) for s in range(args.steps)) / args.steps
-
-    e2e_ms, e2e_steps = float("nan"), 0
-    if not args.no_e2e:
-        # the clock record needs a few hundred ms under load: keep the same step running, untimed, until it has samples
-        # (not when the step holds collectives, as the tensor-parallel model step does: rank 0 alone would wait for
-        # its peers for ever -- and those steps run for seconds anyway, the record is long enough)
-        if rank == 0 and sampler.proc is not None and case.get("parallelism") != "tp":
-            t_end = time.time() + 3.0
-            base = sampler.count()
-            while sampler.count() < base + 8 and time.time() < t_end:
-                for _ in range(1 if case.get("heavy") else 20):
-                    step()
-                torch.cuda.synchronize()
-        clocks = sampler.stop() if rank == 0 else None
-        # ---- end to end through the public call with HOST buffers (pinned H2D of the inputs, kernel, D2H of the result)
-        e2e_steps = 1 if case.get("heavy") else max(3, min(args.steps, 10))
-        for _ in range(0 if case.get("heavy") else 2):
-            case["e2e_step"]()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        e0.record()
-        for _ in range(e2e_steps):
-            case["e2e_step"]()
-        e1.record()
-        barrier()
-        e2e_ms = e0.elapsed_time(e1)
-    else:
-        clocks = None
-
-    t = torch.tensor([total_ms, e2e_ms, kernel_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms, kernel_ms = t.tolist()
-    xlstm_b200.check_device_status(dev)
-
-    if rank == 0:
-        strong = case.get("scaling") == "strong"
-        nrep = 1 if strong else world   # weak scaling: every rank processes its own units
-        value = nrep * case["units"] * args.steps / (total_ms * 1e-3)
-        peak, peak_kind = measured_peak_hbm()
-        achieved = case["bytes"] / (kernel_ms * 1e-3) / 1e9
-        line = {
-            "metric": case["metric"], "value": value, "unit": case["unit"], "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-            "scaling": "strong" if strong else "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": case["workload"], **case["cfg"], "parallelism": f"{case.get('parallelism', 'dp')}{world}", "l2": case["l2"]},
-            "gpu_launches": args.steps * case["launches"],
-            "clocks": clocks,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": case.get("traffic"), "traffic_source": "ncu dram__bytes_read+write of one launch, see profiles/",
-                         "peak_source": peak_kind, "kernel": case["kernel"], "kernel_ms": kernel_ms,
-                         "algorithmic_bytes": case["bytes"], "tensor_tflops": case["flops"] / (kernel_ms * 1e-3) / 1e12},
-        }
-        if not args.no_e2e:
-            line["e2e"] = {"value": nrep * case["units"] * e2e_steps / (e2e_ms * 1e-3), "unit": case["unit"],
-                           "h2d_bytes_per_step": case["h2d"], "d2h_bytes_per_step": case["d2h"], "steps": e2e_steps}
-        if args.case == "chunkwise" and not args.no_cpu_baseline and world == 1 and not args.no_e2e:
-            threads = os.cpu_count() or 1
-            dt = cpu_chunkwise_seconds(threads)
-            line["cpu_baseline"] = {"value": CFG["S"] / dt, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": CPU_SAMPLE}
-        print(json.dumps(line))
+    heavy = bool(case.get("heavy"))
+    m = measure(case, min(args.steps, 2) if heavy else args.steps, 1 if heavy else args.warmup, world, rank, dev,
+                e2e=not args.no_e2e, sampler=sampler, hold_clocks=True)
+    line = record(case, m, world)
+    line["clocks"] = m["clocks"]
+    if case.get("extra"):
+        line.update(case["extra"](m))
     if case.get("teardown"):
         case["teardown"]()   # a live CUDA graph with NCCL kernels keeps the communicator from shutting down
+    del case
+    torch.cuda.empty_cache()
+
+    if args.case == "all" and not args.no_e2e:
+        # the other measurements of the path, in the same process (the model at tensor parallelism = world size)
+        sub = {}
+        if world == 1:
+            for name in ("step", "slstm", "layer_ops"):
+                sub[name] = sub_record(name, dev, rank, world, 20, 3)
+        sub["model7b"] = sub_record("model7b", dev, rank, world, 1, 1)
+        line["sub"] = sub
+    if headline == "chunkwise" and not args.no_cpu_baseline and world == 1 and not args.no_e2e and rank == 0:
+        threads = os.cpu_count() or 1
+        dt = cpu_chunkwise_seconds(threads)
+        line["cpu_baseline"] = {"value": CFG["S"] / dt, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": CPU_SAMPLE}
+    if rank == 0:
+        print(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -212,10 +212,19 @@ def test_tensor_parallel_nccl_decode_on_two_gpus(tmp_path):
         "graphed, _ = model.generate(tokens, 24, use_cuda_graph=True)\n"
         "assert torch.equal(eager, graphed), 'graph replay differs from the host-driven loop'\n"
         "agree = float((ref == eager).float().mean())\n"
-        "assert agree > 0.9, agree   # bf16: the all-reduce changes the summation order\n"
+        "assert agree > 0.9, agree   # bf16: the collectives change the summation order\n"
+        "# token-parallel prefill (reduce-scatter + all-gather per block, two pieces on two streams) against one GPU\n"
+        "assert model.token_parallel_ok(tokens, None, None, None)\n"
+        "lt, st = model.forward(tokens, time_collectives=True)\n"
+        "ls, ss = single.forward(tokens)\n"
+        "err = float((lt.float() - ls.float()).norm() / ls.float().norm())\n"
+        "h0 = rank * 2\n"
+        "errc = float((st[2][0] - ss[2][0][:, h0:h0 + 2]).norm() / ss[2][0][:, h0:h0 + 2].norm())\n"
+        "assert err < 1e-2 and errc < 1e-2, (err, errc)\n"
+        "assert model.comm_calls == 2 * 2 * 3 + 2 and model.comm_ms > 0   # one gather + one scatter per block and piece\n"
         "model.release_graph()\n"
         "dist.barrier(); dist.destroy_process_group()\n"
-        "print('TP_OK', rank, agree)\n")
+        "print('TP_OK', rank, agree, err, errc)\n")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
            "--master-port", "29541", str(script)]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
@@ -244,17 +253,23 @@ def test_continuous_batching_equals_per_document_decoding_on_cpu():
 
 
 @pytest.mark.gpu
-def test_continuous_batching_graph_replay_with_refill_on_gpu():
-    """The same on the GPU: the decode step is a replayed CUDA graph whose static state buffers are the slot pool;
-    refills write prefill states into single rows between replays."""
+@pytest.mark.parametrize("packed,row_len", [(True, 32768), (True, 96), (False, 32768)])
+def test_continuous_batching_graph_replay_with_refill_on_gpu(packed, row_len):
+    """The same on the GPU: the decode step is a replayed CUDA graph whose static state buffers are the slot pool.
+    Admission is a packed prefill (all waiting documents in rows of `row_len` tokens, one forward with cu_seqlens, the
+    per-document final states scattered into the slots) or one prefill per document; both must give, stream by stream,
+    the tokens of the plain greedy loop.  Rows of free slots are skipped by the step kernel (slot map -1)."""
     import xlstm_b200
     cfg = LargeConfig(embedding_dim=128, num_heads=2, num_blocks=2, vocab_size=64)
     model = LargeModel(cfg, procedural_state_dict(cfg, 4), "cuda", torch.float32)
     prompts, counts = _continuous_case()
-    dec = ContinuousDecoder(model, 3)
-    assert dec.graphed
+    dec = ContinuousDecoder(model, 3, row_len=row_len, packed_admission=packed)
+    assert dec.graphed and dec.packed == packed
     outs = dec.run(prompts, counts)
     xlstm_b200.check_device_status()
+    assert int((dec.slot_map >= 0).sum()) == 0 and len(dec.slots.free) == 3   # every slot was handed back
+    if packed:
+        assert dec.prefill_calls < len(prompts)   # several documents per prefill
+    model.release_graph()
     for p, c, o in zip(prompts, counts, outs):
         assert torch.equal(model.generate(p[None].cuda(), c)[0][0].cpu(), o)
-    model.release_graph()

@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import hashlib
 import math
+from contextlib import nullcontext as _nullcontext
 from dataclasses import dataclass
 from typing import Optional
 
@@ -108,8 +109,18 @@ def _rms_norm(x, w, eps):
 
 class LargeModel:
     """Inference-only mirror.  With ``tp_world > 1`` each rank holds ``num_heads / tp_world`` heads (column-parallel
-    q/k/v/o-gate/gate projections, per-head norm, row-parallel out_proj) and a 1/tp_world slice of the FFN width;
-    the two partial sums per block are all-reduced over ``group``."""
+    q/k/v/o-gate/gate projections, per-head norm, row-parallel out_proj).
+
+    Prefill (many tokens, compute-bound) keeps the residual stream SHARDED OVER TOKENS: the partial sums of the
+    row-parallel out_proj are reduce-scattered over the token axis, the residual add, both RMSNorms and the whole FFN run
+    on the rank's own tokens with the full FFN weights, and the normed activations are all-gathered in front of the next
+    block's projections -- one reduce-scatter + one all-gather per block, the traffic of ONE all-reduce, instead of the
+    two all-reduces of the classic scheme.  The batch rows are cut into groups that are issued alternately on two
+    streams, so that one group's collectives run under the other group's GEMMs and cell kernels.
+
+    Decode (one token per stream, bound by streaming the weights) shards the FFN over its WIDTH instead, so that every
+    rank streams 1/tp_world of every weight; that costs a second small all-reduce per block, which a replay of the
+    captured step graph includes.  Every rank therefore holds the full FFN weights; its decode slice is a view of them."""
 
     def __init__(self, cfg: LargeConfig, state_dict: dict, device, dtype=torch.bfloat16, tp_rank: int = 0,
                  tp_world: int = 1, group=None, cell_ops=ops, fused_adjacent: bool = True):
@@ -147,7 +158,12 @@ class LargeModel:
                 up=torch.cat([W(b + "ffn.proj_up_gate.weight")[f0:f1], W(b + "ffn.proj_up.weight")[f0:f1]], 0).contiguous(),
                 down=W(b + "ffn.proj_down.weight")[:, f0:f1].contiguous(),
             )
+            if tp_world > 1:   # token-parallel prefill runs the whole FFN on the rank's own tokens
+                blk["up_full"] = torch.cat([W(b + "ffn.proj_up_gate.weight"), W(b + "ffn.proj_up.weight")], 0).contiguous()
+                blk["down_full"] = W(b + "ffn.proj_down.weight").contiguous()
             self.blocks.append(blk)
+        self.comm_ms = None        # set by forward(..., time_collectives=True): CUDA-event time inside collectives
+        self.comm_bytes = 0
 
     # ------------------------------------------------------------------------------------------------
     def _all_reduce(self, x):
@@ -155,7 +171,7 @@ class LargeModel:
             torch.distributed.all_reduce(x, group=self.group)
         return x
 
-    def _mlstm_layer(self, blk, x, state, cu_seqlens, slot):
+    def _mlstm_layer(self, blk, x, state, cu_seqlens, slot, reduce: bool = True):
         cfg, NHl, dq, dv = self.cfg, self.nh_local, self.dq, self.dv
         B, S, _ = x.shape
         qkvo = F.linear(x, blk["qkvo"])
@@ -177,13 +193,14 @@ class LargeModel:
             h, new_state = self.cell.mlstm_sequence(q, k, v, ig, fg, c, n, m, cu_seqlens=cu_seqlens, eps=cfg.eps)
         if self.fused:
             hg = ops.headnorm_gate(h, o, blk["mh_norm"], eps=cfg.norm_eps)
-            return self._all_reduce(F.linear(hg, blk["out_proj"])), new_state
+            y = F.linear(hg, blk["out_proj"])
+            return (self._all_reduce(y) if reduce else y), new_state
         h = h.transpose(1, 2)                            # (B,S,NHl,dv)
         hf = h.float()
         hn = (hf - hf.mean(-1, keepdim=True)) * torch.rsqrt(hf.var(-1, keepdim=True, unbiased=False) + cfg.norm_eps)
         hn = hn.to(x.dtype).reshape(B, S, NHl * dv) * blk["mh_norm"]
         y = F.linear(torch.sigmoid(o) * hn, blk["out_proj"])
-        return self._all_reduce(y), new_state
+        return (self._all_reduce(y) if reduce else y), new_state
 
     def _add_norm(self, x, y, w):
         """x + y (y may be None) and its RMSNorm, as the reference's block does with two operators (model.py:499-510)."""
@@ -193,9 +210,109 @@ class LargeModel:
             x = x + y
         return x, _rms_norm(x, w, self.cfg.norm_eps)
 
-    def forward(self, tokens, state: Optional[dict] = None, cu_seqlens=None, slot=None, last_only: bool = False):
+    # ------------------------------------------------------------------------------------------------ token-parallel prefill
+    def _gather_tokens(self, x_shard):
+        """(T/world, D) -> (T, D): every rank's tokens, in rank order."""
+        out = torch.empty((x_shard.shape[0] * self.tp_world, x_shard.shape[1]), dtype=x_shard.dtype, device=x_shard.device)
+        torch.distributed.all_gather_into_tensor(out, x_shard.contiguous(), group=self.group)
+        return out
+
+    def _scatter_sum(self, y_full):
+        """(T, D) partial sums -> (T/world, D): the sum over ranks of this rank's tokens."""
+        T = y_full.shape[0]
+        n = T // self.tp_world
+        if torch.distributed.get_backend(self.group) == "gloo":   # (CPU tests: gloo has no reduce-scatter)
+            y = y_full.clone()
+            torch.distributed.all_reduce(y, group=self.group)
+            return y[self.tp_rank * n:(self.tp_rank + 1) * n].contiguous()
+        out = torch.empty((n, y_full.shape[1]), dtype=y_full.dtype, device=y_full.device)
+        torch.distributed.reduce_scatter_tensor(out, y_full.contiguous(), group=self.group)
+        return out
+
+    def _timed(self, fn, x, record):
+        if record is None:
+            return fn(x)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        y = fn(x)
+        e1.record()
+        record.append((e0, e1, x.numel() * x.element_size() if fn == self._scatter_sum else y.numel() * y.element_size()))
+        return y
+
+    def _side_stream(self):
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        return self._side
+
+    def token_parallel_ok(self, tokens, state, cu_seqlens, slot) -> bool:
+        return (self.tp_world > 1 and tokens.shape[1] > 1 and slot is None
+                and (tokens.shape[0] * tokens.shape[1]) % self.tp_world == 0)
+
+    def _forward_token_parallel(self, tokens, state, cu_seqlens, last_only, groups: int = 2, time_collectives: bool = False):
+        """Prefill with the residual stream sharded over tokens (see the class docstring).  Batch rows are cut into
+        `groups` independent pieces; piece g runs on stream g % 2, so its collectives overlap the other piece's compute."""
+        cfg, W, dev = self.cfg, self.tp_world, self.device
+        B, S = tokens.shape
+        if cu_seqlens is not None or B % groups or ((B // groups) * S) % W:
+            groups = 1
+        Bg = B // groups
+        n = Bg * S // W                                   # tokens of a piece that live on this rank
+        cuda = dev.type == "cuda"
+        streams = ([torch.cuda.current_stream(dev)] + ([self._side_stream()] if groups > 1 else [])) if cuda else [None]
+        record = [] if (time_collectives and cuda) else None
+        if cuda and len(streams) > 1:
+            streams[1].wait_stream(streams[0])
+        pieces = []
+        for g in range(groups):
+            flat = tokens[g * Bg:(g + 1) * Bg].reshape(-1)
+            pieces.append(dict(x=self.embedding[flat[self.tp_rank * n:(self.tp_rank + 1) * n]], pending=None, state={}))
+        for i, blk in enumerate(self.blocks):
+            for g, pc in enumerate(pieces):
+                ctx = torch.cuda.stream(streams[g % len(streams)]) if cuda else _nullcontext()
+                with ctx:
+                    pc["x"], xn = self._add_norm(pc["x"], pc["pending"], blk["norm_mlstm"])
+                    xn_full = self._timed(self._gather_tokens, xn, record).reshape(Bg, S, -1)
+                    st_in = None if state is None else tuple(t[g * Bg:(g + 1) * Bg] for t in state[i])
+                    y, st = self._mlstm_layer(blk, xn_full, st_in, cu_seqlens, None, reduce=False)
+                    pc["state"][i] = st
+                    y = self._timed(self._scatter_sum, y.reshape(Bg * S, -1), record)
+                    pc["x"], xn = self._add_norm(pc["x"], y, blk["norm_ffn"])
+                    gz = F.linear(xn, blk["up_full"])
+                    gg, zz = gz.chunk(2, dim=-1)
+                    pc["pending"] = F.linear(F.silu(gg) * zz, blk["down_full"])
+        outs = []
+        for g, pc in enumerate(pieces):
+            ctx = torch.cuda.stream(streams[g % len(streams)]) if cuda else _nullcontext()
+            with ctx:
+                pc["x"], xn = self._add_norm(pc["x"], pc["pending"], self.out_norm)
+                xn_full = self._timed(self._gather_tokens, xn, record).reshape(Bg, S, -1)
+                if last_only:
+                    xn_full = xn_full[:, -1:]
+                logits = F.linear(xn_full, self.lm_head)
+                outs.append(ops.soft_cap(logits, cfg.output_logit_soft_cap) if self.fused else _soft_cap(logits, cfg.output_logit_soft_cap))
+        if cuda and len(streams) > 1:
+            streams[0].wait_stream(streams[1])
+        logits = outs[0] if groups == 1 else torch.cat(outs, 0)
+        new_state = {}
+        for i in range(len(self.blocks)):
+            parts = [pc["state"][i] for pc in pieces]
+            new_state[i] = parts[0] if groups == 1 else tuple(torch.cat([p_[k] for p_ in parts], 0) for k in range(3))
+        if record is not None:
+            torch.cuda.synchronize(dev)
+            self.comm_ms = sum(a.elapsed_time(b_) for a, b_, _ in record)
+            self.comm_bytes = sum(nb for _, _, nb in record)
+            self.comm_calls = len(record)
+        return logits, new_state
+
+    def forward(self, tokens, state: Optional[dict] = None, cu_seqlens=None, slot=None, last_only: bool = False,
+                time_collectives: bool = False, positions=None):
         """tokens (B,S) int64 -> logits (B,S,V) (or (B,1,V) with ``last_only``) and the per-block state dict
-        ``{i: (c,n,m)}`` exactly as ``xLSTMLarge.forward`` returns it (``model.py:126-153``)."""
+        ``{i: (c,n,m)}`` exactly as ``xLSTMLarge.forward`` returns it (``model.py:126-153``).  With ``cu_seqlens`` every
+        interval of the flattened (B*S) token axis is a document of its own and the states have one row per document;
+        ``positions`` (flat token indices) restricts the logits to those tokens, returned as (len(positions), 1, V) --
+        a packed prefill only needs the last token of every document."""
+        if positions is None and self.token_parallel_ok(tokens, state, cu_seqlens, slot):
+            return self._forward_token_parallel(tokens, state, cu_seqlens, last_only, time_collectives=time_collectives)
         cfg = self.cfg
         x = self.embedding[tokens]
         new_state = {}
@@ -207,7 +324,10 @@ class LargeModel:
             x, xn = self._add_norm(x, y, blk["norm_ffn"])
             g, z = F.linear(xn, blk["up"]).chunk(2, dim=-1)
             pending = self._all_reduce(F.linear(F.silu(g) * z, blk["down"]))
-        if last_only:
+        if positions is not None:
+            x = x.reshape(-1, x.shape[-1])[positions][:, None]
+            pending = None if pending is None else pending.reshape(-1, pending.shape[-1])[positions][:, None]
+        elif last_only:
             x = x[:, -1:]
             pending = None if pending is None else pending[:, -1:]
         x, xn = self._add_norm(x, pending, self.out_norm)
@@ -217,8 +337,10 @@ class LargeModel:
         return _soft_cap(logits, cfg.output_logit_soft_cap), new_state
 
     # ------------------------------------------------------------------------------------------------
-    def _capture_decode_graph(self, state, batch: int):
-        """Capture one decode step (all blocks, lm_head, argmax) in a CUDA graph.  The reference's decode loop
+    def _capture_decode_graph(self, state, batch: int, slot_map=None):
+        """Capture one decode step (all blocks, lm_head, argmax) in a CUDA graph.  ``slot_map`` (int32, one entry per
+        row: the row's own index, or -1 while the row is free) makes the step kernel skip free rows, so an idle slot
+        costs no state traffic.  The reference's decode loop
         (``generate.py:79-85``) launches every small operator from the host for every token; replaying a graph
         removes that launch cost.  State lives in static buffers: C is updated in place by the step kernel, n and m
         are copied back into their buffers inside the graph, and the sampled token feeds the next replay."""
@@ -226,8 +348,10 @@ class LargeModel:
         self._g_state = {i: tuple(t for t in st) for i, st in state.items()}
         self._g_tok = torch.zeros(batch, 1, dtype=torch.long, device=dev)
 
+        self._g_slot = slot_map
+
         def body():
-            logits, st = self.forward(self._g_tok, self._g_state, last_only=True)
+            logits, st = self.forward(self._g_tok, self._g_state, last_only=True, slot=self._g_slot)
             dsts, srcs = [], []
             for i, (c, n, m) in st.items():
                 assert c is self._g_state[i][0]
@@ -302,33 +426,49 @@ class LargeModel:
 
 
 class ContinuousDecoder:
-    """Continuous-batch greedy decoding over a fixed pool of state slots (BASELINE config 5: decode slots with refill).
+    """Continuous-batch greedy decoding over a fixed pool of state slots with refill.
 
-    Every stream owns one row of the per-block state pool; a decode step advances ALL rows at once (on CUDA by
-    replaying the captured graph of ``LargeModel``, whose static state buffers ARE the pool).  When a stream has its
-    tokens the host frees the slot (``sharding.SlotPool``) and the next queued document takes it over: its prompt is
-    prefilled as a batch of one, the resulting (C, n, m) are written into the slot's rows and its first generated
-    token into the slot's token cell.  The reference's loop (``generate.py:27-90``) has no refill: it decodes one
-    fixed batch to the end.  Token by token a stream computes what ``LargeModel.generate`` computes for it alone.
-    Rows of free slots keep stepping on stale data; nothing reads them."""
+    Every stream owns one row of the per-block state pool; a decode step advances all ACTIVE rows at once (on CUDA by
+    replaying the captured graph of ``LargeModel``, whose static state buffers ARE the pool; rows of free slots are
+    marked -1 in the slot map the step kernel reads and cost no state traffic).  When a stream has its tokens the host
+    frees the slot (``sharding.SlotPool``) and queued documents take free slots over.
 
-    def __init__(self, model: LargeModel, num_slots: int, use_cuda_graph: Optional[bool] = None):
+    Admission is a PACKED prefill: the waiting documents are packed into rows of ``row_len`` tokens
+    (``sharding.pack_documents``), one forward with ``cu_seqlens`` runs them all -- the cell kernels reset their state at
+    every document boundary and emit every document's own final state -- and those states are scattered into the
+    documents' slots, their first tokens into the slots' token cells.  The reference's loop (``generate.py:27-90``) has no
+    refill: it decodes one fixed batch to the end.  Token by token a stream computes what ``LargeModel.generate`` computes
+    for it alone.  ``packed_admission=False`` prefills every document on its own (the CPU tests use it with the oracle
+    cell, which knows no document offsets)."""
+
+    def __init__(self, model: LargeModel, num_slots: int, use_cuda_graph: Optional[bool] = None, row_len: int = 32768,
+                 max_rows_per_prefill: int = 4, packed_admission: Optional[bool] = None):
         from .sharding import SlotPool
         self.model, self.num_slots = model, num_slots
         cfg, dev = model.cfg, model.device
         self.graphed = (dev.type == "cuda") if use_cuda_graph is None else use_cuda_graph
+        self.packed = (dev.type == "cuda" and model.cell is ops) if packed_admission is None else packed_admission
+        self.row_len, self.max_rows = row_len, max_rows_per_prefill
         self.state = {i: (torch.zeros(num_slots, model.nh_local, model.dq, model.dv, device=dev),
                           torch.zeros(num_slots, model.nh_local, model.dq, device=dev),
                           torch.zeros(num_slots, model.nh_local, 1, device=dev)) for i in range(cfg.num_blocks)}
         self.tok = torch.zeros(num_slots, 1, dtype=torch.long, device=dev)
         self.slots = SlotPool(num_slots)
+        self.slot_map = torch.full((num_slots,), -1, dtype=torch.int32, device=dev) if dev.type == "cuda" and model.cell is ops else None
+        self.prefill_calls = 0
         if self.graphed:
-            model._capture_decode_graph(self.state, num_slots)   # the graph's static buffers are this pool
+            if self.slot_map is not None:
+                self.slot_map.copy_(torch.arange(num_slots, dtype=torch.int32, device=dev))   # capture with every row live
+            model._capture_decode_graph(self.state, num_slots, slot_map=self.slot_map)   # the graph's static buffers are this pool
             self.state, self.tok = model._g_state, model._g_tok
+            if self.slot_map is not None:
+                self.slot_map.fill_(-1)
 
+    # ------------------------------------------------------------------------------------------------ admission
     @torch.no_grad()
-    def _admit(self, slot: int, prompt: torch.Tensor) -> None:
+    def _admit_single(self, slot: int, prompt: torch.Tensor) -> None:
         logits, st = self.model.forward(prompt.reshape(1, -1).to(self.model.device), last_only=True)
+        self.prefill_calls += 1
         for i, (c, n, m) in st.items():
             self.state[i][0][slot].copy_(c[0])
             self.state[i][1][slot].copy_(n[0])
@@ -336,11 +476,57 @@ class ContinuousDecoder:
         self.tok[slot].copy_(torch.argmax(logits[0, -1:], dim=-1))
 
     @torch.no_grad()
+    def _admit_packed(self, slots, prompts) -> None:
+        """slots[i] receives prompts[i].  Documents longer than a row get a row of their own length."""
+        from .sharding import pack_documents
+        dev = self.model.device
+        lengths = [int(p.numel()) for p in prompts]
+        # rows of row_len tokens; a batch that is shorter than one row gets one row of its own size, a document that is
+        # longer than a row widens the rows
+        row_len = max(max(lengths), min(self.row_len, -(-sum(lengths) // 8) * 8))
+        packed = pack_documents(lengths, row_len)
+        # rows in groups of at most max_rows: one forward per group
+        for r0 in range(0, packed.rows, self.max_rows):
+            r1 = min(packed.rows, r0 + self.max_rows)
+            lo, hi = r0 * packed.row_len, r1 * packed.row_len
+            first = next(k for k, c in enumerate(packed.cu_seqlens) if c >= lo)
+            last = max(k for k, c in enumerate(packed.cu_seqlens) if c <= hi)
+            cu = [c - lo for c in packed.cu_seqlens[first:last + 1]]
+            ids = packed.doc_ids[first:last]
+            tokens = torch.zeros((r1 - r0) * packed.row_len, dtype=torch.long, device=dev)
+            docs, rows_of_state, ends = [], [], []
+            for k, d in enumerate(ids):
+                if d < 0:
+                    continue
+                tokens[cu[k]:cu[k + 1]] = prompts[d].to(dev)
+                docs.append(d); rows_of_state.append(k); ends.append(cu[k + 1] - 1)
+            logits, st = self.model.forward(tokens.reshape(r1 - r0, packed.row_len), cu_seqlens=cu,
+                                            positions=torch.tensor(ends, dtype=torch.long, device=dev))
+            self.prefill_calls += 1
+            dst = torch.tensor([slots[d] for d in docs], dtype=torch.long, device=dev)
+            src = torch.tensor(rows_of_state, dtype=torch.long, device=dev)
+            for i, (c, n, m) in st.items():
+                self.state[i][0].index_copy_(0, dst, c.index_select(0, src))
+                self.state[i][1].index_copy_(0, dst, n.index_select(0, src))
+                self.state[i][2].index_copy_(0, dst, m.index_select(0, src).reshape(len(docs), *self.state[i][2].shape[1:]))
+            self.tok.index_copy_(0, dst, torch.argmax(logits[:, -1], dim=-1, keepdim=True))
+
+    def _admit(self, slots, prompts) -> None:
+        if self.packed:
+            self._admit_packed(slots, prompts)
+        else:
+            for s_, p_ in zip(slots, prompts):
+                self._admit_single(s_, p_)
+        if self.slot_map is not None:
+            idx = torch.tensor(slots, dtype=torch.long, device=self.model.device)
+            self.slot_map.index_copy_(0, idx, idx.to(torch.int32))
+
+    @torch.no_grad()
     def _step(self) -> None:
         if self.graphed:
             self.model._graph.replay()
             return
-        logits, st = self.model.forward(self.tok, self.state, last_only=True)
+        logits, st = self.model.forward(self.tok, self.state, last_only=True, slot=self.slot_map)
         for i, (c, n, m) in st.items():
             for dst, src in zip(self.state[i], (c, n, m)):
                 if dst is not src:
@@ -359,18 +545,25 @@ class ContinuousDecoder:
         hist = []            # token column of every step (device tensors; read back once at the end)
         spans = {}           # document -> (slot, first, count)
         while queue or active:
-            while queue and self.slots.free:
-                d = queue.pop()
-                s = self.slots.acquire(d)
-                self._admit(s, prompts[d])
-                active[s] = [d, counts[d], len(hist)]
+            if queue and self.slots.free:
+                batch = []
+                while queue and self.slots.free:
+                    d = queue.pop()
+                    batch.append((self.slots.acquire(d), d))
+                self._admit([s_ for s_, _ in batch], [prompts[d] for _, d in batch])
+                for s_, d in batch:
+                    active[s_] = [d, counts[d], len(hist)]
             hist.append(self.tok[:, 0].clone())      # the token every active slot has just produced
-            for s in list(active):
-                active[s][1] -= 1
-                if active[s][1] == 0:
-                    d, _, first = active.pop(s)
-                    spans[d] = (s, first, counts[d])
-                    self.slots.release(s)
+            freed = []
+            for s_ in list(active):
+                active[s_][1] -= 1
+                if active[s_][1] == 0:
+                    d, _, first = active.pop(s_)
+                    spans[d] = (s_, first, counts[d])
+                    self.slots.release(s_)
+                    freed.append(s_)
+            if freed and self.slot_map is not None:
+                self.slot_map.index_fill_(0, torch.tensor(freed, dtype=torch.long, device=self.model.device), -1)
             if active:
                 self._step()
         cols = torch.stack(hist, dim=1).cpu()          # (slots, steps)
