@@ -150,7 +150,7 @@ def headline_config(world):
             "l2": "inputs (%d MB per step) exceed the 126 MB L2" % (chunkwise_bytes(**CFG) // 10 ** 6)}
 
 
-def run_reference(args, rank):
+def run_reference(args, rank, json_out):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
@@ -167,7 +167,7 @@ def run_reference(args, rank):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": headline_config(args.gpus),
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": CPU_SAMPLE},
-        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), file=json_out, flush=True)
 
 
 # ---------------------------------------------------------------------------------------------- the reference's own sLSTM CUDA backend
@@ -552,8 +552,13 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    # stdout carries the one JSON line and nothing else: whatever libraries print on the way (the reference's JIT build
+    # of its sLSTM extension prints its compiler flags) goes to stderr
+    sys.stdout.flush()
+    json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if args.impl == "reference":
-        run_reference(args, rank)
+        run_reference(args, rank, json_out)
         return
     args.warmup = max(args.warmup, 3)
 
@@ -595,7 +600,7 @@ def main():
         dt = cpu_chunkwise_seconds(threads)
         line["cpu_baseline"] = {"value": CFG["S"] / dt, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": CPU_SAMPLE}
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), file=json_out, flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
