@@ -220,11 +220,23 @@ def test_tensor_parallel_nccl_decode_on_two_gpus(tmp_path):
         "err = float((lt.float() - ls.float()).norm() / ls.float().norm())\n"
         "h0 = rank * 2\n"
         "errc = float((st[2][0] - ss[2][0][:, h0:h0 + 2]).norm() / ss[2][0][:, h0:h0 + 2].norm())\n"
-        "assert err < 1e-2 and errc < 1e-2, (err, errc)\n"
+        "assert err < 3e-2 and errc < 3e-2, (err, errc)   # bf16: partial sums are rounded before they are reduced\n"
+        "# the same pair in fp32 separates the scheme from bf16 rounding: <= 1e-2 with a wide margin\n"
+        "torch.backends.cuda.matmul.allow_tf32 = False\n"
+        "m32 = LargeModel(cfg, sd, dev, torch.float32, tp_rank=rank, tp_world=world)\n"
+        "s32 = LargeModel(cfg, sd, dev, torch.float32)\n"
+        "l32, st32 = m32.forward(tokens)\n"
+        "r32, sr32 = s32.forward(tokens)\n"
+        "err32 = float((l32 - r32).norm() / r32.norm())\n"
+        "errc32 = float((st32[2][0] - sr32[2][0][:, h0:h0 + 2]).norm() / sr32[2][0][:, h0:h0 + 2].norm())\n"
+        "assert err32 < 1e-4 and errc32 < 1e-4, (err32, errc32)\n"
+        "g32, _ = m32.generate(tokens, 24)\n"
+        "gs32, _ = s32.generate(tokens, 24)\n"
+        "assert torch.equal(g32, gs32), 'fp32 tensor-parallel tokens differ from the single-GPU tokens'\n"
         "assert model.comm_calls == 2 * 2 * 3 + 2 and model.comm_ms > 0   # one gather + one scatter per block and piece\n"
         "model.release_graph()\n"
         "dist.barrier(); dist.destroy_process_group()\n"
-        "print('TP_OK', rank, agree, err, errc)\n")
+        "print('TP_OK', rank, agree, err, errc, err32, errc32)\n")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
            "--master-port", "29541", str(script)]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
