@@ -204,6 +204,29 @@ typedef struct xl_soft_cap_params {
 
 int xl_soft_cap(const xl_soft_cap_params* p, void* cuda_stream);
 
+/* Depthwise causal convolution over time with optional SiLU, as in front of the sLSTM cell:
+ * out[b,t,f] = act(bias[f] + sum_j weight[f][j] * x[b, t - (K-1) + j, f]), taps in front of the first token read zero
+ * (CausalConv1d.forward, xlstm/components/conv.py:110-129, with conv_act_fn of xlstm/blocks/slstm/layer.py:133-142).
+ * The reference pads per batch row only, so with several documents packed into a row its convolution reaches across
+ * their boundaries although the cell behind it restarts there; with cu_seqlens a tap never reaches in front of the
+ * first token of its own document.  The convolution is accumulated in fp32 and rounded to `dtype` before the activation,
+ * as the reference's two modules do. */
+typedef struct xl_conv1d_params {
+  const void* x;        /* (B, S, F) through x_sb, x_st (elements); F contiguous */
+  const void* weight;   /* (F, K) contiguous: nn.Conv1d(groups=F).weight[:, 0, :] */
+  const void* bias;     /* (F) or NULL */
+  void* out;            /* (B, S, F) through o_sb, o_st; must not alias x */
+  const int32_t* cu_seqlens;  /* device, num_docs + 1 offsets on the flattened (B*S) axis, or NULL */
+  int32_t B, S, F, K;   /* K <= 8 */
+  int32_t num_docs;
+  int32_t act;          /* 0 = none, 1 = SiLU */
+  int64_t x_sb, x_st, o_sb, o_st;
+  int32_t dtype;
+} xl_conv1d_params;
+
+/* Requires F a multiple of the 16-byte vector (8 bf16 / 4 fp32). */
+int xl_causal_conv1d(const xl_conv1d_params* p, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

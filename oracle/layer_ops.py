@@ -13,7 +13,13 @@ Restates, with explicit rounding points, what the reference computes eagerly:
 
 * ``soft_cap``: ``cap * tanh(values / cap)`` (``components.py:5-22``), every operator in the input dtype.
 
-Pinning: ``tests/golden/make_golden_layer.py`` ran the reference's own ``RMSNorm`` and ``MultiHeadLayerNorm``
+* ``causal_conv1d``: the depthwise causal convolution in front of the sLSTM cell (``CausalConv1d.forward``,
+  ``xlstm/components/conv.py:110-129``: ``nn.Conv1d`` with ``groups = features`` and left padding ``K - 1``) followed by
+  the layer's SiLU (``xlstm/blocks/slstm/layer.py:133-142``); with document offsets every document is convolved alone,
+  which is what the reference gives when it is called once per document.
+
+Pinning: ``tests/golden/make_golden_conv.py`` ran the reference's ``CausalConv1d`` (per document for the packed case);
+``tests/golden/make_golden_layer.py`` ran the reference's own ``RMSNorm`` and ``MultiHeadLayerNorm``
 modules and its ``soft_cap`` function in this container and committed inputs and outputs; ``tests/test_oracle_layer_ops.py`` checks this
 restatement against them.
 """
@@ -50,3 +56,28 @@ def soft_cap(x: torch.Tensor, cap: float, out_float32: bool = False):
     t = torch.tanh(q.float()).to(dt)
     y = (cap * t.float()).to(dt)
     return y.float() if out_float32 else y
+
+
+def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, cu_seqlens=None, silu: bool = True):
+    """x (B,S,F), weight (F,K) [= nn.Conv1d(groups=F).weight[:,0,:]], bias (F).  out[b,t] = bias + sum_j weight[:,j] *
+    x[b, t-(K-1)+j] with zeros in front of the first token of the document (of the row without ``cu_seqlens``), rounded
+    to ``x.dtype``; then SiLU, rounded again."""
+    dt = x.dtype
+    B, S, F_ = x.shape
+    K = weight.shape[1]
+    xf = x.float().reshape(B * S, F_)
+    cu = [b * S for b in range(B + 1)] if cu_seqlens is None else sorted(set([int(c) for c in cu_seqlens] + [b * S for b in range(B + 1)]))
+    out = torch.zeros_like(xf)
+    for a, e in zip(cu[:-1], cu[1:]):
+        if e <= a:
+            continue
+        seg = xf[a:e]
+        acc = torch.zeros_like(seg) if bias is None else bias.float().expand_as(seg).clone()
+        for lag in range(K):
+            if lag < e - a:
+                acc[lag:] += seg[:e - a - lag] * weight[:, K - 1 - lag].float()
+        out[a:e] = acc
+    y = out.to(dt)
+    if silu:
+        y = torch.nn.functional.silu(y.float()).to(dt)
+    return y.reshape(B, S, F_)

@@ -117,3 +117,33 @@ def test_soft_cap_matches_oracle_and_reference_fixture(tag):
         _close(got, O.soft_cap(x.float(), 15.0), torch.float32)
     big = torch.randn(3, 1000003, generator=torch.Generator().manual_seed(1)) * 40
     _close(xlstm_b200.soft_cap(big.cuda(), 30.0), O.soft_cap(big, 30.0), torch.float32)
+
+
+@pytest.mark.parametrize("tag", ["f32", "bf16"])
+def test_causal_conv1d_kernel_matches_reference_module_fixture(tag):
+    import xlstm_b200
+    g, dt = load_golden("conv"), DT[tag]
+    x, w, b = (g[f"{tag}_{k}"].to(dt).cuda() for k in "xwb")
+    _close(xlstm_b200.causal_conv1d(x, w, b), g[f"{tag}_rows"], dt)
+    _close(xlstm_b200.causal_conv1d(x, w, b, cu_seqlens=g["cu"].tolist()), g[f"{tag}_packed"], dt)
+
+
+@pytest.mark.parametrize("tag,B,S,F_,K,bias,silu", [("bf16", 3, 200, 1024, 4, True, True), ("bf16", 2, 70, 72, 3, False, True),
+                                                   ("f32", 2, 129, 260, 4, True, False), ("bf16", 1, 1, 8, 8, True, True),
+                                                   ("f32", 1, 65, 4, 1, True, True)])
+def test_causal_conv1d_kernel_matches_oracle_with_document_boundaries(tag, B, S, F_, K, bias, silu):
+    """Boundaries at tile edges, inside tiles, back to back (empty documents) and at row ends; strided input."""
+    import xlstm_b200
+    dt = DT[tag]
+    g = torch.Generator().manual_seed(B * 1000 + S + F_)
+    wide = (2.0 * torch.randn(B, S, F_ + 16, generator=g)).to(dt)
+    x = wide[:, :, 8:8 + F_] if F_ % 8 == 0 else wide[:, :, :F_].contiguous()   # a column slice of a wider buffer
+    w = torch.randn(F_, K, generator=g).to(dt)
+    b = (0.3 * torch.randn(F_, generator=g)).to(dt) if bias else None
+    cuts = sorted(set([0, B * S] + [r * S for r in range(B)] + [min(B * S, c) for c in (1, 3, 3, 63, 64, 65, 127, 128, 128, S - 1)]))
+    cuts = cuts[:1] + [c for c in cuts[1:] for _ in range(2 if c == 64 else 1)]   # an empty document at offset 64
+    cuts = sorted(c for c in cuts if c <= B * S)
+    for cu in (None, cuts):
+        want = O.causal_conv1d(x, w, b, cu_seqlens=cu, silu=silu)
+        got = xlstm_b200.causal_conv1d(x.cuda(), w.cuda(), None if b is None else b.cuda(), cu_seqlens=cu, silu=silu)
+        _close(got, want, dt)

@@ -339,3 +339,32 @@ def test_reference_slstm_cell_b200_vs_vanilla_small_with_initial_state():
             assert o.shape == o_ref.shape == (Bc, heads, Sc, hidden // heads)
             assert rel_l2(o.float().cpu(), o_ref.cpu()) < 1e-2
             assert rel_l2(s.float().cpu(), s_ref.cpu()) < 1e-2
+
+
+def test_packed_slstm_layers_equal_per_document_runs():
+    """Two sLSTM blocks of the unchanged ``xLSTMBlockStack`` on a packed batch: with the pack-aware convolution in
+    front of the b200 cell (``integration.pack_aware_slstm_layers`` + ``set_document_offsets``) every document comes
+    out as it does when the stack sees it alone; with the reference's own convolution the first tokens of every
+    document but the first of a row are wrong (its taps reach across the boundary)."""
+    from xlstm_b200.integration import pack_aware_slstm_layers, set_document_offsets
+    B, S, D = 2, 96, 256
+    stack = _slstm_stack("b200", torch.bfloat16, num_blocks=2, embedding_dim=D, seed=3)
+    x = torch.randn(B, S, D, generator=torch.Generator().manual_seed(5)).bfloat16().cuda()
+    cu = [0, 40, 96, 96 + 7, 96 + 7, 192]
+    flat = x.reshape(1, B * S, D)
+    with torch.no_grad():
+        alone = torch.cat([stack(flat[:, a:e]) for a, e in zip(cu[:-1], cu[1:]) if e > a], dim=1).reshape(B, S, D)
+        set_document_offsets(stack, cu)          # cells only: the reference convolution still leaks
+        leaky = stack(x)
+        assert pack_aware_slstm_layers(stack) == 2
+        set_document_offsets(stack, cu)
+        packed = stack(x)
+        set_document_offsets(stack, None)
+        rows = stack(x)
+    assert rel_l2(packed.float().cpu(), alone.float().cpu()) < 1e-2
+    assert rel_l2(leaky[:, 40:44].float().cpu(), alone[:, 40:44].float().cpu()) > 5e-2   # what the kernel fixes
+    # without offsets the replaced front computes what the reference front computes for plain rows
+    ref_stack = _slstm_stack("b200", torch.bfloat16, source=None, num_blocks=2, embedding_dim=D, seed=3)
+    with torch.no_grad():
+        want = ref_stack(x)
+    assert rel_l2(rows.float().cpu(), want.float().cpu()) < 1e-2

@@ -45,3 +45,16 @@ def test_soft_cap_matches_reference_function(tag):
         tol = 0.0 if tag == "bf16" else 4e-6
         assert (got.float() - want).abs().max().item() <= tol
         assert torch.equal(O.soft_cap(x, cap, out_float32=True), got.float())
+
+
+@pytest.mark.parametrize("tag", ["f32", "bf16"])
+def test_causal_conv1d_matches_reference_module(tag):
+    """Rows, and rows packed from documents (the reference module run once per document)."""
+    g, dt = load_golden("conv"), DT[tag]
+    x, w, b = (g[f"{tag}_{k}"].to(dt) for k in "xwb")
+    tol = 0.0 if tag == "bf16" else 4e-6
+    assert (O.causal_conv1d(x, w, b).float() - g[f"{tag}_rows"]).abs().max().item() <= tol
+    packed = O.causal_conv1d(x, w, b, cu_seqlens=g["cu"].tolist())
+    assert (packed.float() - g[f"{tag}_packed"]).abs().max().item() <= tol
+    # the fixture itself shows why the offsets matter: without them the taps reach into the previous document
+    assert (g[f"{tag}_rows"] - g[f"{tag}_packed"]).abs().max().item() > 1.0

@@ -16,7 +16,7 @@ XL_F32, XL_BF16 = 0, 1
 EXPORTS = (
     "xl_strerror", "xl_last_cuda_error", "xl_abi_version",
     "xl_mlstm_chunkwise", "xl_mlstm_recurrent", "xl_mlstm_step", "xl_slstm_forward",
-    "xl_add_rmsnorm", "xl_headnorm_gate", "xl_soft_cap",
+    "xl_add_rmsnorm", "xl_headnorm_gate", "xl_soft_cap", "xl_causal_conv1d",
 )
 
 
@@ -85,6 +85,15 @@ class SoftCapParams(C.Structure):
                 ("out_f32", C.c_int32)]
 
 
+class Conv1dParams(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("weight", C.c_void_p), ("bias", C.c_void_p), ("out", C.c_void_p), ("cu_seqlens", C.c_void_p),
+        ("B", C.c_int32), ("S", C.c_int32), ("F", C.c_int32), ("K", C.c_int32), ("num_docs", C.c_int32), ("act", C.c_int32),
+        ("x_sb", C.c_int64), ("x_st", C.c_int64), ("o_sb", C.c_int64), ("o_st", C.c_int64),
+        ("dtype", C.c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -104,7 +113,7 @@ def lib() -> C.CDLL:
         for name, ptype in (("xl_mlstm_chunkwise", MlstmSeqParams), ("xl_mlstm_recurrent", MlstmSeqParams),
                             ("xl_mlstm_step", MlstmStepParams), ("xl_slstm_forward", SlstmParams),
                             ("xl_add_rmsnorm", AddRmsnormParams), ("xl_headnorm_gate", HeadnormGateParams),
-                            ("xl_soft_cap", SoftCapParams)):
+                            ("xl_soft_cap", SoftCapParams), ("xl_causal_conv1d", Conv1dParams)):
             fn = getattr(l, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(ptype), C.c_void_p]

@@ -3,6 +3,8 @@
 //   xl_soft_cap       cap * tanh(x / cap) of gate pre-activations and logits  (components.py:5-22)
 //   xl_headnorm_gate  per-head LayerNorm of the cell output read through its (B,NH,S,DH) strides, weight, output gate
 //                     (xlstm/xlstm_large/model.py:435-449, components.py:171-242)
+//   xl_causal_conv1d  depthwise causal convolution over time + SiLU in front of the sLSTM cell, with document
+//                     boundaries (xlstm/components/conv.py:110-129, xlstm/blocks/slstm/layer.py:133-142)
 // Both are bound by HBM traffic: every element is read once with 16-byte loads, kept in registers across the
 // reduction, and written once.  Rounding points are those of the reference's eager operator sequence (fp32
 // reductions; the normalised value rounded to the model dtype, then the weight product rounded, then the gate).
@@ -223,6 +225,87 @@ __global__ void __launch_bounds__(256) soft_cap_kernel(const T* __restrict__ x, 
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Depthwise causal convolution over time, optional SiLU, document boundaries.
+//   y[b,t,f] = bias[f] + sum_{lag=0}^{K-1} w[f][K-1-lag] x[b,t-lag,f]      (taps that reach in front of the first token of
+//   the document -- or of the row -- read zero), out = silu(round(y)).
+// A thread owns one 16-byte vector of features and walks CONV_TILE consecutive tokens with the last K-1 inputs in
+// registers, so x is read once (plus a K-1 token halo per tile) and out written once: HBM-bound.
+// ---------------------------------------------------------------------------------------------
+constexpr int CONV_THREADS = 128, CONV_TILE = 64, CONV_MAXK = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(CONV_THREADS) causal_conv1d_kernel(const xl_conv1d_params p) {
+  constexpr int V = Vec16<T>::N;
+  const int f0 = (blockIdx.x * CONV_THREADS + threadIdx.x) * V;
+  if (f0 >= p.F) return;
+  const int b = blockIdx.z, K = p.K;
+  const int t0 = blockIdx.y * CONV_TILE, t1 = min(p.S, t0 + CONV_TILE);
+  const T* x = static_cast<const T*>(p.x) + (long long)b * p.x_sb + f0;
+  T* out = static_cast<T*>(p.out) + (long long)b * p.o_sb + f0;
+  // weights by lag: wl[l] multiplies x[t-l] (tap K-1-l of the convolution's weight; zero beyond the kernel size, so that
+  // every index below is a compile-time constant and the arrays stay in registers); win[l-1] = x[t-l]
+  float wl[CONV_MAXK][V], bias[V], win[CONV_MAXK - 1][V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    bias[i] = p.bias ? to_float(static_cast<const T*>(p.bias)[f0 + i]) : 0.f;
+#pragma unroll
+    for (int l = 0; l < CONV_MAXK; ++l) wl[l][i] = l < K ? to_float(static_cast<const T*>(p.weight)[(long long)(f0 + i) * K + (K - 1 - l)]) : 0.f;
+  }
+  // tokens since the first token of the document that holds (b, t0); the next boundary on the flattened axis
+  long long since = t0, next_b = 0x7fffffffffffffffLL;
+  int idx = 0;
+  const long long flat0 = (long long)b * p.S + t0;
+  if (p.cu_seqlens) {
+    int lo = 0, hi = p.num_docs;   // last offset <= flat0
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if ((long long)p.cu_seqlens[mid] <= flat0) lo = mid; else hi = mid - 1;
+    }
+    idx = lo;
+    since = flat0 - (long long)p.cu_seqlens[idx];
+    if (since > t0) since = t0;   // a row start is a start whatever the offsets say
+    next_b = idx + 1 <= p.num_docs ? (long long)p.cu_seqlens[idx + 1] : next_b;
+  }
+#pragma unroll
+  for (int l = 1; l < CONV_MAXK; ++l) {
+    const int t = t0 - l;
+    Vec16<T> v;
+#pragma unroll
+    for (int i = 0; i < V; ++i) v.v[i] = from_float<T>(0.f);
+    if (l < K && t >= 0) v = load16(x + (long long)t * p.x_st);
+#pragma unroll
+    for (int i = 0; i < V; ++i) win[l - 1][i] = to_float(v.v[i]);
+  }
+  for (int t = t0; t < t1; ++t) {
+    const long long flat = (long long)b * p.S + t;
+    while (flat >= next_b) {   // a document starts here (empty documents are stepped over)
+      since = flat - next_b;
+      ++idx;
+      next_b = idx + 1 <= p.num_docs ? (long long)p.cu_seqlens[idx + 1] : 0x7fffffffffffffffLL;
+    }
+    const Vec16<T> cur = load16(x + (long long)t * p.x_st);
+    Vec16<T> o;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const float c = to_float(cur.v[i]);
+      float acc = bias[i];
+      acc = fmaf(wl[0][i], c, acc);
+#pragma unroll
+      for (int l = 1; l < CONV_MAXK; ++l)
+        if (l <= since) acc = fmaf(wl[l][i], win[l - 1][i], acc);
+      float y = to_float(from_float<T>(acc));            // the convolution's output is rounded to T ...
+      if (p.act) y = y * sigmoid_for<T>(y);               // ... before the activation
+      o.v[i] = from_float<T>(y);
+#pragma unroll
+      for (int l = CONV_MAXK - 1; l >= 2; --l) win[l - 1][i] = win[l - 2][i];
+      win[0][i] = c;
+    }
+    store16(out + (long long)t * p.o_st, o);
+    ++since;
+  }
+}
+
 }  // namespace xl
 
 extern "C" int xl_add_rmsnorm(const xl_add_rmsnorm_params* p, void* cuda_stream) {
@@ -300,4 +383,23 @@ extern "C" int xl_soft_cap(const xl_soft_cap_params* p, void* cuda_stream) {
   else
     soft_cap_kernel<__nv_bfloat16, __nv_bfloat16, true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(p->x), static_cast<__nv_bfloat16*>(p->out), p->n, p->cap);
   return check_launch("xl_soft_cap");
+}
+
+extern "C" int xl_causal_conv1d(const xl_conv1d_params* p, void* cuda_stream) {
+  using namespace xl;
+  if (!p || !p->x || !p->weight || !p->out) return XL_ERR_NULL_POINTER;
+  if (p->dtype != XL_F32 && p->dtype != XL_BF16) return XL_ERR_BAD_DTYPE;
+  const int V = p->dtype == XL_F32 ? 4 : 8;
+  if (p->B <= 0 || p->S <= 0 || p->F <= 0 || p->F % V != 0 || p->K < 1) return XL_ERR_BAD_SHAPE;
+  if (p->K > CONV_MAXK || p->B > 65535) return XL_ERR_TOO_LARGE;
+  if (p->cu_seqlens && p->num_docs <= 0) return XL_ERR_BAD_SHAPE;
+  if (p->x_sb % V || p->x_st % V || p->o_sb % V || p->o_st % V || p->x_st < p->F || p->o_st < p->F) return XL_ERR_BAD_STRIDE;
+  if (!aligned16(p->x) || !aligned16(p->out)) return XL_ERR_BAD_ALIGNMENT;
+  if (p->out == p->x) return XL_ERR_ALIASING;   // a tile's halo is read by the neighbouring thread block
+  const dim3 grid((unsigned)((p->F / V + CONV_THREADS - 1) / CONV_THREADS), (unsigned)((p->S + CONV_TILE - 1) / CONV_TILE), (unsigned)p->B);
+  if (grid.y > 65535) return XL_ERR_TOO_LARGE;
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  if (p->dtype == XL_F32) causal_conv1d_kernel<float><<<grid, CONV_THREADS, 0, st>>>(*p);
+  else causal_conv1d_kernel<__nv_bfloat16><<<grid, CONV_THREADS, 0, st>>>(*p);
+  return check_launch("xl_causal_conv1d");
 }

@@ -10,6 +10,11 @@ runs unchanged.
 ``install_slstm_backend()`` teaches ``xlstm.blocks.slstm.cell.sLSTMCell`` the backend name
 ``"b200"`` (the switch at ``cell.py:777-788``), so ``sLSTMLayerConfig(backend="b200")`` and
 ``xLSTMBlockStack`` run unchanged.
+
+``pack_aware_slstm_layers(stack)`` swaps, in every sLSTM layer of a built model, the causal
+convolution + SiLU in front of the cell for the kernel that knows document boundaries, and
+``set_document_offsets(stack, cu_seqlens)`` hands the boundaries of a packed batch to those
+convolutions and to the b200 cells behind them.
 """
 from __future__ import annotations
 
@@ -129,3 +134,64 @@ def install_slstm_backend():
     cell_mod.sLSTMCell.__new__ = staticmethod(__new__)
     _slstm_installed = True
     return sLSTMCell_b200
+
+
+class PackAwareCausalConv1d(torch.nn.Module):
+    """Stands in for the pair ``CausalConv1d`` + ``SiLU`` at the front of the reference's sLSTM layer
+    (xlstm/blocks/slstm/layer.py:133-142).  It owns the SAME ``nn.Conv1d`` parameters (state dicts stay compatible) and
+    computes convolution and activation in one kernel; with document offsets set, no tap reaches across a document
+    boundary -- the reference's module pads per batch row only (xlstm/components/conv.py:110-129), so in a packed row
+    it mixes the last tokens of one document into the first tokens of the next although the cell restarts there.
+    Single-token ``step`` calls go to the reference module (the activation is applied here, since the layer's own
+    activation module is replaced by an identity)."""
+
+    def __init__(self, reference_conv):
+        super().__init__()
+        self.ref = reference_conv
+        self.config = reference_conv.config
+        self._cu_seqlens = None
+
+    def set_document_offsets(self, cu_seqlens):
+        self._cu_seqlens = cu_seqlens
+
+    def reset_parameters(self, **kwargs):
+        self.ref.reset_parameters(**kwargs)
+
+    def forward(self, x, conv_state=None, return_last_state: bool = False):
+        if self.config.kernel_size == 0:
+            return x
+        if conv_state is not None:
+            if self._cu_seqlens is not None:
+                raise ValueError("a packed batch starts every document from an empty convolution state")
+            xx = torch.cat([conv_state, x], dim=1)
+            y = ops.causal_conv1d(xx, self.ref.conv.weight, self.ref.conv.bias, silu=True)[:, conv_state.shape[1]:]
+        else:
+            y = ops.causal_conv1d(x, self.ref.conv.weight, self.ref.conv.bias, cu_seqlens=self._cu_seqlens, silu=True)
+        if return_last_state:
+            full = x if conv_state is None else torch.cat([conv_state, x], dim=1)
+            return y, full[:, -(self.config.kernel_size - 1):]
+        return y
+
+    def step(self, x, conv_state=None):
+        y, state = self.ref.step(x, conv_state=conv_state)
+        return torch.nn.functional.silu(y), state
+
+
+def pack_aware_slstm_layers(model) -> int:
+    """Replaces conv1d + conv_act_fn in every ``sLSTMLayer`` below `model`; returns how many layers were changed."""
+    layer_mod = importlib.import_module("xlstm.blocks.slstm.layer")
+    n = 0
+    for m in model.modules():
+        if isinstance(m, layer_mod.sLSTMLayer) and m.config.conv1d_kernel_size > 0 and not isinstance(m.conv1d, PackAwareCausalConv1d):
+            m.conv1d = PackAwareCausalConv1d(m.conv1d)
+            m.conv_act_fn = torch.nn.Identity()
+            n += 1
+    return n
+
+
+def set_document_offsets(model, cu_seqlens) -> None:
+    """Document boundaries (offsets on the flattened (B*S) token axis, or None to clear) for every pack-aware
+    convolution and every b200 sLSTM cell below `model`."""
+    for m in model.modules():
+        if isinstance(m, PackAwareCausalConv1d) or type(m).__name__ == "sLSTMCell_b200":
+            m.set_document_offsets(cu_seqlens)

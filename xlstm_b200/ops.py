@@ -12,7 +12,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
-from ._lib import (AddRmsnormParams, HeadnormGateParams, MlstmSeqParams, MlstmStepParams, SlstmParams, SoftCapParams, XL_BF16, XL_F32,
+from ._lib import (AddRmsnormParams, Conv1dParams, HeadnormGateParams, MlstmSeqParams, MlstmStepParams, SlstmParams, SoftCapParams, XL_BF16, XL_F32,
                    check, lib)
 
 _DTYPES = {torch.float32: XL_F32, torch.bfloat16: XL_BF16}
@@ -393,4 +393,37 @@ def soft_cap(x, cap: float, out_float32: bool = False, float32_math: bool = Fals
     p.dtype, p.out_f32 = _DTYPES[x.dtype], (2 if float32_math else int(out_float32))
     with torch.cuda.device(x.device):
         check(lib().xl_soft_cap(C.byref(p), _stream_ptr(x.device)), "xl_soft_cap")
+    return out
+
+
+def causal_conv1d(x, weight, bias=None, cu_seqlens=None, silu: bool = True):
+    """Depthwise causal convolution over time and (by default) SiLU, the front of the reference's sLSTM layer
+    (``CausalConv1d.forward``, xlstm/components/conv.py:110-129; activation xlstm/blocks/slstm/layer.py:133-142).
+
+    x (B, S, F); weight (F, K) or the ``nn.Conv1d`` weight (F, 1, K); bias (F) or None.  With ``cu_seqlens`` (offsets on
+    the flattened (B*S) axis) no tap reaches across a document boundary -- the reference's module knows rows only."""
+    _require_cuda(x, weight, bias)
+    if x.dim() != 3 or x.dtype not in _DTYPES:
+        raise ValueError("causal_conv1d: x must be (B,S,F) in float32 or bfloat16")
+    B, S, F_ = x.shape
+    if weight.dim() == 3:
+        weight = weight[:, 0, :]
+    if weight.shape[0] != F_ or weight.dtype != x.dtype or (bias is not None and (bias.shape != (F_,) or bias.dtype != x.dtype)):
+        raise ValueError("causal_conv1d: weight must be (F,K) and bias (F,), both in x's dtype")
+    x = _last_contig(x)
+    out = torch.empty((B, S, F_), dtype=x.dtype, device=x.device)
+    p = Conv1dParams()
+    w = weight.contiguous()
+    p.x, p.weight, p.out = x.data_ptr(), w.data_ptr(), out.data_ptr()
+    p.bias = bias.contiguous().data_ptr() if bias is not None else None
+    nd = 0
+    if cu_seqlens is not None:
+        cu_dev, nd = prepare_cu_seqlens(cu_seqlens, B, S, x.device)
+        p.cu_seqlens = cu_dev.data_ptr()
+    p.B, p.S, p.F, p.K, p.num_docs, p.act = B, S, F_, w.shape[1], nd, int(bool(silu))
+    p.x_sb, p.x_st = x.stride()[:2]
+    p.o_sb, p.o_st = out.stride()[:2]
+    p.dtype = _DTYPES[x.dtype]
+    with torch.cuda.device(x.device):
+        check(lib().xl_causal_conv1d(C.byref(p), _stream_ptr(x.device)), "xl_causal_conv1d")
     return out
