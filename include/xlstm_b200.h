@@ -194,12 +194,17 @@ int xl_headnorm_gate(const xl_headnorm_gate_params* p, void* cuda_stream);
  * cell kernels take for the gates; out_f32 = 2 writes fp32 computed in fp32 from the `dtype` input without the
  * intermediate roundings (for callers that keep the gates in fp32 although the model runs in bf16). */
 typedef struct xl_soft_cap_params {
-  const void* x;   /* n elements, contiguous */
-  void* out;       /* n elements of `dtype`, or of fp32 when out_f32 is 1 or 2; may alias x when the types agree */
+  const void* x;   /* n elements, contiguous -- or, with cols > 0, n / cols rows of cols elements x_row_stride apart */
+  void* out;       /* n elements (contiguous) of `dtype`, or of fp32 when out_f32 is 1 or 2; may alias x when the types
+                      and the layouts agree */
   int64_t n;
   float cap;
   int32_t dtype;
   int32_t out_f32;
+  int64_t cols;          /* 0 = x is contiguous */
+  int64_t x_row_stride;  /* elements; used with cols > 0: x may be a column slice of a wider projection output */
+  const void* bias;      /* (cols) of `dtype` or NULL: added to x first and rounded to `dtype`, as a Linear layer's bias
+                            is (the gate projections of model.py:389-394 carry one); needs cols > 0 */
 } xl_soft_cap_params;
 
 int xl_soft_cap(const xl_soft_cap_params* p, void* cuda_stream);
@@ -226,6 +231,42 @@ typedef struct xl_conv1d_params {
 
 /* Requires F a multiple of the 16-byte vector (8 bf16 / 4 fp32). */
 int xl_causal_conv1d(const xl_conv1d_params* p, void* cuda_stream);
+
+/* out[r, j] = silu(gz[r, j]) * gz[r, F + j], the sigmoid-linear unit rounded to `dtype` before the product as the
+ * reference's eager `act_fn(proj_up_gate(x)) * proj_up(x)` rounds it (xlstm/xlstm_large/model.py:268-277), on the output
+ * of ONE projection that stacks proj_up_gate on proj_up. */
+typedef struct xl_swiglu_params {
+  const void* gz;        /* (rows, 2F) through gz_row_stride (elements) */
+  void* out;             /* (rows, F) contiguous */
+  int64_t rows; int32_t F;
+  int64_t gz_row_stride;
+  int32_t dtype;
+} xl_swiglu_params;
+
+int xl_swiglu(const xl_swiglu_params* p, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Greedy sampling head: tokens[r] = argmax_v soft_cap(logits[r, v]).
+ * Replaces the tail of the reference's decode step: the soft cap of the logits (xlstm/xlstm_large/model.py:149-151,
+ * components.py:5-22, each operator rounded to `dtype`) and greedy_sampling = torch.argmax of the last position
+ * (xlstm/xlstm_large/generate.py:13-15; ties go to the lower index).  Every row is reduced by several thread blocks that
+ * meet in `scratch` memory (candidates and a ticket counter per row).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct xl_greedy_params {
+  const void* logits;     /* (rows, V) un-capped logits, dtype `dtype`, row stride row_stride elements */
+  int64_t* tokens;        /* out (rows) */
+  void* scratch;          /* device memory, 8-byte aligned, at least xl_softcap_argmax_scratch_bytes(rows) bytes, ZEROED ONCE
+                             by the caller; the entry leaves its counters at zero again.  Calls that may overlap on the
+                             device need scratch areas of their own. */
+  int64_t scratch_bytes;
+  int32_t rows, V;
+  int64_t row_stride;
+  float cap;              /* 30 for the logits of xLSTM-Large */
+  int32_t dtype;
+} xl_greedy_params;
+
+int64_t xl_softcap_argmax_scratch_bytes(int32_t rows);
+int xl_softcap_argmax(const xl_greedy_params* p, void* cuda_stream);
 
 #ifdef __cplusplus
 }

@@ -50,8 +50,18 @@ def headnorm_gate(h: torch.Tensor, o_preact: torch.Tensor, weight: torch.Tensor,
     return (g.float() * nw.float()).to(dt)
 
 
-def soft_cap(x: torch.Tensor, cap: float, out_float32: bool = False):
+def swiglu(gz: torch.Tensor):
+    """silu(gz[..., :F]) * gz[..., F:] with the eager sequence's rounding (``act_fn(proj_up_gate(x)) * proj_up(x)``,
+    xlstm/xlstm_large/model.py:268-277)."""
+    dt = gz.dtype
+    g, z = gz.chunk(2, dim=-1)
+    return (torch.nn.functional.silu(g.float()).to(dt).float() * z.float()).to(dt)
+
+
+def soft_cap(x: torch.Tensor, cap: float, out_float32: bool = False, bias: torch.Tensor | None = None):
     dt = x.dtype
+    if bias is not None:   # a Linear layer's bias, rounded with its output
+        x = (x.float() + bias.float()).to(dt)
     q = (x.float() / cap).to(dt)
     t = torch.tanh(q.float()).to(dt)
     y = (cap * t.float()).to(dt)

@@ -147,3 +147,47 @@ def test_causal_conv1d_kernel_matches_oracle_with_document_boundaries(tag, B, S,
         want = O.causal_conv1d(x, w, b, cu_seqlens=cu, silu=silu)
         got = xlstm_b200.causal_conv1d(x.cuda(), w.cuda(), None if b is None else b.cuda(), cu_seqlens=cu, silu=silu)
         _close(got, want, dt)
+
+
+@pytest.mark.parametrize("tag", ["bf16", "f32"])
+@pytest.mark.parametrize("rows,V", [(8, 50304), (1, 50304), (300, 2048), (3, 1000), (5, 7)])
+def test_softcap_argmax_kernel_equals_argmax_of_the_capped_logits(tag, rows, V):
+    """tokens = argmax(soft_cap(logits, 30)) with the reference's rounding and torch.argmax's tie rule.  The inputs are
+    scaled so that many capped values round to the same maximum: the first of them has to win.  Two calls in a row
+    share the scratch area (its counters must come back to zero)."""
+    import xlstm_b200
+    dt = DT[tag]
+    g = torch.Generator().manual_seed(rows * 7 + V)
+    for scale in (4.0, 40.0):
+        x = (scale * torch.randn(rows, V, generator=g)).to(dt)
+        want = torch.argmax(O.soft_cap(x, 30.0), dim=-1)
+        for _ in range(2):
+            got = xlstm_b200.softcap_argmax(x.cuda(), 30.0)
+            assert got.dtype == torch.int64 and torch.equal(got.cpu(), want)
+    # a strided view (the last position of a (B, S, V) tensor)
+    y = (4.0 * torch.randn(4, 3, V, generator=g)).to(dt)
+    assert torch.equal(xlstm_b200.softcap_argmax(y.cuda()[:, -1], 30.0).cpu(), torch.argmax(O.soft_cap(y[:, -1], 30.0), dim=-1))
+
+
+@pytest.mark.parametrize("tag", ["bf16", "f32"])
+def test_swiglu_and_strided_biased_soft_cap_match_oracle(tag):
+    """The two kernels that take launches out of the decode step: the feed-forward's gating on the stacked
+    up-projection, and the soft cap reading the gate columns straight out of the stacked q/k/v/o/gate projection
+    (strided rows) with the gate bias added on the way."""
+    import xlstm_b200
+    dt = DT[tag]
+    g = torch.Generator().manual_seed(17)
+    for rows, F_ in ((8, 10944), (300, 1368), (1, 8)):
+        gz = (2.0 * torch.randn(rows, 2 * F_, generator=g)).to(dt)
+        _close(xlstm_b200.swiglu(gz.cuda()), O.swiglu(gz), dt)
+    wide = (8.0 * torch.randn(5, 7, 12288 + 16, generator=g)).to(dt)
+    bias = torch.randn(16, generator=g).to(dt)
+    gates = wide[..., 12288:]
+    want = O.soft_cap(gates, 15.0, out_float32=True, bias=bias)
+    got = xlstm_b200.soft_cap(wide.cuda()[..., 12288:], 15.0, out_float32=True, bias=bias.cuda())
+    assert got.shape == want.shape and got.dtype == torch.float32
+    _close(got, want, torch.float32 if tag == "f32" else dt)
+    # fp32 arithmetic on the (dtype-rounded) biased input, as the model mirror uses it for the gates
+    got2 = xlstm_b200.soft_cap(wide.cuda()[..., 12288:], 15.0, out_float32=True, float32_math=True, bias=bias.cuda())
+    pre = (gates.float() + bias.float()).to(dt).float()
+    assert float((got2.cpu() - 15.0 * torch.tanh(pre / 15.0)).abs().max()) < 1e-5

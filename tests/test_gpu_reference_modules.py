@@ -362,7 +362,13 @@ def test_packed_slstm_layers_equal_per_document_runs():
         set_document_offsets(stack, None)
         rows = stack(x)
     assert rel_l2(packed.float().cpu(), alone.float().cpu()) < 1e-2
-    assert rel_l2(leaky[:, 40:44].float().cpu(), alone[:, 40:44].float().cpu()) > 5e-2   # what the kernel fixes
+    # what the blocks ADD to the residual stream (the stream itself hides most of a difference): right with the pack-aware
+    # front, visibly wrong on the first tokens behind a boundary with the reference's own convolution
+    add = lambda y: (y.float() - x.float()).cpu()
+    assert rel_l2(add(packed), add(alone)) < 3e-2
+    e_leak, e_ok = rel_l2(add(leaky)[:, 40:43], add(alone)[:, 40:43]), rel_l2(add(packed)[:, 40:43], add(alone)[:, 40:43])
+    print(f"first three tokens behind a boundary, block contribution: reference convolution {e_leak:.3f}, pack-aware {e_ok:.3f}")
+    assert e_leak > 5 * e_ok and e_leak > 5e-2   # what the kernel fixes
     # without offsets the replaced front computes what the reference front computes for plain rows
     ref_stack = _slstm_stack("b200", torch.bfloat16, source=None, num_blocks=2, embedding_dim=D, seed=3)
     with torch.no_grad():

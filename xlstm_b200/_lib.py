@@ -17,6 +17,7 @@ EXPORTS = (
     "xl_strerror", "xl_last_cuda_error", "xl_abi_version",
     "xl_mlstm_chunkwise", "xl_mlstm_recurrent", "xl_mlstm_step", "xl_slstm_forward",
     "xl_add_rmsnorm", "xl_headnorm_gate", "xl_soft_cap", "xl_causal_conv1d",
+    "xl_softcap_argmax", "xl_softcap_argmax_scratch_bytes", "xl_swiglu",
 )
 
 
@@ -82,7 +83,12 @@ class HeadnormGateParams(C.Structure):
 
 class SoftCapParams(C.Structure):
     _fields_ = [("x", C.c_void_p), ("out", C.c_void_p), ("n", C.c_int64), ("cap", C.c_float), ("dtype", C.c_int32),
-                ("out_f32", C.c_int32)]
+                ("out_f32", C.c_int32), ("cols", C.c_int64), ("x_row_stride", C.c_int64), ("bias", C.c_void_p)]
+
+
+class SwigluParams(C.Structure):
+    _fields_ = [("gz", C.c_void_p), ("out", C.c_void_p), ("rows", C.c_int64), ("F", C.c_int32), ("gz_row_stride", C.c_int64),
+                ("dtype", C.c_int32)]
 
 
 class Conv1dParams(C.Structure):
@@ -91,6 +97,13 @@ class Conv1dParams(C.Structure):
         ("B", C.c_int32), ("S", C.c_int32), ("F", C.c_int32), ("K", C.c_int32), ("num_docs", C.c_int32), ("act", C.c_int32),
         ("x_sb", C.c_int64), ("x_st", C.c_int64), ("o_sb", C.c_int64), ("o_st", C.c_int64),
         ("dtype", C.c_int32),
+    ]
+
+
+class GreedyParams(C.Structure):
+    _fields_ = [
+        ("logits", C.c_void_p), ("tokens", C.c_void_p), ("scratch", C.c_void_p), ("scratch_bytes", C.c_int64),
+        ("rows", C.c_int32), ("V", C.c_int32), ("row_stride", C.c_int64), ("cap", C.c_float), ("dtype", C.c_int32),
     ]
 
 
@@ -113,10 +126,13 @@ def lib() -> C.CDLL:
         for name, ptype in (("xl_mlstm_chunkwise", MlstmSeqParams), ("xl_mlstm_recurrent", MlstmSeqParams),
                             ("xl_mlstm_step", MlstmStepParams), ("xl_slstm_forward", SlstmParams),
                             ("xl_add_rmsnorm", AddRmsnormParams), ("xl_headnorm_gate", HeadnormGateParams),
-                            ("xl_soft_cap", SoftCapParams), ("xl_causal_conv1d", Conv1dParams)):
+                            ("xl_soft_cap", SoftCapParams), ("xl_causal_conv1d", Conv1dParams),
+                            ("xl_softcap_argmax", GreedyParams), ("xl_swiglu", SwigluParams)):
             fn = getattr(l, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(ptype), C.c_void_p]
+        l.xl_softcap_argmax_scratch_bytes.restype = C.c_int64
+        l.xl_softcap_argmax_scratch_bytes.argtypes = [C.c_int32]
         _lib = l
     return _lib
 

@@ -5,6 +5,7 @@
 //                     (xlstm/xlstm_large/model.py:435-449, components.py:171-242)
 //   xl_causal_conv1d  depthwise causal convolution over time + SiLU in front of the sLSTM cell, with document
 //                     boundaries (xlstm/components/conv.py:110-129, xlstm/blocks/slstm/layer.py:133-142)
+//   xl_swiglu         silu(gate) * up of the feed-forward block (xlstm/xlstm_large/model.py:268-277)
 // Both are bound by HBM traffic: every element is read once with 16-byte loads, kept in registers across the
 // reduction, and written once.  Rounding points are those of the reference's eager operator sequence (fp32
 // reductions; the normalised value rounded to the model dtype, then the weight product rounded, then the gate).
@@ -212,16 +213,52 @@ __global__ void __launch_bounds__(HNG_WARPS * 32) headnorm_gate_kernel(const xl_
 // soft cap: cap * tanh(x / cap), each operator's result rounded to T
 // ------------------------------------------------------------------------------------------------------------
 template <typename T, typename O, bool ROUND_EACH>
-__global__ void __launch_bounds__(256) soft_cap_kernel(const T* __restrict__ x, O* __restrict__ out, long long n, float cap) {
+__global__ void __launch_bounds__(256) soft_cap_kernel(const T* __restrict__ x, O* __restrict__ out, long long n, float cap,
+                                                       long long cols, long long x_row_stride, const T* __restrict__ bias) {
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    // (rows of `cols` elements `x_row_stride` apart: a column slice of a wider projection output; a bias per column is
+    // added first, rounded to T as the reference's Linear rounds its output)
+    float v;
+    if (cols > 0) {
+      const long long r = i / cols, c = i - r * cols;
+      v = to_float(x[r * x_row_stride + c]);
+      if (bias) v = to_float(from_float<T>(v + to_float(bias[c])));
+    } else {
+      v = to_float(x[i]);
+    }
     if (ROUND_EACH) {
-      const T q = from_float<T>(to_float(x[i]) / cap);
+      const T q = from_float<T>(v / cap);
       const T t = from_float<T>(tanhf(to_float(q)));
       out[i] = from_float<O>(to_float(from_float<T>(cap * to_float(t))));
     } else {
-      out[i] = from_float<O>(cap * tanhf(to_float(x[i]) / cap));
+      out[i] = from_float<O>(cap * tanhf(v / cap));
     }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// SwiGLU: out[r, j] = round(round(silu(gz[r, j])) * gz[r, F + j]) -- the eager sequence of the reference's feed-forward
+// (act_fn(proj_up_gate(x)) * proj_up(x), xlstm/xlstm_large/model.py:268-277) on the output of the fused up-projection.
+// One pass: reads 2F, writes F per row.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ gz, T* __restrict__ out, long long rows, int F,
+                                                     long long gz_row_stride) {
+  constexpr int V = Vec16<T>::N;
+  const long long nvec = rows * (long long)(F / V), stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    const long long r = i / (F / V);
+    const int c = (int)(i - r * (F / V)) * V;
+    const Vec16<T> g = load16(gz + r * gz_row_stride + c), z = load16(gz + r * gz_row_stride + F + c);
+    Vec16<T> o;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const float gv = to_float(g.v[k]);
+      const float sl = to_float(from_float<T>(gv * sigmoid_for<T>(gv)));
+      o.v[k] = from_float<T>(sl * to_float(z.v[k]));
+    }
+    store16(out + r * (long long)F + c, o);
   }
 }
 
@@ -369,20 +406,40 @@ extern "C" int xl_soft_cap(const xl_soft_cap_params* p, void* cuda_stream) {
   if (!p || !p->x || !p->out) return XL_ERR_NULL_POINTER;
   if (p->dtype != XL_F32 && p->dtype != XL_BF16) return XL_ERR_BAD_DTYPE;
   if (p->n < 0 || !(p->cap > 0.f) || p->out_f32 < 0 || p->out_f32 > 2) return XL_ERR_BAD_SHAPE;
+  if (p->cols < 0 || (p->cols > 0 && (p->n % p->cols != 0 || p->x_row_stride < p->cols))) return XL_ERR_BAD_SHAPE;
+  if (p->bias && p->cols <= 0) return XL_ERR_BAD_SHAPE;
   if (p->n == 0) return XL_OK;
-  if (p->out == p->x && p->dtype == XL_BF16 && p->out_f32) return XL_ERR_ALIASING;
+  if (p->out == p->x && ((p->dtype == XL_BF16 && p->out_f32) || (p->cols > 0 && p->x_row_stride != p->cols))) return XL_ERR_ALIASING;
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
   const long long want = (p->n + 255) / 256;
   const unsigned grid = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+  const long long cols = p->cols, rs = p->x_row_stride;
   if (p->dtype == XL_F32)
-    soft_cap_kernel<float, float, false><<<grid, 256, 0, st>>>(static_cast<const float*>(p->x), static_cast<float*>(p->out), p->n, p->cap);
+    soft_cap_kernel<float, float, false><<<grid, 256, 0, st>>>(static_cast<const float*>(p->x), static_cast<float*>(p->out), p->n, p->cap, cols, rs, static_cast<const float*>(p->bias));
   else if (p->out_f32 == 2)
-    soft_cap_kernel<__nv_bfloat16, float, false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(p->x), static_cast<float*>(p->out), p->n, p->cap);
+    soft_cap_kernel<__nv_bfloat16, float, false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(p->x), static_cast<float*>(p->out), p->n, p->cap, cols, rs, static_cast<const __nv_bfloat16*>(p->bias));
   else if (p->out_f32)
-    soft_cap_kernel<__nv_bfloat16, float, true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(p->x), static_cast<float*>(p->out), p->n, p->cap);
+    soft_cap_kernel<__nv_bfloat16, float, true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(p->x), static_cast<float*>(p->out), p->n, p->cap, cols, rs, static_cast<const __nv_bfloat16*>(p->bias));
   else
-    soft_cap_kernel<__nv_bfloat16, __nv_bfloat16, true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(p->x), static_cast<__nv_bfloat16*>(p->out), p->n, p->cap);
+    soft_cap_kernel<__nv_bfloat16, __nv_bfloat16, true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(p->x), static_cast<__nv_bfloat16*>(p->out), p->n, p->cap, cols, rs, static_cast<const __nv_bfloat16*>(p->bias));
   return check_launch("xl_soft_cap");
+}
+
+extern "C" int xl_swiglu(const xl_swiglu_params* p, void* cuda_stream) {
+  using namespace xl;
+  if (!p || !p->gz || !p->out) return XL_ERR_NULL_POINTER;
+  if (p->dtype != XL_F32 && p->dtype != XL_BF16) return XL_ERR_BAD_DTYPE;
+  const int V = p->dtype == XL_F32 ? 4 : 8;
+  if (p->rows < 0 || p->F <= 0 || p->F % V != 0 || p->gz_row_stride < 2LL * p->F || p->gz_row_stride % V != 0) return XL_ERR_BAD_SHAPE;
+  if (!aligned16(p->gz) || !aligned16(p->out)) return XL_ERR_BAD_ALIGNMENT;
+  if (p->out == p->gz) return XL_ERR_ALIASING;
+  if (p->rows == 0) return XL_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  const long long want = (p->rows * (long long)(p->F / V) + 255) / 256;
+  const unsigned grid = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+  if (p->dtype == XL_F32) swiglu_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(p->gz), static_cast<float*>(p->out), p->rows, p->F, p->gz_row_stride);
+  else swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(p->gz), static_cast<__nv_bfloat16*>(p->out), p->rows, p->F, p->gz_row_stride);
+  return check_launch("xl_swiglu");
 }
 
 extern "C" int xl_causal_conv1d(const xl_conv1d_params* p, void* cuda_stream) {

@@ -147,11 +147,15 @@ class LargeModel:
         self.blocks = []
         for i in range(cfg.num_blocks):
             b = f"backbone.blocks.{i}."
-            qkvo = torch.cat([W(b + "mlstm_layer.q.weight")[h0 * dq:h1 * dq], W(b + "mlstm_layer.k.weight")[h0 * dq:h1 * dq],
-                              W(b + "mlstm_layer.v.weight")[h0 * dv:h1 * dv], W(b + "mlstm_layer.ogate_preact.weight")[h0 * dv:h1 * dv]], 0)
+            # one stacked weight for q | k | v | o-gate | i-gate | f-gate: the views below share its memory, and the fused
+            # path runs all six projections as ONE GEMM (the gate bias is added by the soft-cap kernel)
+            qkvo_if = torch.cat([W(b + "mlstm_layer.q.weight")[h0 * dq:h1 * dq], W(b + "mlstm_layer.k.weight")[h0 * dq:h1 * dq],
+                                 W(b + "mlstm_layer.v.weight")[h0 * dv:h1 * dv], W(b + "mlstm_layer.ogate_preact.weight")[h0 * dv:h1 * dv],
+                                 W(b + "mlstm_layer.igate_preact.weight")[h0:h1], W(b + "mlstm_layer.fgate_preact.weight")[h0:h1]], 0).contiguous()
+            n_qkvo = 2 * NHl * dq + 2 * NHl * dv
             blk = dict(
-                norm_mlstm=W(b + "norm_mlstm.weight"), norm_ffn=W(b + "norm_ffn.weight"), qkvo=qkvo.contiguous(),
-                if_w=torch.cat([W(b + "mlstm_layer.igate_preact.weight")[h0:h1], W(b + "mlstm_layer.fgate_preact.weight")[h0:h1]], 0).contiguous(),
+                norm_mlstm=W(b + "norm_mlstm.weight"), norm_ffn=W(b + "norm_ffn.weight"), qkvo_if=qkvo_if,
+                qkvo=qkvo_if[:n_qkvo], if_w=qkvo_if[n_qkvo:],
                 if_b=torch.cat([W(b + "mlstm_layer.igate_preact.bias")[h0:h1], W(b + "mlstm_layer.fgate_preact.bias")[h0:h1]], 0).contiguous(),
                 mh_norm=W(b + "mlstm_layer.multihead_norm.weight")[h0 * dv:h1 * dv].contiguous(),
                 out_proj=W(b + "mlstm_layer.out_proj.weight")[:, h0 * dv:h1 * dv].contiguous(),
@@ -174,11 +178,13 @@ class LargeModel:
     def _mlstm_layer(self, blk, x, state, cu_seqlens, slot, reduce: bool = True):
         cfg, NHl, dq, dv = self.cfg, self.nh_local, self.dq, self.dv
         B, S, _ = x.shape
-        qkvo = F.linear(x, blk["qkvo"])
-        q, k, v, o = torch.split(qkvo, [NHl * dq, NHl * dq, NHl * dv, NHl * dv], dim=-1)
-        if self.fused:   # capped in fp32 like the eager path below: the gates enter exponentials in the cell
-            gates = ops.soft_cap(F.linear(x, blk["if_w"], blk["if_b"]), cfg.gate_soft_cap, out_float32=True, float32_math=True)
+        if self.fused:   # one GEMM for all six projections; the gates are capped in fp32 (they enter exponentials in the cell)
+            allp = F.linear(x, blk["qkvo_if"])
+            q, k, v, o, gpre = torch.split(allp, [NHl * dq, NHl * dq, NHl * dv, NHl * dv, 2 * NHl], dim=-1)
+            gates = ops.soft_cap(gpre, cfg.gate_soft_cap, out_float32=True, float32_math=True, bias=blk["if_b"])
         else:
+            qkvo = F.linear(x, blk["qkvo"])
+            q, k, v, o = torch.split(qkvo, [NHl * dq, NHl * dq, NHl * dv, NHl * dv], dim=-1)
             gates = _soft_cap(F.linear(x, blk["if_w"], blk["if_b"]).float(), cfg.gate_soft_cap)   # (B,S,2*NHl) fp32
         ig, fg = gates[..., :NHl].transpose(1, 2), gates[..., NHl:].transpose(1, 2)          # (B,NHl,S) views
         q = q.reshape(B, S, NHl, dq).transpose(1, 2)     # strided views, no copies (model.py:415-417)
@@ -201,6 +207,13 @@ class LargeModel:
         hn = hn.to(x.dtype).reshape(B, S, NHl * dv) * blk["mh_norm"]
         y = F.linear(torch.sigmoid(o) * hn, blk["out_proj"])
         return (self._all_reduce(y) if reduce else y), new_state
+
+    def _swiglu(self, gz):
+        """silu(gate) * up on the output of the stacked up-projection (``model.py:268-277``)."""
+        if self.fused:
+            return ops.swiglu(gz)
+        g, z = gz.chunk(2, dim=-1)
+        return F.silu(g) * z
 
     def _add_norm(self, x, y, w):
         """x + y (y may be None) and its RMSNorm, as the reference's block does with two operators (model.py:499-510)."""
@@ -248,7 +261,8 @@ class LargeModel:
         return (self.tp_world > 1 and tokens.shape[1] > 1 and slot is None
                 and (tokens.shape[0] * tokens.shape[1]) % self.tp_world == 0)
 
-    def _forward_token_parallel(self, tokens, state, cu_seqlens, last_only, groups: int = 2, time_collectives: bool = False):
+    def _forward_token_parallel(self, tokens, state, cu_seqlens, last_only, groups: int = 2, time_collectives: bool = False,
+                                greedy: bool = False):
         """Prefill with the residual stream sharded over tokens (see the class docstring).  Batch rows are cut into
         `groups` independent pieces; piece g runs on stream g % 2, so its collectives overlap the other piece's compute."""
         cfg, W, dev = self.cfg, self.tp_world, self.device
@@ -277,9 +291,7 @@ class LargeModel:
                     pc["state"][i] = st
                     y = self._timed(self._scatter_sum, y.reshape(Bg * S, -1), record)
                     pc["x"], xn = self._add_norm(pc["x"], y, blk["norm_ffn"])
-                    gz = F.linear(xn, blk["up_full"])
-                    gg, zz = gz.chunk(2, dim=-1)
-                    pc["pending"] = F.linear(F.silu(gg) * zz, blk["down_full"])
+                    pc["pending"] = F.linear(self._swiglu(F.linear(xn, blk["up_full"])), blk["down_full"])
         outs = []
         for g, pc in enumerate(pieces):
             ctx = torch.cuda.stream(streams[g % len(streams)]) if cuda else _nullcontext()
@@ -288,8 +300,7 @@ class LargeModel:
                 xn_full = self._timed(self._gather_tokens, xn, record).reshape(Bg, S, -1)
                 if last_only:
                     xn_full = xn_full[:, -1:]
-                logits = F.linear(xn_full, self.lm_head)
-                outs.append(ops.soft_cap(logits, cfg.output_logit_soft_cap) if self.fused else _soft_cap(logits, cfg.output_logit_soft_cap))
+                outs.append(self._head(xn_full, greedy))
         if cuda and len(streams) > 1:
             streams[0].wait_stream(streams[1])
         logits = outs[0] if groups == 1 else torch.cat(outs, 0)
@@ -304,15 +315,28 @@ class LargeModel:
             self.comm_calls = len(record)
         return logits, new_state
 
+    def _head(self, xn, greedy: bool):
+        """lm_head and soft cap; with `greedy` the argmax of the last position as well (``generate.py:13-15``), on CUDA in
+        one kernel behind the GEMM."""
+        cfg = self.cfg
+        logits = F.linear(xn, self.lm_head)
+        if greedy:
+            if self.fused:
+                return ops.softcap_argmax(logits[:, -1], cfg.output_logit_soft_cap)[:, None]
+            return torch.argmax(_soft_cap(logits[:, -1:], cfg.output_logit_soft_cap), dim=-1)
+        return ops.soft_cap(logits, cfg.output_logit_soft_cap) if self.fused else _soft_cap(logits, cfg.output_logit_soft_cap)
+
     def forward(self, tokens, state: Optional[dict] = None, cu_seqlens=None, slot=None, last_only: bool = False,
-                time_collectives: bool = False, positions=None):
+                time_collectives: bool = False, positions=None, greedy: bool = False):
         """tokens (B,S) int64 -> logits (B,S,V) (or (B,1,V) with ``last_only``) and the per-block state dict
         ``{i: (c,n,m)}`` exactly as ``xLSTMLarge.forward`` returns it (``model.py:126-153``).  With ``cu_seqlens`` every
         interval of the flattened (B*S) token axis is a document of its own and the states have one row per document;
         ``positions`` (flat token indices) restricts the logits to those tokens, returned as (len(positions), 1, V) --
-        a packed prefill only needs the last token of every document."""
+        a packed prefill only needs the last token of every document.  ``greedy`` returns the greedy token of the last
+        position, (rows, 1) int64, in place of the logits."""
         if positions is None and self.token_parallel_ok(tokens, state, cu_seqlens, slot):
-            return self._forward_token_parallel(tokens, state, cu_seqlens, last_only, time_collectives=time_collectives)
+            return self._forward_token_parallel(tokens, state, cu_seqlens, last_only or greedy, time_collectives=time_collectives,
+                                                greedy=greedy)
         cfg = self.cfg
         x = self.embedding[tokens]
         new_state = {}
@@ -322,19 +346,15 @@ class LargeModel:
             y, st = self._mlstm_layer(blk, xn, None if state is None else state[i], cu_seqlens, slot)
             new_state[i] = st
             x, xn = self._add_norm(x, y, blk["norm_ffn"])
-            g, z = F.linear(xn, blk["up"]).chunk(2, dim=-1)
-            pending = self._all_reduce(F.linear(F.silu(g) * z, blk["down"]))
+            pending = self._all_reduce(F.linear(self._swiglu(F.linear(xn, blk["up"])), blk["down"]))
         if positions is not None:
             x = x.reshape(-1, x.shape[-1])[positions][:, None]
             pending = None if pending is None else pending.reshape(-1, pending.shape[-1])[positions][:, None]
-        elif last_only:
+        elif last_only or greedy:
             x = x[:, -1:]
             pending = None if pending is None else pending[:, -1:]
         x, xn = self._add_norm(x, pending, self.out_norm)
-        logits = F.linear(xn, self.lm_head)
-        if self.fused:
-            return ops.soft_cap(logits, cfg.output_logit_soft_cap), new_state
-        return _soft_cap(logits, cfg.output_logit_soft_cap), new_state
+        return self._head(xn, greedy), new_state
 
     # ------------------------------------------------------------------------------------------------
     def _capture_decode_graph(self, state, batch: int, slot_map=None):
@@ -351,14 +371,14 @@ class LargeModel:
         self._g_slot = slot_map
 
         def body():
-            logits, st = self.forward(self._g_tok, self._g_state, last_only=True, slot=self._g_slot)
+            nxt, st = self.forward(self._g_tok, self._g_state, greedy=True, slot=self._g_slot)
             dsts, srcs = [], []
             for i, (c, n, m) in st.items():
                 assert c is self._g_state[i][0]
                 dsts += [self._g_state[i][1], self._g_state[i][2]]
                 srcs += [n, m.reshape(self._g_state[i][2].shape)]
             torch._foreach_copy_(dsts, srcs)   # one multi-tensor launch instead of two small copies per block
-            self._g_tok.copy_(torch.argmax(logits[:, -1:], dim=-1))
+            self._g_tok.copy_(nxt)
 
         snapshot = {i: tuple(t.clone() for t in st) for i, st in self._g_state.items()}
         side = torch.cuda.Stream(device=dev)
@@ -415,8 +435,7 @@ class LargeModel:
                 self._graph.replay()
                 out[:, i:i + 1] = self._g_tok
                 continue
-            logits, state = self.forward(last, state, last_only=True)
-            last = torch.argmax(logits[:, -1:], dim=-1)
+            last, state = self.forward(last, state, greedy=True)
             out[:, i:i + 1] = last
         if use_cuda_graph and max_length > 1:
             state = self._g_state
@@ -467,13 +486,13 @@ class ContinuousDecoder:
     # ------------------------------------------------------------------------------------------------ admission
     @torch.no_grad()
     def _admit_single(self, slot: int, prompt: torch.Tensor) -> None:
-        logits, st = self.model.forward(prompt.reshape(1, -1).to(self.model.device), last_only=True)
+        first, st = self.model.forward(prompt.reshape(1, -1).to(self.model.device), greedy=True)
         self.prefill_calls += 1
         for i, (c, n, m) in st.items():
             self.state[i][0][slot].copy_(c[0])
             self.state[i][1][slot].copy_(n[0])
             self.state[i][2][slot].copy_(m[0].reshape(self.state[i][2][slot].shape))
-        self.tok[slot].copy_(torch.argmax(logits[0, -1:], dim=-1))
+        self.tok[slot].copy_(first[0])
 
     @torch.no_grad()
     def _admit_packed(self, slots, prompts) -> None:
@@ -500,8 +519,8 @@ class ContinuousDecoder:
                     continue
                 tokens[cu[k]:cu[k + 1]] = prompts[d].to(dev)
                 docs.append(d); rows_of_state.append(k); ends.append(cu[k + 1] - 1)
-            logits, st = self.model.forward(tokens.reshape(r1 - r0, packed.row_len), cu_seqlens=cu,
-                                            positions=torch.tensor(ends, dtype=torch.long, device=dev))
+            first, st = self.model.forward(tokens.reshape(r1 - r0, packed.row_len), cu_seqlens=cu, greedy=True,
+                                           positions=torch.tensor(ends, dtype=torch.long, device=dev))
             self.prefill_calls += 1
             dst = torch.tensor([slots[d] for d in docs], dtype=torch.long, device=dev)
             src = torch.tensor(rows_of_state, dtype=torch.long, device=dev)
@@ -509,7 +528,7 @@ class ContinuousDecoder:
                 self.state[i][0].index_copy_(0, dst, c.index_select(0, src))
                 self.state[i][1].index_copy_(0, dst, n.index_select(0, src))
                 self.state[i][2].index_copy_(0, dst, m.index_select(0, src).reshape(len(docs), *self.state[i][2].shape[1:]))
-            self.tok.index_copy_(0, dst, torch.argmax(logits[:, -1], dim=-1, keepdim=True))
+            self.tok.index_copy_(0, dst, first)
 
     def _admit(self, slots, prompts) -> None:
         if self.packed:
@@ -526,12 +545,12 @@ class ContinuousDecoder:
         if self.graphed:
             self.model._graph.replay()
             return
-        logits, st = self.model.forward(self.tok, self.state, last_only=True, slot=self.slot_map)
+        nxt, st = self.model.forward(self.tok, self.state, greedy=True, slot=self.slot_map)
         for i, (c, n, m) in st.items():
             for dst, src in zip(self.state[i], (c, n, m)):
                 if dst is not src:
                     dst.copy_(src.reshape(dst.shape))
-        self.tok.copy_(torch.argmax(logits[:, -1:], dim=-1))
+        self.tok.copy_(nxt)
 
     @torch.no_grad()
     def run(self, prompts, new_tokens):

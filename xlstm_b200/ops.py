@@ -12,7 +12,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
-from ._lib import (AddRmsnormParams, Conv1dParams, HeadnormGateParams, MlstmSeqParams, MlstmStepParams, SlstmParams, SoftCapParams, XL_BF16, XL_F32,
+from ._lib import (AddRmsnormParams, Conv1dParams, GreedyParams, HeadnormGateParams, MlstmSeqParams, MlstmStepParams, SlstmParams, SoftCapParams, SwigluParams, XL_BF16, XL_F32,
                    check, lib)
 
 _DTYPES = {torch.float32: XL_F32, torch.bfloat16: XL_BF16}
@@ -376,23 +376,53 @@ def headnorm_gate(h, o_preact, weight, eps: float = 1e-6):
     return out
 
 
-def soft_cap(x, cap: float, out_float32: bool = False, float32_math: bool = False):
+def soft_cap(x, cap: float, out_float32: bool = False, float32_math: bool = False, bias=None):
     """``cap * tanh(x / cap)`` in one kernel with the rounding of the reference's eager ``soft_cap``
     (xlstm/xlstm_large/components.py:5-22).  ``out_float32`` returns the result (rounded to ``x.dtype``) as
     float32, the type the cell kernels take for gate pre-activations; with ``float32_math`` as well the
-    quotient, tanh and product are not rounded to ``x.dtype`` in between (gates kept in fp32 in a bf16 model)."""
+    quotient, tanh and product are not rounded to ``x.dtype`` in between (gates kept in fp32 in a bf16 model).
+    ``x`` may be a column slice of a wider matrix (last dimension contiguous, one row stride); ``bias`` (last-dimension
+    sized) is added first, which lets the gate projection ride in the q/k/v/o GEMM without its own launch."""
     if float32_math and not out_float32:
         raise ValueError("soft_cap: float32_math needs out_float32")
-    _require_cuda(x)
+    _require_cuda(x, bias)
     if x.dtype not in _DTYPES:
         raise ValueError("soft_cap: float32 or bfloat16 only")
-    xc = x.contiguous()
-    out = torch.empty(xc.shape, dtype=torch.float32 if out_float32 else x.dtype, device=x.device)
+    cols = x.shape[-1]
+    x2 = x.reshape(-1, cols) if x.dim() != 2 else x
+    strided = x2.stride(-1) == 1 and x2.shape[0] > 0 and (x2.stride(0) != cols or bias is not None)
+    if x2.stride(-1) != 1:
+        x2, strided = x2.contiguous(), bias is not None
+    out = torch.empty(x.shape, dtype=torch.float32 if out_float32 else x.dtype, device=x.device)
     p = SoftCapParams()
-    p.x, p.out, p.n, p.cap = xc.data_ptr(), out.data_ptr(), xc.numel(), float(cap)
+    p.x, p.out, p.n, p.cap = x2.data_ptr(), out.data_ptr(), x.numel(), float(cap)
     p.dtype, p.out_f32 = _DTYPES[x.dtype], (2 if float32_math else int(out_float32))
+    if strided:
+        p.cols, p.x_row_stride = cols, x2.stride(0)
+        if bias is not None:
+            if bias.shape != (cols,) or bias.dtype != x.dtype:
+                raise ValueError("soft_cap: bias must have the size of the last dimension and x's dtype")
+            p.bias = bias.contiguous().data_ptr()
     with torch.cuda.device(x.device):
         check(lib().xl_soft_cap(C.byref(p), _stream_ptr(x.device)), "xl_soft_cap")
+    return out
+
+
+def swiglu(gz):
+    """``silu(gz[..., :F]) * gz[..., F:]`` in one kernel, the feed-forward's gating on the output of one projection that
+    stacks ``proj_up_gate`` on ``proj_up`` (xlstm/xlstm_large/model.py:268-277), with the eager sequence's rounding."""
+    _require_cuda(gz)
+    if gz.dtype not in _DTYPES or gz.shape[-1] % 2:
+        raise ValueError("swiglu: float32 or bfloat16, even last dimension")
+    F_ = gz.shape[-1] // 2
+    g2 = gz.reshape(-1, 2 * F_)
+    if g2.stride(-1) != 1:
+        g2 = g2.contiguous()
+    out = torch.empty(gz.shape[:-1] + (F_,), dtype=gz.dtype, device=gz.device)
+    p = SwigluParams()
+    p.gz, p.out, p.rows, p.F, p.gz_row_stride, p.dtype = g2.data_ptr(), out.data_ptr(), g2.shape[0], F_, g2.stride(0), _DTYPES[gz.dtype]
+    with torch.cuda.device(gz.device):
+        check(lib().xl_swiglu(C.byref(p), _stream_ptr(gz.device)), "xl_swiglu")
     return out
 
 
@@ -427,3 +457,34 @@ def causal_conv1d(x, weight, bias=None, cu_seqlens=None, silu: bool = True):
     with torch.cuda.device(x.device):
         check(lib().xl_causal_conv1d(C.byref(p), _stream_ptr(x.device)), "xl_causal_conv1d")
     return out
+
+
+_greedy_scratch: dict[int, torch.Tensor] = {}
+
+
+def softcap_argmax(logits, cap: float):
+    """Greedy tokens of un-capped logits: ``argmax(soft_cap(logits, cap), dim=-1)`` with the reference's rounding and
+    tie rule (xlstm/xlstm_large/model.py:149-151, generate.py:13-15) in one kernel.  ``logits`` is (..., V) with
+    contiguous rows; returns int64 of shape ``logits.shape[:-1]``.  The kernel's scratch area is allocated once per
+    device (and grown when more rows come) and shared by all calls on that device's streams in issue order."""
+    _require_cuda(logits)
+    if logits.dtype not in _DTYPES:
+        raise ValueError("softcap_argmax: float32 or bfloat16 only")
+    V = logits.shape[-1]
+    x = logits.reshape(-1, V)
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    rows = x.shape[0]
+    dev = x.device
+    need = int(lib().xl_softcap_argmax_scratch_bytes(rows))
+    sc = _greedy_scratch.get(dev.index)
+    if sc is None or sc.numel() < need:
+        sc = torch.zeros(max(need, int(lib().xl_softcap_argmax_scratch_bytes(256))), dtype=torch.uint8, device=dev)
+        _greedy_scratch[dev.index] = sc
+    out = torch.empty(rows, dtype=torch.int64, device=dev)
+    p = GreedyParams()
+    p.logits, p.tokens, p.scratch, p.scratch_bytes = x.data_ptr(), out.data_ptr(), sc.data_ptr(), sc.numel()
+    p.rows, p.V, p.row_stride, p.cap, p.dtype = rows, V, x.stride(0), float(cap), _DTYPES[x.dtype]
+    with torch.cuda.device(dev):
+        check(lib().xl_softcap_argmax(C.byref(p), _stream_ptr(dev)), "xl_softcap_argmax")
+    return out.reshape(logits.shape[:-1])
