@@ -384,7 +384,8 @@ def build_case(name, dev, rank):
         def e2e_step():
             out_host.copy_(model.generate(tok_host.to(dev, non_blocking=True), GEN, use_cuda_graph=True)[0], non_blocking=True)
 
-        streamed = [t for blk in model.blocks for k_, t in blk.items() if not k_.endswith("_full")] + [model.out_norm, model.lm_head]
+        streamed = [t for blk in model.blocks for k_, t in blk.items() if not k_.endswith("_full") and k_ not in ("qkvo", "if_w")]
+        streamed += [model.out_norm, model.lm_head]
         weight_bytes = sum(t.numel() * t.element_size() for t in streamed)            # what one decode step streams per rank
         flops_per_token = 2 * (32 * (4096 * (2 * 2048 + 2 * 4096) + 4096 * 16 + 4096 * 4096 + 3 * 4096 * 10944)) + 32 * 8 * 623616
 

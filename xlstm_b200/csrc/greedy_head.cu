@@ -19,6 +19,13 @@ struct GhCand {
   float val;
   int idx;
 };
+// Scratch of one row.  Candidates and counter of a row sit together so that the counter of row r is at the same place
+// whatever the number of rows of a call: a counter must never land where an earlier call left candidates.
+struct GhRow {
+  GhCand cand[GH_MAX_PARTS];
+  unsigned int counter;
+  unsigned int pad;
+};
 
 __device__ __forceinline__ bool gh_better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
 
@@ -29,13 +36,13 @@ template <typename T> __device__ __forceinline__ float gh_capped(T x, float cap)
 }
 
 template <typename T>
-__global__ void __launch_bounds__(GH_THREADS) greedy_head_kernel(const xl_greedy_params p, GhCand* __restrict__ cand,
-                                                                 unsigned int* __restrict__ counter) {
+__global__ void __launch_bounds__(GH_THREADS) greedy_head_kernel(const xl_greedy_params p, GhRow* __restrict__ scratch) {
   __shared__ GhCand s_c[GH_THREADS / 32];
   __shared__ int s_last;
   const int row = blockIdx.y, part = blockIdx.x, parts = gridDim.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const T* x = static_cast<const T*>(p.logits) + (long long)row * p.row_stride;
+  GhRow* mine = scratch + row;
   // slice of this block, in whole 16-byte vectors where the row allows it
   constexpr int V16 = 16 / (int)sizeof(T);
   const bool vec = (p.V % V16 == 0) && (p.row_stride % V16 == 0) && ((reinterpret_cast<uintptr_t>(p.logits) & 15u) == 0);
@@ -72,10 +79,10 @@ __global__ void __launch_bounds__(GH_THREADS) greedy_head_kernel(const xl_greedy
   if (tid == 0) {
     for (int w = 1; w < GH_THREADS / 32; ++w)
       if (gh_better(s_c[w].val, s_c[w].idx, bv, bi)) { bv = s_c[w].val; bi = s_c[w].idx; }
-    cand[(long long)row * GH_MAX_PARTS + part].val = bv;
-    cand[(long long)row * GH_MAX_PARTS + part].idx = bi;
+    mine->cand[part].val = bv;
+    mine->cand[part].idx = bi;
     __threadfence();                                    // the candidate is visible before the ticket is
-    s_last = atomicAdd(&counter[row], 1u) == (unsigned)(parts - 1);
+    s_last = atomicAdd(&mine->counter, 1u) == (unsigned)(parts - 1);
   }
   __syncthreads();
   if (!s_last) return;
@@ -85,7 +92,7 @@ __global__ void __launch_bounds__(GH_THREADS) greedy_head_kernel(const xl_greedy
     float v = -INFINITY;
     int i = 0x7fffffff;
     if (lane < parts) {
-      const volatile GhCand* c = cand + (long long)row * GH_MAX_PARTS + lane;
+      const volatile GhCand* c = mine->cand + lane;
       v = c->val; i = c->idx;
     }
 #pragma unroll
@@ -96,7 +103,7 @@ __global__ void __launch_bounds__(GH_THREADS) greedy_head_kernel(const xl_greedy
     }
     if (lane == 0) {
       p.tokens[row] = (long long)(i == 0x7fffffff ? 0 : i);
-      counter[row] = 0u;                                // ready for the next call
+      mine->counter = 0u;                               // ready for the next call
     }
   }
 }
@@ -114,17 +121,17 @@ static int gh_validate(const xl_greedy_params* p) {
   return XL_OK;
 }
 
-static int gh_launch(const xl_greedy_params* p, GhCand* cand, unsigned int* counter, cudaStream_t st) {
+static int gh_launch(const xl_greedy_params* p, GhRow* scratch, cudaStream_t st) {
   const dim3 grid((unsigned)gh_parts(p->rows), (unsigned)p->rows);
-  if (p->dtype == XL_F32) greedy_head_kernel<float><<<grid, GH_THREADS, 0, st>>>(*p, cand, counter);
-  else greedy_head_kernel<__nv_bfloat16><<<grid, GH_THREADS, 0, st>>>(*p, cand, counter);
+  if (p->dtype == XL_F32) greedy_head_kernel<float><<<grid, GH_THREADS, 0, st>>>(*p, scratch);
+  else greedy_head_kernel<__nv_bfloat16><<<grid, GH_THREADS, 0, st>>>(*p, scratch);
   return check_launch("xl_softcap_argmax");
 }
 
 }  // namespace xl
 
 extern "C" int64_t xl_softcap_argmax_scratch_bytes(int32_t rows) {
-  return rows <= 0 ? 0 : (int64_t)rows * (xl::GH_MAX_PARTS * (int64_t)sizeof(xl::GhCand) + (int64_t)sizeof(unsigned int));
+  return rows <= 0 ? 0 : (int64_t)rows * (int64_t)sizeof(xl::GhRow);
 }
 
 extern "C" int xl_softcap_argmax(const xl_greedy_params* p, void* cuda_stream) {
@@ -134,7 +141,5 @@ extern "C" int xl_softcap_argmax(const xl_greedy_params* p, void* cuda_stream) {
   if (!p->scratch) return XL_ERR_NULL_POINTER;
   if (p->scratch_bytes < xl_softcap_argmax_scratch_bytes(p->rows)) return XL_ERR_TOO_LARGE;
   if (reinterpret_cast<uintptr_t>(p->scratch) & 7u) return XL_ERR_BAD_ALIGNMENT;
-  GhCand* cand = static_cast<GhCand*>(p->scratch);
-  unsigned int* counter = reinterpret_cast<unsigned int*>(cand + (size_t)p->rows * GH_MAX_PARTS);
-  return gh_launch(p, cand, counter, static_cast<cudaStream_t>(cuda_stream));
+  return gh_launch(p, static_cast<GhRow*>(p->scratch), static_cast<cudaStream_t>(cuda_stream));
 }

@@ -402,7 +402,7 @@ class LargeModel:
         """Every weight tensor this rank holds (its share under tensor parallelism)."""
         out = [self.embedding, self.out_norm, self.lm_head]
         for blk in self.blocks:
-            out += [v for v in blk.values() if isinstance(v, torch.Tensor)]
+            out += [v for k, v in blk.items() if isinstance(v, torch.Tensor) and k not in ("qkvo", "if_w")]   # (views of qkvo_if)
         return out
 
     def release_graph(self):
