@@ -268,6 +268,28 @@ typedef struct xl_greedy_params {
 int64_t xl_softcap_argmax_scratch_bytes(int32_t rows);
 int xl_softcap_argmax(const xl_greedy_params* p, void* cuda_stream);
 
+/* The greedy head for callers that cannot hand it scratch memory.  (No counterpart in the reference: its decode loop
+ * leaves all device memory to PyTorch's allocator.)
+ *
+ * xl_softcap_argmax needs a scratch area from its caller.  A caller that runs under a fixed device-memory plan -- a C or
+ * C++ serving loop whose buffers were all placed at start-up, a plugin inside a host that owns the GPU's memory, code on
+ * a latency path where an allocation (which may synchronise the whole device) is not allowed -- has none to give and may
+ * not call cudaMalloc for one.  This entry computes the same tokens from the same `logits` into the same `tokens` and
+ * takes its scratch from an array built into the library instead: 270 336 bytes of device memory on every GPU that loads
+ * the library, held until the process exits.  `scratch` and `scratch_bytes` of the parameter block are ignored.  It calls
+ * no allocating routine (no cudaMalloc / cudaFree, no library that allocates).
+ *
+ * Limits and rules:
+ *   - at most xl_softcap_argmax_noalloc_max_rows() = 1024 rows per call; more returns XL_ERR_TOO_LARGE and launches
+ *     nothing (xl_strerror: "request exceeds a fixed capacity of this entry point");
+ *   - the device that is current at the call is the one whose array is used; the first call on a device looks the
+ *     array's address up (a CUDA runtime query).  Make that first call once during start-up, before any stream capture;
+ *   - all calls on one device share the one array.  Calls issued to the same stream, or otherwise ordered on the device,
+ *     are safe back to back (each clears the rows it uses first); calls that may OVERLAP on the device race on it --
+ *     use xl_softcap_argmax with separate scratch areas for those. */
+int32_t xl_softcap_argmax_noalloc_max_rows(void);
+int xl_softcap_argmax_noalloc(const xl_greedy_params* p, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

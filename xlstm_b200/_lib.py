@@ -18,6 +18,7 @@ EXPORTS = (
     "xl_mlstm_chunkwise", "xl_mlstm_recurrent", "xl_mlstm_step", "xl_slstm_forward",
     "xl_add_rmsnorm", "xl_headnorm_gate", "xl_soft_cap", "xl_causal_conv1d",
     "xl_softcap_argmax", "xl_softcap_argmax_scratch_bytes", "xl_swiglu",
+    "xl_softcap_argmax_noalloc", "xl_softcap_argmax_noalloc_max_rows",
 )
 
 
@@ -127,12 +128,14 @@ def lib() -> C.CDLL:
                             ("xl_mlstm_step", MlstmStepParams), ("xl_slstm_forward", SlstmParams),
                             ("xl_add_rmsnorm", AddRmsnormParams), ("xl_headnorm_gate", HeadnormGateParams),
                             ("xl_soft_cap", SoftCapParams), ("xl_causal_conv1d", Conv1dParams),
-                            ("xl_softcap_argmax", GreedyParams), ("xl_swiglu", SwigluParams)):
+                            ("xl_softcap_argmax", GreedyParams), ("xl_swiglu", SwigluParams),
+                            ("xl_softcap_argmax_noalloc", GreedyParams)):
             fn = getattr(l, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(ptype), C.c_void_p]
         l.xl_softcap_argmax_scratch_bytes.restype = C.c_int64
         l.xl_softcap_argmax_scratch_bytes.argtypes = [C.c_int32]
+        l.xl_softcap_argmax_noalloc_max_rows.restype = C.c_int32
         _lib = l
     return _lib
 

@@ -143,3 +143,43 @@ extern "C" int xl_softcap_argmax(const xl_greedy_params* p, void* cuda_stream) {
   if (reinterpret_cast<uintptr_t>(p->scratch) & 7u) return XL_ERR_BAD_ALIGNMENT;
   return gh_launch(p, static_cast<GhRow*>(p->scratch), static_cast<cudaStream_t>(cuda_stream));
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same head for callers that cannot allocate device memory.
+//
+// Its scratch is a file-scope array in device memory, part of the library image: every GPU on which the library is
+// loaded holds GH_STATIC_MAX_ROWS * sizeof(GhRow) = 270 336 bytes of it until the process exits.  In host code the name
+// of the array is only a stand-in for the symbol, not a device address, so the address is asked for once per device
+// (cudaGetSymbolAddress, with that device current) and handed to the kernel like any other scratch pointer.
+// ---------------------------------------------------------------------------------------------
+namespace xl {
+
+constexpr int GH_STATIC_MAX_ROWS = 1024;
+constexpr int GH_MAX_DEVICES = 64;
+static __device__ __align__(256) GhRow g_gh_static_scratch[GH_STATIC_MAX_ROWS];
+static GhRow* g_gh_static_ptr[GH_MAX_DEVICES];   // device address of the array, per device; filled on first use
+
+}  // namespace xl
+
+extern "C" int32_t xl_softcap_argmax_noalloc_max_rows(void) { return xl::GH_STATIC_MAX_ROWS; }
+
+extern "C" int xl_softcap_argmax_noalloc(const xl_greedy_params* p, void* cuda_stream) {
+  using namespace xl;
+  int rc = gh_validate(p);
+  if (rc != XL_OK) return rc;
+  if (p->rows > GH_STATIC_MAX_ROWS) return XL_ERR_TOO_LARGE;   // the built-in scratch holds GH_STATIC_MAX_ROWS rows
+  int dev = -1;
+  XL_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= GH_MAX_DEVICES) return XL_ERR_TOO_LARGE;
+  if (!g_gh_static_ptr[dev]) {   // set-up, once per device, with that device current (it is: cudaGetDevice said so)
+    void* sym = nullptr;
+    XL_CUDA_TRY(cudaGetSymbolAddress(&sym, g_gh_static_scratch));
+    g_gh_static_ptr[dev] = static_cast<GhRow*>(sym);
+  }
+  GhRow* scratch = g_gh_static_ptr[dev];
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  // The array keeps what the last call left.  A call that ran to its end left the counters at zero, but nothing here
+  // relies on that: the rows this call uses are cleared first, in stream order.
+  XL_CUDA_TRY(cudaMemsetAsync(scratch, 0, (size_t)p->rows * sizeof(GhRow), st));
+  return gh_launch(p, scratch, st);
+}
