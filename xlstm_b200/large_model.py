@@ -138,6 +138,9 @@ class LargeModel:
         dq, dv = cfg.qk_dim // NH, cfg.v_dim // NH
         self.dq, self.dv = dq, dv
         h0, h1 = tp_rank * NHl, (tp_rank + 1) * NHl
+        # zero rows behind the 2 * NHl gate rows of the stacked projection weight: its output rows then are a multiple of
+        # 16 elements long, which keeps every column slice (q, k, v, o) on the 16-byte alignment TMA and vector loads need
+        self.gate_pad = (-2 * NHl) % 16
         f0, f1 = tp_rank * cfg.ffn_dim // tp_world, (tp_rank + 1) * cfg.ffn_dim // tp_world
 
         def W(name):
@@ -151,11 +154,12 @@ class LargeModel:
             # path runs all six projections as ONE GEMM (the gate bias is added by the soft-cap kernel)
             qkvo_if = torch.cat([W(b + "mlstm_layer.q.weight")[h0 * dq:h1 * dq], W(b + "mlstm_layer.k.weight")[h0 * dq:h1 * dq],
                                  W(b + "mlstm_layer.v.weight")[h0 * dv:h1 * dv], W(b + "mlstm_layer.ogate_preact.weight")[h0 * dv:h1 * dv],
-                                 W(b + "mlstm_layer.igate_preact.weight")[h0:h1], W(b + "mlstm_layer.fgate_preact.weight")[h0:h1]], 0).contiguous()
+                                 W(b + "mlstm_layer.igate_preact.weight")[h0:h1], W(b + "mlstm_layer.fgate_preact.weight")[h0:h1],
+                                 torch.zeros(self.gate_pad, cfg.embedding_dim, device=self.device, dtype=dtype)], 0).contiguous()
             n_qkvo = 2 * NHl * dq + 2 * NHl * dv
             blk = dict(
                 norm_mlstm=W(b + "norm_mlstm.weight"), norm_ffn=W(b + "norm_ffn.weight"), qkvo_if=qkvo_if,
-                qkvo=qkvo_if[:n_qkvo], if_w=qkvo_if[n_qkvo:],
+                qkvo=qkvo_if[:n_qkvo], if_w=qkvo_if[n_qkvo:n_qkvo + 2 * NHl],
                 if_b=torch.cat([W(b + "mlstm_layer.igate_preact.bias")[h0:h1], W(b + "mlstm_layer.fgate_preact.bias")[h0:h1]], 0).contiguous(),
                 mh_norm=W(b + "mlstm_layer.multihead_norm.weight")[h0 * dv:h1 * dv].contiguous(),
                 out_proj=W(b + "mlstm_layer.out_proj.weight")[:, h0 * dv:h1 * dv].contiguous(),
@@ -180,7 +184,7 @@ class LargeModel:
         B, S, _ = x.shape
         if self.fused:   # one GEMM for all six projections; the gates are capped in fp32 (they enter exponentials in the cell)
             allp = F.linear(x, blk["qkvo_if"])
-            q, k, v, o, gpre = torch.split(allp, [NHl * dq, NHl * dq, NHl * dv, NHl * dv, 2 * NHl], dim=-1)
+            q, k, v, o, gpre, _ = torch.split(allp, [NHl * dq, NHl * dq, NHl * dv, NHl * dv, 2 * NHl, self.gate_pad], dim=-1)
             gates = ops.soft_cap(gpre, cfg.gate_soft_cap, out_float32=True, float32_math=True, bias=blk["if_b"])
         else:
             qkvo = F.linear(x, blk["qkvo"])
