@@ -22,6 +22,11 @@ def _oracle_cell():
     from oracle import mlstm as O
 
     def seq(q, k, v, i, f, c=None, n=None, m=None, cu_seqlens=None, eps=1e-6):
+        if cu_seqlens is not None:   # packed rows: every document alone, states with one row per document
+            B, NH, S, _ = q.shape
+            flat = lambda t: t.transpose(0, 1).reshape(NH, B * S, *t.shape[3:])
+            h, (cc, nn, mm) = O.mlstm_packed(flat(q), flat(k), flat(v), flat(i), flat(f), [int(x) for x in cu_seqlens], eps=eps)
+            return h.reshape(NH, B, S, -1).transpose(0, 1).to(q.dtype), (cc, nn, mm)
         h, st = O.mlstm_inference(q, k, v, i, f, c, n, m, eps=eps)
         return h.to(q.dtype), st
 
@@ -262,6 +267,11 @@ def test_continuous_batching_equals_per_document_decoding_on_cpu():
         assert torch.equal(model.generate(p[None], c)[0][0], o)
     with pytest.raises(ValueError):
         dec.run(prompts, [1, 2])
+    # packed admission (rows of 96 tokens, at most one row per prefill): the same tokens from fewer prefills
+    packed = ContinuousDecoder(model, 3, row_len=96, max_rows_per_prefill=1, packed_admission=True)
+    outs2 = packed.run(prompts, counts)
+    assert all(torch.equal(a, b) for a, b in zip(outs, outs2))
+    assert packed.prefill_calls < dec.prefill_calls == len(prompts)
 
 
 @pytest.mark.gpu
