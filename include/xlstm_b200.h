@@ -246,6 +246,37 @@ typedef struct xl_swiglu_params {
 int xl_swiglu(const xl_swiglu_params* p, void* cuda_stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Tensor-parallel decode: x_out = x + sum over ranks of partial, normed = RMSNorm(x_out) * weight, in ONE kernel over peer
+ * memory.  (The reference has no tensor parallelism; this fuses what follows its row-parallel projections
+ * out_proj / proj_down, model.py:373-377, 268-277, 499-510, when heads are split over GPUs: the all-reduce of their partial
+ * sums, the residual add and the next RMSNorm.)  One thread block per row pushes its rank's partial row into every
+ * rank's receive area with plain peer stores, publishes a flag, waits (bounded) for all ranks' flags in its own area and
+ * reduces from LOCAL memory in rank order.  Every rank must make the same sequence of calls with the same `rows`.
+ * Receive areas and flags must be mapped on every rank (peer access / symmetric memory) and zero-initialised once; no
+ * multicast and no library operates on the peer pointers, only this kernel's loads and stores.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct xl_peer_reduce_params {
+  const void* partial;          /* (rows, D) this rank's partial sums, row stride partial_sr */
+  void* const* peer_recv;       /* device array [world]: rank r's receive area as seen from this rank */
+  const void* recv_local;       /* this rank's own receive area: [2][world][rows_max][D] elements of `dtype` */
+  uint32_t* const* peer_flags;  /* device array [world]: rank r's flag area [2][world][rows_max] */
+  const uint32_t* flags_local;
+  uint32_t* epoch;              /* (rows_max) per-row call counters in this rank's memory, zero-initialised once */
+  const void* x;                /* (rows, D) residual stream, row stride x_sr */
+  const void* weight;           /* (D) */
+  void* x_out;                  /* (rows, D), stride xo_sr; may alias x */
+  void* normed;                 /* (rows, D), stride n_sr */
+  int32_t* status;              /* device word or NULL: set to 3 when a peer's rows did not arrive in time */
+  int32_t rank, world, rows, D, rows_max;
+  int64_t partial_sr, x_sr, xo_sr, n_sr;
+  float eps;
+  int32_t dtype;
+} xl_peer_reduce_params;
+
+/* Requires world <= 8, rows <= rows_max, D a multiple of the 16-byte vector and D <= 8192 (bf16) / 4096 (fp32). */
+int xl_peer_reduce_add_rmsnorm(const xl_peer_reduce_params* p, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Greedy sampling head: tokens[r] = argmax_v soft_cap(logits[r, v]).
  * Replaces the tail of the reference's decode step: the soft cap of the logits (xlstm/xlstm_large/model.py:149-151,
  * components.py:5-22, each operator rounded to `dtype`) and greedy_sampling = torch.argmax of the last position

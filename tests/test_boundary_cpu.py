@@ -30,7 +30,7 @@ def test_struct_layouts_match_header_field_order():
                           ("xl_slstm_params", _lib.SlstmParams), ("xl_add_rmsnorm_params", _lib.AddRmsnormParams),
                           ("xl_headnorm_gate_params", _lib.HeadnormGateParams), ("xl_soft_cap_params", _lib.SoftCapParams),
                           ("xl_conv1d_params", _lib.Conv1dParams), ("xl_greedy_params", _lib.GreedyParams),
-                          ("xl_swiglu_params", _lib.SwigluParams)):
+                          ("xl_swiglu_params", _lib.SwigluParams), ("xl_peer_reduce_params", _lib.PeerReduceParams)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), header, re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         names = []

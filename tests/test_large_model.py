@@ -238,6 +238,15 @@ def test_tensor_parallel_nccl_decode_on_two_gpus(tmp_path):
         "g32, _ = m32.generate(tokens, 24)\n"
         "gs32, _ = s32.generate(tokens, 24)\n"
         "assert torch.equal(g32, gs32), 'fp32 tensor-parallel tokens differ from the single-GPU tokens'\n"
+        "# decode with the all-reduce + residual add + RMSNorm fused into one kernel over peer memory (graph replay)\n"
+        "if m32.enable_peer_reduce():\n"
+        "    p32, _ = m32.generate(tokens, 24, use_cuda_graph=True)\n"
+        "    import xlstm_b200; xlstm_b200.check_device_status(dev)\n"
+        "    assert torch.equal(p32, gs32), 'peer-memory decode differs from the single-GPU tokens'\n"
+        "    assert model.peer is not None   # the bf16 model's graph above was captured with it, too\n"
+        "    m32.release_graph(); print('PEER_OK', rank)\n"
+        "else:\n"
+        "    print('PEER_UNAVAILABLE', rank, m32.peer_unavailable)\n"
         "assert model.comm_calls == 2 * 2 * 3 + 2 and model.comm_ms > 0   # one gather + one scatter per block and piece\n"
         "model.release_graph()\n"
         "dist.barrier(); dist.destroy_process_group()\n"

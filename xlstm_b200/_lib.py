@@ -18,7 +18,7 @@ EXPORTS = (
     "xl_mlstm_chunkwise", "xl_mlstm_recurrent", "xl_mlstm_step", "xl_slstm_forward",
     "xl_add_rmsnorm", "xl_headnorm_gate", "xl_soft_cap", "xl_causal_conv1d",
     "xl_softcap_argmax", "xl_softcap_argmax_scratch_bytes", "xl_swiglu",
-    "xl_softcap_argmax_noalloc", "xl_softcap_argmax_noalloc_max_rows",
+    "xl_softcap_argmax_noalloc", "xl_softcap_argmax_noalloc_max_rows", "xl_peer_reduce_add_rmsnorm",
 )
 
 
@@ -108,6 +108,17 @@ class GreedyParams(C.Structure):
     ]
 
 
+class PeerReduceParams(C.Structure):
+    _fields_ = [
+        ("partial", C.c_void_p), ("peer_recv", C.c_void_p), ("recv_local", C.c_void_p), ("peer_flags", C.c_void_p),
+        ("flags_local", C.c_void_p), ("epoch", C.c_void_p), ("x", C.c_void_p), ("weight", C.c_void_p), ("x_out", C.c_void_p),
+        ("normed", C.c_void_p), ("status", C.c_void_p),
+        ("rank", C.c_int32), ("world", C.c_int32), ("rows", C.c_int32), ("D", C.c_int32), ("rows_max", C.c_int32),
+        ("partial_sr", C.c_int64), ("x_sr", C.c_int64), ("xo_sr", C.c_int64), ("n_sr", C.c_int64),
+        ("eps", C.c_float), ("dtype", C.c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -129,7 +140,7 @@ def lib() -> C.CDLL:
                             ("xl_add_rmsnorm", AddRmsnormParams), ("xl_headnorm_gate", HeadnormGateParams),
                             ("xl_soft_cap", SoftCapParams), ("xl_causal_conv1d", Conv1dParams),
                             ("xl_softcap_argmax", GreedyParams), ("xl_swiglu", SwigluParams),
-                            ("xl_softcap_argmax_noalloc", GreedyParams)):
+                            ("xl_softcap_argmax_noalloc", GreedyParams), ("xl_peer_reduce_add_rmsnorm", PeerReduceParams)):
             fn = getattr(l, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(ptype), C.c_void_p]

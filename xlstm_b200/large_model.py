@@ -172,6 +172,8 @@ class LargeModel:
             self.blocks.append(blk)
         self.comm_ms = None        # set by forward(..., time_collectives=True): CUDA-event time inside collectives
         self.comm_bytes = 0
+        self.peer = None           # PeerReducer of the decode step (enable_peer_reduce)
+        self.peer_unavailable = None
 
     # ------------------------------------------------------------------------------------------------
     def _all_reduce(self, x):
@@ -218,6 +220,33 @@ class LargeModel:
             return ops.swiglu(gz)
         g, z = gz.chunk(2, dim=-1)
         return F.silu(g) * z
+
+    def enable_peer_reduce(self, rows_max: int = 256) -> bool:
+        """Tensor-parallel decode without NCCL launches: the all-reduce of each row-parallel projection's partial sums is
+        fused with the residual add and the following RMSNorm into one kernel over peer memory (``peer.PeerReducer``).
+        Every rank must call this; returns False (and keeps NCCL) where symmetric memory cannot be set up."""
+        if self.tp_world == 1 or not self.fused:
+            return False
+        if self.peer is None and self.peer_unavailable is None:
+            from .peer import PeerReducer
+            self.peer, self.peer_unavailable = PeerReducer.create(self.group, self.device, rows_max, self.cfg.embedding_dim, self.dtype)
+            # all ranks or none: a rank that failed makes the others fall back too
+            okt = torch.tensor([1 if self.peer is not None else 0], device=self.device)
+            torch.distributed.all_reduce(okt, op=torch.distributed.ReduceOp.MIN, group=self.group)
+            if int(okt.item()) == 0:
+                self.peer = None
+                self.peer_unavailable = self.peer_unavailable or "another rank could not set up symmetric memory"
+        return self.peer is not None
+
+    def _reduce_add_norm(self, x, y_partial, w):
+        """``_add_norm`` on the SUM over ranks of `y_partial`: one peer-memory kernel when it is enabled and the rows fit,
+        an all-reduce followed by the add + norm kernel otherwise."""
+        if y_partial is None or self.tp_world == 1:
+            return self._add_norm(x, y_partial, w)
+        rows = x.numel() // x.shape[-1]
+        if self.peer is not None and rows <= self.peer.rows_max and x.is_contiguous():
+            return self.peer.reduce_add_rmsnorm(y_partial, x, w, self.cfg.norm_eps)
+        return self._add_norm(x, self._all_reduce(y_partial), w)
 
     def _add_norm(self, x, y, w):
         """x + y (y may be None) and its RMSNorm, as the reference's block does with two operators (model.py:499-510)."""
@@ -344,20 +373,23 @@ class LargeModel:
         cfg = self.cfg
         x = self.embedding[tokens]
         new_state = {}
-        pending = None   # output of the previous sub-block, added to the residual stream by the next norm call
+        pending = None   # output of the previous sub-block (a PARTIAL sum under tensor parallelism): reduced over the ranks
+        # and added to the residual stream by the next norm call
         for i, blk in enumerate(self.blocks):
-            x, xn = self._add_norm(x, pending, blk["norm_mlstm"])
-            y, st = self._mlstm_layer(blk, xn, None if state is None else state[i], cu_seqlens, slot)
+            x, xn = self._reduce_add_norm(x, pending, blk["norm_mlstm"])
+            y, st = self._mlstm_layer(blk, xn, None if state is None else state[i], cu_seqlens, slot, reduce=False)
             new_state[i] = st
-            x, xn = self._add_norm(x, y, blk["norm_ffn"])
-            pending = self._all_reduce(F.linear(self._swiglu(F.linear(xn, blk["up"])), blk["down"]))
+            x, xn = self._reduce_add_norm(x, y, blk["norm_ffn"])
+            pending = F.linear(self._swiglu(F.linear(xn, blk["up"])), blk["down"])
         if positions is not None:
             x = x.reshape(-1, x.shape[-1])[positions][:, None]
             pending = None if pending is None else pending.reshape(-1, pending.shape[-1])[positions][:, None]
         elif last_only or greedy:
             x = x[:, -1:]
             pending = None if pending is None else pending[:, -1:]
-        x, xn = self._add_norm(x, pending, self.out_norm)
+        if pending is not None and not x.is_contiguous():
+            x, pending = x.contiguous(), pending.contiguous()
+        x, xn = self._reduce_add_norm(x, pending, self.out_norm)
         return self._head(xn, greedy), new_state
 
     # ------------------------------------------------------------------------------------------------
@@ -369,6 +401,8 @@ class LargeModel:
         removes that launch cost.  State lives in static buffers: C is updated in place by the step kernel, n and m
         are copied back into their buffers inside the graph, and the sampled token feeds the next replay."""
         dev = self.device
+        if self.tp_world > 1:
+            self.enable_peer_reduce(max(batch, 256))   # (keeps NCCL where symmetric memory is not available)
         self._g_state = {i: tuple(t for t in st) for i, st in state.items()}
         self._g_tok = torch.zeros(batch, 1, dtype=torch.long, device=dev)
 
