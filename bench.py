@@ -418,12 +418,14 @@ def build_case(name, dev, rank):
             if world > 1:
                 out["prefill_collectives"] = {
                     "scheme": "per block one all-gather (normed activations) + one reduce-scatter (out_proj partial sums) over the "
-                              "token axis, two batch pieces on two streams; decode: two all-reduces per block inside the step graph",
+                              "token axis, two batch pieces on two streams; decode: two reductions per block inside the step graph",
                     "calls": model.comm_calls, "bytes_per_call": model.comm_bytes // max(model.comm_calls, 1),
                     "event_ms_sum": model.comm_ms,
                     "note": "CUDA-event time around each collective on its own stream, summed; the two streams overlap, so the sum "
                             "can exceed the share of the prefill the collectives expose",
-                    "decode_all_reduce_bytes": B * 4096 * 2, "decode_all_reduces_per_step": 64}
+                    "decode_all_reduce_bytes": B * 4096 * 2, "decode_all_reduces_per_step": 65,
+                    "decode_reduce": ("one kernel per all-reduce + residual add + RMSNorm over peer memory (one-shot push)"
+                                      if model.peer is not None else "NCCL all-reduce + add/norm kernel (%s)" % model.peer_unavailable)}
             return out
 
         cfg = dict(model="xLSTM-7B-shaped (random init)", embedding_dim=4096, num_heads=8, num_blocks=32, vocab_size=50304,
