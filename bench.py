@@ -19,6 +19,7 @@ prints one of them as a line of its own:
   layer_ops     residual add + RMSNorm and per-head norm + output gate at the 7B prefill shapes
   chunkwise_b1  the headline kernel on one sequence (B=1): the size used for profiler captures
   model7b       the xLSTM-7B-shaped model (random init, bf16): prefill 8 x 8192 + 512 greedy tokens, strong scaling
+  decode7b      one graph-replayed decode step of that model at batch 8
   continuous7b  continuous batching: packed prefill of log-normal documents into a pool of decode slots with refill
 
 `--impl reference` times the reference's native CPU formulation (the oracle port) on the host cores.
@@ -362,6 +363,22 @@ def build_case(name, dev, rank):
                     h2d=sum(lens) * 8, d2h=(NSLOT // world) * steps_est * 8, l2="weights (13.7 GB) exceed the 126 MB L2",
                     launches=steps_est + 32 * 8, heavy=True,
                     extra=lambda m: {"prefill_calls_per_run": dec.prefill_calls // max(m["steps"] + m["warmup"] + m["e2e_steps"], 1)})
+    if name == "decode7b":
+        # one graph-replayed decode step of the 7B-shaped mirror at batch 8 (the unit the launch-list profile lists)
+        from xlstm_b200.large_model import LargeConfig, LargeModel, procedural_state_dict
+        mcfg = LargeConfig(embedding_dim=4096, num_heads=8, num_blocks=32, vocab_size=50304)
+        sd = procedural_state_dict(mcfg, seed=0, dtype=torch.bfloat16, device=dev, gen_device=dev)
+        model = LargeModel(mcfg, sd, dev, torch.bfloat16)
+        del sd
+        torch.cuda.empty_cache()
+        tok = torch.randint(0, mcfg.vocab_size, (8, 128), generator=torch.Generator().manual_seed(5)).to(dev)
+        model.generate(tok, 4, use_cuda_graph=True)   # prefill, capture
+        weight_bytes = sum(t.numel() * t.element_size() for t in model.parameters_on_device() if t is not model.embedding)
+        return dict(step=lambda: model._graph.replay(), e2e_step=lambda: model._graph.replay(), teardown=model.release_graph,
+                    units=8, unit="tokens/s", metric="xlstm7b_decode_step_tokens_per_s", workload="xlstm7b_decode_step_batch8",
+                    cfg=dict(model="xLSTM-7B-shaped (random init)", batch=8), bytes=weight_bytes + 32 * step_bytes(8, 8, 256, 512),
+                    flops=0, kernel="one replay of the captured decode step (325 kernels)", h2d=0, d2h=0,
+                    l2="weights (13.7 GB) exceed the 126 MB L2", launches=325)
     if name == "model7b":
         # xLSTM-7B-shaped model, random-init bf16: prefill 8 x 8192 tokens, then 512 greedy tokens.  Heads are
         # tensor-parallel over the ranks (strong scaling): dense layers are library GEMMs, the cell is ours.
@@ -459,11 +476,13 @@ def measure(case, steps, warmup, world, rank, dev, e2e=True, sampler=None, hold_
     xlstm_b200.check_device_status(dev)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
     barrier()
+    torch.cuda.profiler.start()   # (a profiler run with --profile-from-start off sees the timed steps only)
     ev[0].record()
     for i in range(steps):
         step()
         ev[i + 1].record()
     barrier()
+    torch.cuda.profiler.stop()
     total_ms = ev[0].elapsed_time(ev[-1])
     kernel_ms = sum(ev[i].elapsed_time(ev[i + 1]) for i in range(steps)) / steps
     clocks = None
@@ -547,7 +566,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--case", default="all", choices=["all", "chunkwise", "chunkwise_b1", "step", "slstm", "layer_ops", "model7b", "continuous7b"])
+    ap.add_argument("--case", default="all", choices=["all", "chunkwise", "chunkwise_b1", "step", "slstm", "layer_ops", "model7b", "decode7b", "continuous7b"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="profiling runs: device-resident loop only")
     args = ap.parse_args()
