@@ -176,7 +176,10 @@ int xl_add_rmsnorm(const xl_add_rmsnorm_params* p, void* cuda_stream);
  * transpose copy. */
 typedef struct xl_headnorm_gate_params {
   const void* h;       /* (B, NH, S, DH) through h_sb, h_sh, h_st (elements); DH contiguous */
-  const void* o;       /* gate pre-activations (B, S, NH*DH) through o_sb, o_st; NH*DH contiguous */
+  const void* o;       /* gate pre-activations (B, S, NH*DH) through o_sb, o_st; NH*DH contiguous.  NULL = no gate: the
+                          kernel then is the group norm behind the sLSTM cell, out = (h - mean) * rstd * weight rounded
+                          once (MultiHeadLayerNorm.forward, xlstm/components/ln.py:52-68, called at
+                          xlstm/blocks/slstm/layer.py:157; pass weight = 1 + the module's residual weight) */
   const void* weight;  /* (NH*DH) */
   void* out;           /* (B, S, NH*DH) contiguous */
   int32_t B, NH, S, DH;

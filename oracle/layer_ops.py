@@ -91,3 +91,14 @@ def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | No
     if silu:
         y = torch.nn.functional.silu(y.float()).to(dt)
     return y.reshape(B, S, F_)
+
+
+def head_group_norm(h: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5):
+    """h (B,NH,S,DH), weight (NH*DH,) [already 1 + residual weight] -> (B,S,NH*DH): ``F.group_norm`` over every head of
+    every token, rounded once (``MultiHeadLayerNorm.forward``, xlstm/components/ln.py:52-68)."""
+    dt = h.dtype
+    B, NH, S, DH = h.shape
+    hf = h.transpose(1, 2).float()
+    c = hf - hf.mean(dim=-1, keepdim=True)
+    n = c * torch.rsqrt(hf.var(dim=-1, keepdim=True, unbiased=False) + eps)
+    return (n.reshape(B, S, NH * DH) * weight.float()).to(dt)

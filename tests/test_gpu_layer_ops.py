@@ -191,3 +191,19 @@ def test_swiglu_and_strided_biased_soft_cap_match_oracle(tag):
     got2 = xlstm_b200.soft_cap(wide.cuda()[..., 12288:], 15.0, out_float32=True, float32_math=True, bias=bias.cuda())
     pre = (gates.float() + bias.float()).to(dt).float()
     assert float((got2.cpu() - 15.0 * torch.tanh(pre / 15.0)).abs().max()) < 1e-5
+
+
+@pytest.mark.parametrize("tag", ["bf16", "f32"])
+def test_head_group_norm_without_gate_matches_torch_group_norm(tag):
+    """The epilogue of the sLSTM layer: per-head group norm of the (B,NH,S,DH) cell output, against torch's own
+    ``F.group_norm`` on the transposed copy (what the reference module calls) and against the oracle."""
+    import xlstm_b200
+    dt = DT[tag]
+    g = torch.Generator().manual_seed(23)
+    B, NH, S, DH = 3, 4, 37, 256
+    h = (2.0 * torch.randn(B, NH, S, DH, generator=g) + 0.3).to(dt)
+    w = (1.0 + 0.1 * torch.randn(NH * DH, generator=g)).to(dt)
+    got = xlstm_b200.headnorm_gate(h.cuda(), None, w.cuda(), eps=1e-5)
+    want = torch.nn.functional.group_norm(h.transpose(1, 2).reshape(B * S, NH * DH).float(), NH, w.float(), None, 1e-5).to(dt)
+    _close(got.reshape(B * S, NH * DH), want, dt)
+    _close(got, O.head_group_norm(h, w, 1e-5), dt)

@@ -71,6 +71,16 @@ __device__ __forceinline__ Vec16<__nv_bfloat16> normalise_weight_gate(const Vec1
   return y;
 }
 
+// Without a gate (o == NULL): out = round((h - mean) * r * w), one rounding, as a group norm computes it
+// (F.group_norm in MultiHeadLayerNorm.forward, xlstm/components/ln.py:52-68).
+template <typename T>
+__device__ __forceinline__ Vec16<T> normalise_weight(const Vec16<T>& h, const Vec16<T>& w, float mean, float r) {
+  Vec16<T> y;
+#pragma unroll
+  for (int i = 0; i < Vec16<T>::N; ++i) y.v[i] = from_float<T>(((to_float(h.v[i]) - mean) * r) * to_float(w.v[i]));
+  return y;
+}
+
 __device__ __forceinline__ float warp_sum(float x) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
@@ -173,7 +183,7 @@ __global__ void __launch_bounds__(HNG_WARPS * 32) headnorm_gate_kernel(const xl_
     const int e = (c * 32 + lane) * V;
     if (e < p.DH) {
       hv[c] = load16(h + e);
-      ov[c] = load16(o + e);
+      if (p.o) ov[c] = load16(o + e);
       wv[c] = load16(w + e);
     }
   }
@@ -204,7 +214,7 @@ __global__ void __launch_bounds__(HNG_WARPS * 32) headnorm_gate_kernel(const xl_
   for (int c = 0; c < NC; ++c) {
     const int e = (c * 32 + lane) * V;
     if (e < p.DH) {
-      store16(out + e, normalise_weight_gate(hv[c], ov[c], wv[c], mean, r));
+      store16(out + e, p.o ? normalise_weight_gate(hv[c], ov[c], wv[c], mean, r) : normalise_weight<T>(hv[c], wv[c], mean, r));
     }
   }
 }
@@ -376,13 +386,13 @@ extern "C" int xl_add_rmsnorm(const xl_add_rmsnorm_params* p, void* cuda_stream)
 
 extern "C" int xl_headnorm_gate(const xl_headnorm_gate_params* p, void* cuda_stream) {
   using namespace xl;
-  if (!p || !p->h || !p->o || !p->weight || !p->out) return XL_ERR_NULL_POINTER;
+  if (!p || !p->h || !p->weight || !p->out) return XL_ERR_NULL_POINTER;
   if (p->dtype != XL_F32 && p->dtype != XL_BF16) return XL_ERR_BAD_DTYPE;
   const int V = p->dtype == XL_F32 ? 4 : 8;
   if (p->B <= 0 || p->NH <= 0 || p->S <= 0 || p->DH <= 0 || p->DH % V != 0) return XL_ERR_BAD_SHAPE;
   if (p->DH > 32 * ADJ_MAXC * V) return XL_ERR_TOO_LARGE;
-  if (p->h_sb % V || p->h_sh % V || p->h_st % V || p->o_sb % V || p->o_st % V) return XL_ERR_BAD_STRIDE;
-  if (!aligned16(p->h) || !aligned16(p->o) || !aligned16(p->weight) || !aligned16(p->out)) return XL_ERR_BAD_ALIGNMENT;
+  if (p->h_sb % V || p->h_sh % V || p->h_st % V || (p->o && (p->o_sb % V || p->o_st % V))) return XL_ERR_BAD_STRIDE;
+  if (!aligned16(p->h) || (p->o && !aligned16(p->o)) || !aligned16(p->weight) || !aligned16(p->out)) return XL_ERR_BAD_ALIGNMENT;
   if (p->out == p->h || p->out == p->o) return XL_ERR_ALIASING;
   const long long per_row = (long long)p->S * p->NH;
   if (per_row > 0x7fffffffLL || p->B > 65535) return XL_ERR_TOO_LARGE;

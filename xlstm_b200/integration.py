@@ -177,14 +177,42 @@ class PackAwareCausalConv1d(torch.nn.Module):
         return torch.nn.functional.silu(y), state
 
 
+class HeadGroupNorm(torch.nn.Module):
+    """Stands in for the ``MultiHeadLayerNorm`` behind the sLSTM cell (xlstm/blocks/slstm/layer.py:157;
+    xlstm/components/ln.py:52-68): the per-head group norm of the cell output in one kernel that reads the cell's
+    (B, NH, S, DH) layout through its strides and writes (B, S, NH*DH) -- the transposes on either side of the reference
+    module become views.  It owns the same parameters (``weight`` is the reference's residual weight; 1 + weight is
+    applied), eps included."""
+
+    def __init__(self, reference_norm):
+        super().__init__()
+        if reference_norm.bias is not None:
+            raise ValueError("the kernel covers the bias-free norm the sLSTM layer builds")
+        self.ref = reference_norm
+
+    def reset_parameters(self):
+        self.ref.reset_parameters()
+
+    def forward(self, x):
+        B, NH, S, DH = x.shape
+        w = self.ref.weight_proxy
+        w = torch.ones(NH * DH, dtype=x.dtype, device=x.device) if w is None else w.to(x.dtype)
+        out = ops.headnorm_gate(x, None, w, eps=self.ref.eps)            # (B, S, NH*DH)
+        return out.view(B, S, NH, DH).transpose(1, 2)                   # the caller transposes back and flattens: views
+
+
 def pack_aware_slstm_layers(model) -> int:
-    """Replaces conv1d + conv_act_fn in every ``sLSTMLayer`` below `model`; returns how many layers were changed."""
+    """Replaces conv1d + conv_act_fn in front of the cell, and the group norm behind it, in every ``sLSTMLayer`` below
+    `model`; returns how many layers were changed."""
     layer_mod = importlib.import_module("xlstm.blocks.slstm.layer")
     n = 0
     for m in model.modules():
-        if isinstance(m, layer_mod.sLSTMLayer) and m.config.conv1d_kernel_size > 0 and not isinstance(m.conv1d, PackAwareCausalConv1d):
-            m.conv1d = PackAwareCausalConv1d(m.conv1d)
-            m.conv_act_fn = torch.nn.Identity()
+        if isinstance(m, layer_mod.sLSTMLayer) and not isinstance(m.group_norm, HeadGroupNorm):
+            if m.config.conv1d_kernel_size > 0:
+                m.conv1d = PackAwareCausalConv1d(m.conv1d)
+                m.conv_act_fn = torch.nn.Identity()
+            if m.group_norm.bias is None:
+                m.group_norm = HeadGroupNorm(m.group_norm)
             n += 1
     return n
 

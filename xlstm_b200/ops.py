@@ -354,22 +354,26 @@ def headnorm_gate(h, o_preact, weight, eps: float = 1e-6):
     """``sigmoid(o_preact) * (LayerNorm over DH of h, per head) * weight`` -> (B, S, NH*DH).
 
     ``h`` is the cell output (B, NH, S, DH), read through its strides (no transpose copy); ``o_preact`` is
-    (B, S, NH*DH), possibly a column slice of a wider projection output.  Follows MultiHeadLayerNorm.forward
+    (B, S, NH*DH), possibly a column slice of a wider projection output, or None: then the result is the plain
+    per-head group norm ``(h - mean) * rstd * weight`` rounded once, the epilogue of the reference's sLSTM layer
+    (``MultiHeadLayerNorm``, xlstm/components/ln.py:52-68; xlstm/blocks/slstm/layer.py:157).  Follows MultiHeadLayerNorm.forward
     and the output gate of the reference layer (components.py:188-242, xlstm_large/model.py:445-449)."""
     _require_cuda(h, o_preact, weight)
-    if h.dim() != 4 or h.dtype not in _DTYPES or o_preact.dtype != h.dtype or weight.dtype != h.dtype:
+    if h.dim() != 4 or h.dtype not in _DTYPES or (o_preact is not None and o_preact.dtype != h.dtype) or weight.dtype != h.dtype:
         raise ValueError("headnorm_gate: h must be (B,NH,S,DH); h, o_preact and weight must share float32 or bfloat16")
     B, NH, S, DH = h.shape
-    if o_preact.shape != (B, S, NH * DH) or weight.shape != (NH * DH,):
+    if (o_preact is not None and o_preact.shape != (B, S, NH * DH)) or weight.shape != (NH * DH,):
         raise ValueError("headnorm_gate: o_preact must be (B,S,NH*DH) and weight (NH*DH,)")
     h = _last_contig(h)
-    o = _last_contig(o_preact)
+    o = _last_contig(o_preact) if o_preact is not None else None
     out = torch.empty((B, S, NH * DH), dtype=h.dtype, device=h.device)
     p = HeadnormGateParams()
-    p.h, p.o, p.weight, p.out = h.data_ptr(), o.data_ptr(), weight.contiguous().data_ptr(), out.data_ptr()
+    p.h, p.weight, p.out = h.data_ptr(), weight.contiguous().data_ptr(), out.data_ptr()
     p.B, p.NH, p.S, p.DH = B, NH, S, DH
     p.h_sb, p.h_sh, p.h_st = h.stride()[:3]
-    p.o_sb, p.o_st = o.stride()[:2]
+    if o is not None:
+        p.o = o.data_ptr()
+        p.o_sb, p.o_st = o.stride()[:2]
     p.eps, p.dtype = eps, _DTYPES[h.dtype]
     with torch.cuda.device(h.device):
         check(lib().xl_headnorm_gate(C.byref(p), _stream_ptr(h.device)), "xl_headnorm_gate")
