@@ -349,14 +349,15 @@ def test_packed_slstm_layers_equal_per_document_runs():
     from xlstm_b200.integration import pack_aware_slstm_layers, set_document_offsets
     B, S, D = 2, 96, 256
     stack = _slstm_stack("b200", torch.bfloat16, num_blocks=2, embedding_dim=D, seed=3)
+    leaky_stack = _slstm_stack("b200", torch.bfloat16, num_blocks=2, embedding_dim=D, seed=3)   # same weights, reference front
     x = torch.randn(B, S, D, generator=torch.Generator().manual_seed(5)).bfloat16().cuda()
     cu = [0, 40, 96, 96 + 7, 96 + 7, 192]
     flat = x.reshape(1, B * S, D)
+    assert pack_aware_slstm_layers(stack) == 2
     with torch.no_grad():
         alone = torch.cat([stack(flat[:, a:e]) for a, e in zip(cu[:-1], cu[1:]) if e > a], dim=1).reshape(B, S, D)
-        set_document_offsets(stack, cu)          # cells only: the reference convolution still leaks
-        leaky = stack(x)
-        assert pack_aware_slstm_layers(stack) == 2
+        set_document_offsets(leaky_stack, cu)    # cells only: the reference convolution still reaches across boundaries
+        leaky = leaky_stack(x)
         set_document_offsets(stack, cu)
         packed = stack(x)
         set_document_offsets(stack, None)
@@ -368,10 +369,10 @@ def test_packed_slstm_layers_equal_per_document_runs():
     assert rel_l2(add(packed), add(alone)) < 3e-2
     e_leak, e_ok = rel_l2(add(leaky)[:, 40:43], add(alone)[:, 40:43]), rel_l2(add(packed)[:, 40:43], add(alone)[:, 40:43])
     print(f"first three tokens behind a boundary, block contribution: reference convolution {e_leak:.3f}, pack-aware {e_ok:.3f}")
-    assert e_ok < 2e-3 and e_leak > 5e-3   # what the kernel fixes (with the layer's small default initialisation the leak is a
+    assert e_ok < 2e-3 and e_leak > 1e-2   # what the kernel fixes (with the layer's small default initialisation the leak is a
     # percent-level error of the block's contribution; the fixture of the convolution alone shows it at full size)
     # without offsets the replaced front computes what the reference front computes for plain rows
-    ref_stack = _slstm_stack("b200", torch.bfloat16, source=None, num_blocks=2, embedding_dim=D, seed=3)
+    set_document_offsets(leaky_stack, None)
     with torch.no_grad():
-        want = ref_stack(x)
+        want = leaky_stack(x)
     assert rel_l2(rows.float().cpu(), want.float().cpu()) < 1e-2
