@@ -213,6 +213,46 @@ def slstm_reference_cuda(cfg, dev, our_ms):
         return {"reference_cuda_unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
 
 
+def slstm_gate_projections(cfg, dev):
+    """The front of the same sLSTM layer: four headwise gate projections + concatenation at the cell's shape, as ONE
+    kernel (xl_headwise_proj) and as the reference layer's eager operators (four einsum calls and torch.cat,
+    xlstm/components/linear_headwise.py:75-82, xlstm/blocks/slstm/layer.py:145-154), device-timed."""
+    import xlstm_b200
+    B, S, NH, DH = cfg["B"], cfg["S"], cfg["NH"], cfg["DH"]
+    D = NH * DH
+    g = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn(B, S, D, device=dev, generator=g).bfloat16()
+    xc = torch.randn(B, S, D, device=dev, generator=g).bfloat16()
+    ws = [(torch.randn(NH, DH, DH, device=dev, generator=g) / DH ** 0.5).bfloat16() for _ in range(4)]
+
+    def eager():
+        outs = []
+        for w, inp in zip(ws, (xc, xc, x, x)):
+            outs.append(torch.einsum("...hd,hod->...ho", inp.view(B, S, NH, DH), w).reshape(B, S, D))
+        return torch.cat(outs, dim=-1)
+
+    def timed(fn, n=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    ours = timed(lambda: xlstm_b200.headwise_proj([x, xc], ws, [1, 1, 0, 0]))
+    ref = timed(eager)
+    nbytes = (2 + 4) * B * S * D * 2 + 4 * NH * DH * DH * 2   # both inputs read, four gate planes written, weights once
+    peak, src = measured_peak_hbm()
+    return {"gate_projections": {"kernel": "headwise_proj_kernel<%d>" % DH, "ms": ours, "eager_ms": ref, "speedup_vs_eager": ref / ours,
+                                 "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / ours / 1e6,
+                                 "frac_of_hbm_peak": nbytes / ours / 1e6 / peak, "peak_source": src,
+                                 "flops": 2 * 4 * B * S * NH * DH * DH}}
+
+
 # ---------------------------------------------------------------------------------------------- GPU cases
 def build_case(name, dev, rank):
     """Returns dict(step=callable on device-resident inputs, e2e_step=callable with host buffers or None,
@@ -291,7 +331,7 @@ def build_case(name, dev, rank):
                     kernel="slstm_forward_kernel<256>", h2d=wx_h.numel() * 2, d2h=o_host.numel() * 2,
                     l2="inputs (%d MB) exceed the 126 MB L2" % (slstm_bytes(**cfg) // 10 ** 6), launches=1,
                     traffic=323.9e6, traffic_source="constant: ncu dram__bytes_read.sum + dram__bytes_write.sum of ONE captured launch of this workload, not measured in this run",
-                    extra=lambda m: slstm_reference_cuda(cfg, dev, m["kernel_ms"]))
+                    extra=lambda m: {**slstm_reference_cuda(cfg, dev, m["kernel_ms"]), **slstm_gate_projections(cfg, dev)})
     if name == "layer_ops":
         # the two fused operators next to the cell, at the 7B layer's prefill shapes (8 x 8192 tokens, D = 4096)
         B, S, NH, DH = 8, 8192, 8, 512

@@ -248,6 +248,26 @@ typedef struct xl_swiglu_params {
 
 int xl_swiglu(const xl_swiglu_params* p, void* cuda_stream);
 
+/* Headwise (block-diagonal) projections of the sLSTM layer, up to four in one launch, written into the cell's input layout:
+ *   out[r, s, h, :] = W_s[h] x_{in_sel[s]}[r, h*DH : (h+1)*DH]          W_s: (NH, DH, DH) = LinearHeadwiseExpand.weight
+ * replaces `self.fgate(x_conv), self.igate(x_conv), self.zgate(x), self.ogate(x)` and the `torch.cat` behind them
+ * (xlstm/blocks/slstm/layer.py:145-154; xlstm/components/linear_headwise.py:75-82, bias=False as the layer builds them).
+ * bf16 operands, fp32 accumulation on the tensor cores, one rounding to bf16. */
+typedef struct xl_headwise_params {
+  const void* x[2];        /* two inputs (rows, NH*DH), row strides x_row_stride[] (elements); x[1] may be NULL if unused */
+  const void* w[4];        /* per slot (NH, DH, DH) contiguous, [head][out][in] */
+  void* out;               /* (rows, n_slots, NH, DH) through out_row_stride */
+  int32_t* status;         /* device word or NULL: set to 1 if a bounded wait inside the kernel expired */
+  int32_t in_sel[4];       /* which input slot s reads: 0 or 1 */
+  int64_t rows;
+  int32_t NH, DH;          /* DH in {64, 128, 256} */
+  int32_t n_slots;         /* 1..4 */
+  int32_t dtype;           /* XL_BF16 */
+  int64_t x_row_stride[2], out_row_stride;   /* multiples of 8 elements */
+} xl_headwise_params;
+
+int xl_headwise_proj(const xl_headwise_params* p, void* cuda_stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Tensor-parallel decode: x_out = x + sum over ranks of partial, normed = RMSNorm(x_out) * weight, in ONE kernel over peer
  * memory.  (The reference has no tensor parallelism; this fuses what follows its row-parallel projections

@@ -102,3 +102,20 @@ def head_group_norm(h: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5):
     c = hf - hf.mean(dim=-1, keepdim=True)
     n = c * torch.rsqrt(hf.var(dim=-1, keepdim=True, unbiased=False) + eps)
     return (n.reshape(B, S, NH * DH) * weight.float()).to(dt)
+
+
+def headwise_proj(inputs, weights, in_sel=None):
+    """``LinearHeadwiseExpand.forward`` per slot (xlstm/components/linear_headwise.py:75-82, no bias) and the concatenation
+    of the sLSTM layer (xlstm/blocks/slstm/layer.py:145-154): inputs (..., NH*DH), weights (NH, DH_out, DH_in) each;
+    fp32 accumulation, one rounding to the input dtype; result (..., n * NH * DH_out), slot-major."""
+    if isinstance(inputs, torch.Tensor):
+        inputs = [inputs]
+    in_sel = [0] * len(weights) if in_sel is None else list(in_sel)
+    outs = []
+    for w, sel in zip(weights, in_sel):
+        x = inputs[sel]
+        NH = w.shape[0]
+        xh = x.float().reshape(*x.shape[:-1], NH, -1)
+        y = torch.einsum("...hd,hod->...ho", xh, w.float())
+        outs.append(y.reshape(*x.shape[:-1], -1).to(x.dtype))
+    return torch.cat(outs, dim=-1)

@@ -6,7 +6,7 @@ oracle only where the fp32 reduction order moves a value across a rounding bound
 import pytest
 import torch
 
-from conftest import load_golden
+from conftest import load_golden, rel_l2
 from oracle import layer_ops as O
 
 pytestmark = pytest.mark.gpu
@@ -207,3 +207,41 @@ def test_head_group_norm_without_gate_matches_torch_group_norm(tag):
     want = torch.nn.functional.group_norm(h.transpose(1, 2).reshape(B * S, NH * DH).float(), NH, w.float(), None, 1e-5).to(dt)
     _close(got.reshape(B * S, NH * DH), want, dt)
     _close(got, O.head_group_norm(h, w, 1e-5), dt)
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_headwise_proj_kernel_matches_reference_modules_fixture(tag):
+    """The four gate projections of the reference's sLSTM layer and their concatenation, in one launch."""
+    import xlstm_b200
+    g = load_golden("headwise")
+    bf = lambda t: t.view(torch.bfloat16)
+    x, xc, want = bf(g[f"{tag}_x"]).cuda(), bf(g[f"{tag}_xc"]).cuda(), bf(g[f"{tag}_y"])
+    got = xlstm_b200.headwise_proj([x, xc], [bf(g[f"{tag}_w{i}"]).cuda() for i in range(4)], [1, 1, 0, 0])
+    xlstm_b200.check_device_status()
+    assert got.shape == want.shape
+    _close(got, want.float(), torch.bfloat16)
+
+
+@pytest.mark.parametrize("rows,NH,DH,nslots", [(16 * 2048 // 8, 4, 256, 4), (1, 4, 256, 4), (129, 2, 128, 3), (300, 5, 64, 1), (127, 1, 256, 2)])
+def test_headwise_proj_kernel_matches_oracle(rows, NH, DH, nslots):
+    """Row counts around the 128-row tile, all three block sizes, fewer than four slots, a strided second input."""
+    import xlstm_b200
+    g = torch.Generator().manual_seed(rows + NH + DH)
+    D = NH * DH
+    x = torch.randn(rows, D, generator=g).bfloat16()
+    wide = torch.randn(rows, D + 64, generator=g).bfloat16()
+    xc = wide[:, 32:32 + D]                     # a column slice of a wider buffer: row stride D + 64
+    ws = [(torch.randn(NH, DH, DH, generator=g) / DH ** 0.5).bfloat16() for _ in range(nslots)]
+    sel = [1, 1, 0, 0][:nslots]
+    want = O.headwise_proj([x, xc], ws, sel)
+    got = xlstm_b200.headwise_proj([x.cuda(), wide.cuda()[:, 32:32 + D]], [w.cuda() for w in ws], sel)
+    xlstm_b200.check_device_status()
+    # one bf16 ulp, plus an absolute term for sums that cancel (fp32 accumulation in another order)
+    diff = (got.float().cpu() - want.float()).abs()
+    assert (diff <= want.float().abs() * 2.0 ** -7 + 1e-4).all(), float(diff.max())
+    assert rel_l2(got.float().cpu(), want.float()) < 2e-3
+    # a (B, S, D) input comes back as (B, S, n * D)
+    if rows % 2 == 0:
+        got3 = xlstm_b200.headwise_proj([x.cuda().view(2, rows // 2, D)], [ws[0].cuda()])
+        assert got3.shape == (2, rows // 2, D)
+        assert torch.equal(got3.reshape(rows, D), xlstm_b200.headwise_proj([x.cuda()], [ws[0].cuda()]))

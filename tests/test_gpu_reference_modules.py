@@ -376,3 +376,22 @@ def test_packed_slstm_layers_equal_per_document_runs():
     with torch.no_grad():
         want = leaky_stack(x)
     assert rel_l2(rows.float().cpu(), want.float().cpu()) < 1e-2
+
+
+def test_slstm_layers_with_fused_gate_projections_equal_the_layers_own():
+    """The unchanged ``xLSTMBlockStack`` (two sLSTM blocks, b200 cell) before and after every layer's four headwise gate
+    projections + concatenation are handed to the one-launch kernel: same parameters, same output up to the summation
+    order inside the projections."""
+    from xlstm_b200.integration import fuse_slstm_gate_projections
+    B, S, D = 2, 200, 256
+    stack = _slstm_stack("b200", torch.bfloat16, num_blocks=2, embedding_dim=D, seed=4)
+    x = torch.randn(B, S, D, generator=torch.Generator().manual_seed(6)).bfloat16().cuda()
+    keys = sorted(stack.state_dict().keys())
+    with torch.no_grad():
+        want = stack(x)
+        assert fuse_slstm_gate_projections(stack) == 2
+        got = stack(x)
+    assert sorted(stack.state_dict().keys()) == keys
+    e = rel_l2((got.float() - x.float()).cpu(), (want.float() - x.float()).cpu())   # on what the blocks add to the stream
+    print(f"block contribution, fused vs the layer's own projections: {e:.2e}")
+    assert e < 1e-2 and rel_l2(got.float().cpu(), want.float().cpu()) < 2e-3

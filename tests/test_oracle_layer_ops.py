@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-from conftest import load_golden
+from conftest import load_golden, rel_l2
 from oracle import layer_ops as O
 
 DT = {"f32": torch.float32, "bf16": torch.bfloat16}
@@ -58,3 +58,14 @@ def test_causal_conv1d_matches_reference_module(tag):
     assert (packed.float() - g[f"{tag}_packed"]).abs().max().item() <= tol
     # the fixture itself shows why the offsets matter: without them the taps reach into the previous document
     assert (g[f"{tag}_rows"] - g[f"{tag}_packed"]).abs().max().item() > 1.0
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_headwise_proj_matches_reference_modules(tag):
+    """Four ``LinearHeadwiseExpand`` modules of the reference, used as its sLSTM layer uses them, and the concatenation."""
+    g = load_golden("headwise")
+    bf = lambda t: t.view(torch.bfloat16)
+    x, xc, want = bf(g[f"{tag}_x"]), bf(g[f"{tag}_xc"]), bf(g[f"{tag}_y"]).float()
+    got = O.headwise_proj([x, xc], [bf(g[f"{tag}_w{i}"]) for i in range(4)], [1, 1, 0, 0]).float()
+    d = (got - want).abs()
+    assert (d > 0).float().mean().item() < 1e-3 and rel_l2(got, want) < 1e-6   # the summation order may move a last bit

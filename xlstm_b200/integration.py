@@ -201,6 +201,47 @@ class HeadGroupNorm(torch.nn.Module):
         return out.view(B, S, NH, DH).transpose(1, 2)                   # the caller transposes back and flattens: views
 
 
+def _slstm_layer_forward_fused(self, x, conv_state=None, slstm_state=None, return_last_state=False, **kwargs):
+    """``sLSTMLayer.forward`` (xlstm/blocks/slstm/layer.py:123-162) with the four headwise gate projections and their
+    concatenation done by ONE kernel that writes the cell's (B, S, 4, NH, DH) input directly (`xl_headwise_proj`); every
+    other step calls the layer's own sub-modules as the reference does."""
+    B, S, _ = x.shape
+    if self.config.conv1d_kernel_size > 0:
+        if return_last_state:
+            x_conv, conv_state = self.conv1d(x, conv_state, return_last_state=True)
+        else:
+            x_conv = self.conv1d(x, conv_state, return_last_state=False)
+        x_conv = self.conv_act_fn(x_conv)
+    else:
+        x_conv = x
+    gates = (self.fgate, self.igate, self.zgate, self.ogate)   # the order in which the reference concatenates them
+    DH = gates[0].weight.shape[-1]
+    fusable = (x.is_cuda and x.dtype == torch.bfloat16 and DH in (64, 128, 256)
+               and all(g.bias is None and g.weight.shape[1] == DH and g.weight.dtype == torch.bfloat16 for g in gates))
+    if fusable:
+        wx = ops.headwise_proj([x, x_conv], [g.weight for g in gates], [1, 1, 0, 0])
+    else:
+        wx = torch.cat([self.fgate(x_conv), self.igate(x_conv), self.zgate(x), self.ogate(x)], dim=-1)
+    y, slstm_state = self.slstm_cell(wx, state=slstm_state)
+    y = self.dropout(y)
+    out = self.group_norm(y).transpose(1, 2).view(B, S, -1)
+    if return_last_state:
+        return out, {"conv_state": conv_state, "slstm_state": slstm_state}
+    return out
+
+
+def fuse_slstm_gate_projections(model) -> int:
+    """Gives every ``sLSTMLayer`` instance below `model` a forward that computes its four gate projections with one
+    kernel (the class and its parameters are untouched: state dicts load and save as before); returns how many."""
+    layer_mod = importlib.import_module("xlstm.blocks.slstm.layer")
+    n = 0
+    for m in model.modules():
+        if isinstance(m, layer_mod.sLSTMLayer) and "forward" not in m.__dict__:
+            m.forward = types.MethodType(_slstm_layer_forward_fused, m)
+            n += 1
+    return n
+
+
 def pack_aware_slstm_layers(model) -> int:
     """Replaces conv1d + conv_act_fn in front of the cell, and the group norm behind it, in every ``sLSTMLayer`` below
     `model`; returns how many layers were changed."""

@@ -12,7 +12,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
-from ._lib import (AddRmsnormParams, Conv1dParams, GreedyParams, HeadnormGateParams, MlstmSeqParams, MlstmStepParams, SlstmParams, SoftCapParams, SwigluParams, XL_BF16, XL_F32,
+from ._lib import (AddRmsnormParams, Conv1dParams, HeadwiseParams, GreedyParams, HeadnormGateParams, MlstmSeqParams, MlstmStepParams, SlstmParams, SoftCapParams, SwigluParams, XL_BF16, XL_F32,
                    check, lib)
 
 _DTYPES = {torch.float32: XL_F32, torch.bfloat16: XL_BF16}
@@ -461,6 +461,54 @@ def causal_conv1d(x, weight, bias=None, cu_seqlens=None, silu: bool = True):
     with torch.cuda.device(x.device):
         check(lib().xl_causal_conv1d(C.byref(p), _stream_ptr(x.device)), "xl_causal_conv1d")
     return out
+
+
+def headwise_proj(inputs, weights, in_sel=None):
+    """Up to four headwise (block-diagonal) projections in one launch, stacked in the sLSTM cell's input layout: the
+    reference's ``LinearHeadwiseExpand.forward`` per gate (xlstm/components/linear_headwise.py:75-82, bias-free as the layer
+    builds them) and the ``torch.cat`` of xlstm/blocks/slstm/layer.py:145-154.
+
+    ``inputs``: one or two (..., NH*DH) bfloat16 tensors; ``weights``: list of (NH, DH, DH) parameters, slot order;
+    ``in_sel[s]``: which input slot s projects (default: all the first).  Returns (..., len(weights) * NH * DH): slot-major,
+    then head, then feature -- what the cell views as (.., 4, NH, DH)."""
+    if isinstance(inputs, torch.Tensor):
+        inputs = [inputs]
+    inputs, weights = list(inputs), list(weights)
+    n = len(weights)
+    in_sel = [0] * n if in_sel is None else [int(i) for i in in_sel]
+    _require_cuda(*inputs, *weights)
+    if not (1 <= n <= 4) or not (1 <= len(inputs) <= 2) or len(in_sel) != n or any(i not in range(len(inputs)) for i in in_sel):
+        raise ValueError("headwise_proj: one to four weights, one or two inputs, in_sel entries index the inputs")
+    NH, DH, DH_in = weights[0].shape
+    if DH != DH_in or DH not in (64, 128, 256):
+        raise ValueError("headwise_proj: square per-head blocks of 64, 128 or 256 features only")
+    D = NH * DH
+    lead = inputs[0].shape[:-1]
+    for x in inputs:
+        if x.dtype != torch.bfloat16 or x.shape[-1] != D or x.shape[:-1] != lead:
+            raise ValueError("headwise_proj: inputs must be bfloat16 (..., NH*DH) of one shape")
+    for w in weights:
+        if w.dtype != torch.bfloat16 or tuple(w.shape) != (NH, DH, DH):
+            raise ValueError("headwise_proj: weights must be bfloat16 (NH, DH, DH)")
+    xs = [_last_contig(x).reshape(-1, D) for x in inputs]
+    xs = [x if x.stride(0) % 8 == 0 else x.contiguous() for x in xs]
+    ws = [w.contiguous() for w in weights]
+    rows = xs[0].shape[0]
+    out = torch.empty((rows, n * D), dtype=torch.bfloat16, device=xs[0].device)
+    p = HeadwiseParams()
+    for i, x in enumerate(xs):
+        p.x[i] = x.data_ptr()
+        p.x_row_stride[i] = x.stride(0)
+    for s_, w in enumerate(ws):
+        p.w[s_] = w.data_ptr()
+        p.in_sel[s_] = in_sel[s_]
+    p.out, p.out_row_stride = out.data_ptr(), out.stride(0)
+    dev = xs[0].device
+    p.status = status_word(dev).data_ptr()
+    p.rows, p.NH, p.DH, p.n_slots, p.dtype = rows, NH, DH, n, _DTYPES[torch.bfloat16]
+    with torch.cuda.device(dev):
+        check(lib().xl_headwise_proj(C.byref(p), _stream_ptr(dev)), "xl_headwise_proj")
+    return out.reshape(*lead, n * D)
 
 
 _greedy_scratch: dict[int, torch.Tensor] = {}
