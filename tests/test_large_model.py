@@ -281,6 +281,12 @@ def test_continuous_batching_equals_per_document_decoding_on_cpu():
     outs2 = packed.run(prompts, counts)
     assert all(torch.equal(a, b) for a, b in zip(outs, outs2))
     assert packed.prefill_calls < dec.prefill_calls == len(prompts)
+    # eviction: with documents waiting, a stream gives its slot up after two tokens and resumes later from its parked state
+    sliced = ContinuousDecoder(model, 3)
+    outs3 = sliced.run(prompts, counts, quantum=2)
+    assert sliced.evictions > 0 and sliced.prefill_calls == len(prompts)      # resumed without a second prefill
+    assert all(torch.equal(a, b) for a, b in zip(outs, outs3))
+    assert len(sliced.slots.free) == 3 and not sliced.slots.owner
 
 
 @pytest.mark.gpu
@@ -301,6 +307,11 @@ def test_continuous_batching_graph_replay_with_refill_on_gpu(packed, row_len):
     assert int((dec.slot_map >= 0).sum()) == 0 and len(dec.slots.free) == 3   # every slot was handed back
     if packed:
         assert dec.prefill_calls < len(prompts)   # several documents per prefill
+    # time slicing with eviction (states parked on the host), same graph, same tokens
+    outs_sliced = dec.run(prompts, counts, quantum=3, park_on_host=True)
+    xlstm_b200.check_device_status()
+    assert dec.evictions > 0 and int((dec.slot_map >= 0).sum()) == 0
+    assert all(torch.equal(a, b) for a, b in zip(outs, outs_sliced))
     model.release_graph()
     for p, c, o in zip(prompts, counts, outs):
         assert torch.equal(model.generate(p[None].cuda(), c)[0][0].cpu(), o)

@@ -590,40 +590,90 @@ class ContinuousDecoder:
                     dst.copy_(src.reshape(dst.shape))
         self.tok.copy_(nxt)
 
+    # ------------------------------------------------------------------------------------------------ eviction
     @torch.no_grad()
-    def run(self, prompts, new_tokens):
+    def _evict(self, slot: int, park_on_host: bool):
+        """Takes a running stream out of its slot: its whole recurrent state (C, n, m of every block -- constant size, no
+        cache that grows) and its pending token are copied to a parking buffer, the slot is marked inactive."""
+        def park(t):
+            return t.to("cpu", non_blocking=False) if park_on_host else t.clone()
+        parcel = ({i: tuple(park(x[slot]) for x in self.state[i]) for i in self.state}, park(self.tok[slot]))
+        if self.slot_map is not None:
+            self.slot_map[slot] = -1
+        return parcel
+
+    @torch.no_grad()
+    def _resume(self, slot: int, parcel) -> None:
+        st, tok = parcel
+        for i, parts in st.items():
+            for dst, src in zip(self.state[i], parts):
+                dst[slot].copy_(src.to(dst.device))
+        self.tok[slot].copy_(tok.to(self.tok.device))
+        if self.slot_map is not None:
+            self.slot_map[slot] = slot
+
+    @torch.no_grad()
+    def run(self, prompts, new_tokens, quantum: Optional[int] = None, park_on_host: bool = False):
         """prompts: sequence of 1-D int64 tensors; new_tokens: int or per-document counts (>= 1).  Returns the list of
-        generated token tensors in the order of ``prompts``."""
+        generated token tensors in the order of ``prompts``.
+
+        ``quantum``: with documents waiting and no slot free, a stream that has decoded ``quantum`` tokens since it was
+        (re)admitted is EVICTED -- state and pending token parked (on the device, or on the host with ``park_on_host``) --
+        and queues up behind the waiting documents; it later resumes from the parked state in whatever slot is free,
+        without a second prefill.  Tokens are the same with and without eviction."""
         counts = [int(new_tokens)] * len(prompts) if isinstance(new_tokens, int) else [int(x) for x in new_tokens]
         if len(counts) != len(prompts) or any(c < 1 for c in counts):
             raise ValueError("one positive token count per prompt")
+        if quantum is not None and quantum < 1:
+            raise ValueError("quantum must be positive")
         queue = list(range(len(prompts)))[::-1]
-        active = {}          # slot -> [document, tokens still to produce, position of its first token in `hist`]
+        parked = {}          # document -> parcel of an evicted stream
+        left = dict(enumerate(counts))   # document -> tokens still to produce
+        active = {}          # slot -> [document, position of the first token of this residency in `hist`, steps in this residency]
         hist = []            # token column of every step (device tensors; read back once at the end)
-        spans = {}           # document -> (slot, first, count)
+        spans = {d: [] for d in range(len(prompts))}   # document -> [(slot, first, count)] in order
+        self.evictions = 0
         while queue or active:
             if queue and self.slots.free:
-                batch = []
+                fresh, back = [], []
                 while queue and self.slots.free:
                     d = queue.pop()
-                    batch.append((self.slots.acquire(d), d))
-                self._admit([s_ for s_, _ in batch], [prompts[d] for _, d in batch])
-                for s_, d in batch:
-                    active[s_] = [d, counts[d], len(hist)]
+                    (back if d in parked else fresh).append((self.slots.acquire(d), d))
+                if fresh:
+                    self._admit([s_ for s_, _ in fresh], [prompts[d] for _, d in fresh])
+                for s_, d in back:
+                    self._resume(s_, parked.pop(d))
+                for s_, d in fresh + back:
+                    active[s_] = [d, len(hist), 0]
             hist.append(self.tok[:, 0].clone())      # the token every active slot has just produced
             freed = []
             for s_ in list(active):
-                active[s_][1] -= 1
-                if active[s_][1] == 0:
-                    d, _, first = active.pop(s_)
-                    spans[d] = (s_, first, counts[d])
+                d = active[s_][0]
+                left[d] -= 1
+                active[s_][2] += 1
+                if left[d] == 0:
+                    _, first, n = active.pop(s_)
+                    spans[d].append((s_, first, n))
                     self.slots.release(s_)
                     freed.append(s_)
             if freed and self.slot_map is not None:
                 self.slot_map.index_fill_(0, torch.tensor(freed, dtype=torch.long, device=self.model.device), -1)
             if active:
                 self._step()
+            # eviction: between steps, with nothing in flight for the stream (its state and next token are complete)
+            if quantum is not None and queue and not self.slots.free:
+                waiting = len(queue)
+                for s_ in sorted(active, key=lambda k: -active[k][2]):
+                    if waiting == 0 or active[s_][2] < quantum:
+                        break
+                    d, first, n = active.pop(s_)
+                    spans[d].append((s_, first, n))
+                    parked[d] = self._evict(s_, park_on_host)
+                    self.slots.release(s_)
+                    queue.insert(0, d)          # behind every document that is waiting now
+                    self.evictions += 1
+                    waiting -= 1
         cols = torch.stack(hist, dim=1).cpu()          # (slots, steps)
         if self.model.device.type == "cuda" and self.model.cell is ops:
             ops.check_device_status(self.model.device)
-        return [cols[spans[d][0], spans[d][1]:spans[d][1] + spans[d][2]].clone() for d in range(len(prompts))]
+        return [torch.cat([cols[s_, first:first + n] for s_, first, n in spans[d]]).clone() for d in range(len(prompts))]
