@@ -1,7 +1,7 @@
 """The host-side mirror of the reference's xLSTM-Large model.
 
 CPU: with the CPU oracle as its cell, the mirror must reproduce the golden outputs of the unchanged reference
-model (tests/golden/make_golden_model.py, BASELINE config 1), and two gloo ranks in head-parallel mode must
+model (tests/golden/make_golden_model.py: 512 features, 4 heads, 6 blocks), and two gloo ranks in head-parallel mode must
 reproduce the single-rank logits.  GPU: the same golden with the CUDA kernels as the cell."""
 import os
 import random

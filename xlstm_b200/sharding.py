@@ -1,8 +1,8 @@
 """Host-side planning for packed ragged batches and their data-parallel sharding.
 
 The recurrent cells need no exchange between documents, so a multi-GPU run splits DOCUMENTS over ranks and
-uses no collective on the data path (BASELINE config 5: 512 documents, log-normal lengths, rows of 32768
-tokens).  Everything here is plain Python on the host; the kernels only ever see `cu_seqlens`.
+uses no collective on the data path (the continuous-batching workload: 512 documents, log-normal lengths, rows of
+32768 tokens).  Everything here is plain Python on the host; the kernels only ever see `cu_seqlens`.
 """
 from __future__ import annotations
 
