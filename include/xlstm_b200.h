@@ -268,20 +268,6 @@ typedef struct xl_headwise_params {
 
 int xl_headwise_proj(const xl_headwise_params* p, void* cuda_stream);
 
-/* y[m, :] = W x[m, :] for M <= 32 rows of x: the linear layers of one decode step (`nn.Linear` without bias:
- * xlstm/xlstm_large/model.py:268-277 feed-forward, 383-396 q/k/v/gate projections, 443-449 out_proj, 144-151 lm_head) as a
- * kernel that streams the weight matrix once.  bf16 operands, fp32 accumulation, one rounding to bf16. */
-typedef struct xl_gemv_params {
-  const void* x;     /* (M, K) through x_rs */
-  const void* w;     /* (N, K) through w_rs: nn.Linear.weight, or a row/column slice of one */
-  void* y;           /* (M, N) through y_rs */
-  int32_t M, N, K;   /* M <= 32 (more returns XL_ERR_TOO_LARGE: use a GEMM); K a multiple of 8 */
-  int64_t x_rs, w_rs, y_rs;   /* row strides in elements; x_rs and w_rs multiples of 8 */
-  int32_t dtype;     /* XL_BF16 */
-} xl_gemv_params;
-
-int xl_decode_gemv(const xl_gemv_params* p, void* cuda_stream);
-
 /* ------------------------------------------------------------------------------------------------
  * Tensor-parallel decode: x_out = x + sum over ranks of partial, normed = RMSNorm(x_out) * weight, in ONE kernel over peer
  * memory.  (The reference has no tensor parallelism; this fuses what follows its row-parallel projections

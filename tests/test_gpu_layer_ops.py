@@ -245,27 +245,3 @@ def test_headwise_proj_kernel_matches_oracle(rows, NH, DH, nslots):
         got3 = xlstm_b200.headwise_proj([x.cuda().view(2, rows // 2, D)], [ws[0].cuda()])
         assert got3.shape == (2, rows // 2, D)
         assert torch.equal(got3.reshape(rows, D), xlstm_b200.headwise_proj([x.cuda()], [ws[0].cuda()]))
-
-
-@pytest.mark.parametrize("M,N,K,w_cols", [(8, 12304, 4096, 4096), (8, 4096, 10944, 10944), (3, 50304, 4096, 4096), (17, 100, 136, 136),
-                                          (1, 16, 8, 8), (8, 512, 1368, 10944), (32, 72, 4096, 4096), (8, 21, 64, 64)])
-def test_decode_linear_kernel_matches_linear_in_fp32(M, N, K, w_cols):
-    """The weight-streaming kernel of the decode step's linear layers against fp32 ``x @ W.T`` of the same bf16 operands,
-    rounded once: feature counts that are no multiple of 16, a contraction that is no multiple of 32, more than one 8-row
-    tile of x, a weight that is a column slice of a wider matrix (tensor-parallel down-projection)."""
-    import xlstm_b200
-    g = torch.Generator().manual_seed(M * 31 + N + K)
-    x = torch.randn(2, M, K, generator=g).bfloat16()[0]
-    wide = (torch.randn(N, w_cols, generator=g) / K ** 0.5).bfloat16()
-    w = wide[:, w_cols - K:]
-    want = (x.float() @ w.float().T).bfloat16().float()
-    got = xlstm_b200.decode_linear(x.cuda(), wide.cuda()[:, w_cols - K:]).float().cpu()
-    assert got.shape == (M, N)
-    diff = (got - want).abs()
-    assert (diff <= want.abs() * 2.0 ** -7 + 1e-4).all(), float(diff.max())
-    assert rel_l2(got, want) < 2e-3
-    # leading dimensions are kept
-    if M % 2 == 0:
-        assert xlstm_b200.decode_linear(x.cuda().view(2, M // 2, K), wide.cuda()[:, w_cols - K:]).shape == (2, M // 2, N)
-    with pytest.raises(ValueError):
-        xlstm_b200.decode_linear(torch.zeros(33, K, dtype=torch.bfloat16, device="cuda"), wide.cuda()[:, w_cols - K:])

@@ -18,7 +18,7 @@ EXPORTS = (
     "xl_mlstm_chunkwise", "xl_mlstm_recurrent", "xl_mlstm_step", "xl_slstm_forward",
     "xl_add_rmsnorm", "xl_headnorm_gate", "xl_soft_cap", "xl_causal_conv1d",
     "xl_softcap_argmax", "xl_softcap_argmax_scratch_bytes", "xl_swiglu",
-    "xl_softcap_argmax_noalloc", "xl_softcap_argmax_noalloc_max_rows", "xl_peer_reduce_add_rmsnorm", "xl_headwise_proj", "xl_decode_gemv",
+    "xl_softcap_argmax_noalloc", "xl_softcap_argmax_noalloc_max_rows", "xl_peer_reduce_add_rmsnorm", "xl_headwise_proj",
 )
 
 
@@ -107,15 +107,6 @@ class HeadwiseParams(C.Structure):
         ("in_sel", C.c_int32 * 4),
         ("rows", C.c_int64), ("NH", C.c_int32), ("DH", C.c_int32), ("n_slots", C.c_int32), ("dtype", C.c_int32),
         ("x_row_stride", C.c_int64 * 2), ("out_row_stride", C.c_int64),
-    ]
-
-
-class GemvParams(C.Structure):
-    _fields_ = [
-        ("x", C.c_void_p), ("w", C.c_void_p), ("y", C.c_void_p),
-        ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
-        ("x_rs", C.c_int64), ("w_rs", C.c_int64), ("y_rs", C.c_int64),
-        ("dtype", C.c_int32),
     ]
 
 

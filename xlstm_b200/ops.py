@@ -12,7 +12,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
-from ._lib import (AddRmsnormParams, Conv1dParams, GemvParams, HeadwiseParams, GreedyParams, HeadnormGateParams, MlstmSeqParams, MlstmStepParams, SlstmParams, SoftCapParams, SwigluParams, XL_BF16, XL_F32,
+from ._lib import (AddRmsnormParams, Conv1dParams, HeadwiseParams, GreedyParams, HeadnormGateParams, MlstmSeqParams, MlstmStepParams, SlstmParams, SoftCapParams, SwigluParams, XL_BF16, XL_F32,
                    check, lib)
 
 _DTYPES = {torch.float32: XL_F32, torch.bfloat16: XL_BF16}
@@ -461,41 +461,6 @@ def causal_conv1d(x, weight, bias=None, cu_seqlens=None, silu: bool = True):
     with torch.cuda.device(x.device):
         check(lib().xl_causal_conv1d(C.byref(p), _stream_ptr(x.device)), "xl_causal_conv1d")
     return out
-
-
-DECODE_LINEAR_MAX_ROWS = 32
-
-
-def decode_linear_ok(x, weight) -> bool:
-    """Whether `decode_linear` takes this pair (a few bf16 rows on the GPU, 16-byte aligned rows)."""
-    rows = x.numel() // max(1, x.shape[-1])
-    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.dim() == 2
-            and 1 <= rows <= DECODE_LINEAR_MAX_ROWS and x.shape[-1] == weight.shape[1] and weight.shape[1] % 8 == 0
-            and weight.stride(1) == 1 and weight.stride(0) % 8 == 0 and weight.data_ptr() % 16 == 0)
-
-
-def decode_linear(x, weight):
-    """``F.linear(x, weight)`` (no bias) for at most 32 rows of x: the projections of one decode step (``nn.Linear`` of
-    xlstm/xlstm_large/model.py:268-277, 383-396, 443-449, 144-151) as a kernel that streams the weights once.
-    x (..., K) bfloat16, weight (N, K) bfloat16 (rows may be strided: a slice of a larger matrix); returns (..., N)."""
-    _require_cuda(x, weight)
-    if not decode_linear_ok(x, weight):
-        raise ValueError("decode_linear: bfloat16 x with at most 32 rows and a bfloat16 (N, K) weight with K % 8 == 0 and "
-                         "16-byte aligned rows")
-    K = x.shape[-1]
-    x2 = _last_contig(x).reshape(-1, K)
-    if x2.stride(0) % 8 != 0 or x2.data_ptr() % 16 != 0:
-        x2 = x2.contiguous()
-    M, N = x2.shape[0], weight.shape[0]
-    y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
-    p = GemvParams()
-    p.x, p.w, p.y = x2.data_ptr(), weight.data_ptr(), y.data_ptr()
-    p.M, p.N, p.K = M, N, K
-    p.x_rs, p.w_rs, p.y_rs = x2.stride(0), weight.stride(0), y.stride(0)
-    p.dtype = _DTYPES[torch.bfloat16]
-    with torch.cuda.device(x.device):
-        check(lib().xl_decode_gemv(C.byref(p), _stream_ptr(x.device)), "xl_decode_gemv")
-    return y.reshape(*x.shape[:-1], N)
 
 
 def headwise_proj(inputs, weights, in_sel=None):
