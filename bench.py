@@ -16,6 +16,7 @@ prints one of them as a line of its own:
   step          mLSTM decode step, 256 streams x 8 heads (xLSTM-7B head shapes), state resident in HBM
   slstm         sLSTM forward at the block-stack benchmark's cell shape (B=16, S=2048, NH=4, DH=256), next to the
                 reference's own CUDA backend when the reference package is present
+  headwise      the four headwise gate projections + concatenation of the sLSTM layer at the same shape
   layer_ops     residual add + RMSNorm and per-head norm + output gate at the 7B prefill shapes
   chunkwise_b1  the headline kernel on one sequence (B=1): the size used for profiler captures
   model7b       the xLSTM-7B-shaped model (random init, bf16): prefill 8 x 8192 + 512 greedy tokens, strong scaling
@@ -332,6 +333,30 @@ def build_case(name, dev, rank):
                     l2="inputs (%d MB) exceed the 126 MB L2" % (slstm_bytes(**cfg) // 10 ** 6), launches=1,
                     traffic=323.9e6, traffic_source="constant: ncu dram__bytes_read.sum + dram__bytes_write.sum of ONE captured launch of this workload, not measured in this run",
                     extra=lambda m: {**slstm_reference_cuda(cfg, dev, m["kernel_ms"]), **slstm_gate_projections(cfg, dev)})
+    if name == "headwise":
+        # the four headwise gate projections + concatenation in front of the sLSTM cell, at the cell's benchmark shape
+        cfg = dict(SLSTM_CFG)
+        B, S, NH, DH = cfg["B"], cfg["S"], cfg["NH"], cfg["DH"]
+        D = NH * DH
+        g = torch.Generator().manual_seed(5 + rank)
+        host = [torch.randn(B, S, D, generator=g).bfloat16().pin_memory() for _ in range(2)]
+        x, xc = [t.to(dev) for t in host]
+        ws = [(torch.randn(NH, DH, DH, generator=g) / DH ** 0.5).bfloat16().to(dev) for _ in range(4)]
+        out_host = torch.empty(B, S, 4 * D, dtype=torch.bfloat16).pin_memory()
+
+        def step():
+            return xlstm_b200.headwise_proj([x, xc], ws, [1, 1, 0, 0])
+
+        def e2e_step():
+            xd, xcd = [t.to(dev, non_blocking=True) for t in host]
+            out_host.copy_(xlstm_b200.headwise_proj([xd, xcd], ws, [1, 1, 0, 0]), non_blocking=True)
+
+        nbytes = (2 + 4) * B * S * D * 2 + 4 * NH * DH * DH * 2
+        return dict(step=step, e2e_step=e2e_step, units=B * S, unit="tokens/s", metric="slstm_gate_projections_tokens_per_s",
+                    workload="slstm_layer_gate_projections_config3", cfg=cfg, bytes=nbytes, flops=2 * 4 * B * S * NH * DH * DH,
+                    kernel="headwise_proj_kernel<256>", h2d=2 * B * S * D * 2, d2h=4 * B * S * D * 2,
+                    l2="operands (%d MB per step) exceed the 126 MB L2" % (nbytes // 10 ** 6), launches=1,
+                    traffic=None, traffic_source="not captured")
     if name == "layer_ops":
         # the two fused operators next to the cell, at the 7B layer's prefill shapes (8 x 8192 tokens, D = 4096)
         B, S, NH, DH = 8, 8192, 8, 512
@@ -606,7 +631,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--case", default="all", choices=["all", "chunkwise", "chunkwise_b1", "step", "slstm", "layer_ops", "model7b", "decode7b", "continuous7b"])
+    ap.add_argument("--case", default="all", choices=["all", "chunkwise", "chunkwise_b1", "step", "slstm", "headwise", "layer_ops", "model7b", "decode7b", "continuous7b"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="profiling runs: device-resident loop only")
     args = ap.parse_args()

@@ -10,7 +10,8 @@
 // products run while this one's result leaves); the epilogue warps round to bf16, stage 64-column boxes in shared memory
 // and hand them to TMA stores.  Weights (a few MB) stay L2-resident; the kernel is bound by the output stream.
 //
-// Warp roles: 0 TMA loads, 1 UMMA issue (+ tensor-memory allocation), 2..5 epilogue (tensor-memory lane = row).
+// Warp roles: 0 TMA loads, 1 UMMA issue (+ tensor-memory allocation), 2..5 and 6..9 two epilogue groups (tensor-memory
+// lane = row; a group takes every other 64-column box of a result, with its own staging boxes and store queue).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -19,7 +20,7 @@ namespace xl {
 
 constexpr int HW_ROWS = 128;      // rows per CTA (UMMA M)
 constexpr int HW_STAGES = 3;
-constexpr int HW_THREADS = 192;
+constexpr int HW_THREADS = 320;    // 10 warps: TMA, UMMA, two epilogue groups of four
 constexpr int HW_A_BYTES = HW_ROWS * 128;   // [128 rows x 64 bf16]
 
 struct HwMaps {
@@ -31,8 +32,8 @@ struct HwLayout {
   static constexpr int KB = DH / 64;                 // 64-feature blocks of the contraction (and of the output columns)
   static constexpr int B_BYTES = DH * 128;           // [DH rows x 64 bf16]
   static constexpr int STAGE_BYTES = HW_A_BYTES + B_BYTES;
-  static constexpr int OFF_OUT = HW_STAGES * STAGE_BYTES;     // 2 x [128 x 64] bf16 staging boxes of the result
-  static constexpr int OFF_BAR = OFF_OUT + 2 * HW_A_BYTES;
+  static constexpr int OFF_OUT = HW_STAGES * STAGE_BYTES;     // 2 groups x 2 x [128 x 64] bf16 staging boxes of the result
+  static constexpr int OFF_BAR = OFF_OUT + 4 * HW_A_BYTES;
   static constexpr int NBAR = 2 * HW_STAGES + 4;     // full, empty per stage; accumulator full / empty x 2
   static constexpr int TOTAL = OFF_BAR + NBAR * 8 + 16;
   static constexpr int DYN_SMEM = TOTAL + 1024;
@@ -52,7 +53,7 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src_smem
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_sync(int group) { asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory"); }
 
 template <int DH>
 __global__ void __launch_bounds__(HW_THREADS, 1) headwise_proj_kernel(const __grid_constant__ HwMaps maps, const xl_headwise_params p) {
@@ -76,7 +77,7 @@ __global__ void __launch_bounds__(HW_THREADS, 1) headwise_proj_kernel(const __gr
 
   if (tid == 0) {
     for (int s = 0; s < HW_STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(bar_acc_full(a), 1); mbar_init(bar_acc_empty(a), 128); }
+    for (int a = 0; a < 2; ++a) { mbar_init(bar_acc_full(a), 1); mbar_init(bar_acc_empty(a), 256); }
     fence_barrier_init();
     tma_prefetch_desc(&maps.x[0]); tma_prefetch_desc(&maps.out);
   }
@@ -138,23 +139,25 @@ __global__ void __launch_bounds__(HW_THREADS, 1) headwise_proj_kernel(const __gr
     // ================================================================================ epilogue
     const int q = warp & 3;                       // tensor-memory lane quarter this warp can read
     const int r = q * 32 + lane;                  // row of the tile
-    const int te = tid - 64;                      // 0..127
+    const int grp = (warp - 2) >> 2;              // epilogue group 0 / 1
+    const int te = (tid - 64) & 127;              // thread within the group
     const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+    const uint32_t stage0 = LY::OFF_OUT + grp * 2 * HW_A_BYTES;
     int box = 0;
     for (int slot = 0; slot < nslots && ok; ++slot) {
       if (!mbar_wait(bar_acc_full(slot & 1), (uint32_t)(slot >> 1) & 1u)) { ok = false; break; }
       tc_fence_after();
       const uint32_t acc = tmem + lane_base + (uint32_t)(slot & 1) * DH;
 #pragma unroll 1
-      for (int cb = 0; cb < KB; ++cb, ++box) {
+      for (int cb = (KB > 1 ? grp : 0); cb < (KB > 1 || grp == 0 ? KB : 0); cb += (KB > 1 ? 2 : 1), ++box) {
         uint32_t v0[32], v1[32];
         tmem_ld_x32(acc + cb * 64, v0);
         tmem_ld_x32(acc + cb * 64 + 32, v1);
         tc_wait_ld();
-        // the staging box used two boxes ago must have been read by its TMA store
+        // the staging box this group used two boxes ago must have been read by its TMA store
         if (te == 0) tma_store_wait_read<1>();
-        epilogue_sync();
-        unsigned char* stg = smem + LY::OFF_OUT + (box & 1) * HW_A_BYTES + r * 128;
+        epilogue_sync(grp);
+        unsigned char* stg = smem + stage0 + (box & 1) * HW_A_BYTES + r * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {   // 16-byte pieces of the row's 64 columns, swizzled like a TMA box
           const uint32_t* src = (c < 4) ? &v0[8 * c] : &v1[8 * (c - 4)];
@@ -166,9 +169,9 @@ __global__ void __launch_bounds__(HW_THREADS, 1) headwise_proj_kernel(const __gr
           *reinterpret_cast<uint4*>(stg + ((c ^ (r & 7)) << 4)) = w;
         }
         fence_proxy_async_smem();
-        epilogue_sync();
+        epilogue_sync(grp);
         if (te == 0) {
-          tma_store_2d(&maps.out, sbase + LY::OFF_OUT + (box & 1) * HW_A_BYTES, (slot * p.NH + head) * DH + cb * 64, row0);
+          tma_store_2d(&maps.out, sbase + stage0 + (box & 1) * HW_A_BYTES, (slot * p.NH + head) * DH + cb * 64, row0);
           tma_store_commit();
         }
       }
