@@ -222,9 +222,11 @@ def test_headwise_proj_kernel_matches_reference_modules_fixture(tag):
     _close(got, want.float(), torch.bfloat16)
 
 
-@pytest.mark.parametrize("rows,NH,DH,nslots", [(16 * 2048 // 8, 4, 256, 4), (1, 4, 256, 4), (129, 2, 128, 3), (300, 5, 64, 1), (127, 1, 256, 2)])
+@pytest.mark.parametrize("rows,NH,DH,nslots", [(16 * 2048 // 8, 4, 256, 4), (1, 4, 256, 4), (129, 2, 128, 3), (300, 5, 64, 1), (127, 1, 256, 2),
+                                                 (300, 2, 128, 4), (641, 1, 256, 4)])
 def test_headwise_proj_kernel_matches_oracle(rows, NH, DH, nslots):
-    """Row counts around the 128-row tile, all three block sizes, fewer than four slots, a strided second input."""
+    """Row counts around the 128-row tile (pairs of tiles share the weight tiles from 129 rows on: an odd number of tiles
+    leaves half a pair empty), all three block sizes, fewer than four slots, a strided second input."""
     import xlstm_b200
     g = torch.Generator().manual_seed(rows + NH + DH)
     D = NH * DH

@@ -179,6 +179,44 @@ __device__ __forceinline__ void umma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uin
       : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------
+// Pairs of CTAs (cluster of two) driving cta_group::2 UMMAs: one thread of the leader CTA issues; each CTA supplies its own
+// A rows and HALF of the B rows (N/2, in rank order) from the same shared-memory offsets, and receives its own rows of
+// the accumulator.  Tensor memory is allocated per CTA (cta_group::1) -- both get the same base when each takes all of it.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+  uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank)); return r;
+}
+// arrival on a barrier of another CTA of the cluster (CTA-scope release, as consumer-release barriers of 2-CTA pipelines
+// use it: what the arrival orders is consumed by the arriving CTA's own tensor core; a cluster-scope release costs
+// 750-1500 cycles per arrival here)
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void umma2_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %5};\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "n"(UMMA_DESC_HI_SW128)
+      : "memory");
+}
+// arrives (count 1) on the barrier at this offset in BOTH CTAs of the pair when all UMMAs issued before have completed
+__device__ __forceinline__ void umma2_commit_both(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t}" ::"r"(bar), "h"((uint16_t)3)
+      : "memory");
+}
+
 // Instruction descriptor for kind::f16 with bf16 operands and fp32 accumulation.
 // a_mn / b_mn: operand is MN-major (1) or K-major (0) in shared memory.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, int a_mn, int b_mn) {

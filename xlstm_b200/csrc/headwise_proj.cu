@@ -188,6 +188,202 @@ __global__ void __launch_bounds__(HW_THREADS, 1) headwise_proj_kernel(const __gr
 }
 
 // ---------------------------------------------------------------------------------------------
+// Pair variant: two CTAs (two neighbouring 128-row tiles of one head) form a cluster and share every weight tile -- each
+// loads only HALF of it (DH/2 rows) and one cta_group::2 UMMA (M = 256, N = DH) of the leader drives both tensor cores,
+// each on its own rows.  That takes a third off the L2 -> shared-memory traffic, which bounds this kernel (weights are
+// re-read by every row tile).  With N = DH >= 128 the pair instruction runs at the rate of the single-CTA one.
+// The other CTA's warp 1 forwards "stage landed" to the leader; accumulator-free arrivals come one per warp.
+// ---------------------------------------------------------------------------------------------
+constexpr int HWP_STAGES = 4;
+
+template <int DH>
+struct HwPairLayout {
+  static constexpr int KB = DH / 64;
+  static constexpr int B_BYTES = (DH / 2) * 128;     // this CTA's half of the [DH x 64] weight tile
+  static constexpr int STAGE_BYTES = HW_A_BYTES + B_BYTES;
+  static constexpr int OFF_OUT = HWP_STAGES * STAGE_BYTES;
+  static constexpr int OFF_BAR = OFF_OUT + 4 * HW_A_BYTES;
+  static constexpr int NBAR = 3 * HWP_STAGES + 4;    // full, empty, peer-full per stage; accumulator full / empty x 2
+  static constexpr int TOTAL = OFF_BAR + NBAR * 8 + 16;
+  static constexpr int DYN_SMEM = TOTAL + 1024;
+  static constexpr uint32_t TMEM_COLS = 2 * DH >= 512 ? 512 : (2 * DH >= 256 ? 256 : 128);
+};
+
+template <int DH>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(HW_THREADS, 1)
+headwise_proj_pair_kernel(const __grid_constant__ HwMaps maps, const xl_headwise_params p) {
+  using LY = HwPairLayout<DH>;
+  constexpr int KB = LY::KB;
+  extern __shared__ unsigned char hw_smem_raw[];
+  unsigned char* smem = hw_smem_raw + ((1024u - (smem_u32(hw_smem_raw) & 1023u)) & 1023u);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + LY::OFF_BAR;
+  auto bar_full = [&](int s) { return bar0 + 8u * (uint32_t)s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (uint32_t)(HWP_STAGES + s); };
+  auto bar_pfull = [&](int s) { return bar0 + 8u * (uint32_t)(2 * HWP_STAGES + s); };       // leader: the other CTA's stage landed
+  auto bar_acc_full = [&](int a) { return bar0 + 8u * (uint32_t)(3 * HWP_STAGES + a); };
+  auto bar_acc_empty = [&](int a) { return bar0 + 8u * (uint32_t)(3 * HWP_STAGES + 2 + a); };  // leader: 8 warps of each CTA
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + LY::OFF_BAR + LY::NBAR * 8);
+
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+  const uint32_t rank = cluster_ctarank();
+  const int nslots = p.n_slots;
+  // persistent: the pair walks work items (pair of row tiles, head); the rings of stages and accumulators run on across
+  // items, so loads, products and stores of neighbouring items overlap
+  const int n_pairs = (int)((p.rows + 2 * HW_ROWS - 1) / (2 * HW_ROWS));
+  const int total_items = n_pairs * p.NH, n_clusters = (int)gridDim.x / 2, first_item = (int)blockIdx.x / 2;
+  auto item_row0 = [&](int item) { return ((item / p.NH) * 2 + (int)rank) * HW_ROWS; };
+  auto item_head = [&](int item) { return item % p.NH; };
+  bool ok = true;
+
+  if (tid == 0) {
+    for (int s = 0; s < HWP_STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); mbar_init(bar_pfull(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(bar_acc_full(a), 1); mbar_init(bar_acc_empty(a), 16); }
+    fence_barrier_init();
+    tma_prefetch_desc(&maps.x[0]); tma_prefetch_desc(&maps.out);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(smem_u32(s_tmem), LY::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  cluster_sync_all();   // barriers and tensor memory of BOTH CTAs exist before anything crosses over
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+  const uint32_t lead_bar0 = mapa_u32(bar0, 0);
+
+  if (warp == 0) {
+    // ================================================================================ TMA loads (each CTA its own)
+    if (lane == 0) {
+      int it = 0;
+      for (int item = first_item; item < total_items && ok; item += n_clusters) {
+        const int row0 = item_row0(item), head = item_head(item);
+        for (int slot = 0; slot < nslots && ok; ++slot) {
+          const CUtensorMap* xm = &maps.x[p.in_sel[slot] ? 1 : 0];
+          for (int kb = 0; kb < KB; ++kb, ++it) {
+            const int st = it % HWP_STAGES;
+            if (!mbar_wait(bar_empty(st), ((uint32_t)(it / HWP_STAGES) & 1u) ^ 1u)) { ok = false; break; }
+            const uint32_t dst = sbase + st * LY::STAGE_BYTES;
+            mbar_expect_tx(bar_full(st), LY::STAGE_BYTES);
+            tma_load_2d(dst, xm, bar_full(st), head * DH + kb * 64, row0);
+            tma_load_2d(dst + HW_A_BYTES, &maps.w[slot], bar_full(st), kb * 64, head * DH + (int)rank * (DH / 2));
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (__shfl_sync(0xffffffffu, rank, 0) == 0) {
+      // ============================================================================== UMMA issue (leader of the pair)
+      constexpr uint32_t IDESC = umma_idesc_bf16(2 * HW_ROWS, DH, 0, 0);
+      constexpr uint32_t LBO_K = (16u >> 4) << 16;
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0), sbase_u = __shfl_sync(0xffffffffu, sbase, 0) & 0x3FFFFu;
+      int n_items = 0;
+      for (int item = first_item; item < total_items; item += n_clusters) ++n_items;
+      const int nslots_u = __shfl_sync(0xffffffffu, nslots * n_items, 0);   // accumulator uses of this pair, all items
+      bool okm = true;
+      int it = 0;
+#pragma unroll 1
+      for (int slot = 0; slot < nslots_u; ++slot) {
+        const uint32_t acc = tmem_u + (uint32_t)(slot & 1) * DH;
+        okm = okm && mbar_wait(bar_acc_empty(slot & 1), ((uint32_t)(slot >> 1) & 1u) ^ 1u);
+        tc_fence_after();
+#pragma unroll 1
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int st = it % HWP_STAGES;
+          okm = okm && mbar_wait(bar_full(st), (uint32_t)(it / HWP_STAGES) & 1u);
+          okm = okm && mbar_wait(bar_pfull(st), (uint32_t)(it / HWP_STAGES) & 1u);
+          tc_fence_after();
+          const uint32_t a = sbase_u + st * LY::STAGE_BYTES, b = a + HW_A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma2_ss_lo(acc, LBO_K + ((a + kk * 32) >> 4), LBO_K + ((b + kk * 32) >> 4), IDESC, (kb | kk) != 0);
+          umma2_commit_both(bar_empty(st));   // both CTAs may refill the stage when these products have read it
+        }
+        umma2_commit_both(bar_acc_full(slot & 1));
+      }
+      ok = okm;
+    } else {
+      // ============================================================================== the other CTA: forward "stage landed"
+      if (lane == 0) {
+        int n_items = 0;
+        for (int item = first_item; item < total_items; item += n_clusters) ++n_items;
+        const int total_it = nslots * KB * n_items;
+        for (int it = 0; it < total_it; ++it) {
+          const int st = it % HWP_STAGES;
+          if (!mbar_wait(bar_full(st), (uint32_t)(it / HWP_STAGES) & 1u)) { ok = false; break; }
+          mbar_arrive_remote(lead_bar0 + 8u * (uint32_t)(2 * HWP_STAGES + st));
+        }
+      }
+      __syncwarp();
+    }
+  } else {
+    // ================================================================================ epilogue (each CTA its own rows)
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const int grp = (warp - 2) >> 2;
+    const int te = (tid - 64) & 127;
+    const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+    const uint32_t stage0 = LY::OFF_OUT + grp * 2 * HW_A_BYTES;
+    int box = 0, gs = 0;   // staging boxes and accumulator uses so far, all items
+    for (int item = first_item; item < total_items && ok; item += n_clusters) {
+    const int row0 = item_row0(item), head = item_head(item);
+    for (int slot = 0; slot < nslots && ok; ++slot, ++gs) {
+      if (!mbar_wait(bar_acc_full(gs & 1), (uint32_t)(gs >> 1) & 1u)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t acc = tmem + lane_base + (uint32_t)(gs & 1) * DH;
+      // this group's boxes of the result (every other 64-column box): all of them out of tensor memory first, so that the
+      // accumulator goes back to the UMMA issuer before the staging and the stores start
+      constexpr int NBX = KB / 2;   // KB >= 2 here (DH >= 128)
+      uint32_t v[NBX][64];
+#pragma unroll
+      for (int i = 0; i < NBX; ++i) {
+        tmem_ld_x32(acc + (2 * i + grp) * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[i][0]));
+        tmem_ld_x32(acc + (2 * i + grp) * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[i][32]));
+      }
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {   // one arrival per warp on the leader's barrier
+        if (rank == 0) mbar_arrive(bar_acc_empty(gs & 1));
+        else mbar_arrive_remote(lead_bar0 + 8u * (uint32_t)(3 * HWP_STAGES + 2 + (gs & 1)));
+      }
+#pragma unroll
+      for (int i = 0; i < NBX; ++i, ++box) {
+        const int cb = 2 * i + grp;
+        if (te == 0) tma_store_wait_read<1>();   // the staging box used two boxes ago has been read by its store
+        epilogue_sync(grp);
+        unsigned char* stg = smem + stage0 + (box & 1) * HW_A_BYTES + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(v[i][8 * c + 0]), __uint_as_float(v[i][8 * c + 1]));
+          w.y = pack_bf16x2(__uint_as_float(v[i][8 * c + 2]), __uint_as_float(v[i][8 * c + 3]));
+          w.z = pack_bf16x2(__uint_as_float(v[i][8 * c + 4]), __uint_as_float(v[i][8 * c + 5]));
+          w.w = pack_bf16x2(__uint_as_float(v[i][8 * c + 6]), __uint_as_float(v[i][8 * c + 7]));
+          *reinterpret_cast<uint4*>(stg + ((c ^ (r & 7)) << 4)) = w;
+        }
+        fence_proxy_async_smem();
+        epilogue_sync(grp);
+        if (te == 0 && row0 < p.rows) {
+          tma_store_2d(&maps.out, sbase + stage0 + (box & 1) * HW_A_BYTES, (slot * p.NH + head) * DH + cb * 64, row0);
+          tma_store_commit();
+        }
+      }
+    }
+    }
+    if (te == 0) tma_store_wait_all();
+  }
+
+  if (!ok && p.status) atomicExch(p.status, 1);
+  tc_fence_before();
+  cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while the other may still reach into it
+  if (warp == 1) tmem_dealloc(tmem, LY::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 typedef CUresult (*hw_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -224,6 +420,36 @@ static int hw_make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t c
     return XL_ERR_BAD_STRIDE;
   }
   return XL_OK;
+}
+
+template <int DH>
+static int launch_headwise_pair(const HwMaps& maps, const xl_headwise_params* p, cudaStream_t st) {
+  using LY = HwPairLayout<DH>;
+  static_assert(LY::DYN_SMEM <= 227 * 1024, "shared memory budget");
+  auto kern = headwise_proj_pair_kernel<DH>;
+  XL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LY::DYN_SMEM));
+  // persistent pairs: as many clusters as can be resident at once (a tile past the last row loads zeros, stores nothing)
+  const long long items = ((p->rows + 2 * HW_ROWS - 1) / (2 * HW_ROWS)) * (long long)p->NH;
+  int resident = 0;
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * 74);
+    cfg.blockDim = dim3(HW_THREADS);
+    cfg.dynamicSmemBytes = LY::DYN_SMEM;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&resident, kern, &cfg) != cudaSuccess || resident < 1) {
+      (void)cudaGetLastError();
+      cfg.attrs = nullptr; cfg.numAttrs = 0;   // (the kernel carries its cluster shape itself)
+      if (cudaOccupancyMaxActiveClusters(&resident, kern, &cfg) != cudaSuccess || resident < 1) { (void)cudaGetLastError(); resident = 64; }
+    }
+    if (resident > 74) resident = 74;
+  }
+  const unsigned clusters = (unsigned)(items < resident ? items : resident);
+  kern<<<dim3(2 * clusters), HW_THREADS, LY::DYN_SMEM, st>>>(maps, *p);
+  return check_launch("xl_headwise_proj");
 }
 
 template <int DH>
@@ -268,12 +494,15 @@ extern "C" int xl_headwise_proj(const xl_headwise_params* p, void* cuda_stream) 
     const int src = use[i] ? i : (use[0] ? 0 : 1);   // an unused input slot gets a valid map of the other one
     if ((rc = hw_make_map(&maps.x[i], p->x[src], p->rows, D, p->x_row_stride[src], HW_ROWS)) != XL_OK) return rc;
   }
+  // pairs of row tiles share the weight tiles (each CTA loads half of one) where the pair instruction runs at full rate
+  const bool pair = p->DH >= 128 && p->rows > HW_ROWS;
   for (int s = 0; s < 4; ++s) {
     const int src = s < p->n_slots ? s : 0;
-    if ((rc = hw_make_map(&maps.w[s], p->w[src], D, p->DH, p->DH, p->DH)) != XL_OK) return rc;
+    if ((rc = hw_make_map(&maps.w[s], p->w[src], D, p->DH, p->DH, pair ? p->DH / 2 : p->DH)) != XL_OK) return rc;
   }
   if ((rc = hw_make_map(&maps.out, p->out, p->rows, (int64_t)p->n_slots * D, p->out_row_stride, HW_ROWS)) != XL_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  if (pair) return p->DH == 128 ? launch_headwise_pair<128>(maps, p, st) : launch_headwise_pair<256>(maps, p, st);
   switch (p->DH) {
     case 64: return launch_headwise<64>(maps, p, st);
     case 128: return launch_headwise<128>(maps, p, st);
