@@ -104,7 +104,7 @@ __device__ __forceinline__ void stmatrix_x4_trans(uint32_t addr, uint32_t r0, ui
 }
 
 // ---------------------------------------------------------------------------------------------
-// TMA (cp.async.bulk.tensor), no multicast anywhere
+// TMA (cp.async.bulk.tensor): every CTA issues its own plain loads
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap, uint32_t bar, int c0, int c1, int c2,
                                             int c3) {
@@ -208,12 +208,15 @@ __device__ __forceinline__ void umma2_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint
       "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "n"(UMMA_DESC_HI_SW128)
       : "memory");
 }
-// arrives (count 1) on the barrier at this offset in BOTH CTAs of the pair when all UMMAs issued before have completed
+// arrives (count 1) on the barrier at this offset in BOTH CTAs of the pair when all UMMAs issued before have completed:
+// one commit per CTA, each to that CTA's copy of the barrier through the cluster window
 __device__ __forceinline__ void umma2_commit_both(uint32_t bar) {
+  const uint32_t b0 = mapa_u32(bar, 0), b1 = mapa_u32(bar, 1);
   asm volatile(
       "{\n\t.reg .pred q;\n\t"
       "elect.sync _|q, 0xffffffff;\n\t"
-      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t}" ::"r"(bar), "h"((uint16_t)3)
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}" ::"r"(b0), "r"(b1)
       : "memory");
 }
 
