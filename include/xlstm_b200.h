@@ -122,6 +122,24 @@ typedef struct xl_mlstm_step_params {
 
 int xl_mlstm_step(const xl_mlstm_step_params* p, void* cuda_stream);
 
+/* One decode step of the mLSTM LAYER's cell part in one kernel: soft cap of the two gate pre-activations
+ * (xlstm/xlstm_large/model.py:389-394; fp32 arithmetic on the projection's output + bias), the step above, and behind it
+ * the per-head norm, its weight and the output gate (model.py:435-449, components.py:188-242), written as the
+ * (B, NH*DHV) input of out_proj.  `step.igate`, `step.fgate` and `step.h` are not used.  The thread blocks of a head
+ * exchange the norm's partial sums through distributed shared memory (one cluster per (stream, head)): DHV <= 1024. */
+typedef struct xl_mlstm_decode_cell_params {
+  xl_mlstm_step_params step;
+  const void* gates_raw;    /* (B, 2*NH): input-gate pre-activations of all heads, then forget-gate; row stride gr_sb */
+  const void* gate_bias;    /* (2*NH) or NULL */
+  const void* ogate;        /* (B, NH*DHV) output-gate pre-activations; row stride o_sb */
+  const void* norm_weight;  /* (NH*DHV) */
+  void* hg;                 /* out (B, NH*DHV); row stride hg_sb */
+  int64_t gr_sb, o_sb, hg_sb;
+  float gate_cap, norm_eps;
+} xl_mlstm_decode_cell_params;
+
+int xl_mlstm_decode_cell(const xl_mlstm_decode_cell_params* p, void* cuda_stream);
+
 /* ------------------------------------------------------------------------------------------------
  * sLSTM forward over a sequence, one persistent kernel: one thread-block cluster per (head, group of 16 batch
  * rows), each CTA's slice of the recurrent matrix resident in registers as tensor-core fragments, the new h

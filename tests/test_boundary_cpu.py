@@ -31,7 +31,7 @@ def test_struct_layouts_match_header_field_order():
                           ("xl_headnorm_gate_params", _lib.HeadnormGateParams), ("xl_soft_cap_params", _lib.SoftCapParams),
                           ("xl_conv1d_params", _lib.Conv1dParams), ("xl_greedy_params", _lib.GreedyParams),
                           ("xl_swiglu_params", _lib.SwigluParams), ("xl_peer_reduce_params", _lib.PeerReduceParams),
-                          ("xl_headwise_params", _lib.HeadwiseParams)):
+                          ("xl_headwise_params", _lib.HeadwiseParams), ("xl_mlstm_decode_cell_params", _lib.MlstmDecodeCellParams)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), header, re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         body = re.sub(r"\[\d+\]", "", body)   # array members: the name is what counts

@@ -267,3 +267,45 @@ def test_prefill_from_pinned_host_buffers_equals_device_call():
     h, (c, n, m) = xlstm_b200.mlstm_sequence(*_cuda(q, k, v, i, f), kernel="chunkwise")
     assert torch.equal(h_host, h.cpu()) and torch.equal(c_host, c.cpu())
     assert torch.equal(n_host, n.cpu()) and torch.equal(m_host, m.cpu())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B,NH,DQ,DV,with_slots", [(8, 8, 256, 512, False), (5, 3, 64, 128, True), (2, 2, 128, 1024, True), (3, 4, 32, 40, False)])
+def test_fused_decode_cell_equals_cap_step_norm_gate(dtype, B, NH, DQ, DV, with_slots):
+    """One kernel for gate soft cap + cell step + per-head norm + output gate against the three separate kernels: the
+    states bit for bit (same arithmetic), the gated output up to the summation order of the norm's two sums (the thread
+    blocks of a head exchange partial sums through distributed shared memory)."""
+    import xlstm_b200
+    from xlstm_b200 import ops
+    if dtype == torch.float32 and DV > 512:
+        pytest.skip("the separate norm kernel takes at most 512 fp32 columns per head")
+    g = torch.Generator().manual_seed(B * 100 + NH * 10 + DV)
+    rnd = lambda *shape: torch.randn(*shape, generator=g)
+    q, k, v = rnd(B, NH, DQ).to(dtype).cuda(), rnd(B, NH, DQ).to(dtype).cuda(), rnd(B, NH, DV).to(dtype).cuda()
+    wide = (4.0 * rnd(B, 2 * NH + 24)).to(dtype).cuda()
+    gates_raw = wide[:, 8:8 + 2 * NH]                      # a column slice of a wider projection output
+    bias = torch.cat([torch.zeros(NH), 3.0 + torch.zeros(NH)]).to(dtype).cuda()
+    ogate, w = rnd(B, NH * DV).to(dtype).cuda(), (1.0 + 0.1 * rnd(NH * DV)).to(dtype).cuda()
+    N = B + 3 if with_slots else B
+    pool = [rnd(N, NH, DQ, DV).cuda(), rnd(N, NH, DQ).cuda(), rnd(N, NH, 1).cuda()]
+    slot = None
+    if with_slots:
+        slot = torch.tensor([N - 1 - 2 * j if j % 3 != 1 else -1 for j in range(B)], dtype=torch.int32)   # every third stream inactive
+    # the three kernels
+    gates = ops.soft_cap(gates_raw, 15.0, out_float32=True, float32_math=True, bias=bias)
+    c1 = [t.clone() for t in pool]
+    h, st1 = xlstm_b200.mlstm_step(q, k, v, gates[:, :NH], gates[:, NH:], *c1, slot=slot)
+    want = xlstm_b200.headnorm_gate(h[:, :, None], ogate[:, None], w)[:, 0]
+    # the one kernel
+    c2 = [t.clone() for t in pool]
+    got, st2 = ops.mlstm_decode_cell(q, k, v, gates_raw, bias, 15.0, ogate, w, *c2, slot=slot)
+    xlstm_b200.check_device_status()
+    for a, b_ in zip(st1, st2):
+        assert torch.equal(a, b_)
+    assert got.shape == (B, NH * DV)
+    d = (got.float() - want.float()).abs()
+    tol = 2.0 ** -7 if dtype == torch.bfloat16 else 1e-5
+    assert (d <= want.float().abs() * tol + 1e-5).all(), float(d.max())
+    if with_slots:   # inactive streams: zero output, pool untouched
+        idle = [j for j in range(B) if int(slot[j]) < 0]
+        assert float(got[idle].float().abs().max()) == 0.0

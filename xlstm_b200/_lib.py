@@ -18,7 +18,7 @@ EXPORTS = (
     "xl_mlstm_chunkwise", "xl_mlstm_recurrent", "xl_mlstm_step", "xl_slstm_forward",
     "xl_add_rmsnorm", "xl_headnorm_gate", "xl_soft_cap", "xl_causal_conv1d",
     "xl_softcap_argmax", "xl_softcap_argmax_scratch_bytes", "xl_swiglu",
-    "xl_softcap_argmax_noalloc", "xl_softcap_argmax_noalloc_max_rows", "xl_peer_reduce_add_rmsnorm", "xl_headwise_proj",
+    "xl_softcap_argmax_noalloc", "xl_softcap_argmax_noalloc_max_rows", "xl_peer_reduce_add_rmsnorm", "xl_headwise_proj", "xl_mlstm_decode_cell",
 )
 
 
@@ -98,6 +98,15 @@ class Conv1dParams(C.Structure):
         ("B", C.c_int32), ("S", C.c_int32), ("F", C.c_int32), ("K", C.c_int32), ("num_docs", C.c_int32), ("act", C.c_int32),
         ("x_sb", C.c_int64), ("x_st", C.c_int64), ("o_sb", C.c_int64), ("o_st", C.c_int64),
         ("dtype", C.c_int32),
+    ]
+
+
+class MlstmDecodeCellParams(C.Structure):
+    _fields_ = [
+        ("step", MlstmStepParams),
+        ("gates_raw", C.c_void_p), ("gate_bias", C.c_void_p), ("ogate", C.c_void_p), ("norm_weight", C.c_void_p), ("hg", C.c_void_p),
+        ("gr_sb", C.c_int64), ("o_sb", C.c_int64), ("hg_sb", C.c_int64),
+        ("gate_cap", C.c_float), ("norm_eps", C.c_float),
     ]
 
 

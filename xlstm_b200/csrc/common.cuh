@@ -41,6 +41,12 @@ template <typename T> __device__ __forceinline__ T from_float(float x);
 template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
+// Sigmoid of a gate, rounded to T by the caller right away: for bf16 the hardware exponential and reciprocal (a few fp32
+// ulp) are far inside the rounding step; fp32 keeps the exact forms.
+template <typename T> __device__ __forceinline__ float sigmoid_for(float x);
+template <> __device__ __forceinline__ float sigmoid_for<float>(float x) { return 1.f / (1.f + expf(-x)); }
+template <> __device__ __forceinline__ float sigmoid_for<__nv_bfloat16>(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -190,6 +196,9 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 __device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
   uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank)); return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
 }
 // arrival on a barrier of another CTA of the cluster (CTA-scope release, as consumer-release barriers of 2-CTA pipelines
 // use it: what the arrival orders is consumed by the arriving CTA's own tensor core; a cluster-scope release costs

@@ -39,10 +39,6 @@ __device__ __forceinline__ void store16(T* p, const Vec16<T>& r) {
 // The gate is rounded to T right away: for bf16 the hardware exponential and reciprocal (a few fp32 ulp) are far
 // inside the rounding step and keep the kernel on the memory roofline (with expf and an IEEE division the kernel
 // was bound by instruction issue: 0.49 ms against 0.25 ms of traffic at the 7B shapes); fp32 keeps the exact forms.
-template <typename T> __device__ __forceinline__ float sigmoid_for(float x);
-template <> __device__ __forceinline__ float sigmoid_for<float>(float x) { return 1.f / (1.f + expf(-x)); }
-template <> __device__ __forceinline__ float sigmoid_for<__nv_bfloat16>(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
-
 // out = round(round(sigmoid(o)) * round(round((h - mean) * r) * w)), the eager reference's rounding sequence.
 __device__ __forceinline__ Vec16<float> normalise_weight_gate(const Vec16<float>& h, const Vec16<float>& o,
                                                               const Vec16<float>& w, float mean, float r) {

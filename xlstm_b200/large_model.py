@@ -187,6 +187,14 @@ class LargeModel:
         if self.fused:   # one GEMM for all six projections; the gates are capped in fp32 (they enter exponentials in the cell)
             allp = F.linear(x, blk["qkvo_if"])
             q, k, v, o, gpre, _ = torch.split(allp, [NHl * dq, NHl * dq, NHl * dv, NHl * dv, 2 * NHl, self.gate_pad], dim=-1)
+            if S == 1 and cu_seqlens is None and self.cell is ops and dv <= 1024:
+                # decode: gate cap, cell step, per-head norm and output gate in one kernel
+                c, n, m = state if state is not None else (None, None, None)
+                hg, new_state = ops.mlstm_decode_cell(q.reshape(B, NHl, dq), k.reshape(B, NHl, dq), v.reshape(B, NHl, dv), gpre, blk["if_b"],
+                                                      cfg.gate_soft_cap, o, blk["mh_norm"], c, n, m, slot=slot, eps=cfg.eps,
+                                                      norm_eps=cfg.norm_eps)
+                y = F.linear(hg.reshape(B, 1, NHl * dv), blk["out_proj"])
+                return (self._all_reduce(y) if reduce else y), new_state
             gates = ops.soft_cap(gpre, cfg.gate_soft_cap, out_float32=True, float32_math=True, bias=blk["if_b"])
         else:
             qkvo = F.linear(x, blk["qkvo"])

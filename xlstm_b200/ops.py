@@ -12,7 +12,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
-from ._lib import (AddRmsnormParams, Conv1dParams, HeadwiseParams, GreedyParams, HeadnormGateParams, MlstmSeqParams, MlstmStepParams, SlstmParams, SoftCapParams, SwigluParams, XL_BF16, XL_F32,
+from ._lib import (AddRmsnormParams, Conv1dParams, HeadwiseParams, GreedyParams, HeadnormGateParams, MlstmDecodeCellParams, MlstmSeqParams, MlstmStepParams, SlstmParams, SoftCapParams, SwigluParams, XL_BF16, XL_F32,
                    check, lib)
 
 _DTYPES = {torch.float32: XL_F32, torch.bfloat16: XL_BF16}
@@ -215,17 +215,9 @@ def prepare_slots(slot, B: int, n_slots: int, device) -> torch.Tensor:
     return torch.tensor(vals, dtype=torch.int32, device=device)
 
 
-def mlstm_step(q, k, v, i, f, c, n, m, slot=None, eps: float = 1e-6, inplace: bool = True):
-    """One decode step.  q,k (B,NH,DHQK), v (B,NH,DHV), i,f (B,NH[,1]); state pool c (N,NH,DHQK,DHV),
-    n (N,NH,DHQK), m (N,NH[,1]) fp32; ``slot`` (B,) selects each stream's pool row (default: row b; a negative
-    entry marks an inactive stream whose pool rows stay untouched; see :func:`prepare_slots`).
-
-    With ``inplace`` the large C state is updated where it lives and the SAME tensor object is returned,
-    so a caller that copies the returned state back into its own buffers (xlstm_large/model.py:221-225)
-    performs a no-op for C.  n and m are always returned as new small tensors (several thread blocks
-    read the old values while one writes).  Without a pool (c is None) the state starts from zero.
-    """
-    _require_cuda(q, k, v, i, f, c, n, m)
+def _step_state_params(p, q, k, v, c, n, m, slot, eps, inplace):
+    """Fills the part of ``MlstmStepParams`` that the plain step and the fused decode cell share (inputs, state pool,
+    slots); returns the output state tensors and the (possibly converted) tensors that must stay alive for the launch."""
     B, NH, DHQK = q.shape
     DHV = v.shape[-1]
     dev = q.device
@@ -234,9 +226,6 @@ def mlstm_step(q, k, v, i, f, c, n, m, slot=None, eps: float = 1e-6, inplace: bo
             raise ValueError("`slot` addresses rows of a state pool: pass c, n, m")
         slot = prepare_slots(slot, B, c.shape[0], dev)
     q, k, v = _last_contig(q), _last_contig(k), _last_contig(v)
-    i, f = _gate(i).reshape(B, NH), _gate(f).reshape(B, NH)
-    if i.stride() != f.stride():
-        i, f = i.contiguous(), f.contiguous()
     have = c is not None
     if have:
         if c.dtype != torch.float32 or not c.is_contiguous() or not n.is_contiguous():
@@ -254,11 +243,7 @@ def mlstm_step(q, k, v, i, f, c, n, m, slot=None, eps: float = 1e-6, inplace: bo
         c_out.copy_(c)  # rows not addressed by `slot` keep their contents
     n_out = n.clone() if (have and slot is not None) else torch.empty(N, NH, DHQK, dtype=torch.float32, device=dev)
     m_out = m.clone() if (have and slot is not None) else torch.empty(N, NH, 1, dtype=torch.float32, device=dev)
-    h = torch.empty(B, NH, DHV, dtype=q.dtype, device=dev)
-
-    p = MlstmStepParams()
-    p.q, p.k, p.v, p.h = q.data_ptr(), k.data_ptr(), v.data_ptr(), h.data_ptr()
-    p.igate, p.fgate = i.data_ptr(), f.data_ptr()
+    p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     if have:
         p.c_in, p.n_in, p.m_in = c.data_ptr(), n.data_ptr(), m.data_ptr()
     p.c_out, p.n_out, p.m_out = c_out.data_ptr(), n_out.data_ptr(), m_out.data_ptr()
@@ -268,12 +253,71 @@ def mlstm_step(q, k, v, i, f, c, n, m, slot=None, eps: float = 1e-6, inplace: bo
     p.q_sb, p.q_sh = q.stride()[:2]
     p.k_sb, p.k_sh = k.stride()[:2]
     p.v_sb, p.v_sh = v.stride()[:2]
+    p.eps, p.dtype = eps, _DTYPES[q.dtype]
+    return (c_out, n_out, m_out), (q, k, v, m, slot)
+
+
+def mlstm_step(q, k, v, i, f, c, n, m, slot=None, eps: float = 1e-6, inplace: bool = True):
+    """One decode step.  q,k (B,NH,DHQK), v (B,NH,DHV), i,f (B,NH[,1]); state pool c (N,NH,DHQK,DHV),
+    n (N,NH,DHQK), m (N,NH[,1]) fp32; ``slot`` (B,) selects each stream's pool row (default: row b; a negative
+    entry marks an inactive stream whose pool rows stay untouched; see :func:`prepare_slots`).
+
+    With ``inplace`` the large C state is updated where it lives and the SAME tensor object is returned,
+    so a caller that copies the returned state back into its own buffers (xlstm_large/model.py:221-225)
+    performs a no-op for C.  n and m are always returned as new small tensors (several thread blocks
+    read the old values while one writes).  Without a pool (c is None) the state starts from zero.
+    """
+    _require_cuda(q, k, v, i, f, c, n, m)
+    B, NH, _ = q.shape
+    dev = q.device
+    i, f = _gate(i).reshape(B, NH), _gate(f).reshape(B, NH)
+    if i.stride() != f.stride():
+        i, f = i.contiguous(), f.contiguous()
+    p = MlstmStepParams()
+    state, keep = _step_state_params(p, q, k, v, c, n, m, slot, eps, inplace)
+    h = torch.empty(B, NH, v.shape[-1], dtype=q.dtype, device=dev)
+    p.h = h.data_ptr()
+    p.igate, p.fgate = i.data_ptr(), f.data_ptr()
     p.h_sb, p.h_sh = h.stride()[:2]
     p.g_sb, p.g_sh = i.stride()
-    p.eps, p.dtype = eps, _DTYPES[q.dtype]
     with torch.cuda.device(dev):
         check(lib().xl_mlstm_step(C.byref(p), _stream_ptr(dev)), "xl_mlstm_step")
-    return h, (c_out, n_out, m_out)
+    return h, state
+
+
+def mlstm_decode_cell(q, k, v, gates_raw, gate_bias, gate_cap: float, ogate, norm_weight, c, n, m, slot=None,
+                      eps: float = 1e-6, norm_eps: float = 1e-6):
+    """The cell part of one decode step of the mLSTM layer in ONE kernel: soft cap of the gate pre-activations
+    (xlstm/xlstm_large/model.py:389-394, fp32 arithmetic), the step of :func:`mlstm_step` (C updated in place), and the
+    per-head norm + weight + output gate behind it (model.py:435-449).
+
+    q,k (B,NH,DHQK), v (B,NH,DHV) as for the step; ``gates_raw`` (B, 2*NH): the projection's input-gate columns of all
+    heads, then its forget-gate columns (a column slice of the stacked projection output is fine); ``gate_bias`` (2*NH)
+    or None; ``ogate`` (B, NH*DHV); ``norm_weight`` (NH*DHV).  Returns (B, NH*DHV), the input of out_proj, and the
+    state like :func:`mlstm_step`."""
+    _require_cuda(q, k, v, gates_raw, gate_bias, ogate, norm_weight, c, n, m)
+    B, NH, _ = q.shape
+    DHV = v.shape[-1]
+    dev, dt = q.device, q.dtype
+    if DHV > 1024:
+        raise ValueError("mlstm_decode_cell: head value width above 1024")
+    gates_raw, ogate = _last_contig(gates_raw).reshape(B, 2 * NH), _last_contig(ogate).reshape(B, NH * DHV)
+    if gates_raw.dtype != dt or ogate.dtype != dt or norm_weight.dtype != dt or (gate_bias is not None and gate_bias.dtype != dt):
+        raise ValueError("mlstm_decode_cell: gates, output gate, bias and norm weight in the dtype of q")
+    norm_weight = norm_weight.contiguous()
+    if norm_weight.numel() != NH * DHV or (gate_bias is not None and gate_bias.numel() != 2 * NH):
+        raise ValueError("mlstm_decode_cell: norm weight (NH*DHV), gate bias (2*NH)")
+    f = MlstmDecodeCellParams()
+    state, keep = _step_state_params(f.step, q, k, v, c, n, m, slot, eps, True)
+    hg = torch.empty(B, NH * DHV, dtype=dt, device=dev)
+    gate_bias = gate_bias.contiguous() if gate_bias is not None else None
+    f.gates_raw, f.ogate, f.norm_weight, f.hg = gates_raw.data_ptr(), ogate.data_ptr(), norm_weight.data_ptr(), hg.data_ptr()
+    f.gate_bias = gate_bias.data_ptr() if gate_bias is not None else None
+    f.gr_sb, f.o_sb, f.hg_sb = gates_raw.stride(0), ogate.stride(0), hg.stride(0)
+    f.gate_cap, f.norm_eps = float(gate_cap), float(norm_eps)
+    with torch.cuda.device(dev):
+        check(lib().xl_mlstm_decode_cell(C.byref(f), _stream_ptr(dev)), "xl_mlstm_decode_cell")
+    return hg, state
 
 
 def slstm_forward(wx, R, bias, state0=None, cu_seqlens=None):
