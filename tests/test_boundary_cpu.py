@@ -69,6 +69,36 @@ def test_entry_points_validate_before_launching():
     assert l.xl_mlstm_recurrent(ctypes.byref(p), None) == -9  # n_out aliases n0
 
 
+def test_newer_entry_points_validate_before_launching():
+    from xlstm_b200 import _lib
+    l = _lib.lib()
+    hw = _lib.HeadwiseParams()
+    assert l.xl_headwise_proj(ctypes.byref(hw), None) == -1          # null pointers
+    hw.x[0], hw.out, hw.w[0] = 0x1000, 0x2000, 0x3000
+    hw.dtype, hw.n_slots, hw.NH, hw.DH, hw.rows = 1, 1, 2, 96, 4
+    assert l.xl_headwise_proj(ctypes.byref(hw), None) == -6          # block size not covered
+    hw.DH, hw.n_slots = 64, 5
+    assert l.xl_headwise_proj(ctypes.byref(hw), None) == -2          # more than four slots
+    hw.n_slots, hw.dtype = 1, 0
+    assert l.xl_headwise_proj(ctypes.byref(hw), None) == -5          # bf16 only
+    hw.dtype = 1
+    hw.x_row_stride[0], hw.out_row_stride = 100, 128
+    assert l.xl_headwise_proj(ctypes.byref(hw), None) == -3          # row stride below NH * DH
+    dc = _lib.MlstmDecodeCellParams()
+    assert l.xl_mlstm_decode_cell(ctypes.byref(dc), None) == -1
+    for name in ("q", "k", "v", "c_out", "n_out", "m_out"):
+        setattr(dc.step, name, 0x1000)
+    dc.step.B, dc.step.NH, dc.step.DHQK, dc.step.DHV, dc.step.dtype = 2, 2, 64, 128, 1
+    assert l.xl_mlstm_decode_cell(ctypes.byref(dc), None) == -1      # the fused operands are missing
+    dc.gates_raw = dc.ogate = dc.norm_weight = dc.hg = 0x2000
+    dc.gate_cap = 15.0
+    dc.step.DHV = 2048
+    assert l.xl_mlstm_decode_cell(ctypes.byref(dc), None) == -6      # more than eight blocks per head
+    dc.step.DHV = 128
+    dc.gr_sb, dc.o_sb, dc.hg_sb = 2, 256, 256
+    assert l.xl_mlstm_decode_cell(ctypes.byref(dc), None) == -3      # gate rows shorter than 2 * NH
+
+
 def test_ops_refuse_cpu_tensors():
     import xlstm_b200
     q = torch.zeros(1, 1, 64, 64)
