@@ -55,6 +55,32 @@ template <int N> __device__ __forceinline__ void tma_store_wait_read() { asm vol
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void epilogue_sync(int group) { asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory"); }
 
+// One [128 rows x 64 columns] box of a result on its way out, called by the 128 threads of an epilogue group: the thread's
+// row (64 fp32 values, `v`) is rounded to bf16 and written into the group's staging box with the TMA swizzle, then the
+// group's first thread hands the box to a TMA store.  `stage` is the shared-memory address of the staging box; the box the
+// group used two boxes ago must have been read by its store before it is overwritten.
+__device__ __forceinline__ void hw_store_box(unsigned char* smem_stage, uint32_t stage, const uint32_t (&v)[64], int r, int grp, int te,
+                                             const CUtensorMap* out_map, int col, int row0, bool in_range) {
+  if (te == 0) tma_store_wait_read<1>();
+  epilogue_sync(grp);
+  unsigned char* stg = smem_stage + r * 128;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {   // 16-byte pieces of the row's 64 columns
+    uint4 w;
+    w.x = pack_bf16x2(__uint_as_float(v[8 * c + 0]), __uint_as_float(v[8 * c + 1]));
+    w.y = pack_bf16x2(__uint_as_float(v[8 * c + 2]), __uint_as_float(v[8 * c + 3]));
+    w.z = pack_bf16x2(__uint_as_float(v[8 * c + 4]), __uint_as_float(v[8 * c + 5]));
+    w.w = pack_bf16x2(__uint_as_float(v[8 * c + 6]), __uint_as_float(v[8 * c + 7]));
+    *reinterpret_cast<uint4*>(stg + ((c ^ (r & 7)) << 4)) = w;
+  }
+  fence_proxy_async_smem();
+  epilogue_sync(grp);
+  if (te == 0 && in_range) {
+    tma_store_2d(out_map, stage, col, row0);
+    tma_store_commit();
+  }
+}
+
 template <int DH>
 __global__ void __launch_bounds__(HW_THREADS, 1) headwise_proj_kernel(const __grid_constant__ HwMaps maps, const xl_headwise_params p) {
   using LY = HwLayout<DH>;
@@ -150,30 +176,12 @@ __global__ void __launch_bounds__(HW_THREADS, 1) headwise_proj_kernel(const __gr
       const uint32_t acc = tmem + lane_base + (uint32_t)(slot & 1) * DH;
 #pragma unroll 1
       for (int cb = (KB > 1 ? grp : 0); cb < (KB > 1 || grp == 0 ? KB : 0); cb += (KB > 1 ? 2 : 1), ++box) {
-        uint32_t v0[32], v1[32];
-        tmem_ld_x32(acc + cb * 64, v0);
-        tmem_ld_x32(acc + cb * 64 + 32, v1);
+        uint32_t v[64];
+        tmem_ld_x32(acc + cb * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+        tmem_ld_x32(acc + cb * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
         tc_wait_ld();
-        // the staging box this group used two boxes ago must have been read by its TMA store
-        if (te == 0) tma_store_wait_read<1>();
-        epilogue_sync(grp);
-        unsigned char* stg = smem + stage0 + (box & 1) * HW_A_BYTES + r * 128;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {   // 16-byte pieces of the row's 64 columns, swizzled like a TMA box
-          const uint32_t* src = (c < 4) ? &v0[8 * c] : &v1[8 * (c - 4)];
-          uint4 w;
-          w.x = pack_bf16x2(__uint_as_float(src[0]), __uint_as_float(src[1]));
-          w.y = pack_bf16x2(__uint_as_float(src[2]), __uint_as_float(src[3]));
-          w.z = pack_bf16x2(__uint_as_float(src[4]), __uint_as_float(src[5]));
-          w.w = pack_bf16x2(__uint_as_float(src[6]), __uint_as_float(src[7]));
-          *reinterpret_cast<uint4*>(stg + ((c ^ (r & 7)) << 4)) = w;
-        }
-        fence_proxy_async_smem();
-        epilogue_sync(grp);
-        if (te == 0) {
-          tma_store_2d(&maps.out, sbase + stage0 + (box & 1) * HW_A_BYTES, (slot * p.NH + head) * DH + cb * 64, row0);
-          tma_store_commit();
-        }
+        const uint32_t off = stage0 + (box & 1) * HW_A_BYTES;
+        hw_store_box(smem + off, sbase + off, v, r, grp, te, &maps.out, (slot * p.NH + head) * DH + cb * 64, row0, true);
       }
       tc_fence_before();
       mbar_arrive(bar_acc_empty(slot & 1));
@@ -352,25 +360,8 @@ headwise_proj_pair_kernel(const __grid_constant__ HwMaps maps, const xl_headwise
       }
 #pragma unroll
       for (int i = 0; i < NBX; ++i, ++box) {
-        const int cb = 2 * i + grp;
-        if (te == 0) tma_store_wait_read<1>();   // the staging box used two boxes ago has been read by its store
-        epilogue_sync(grp);
-        unsigned char* stg = smem + stage0 + (box & 1) * HW_A_BYTES + r * 128;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint4 w;
-          w.x = pack_bf16x2(__uint_as_float(v[i][8 * c + 0]), __uint_as_float(v[i][8 * c + 1]));
-          w.y = pack_bf16x2(__uint_as_float(v[i][8 * c + 2]), __uint_as_float(v[i][8 * c + 3]));
-          w.z = pack_bf16x2(__uint_as_float(v[i][8 * c + 4]), __uint_as_float(v[i][8 * c + 5]));
-          w.w = pack_bf16x2(__uint_as_float(v[i][8 * c + 6]), __uint_as_float(v[i][8 * c + 7]));
-          *reinterpret_cast<uint4*>(stg + ((c ^ (r & 7)) << 4)) = w;
-        }
-        fence_proxy_async_smem();
-        epilogue_sync(grp);
-        if (te == 0 && row0 < p.rows) {
-          tma_store_2d(&maps.out, sbase + stage0 + (box & 1) * HW_A_BYTES, (slot * p.NH + head) * DH + cb * 64, row0);
-          tma_store_commit();
-        }
+        const uint32_t off = stage0 + (box & 1) * HW_A_BYTES;
+        hw_store_box(smem + off, sbase + off, v[i], r, grp, te, &maps.out, (slot * p.NH + head) * DH + (2 * i + grp) * 64, row0, row0 < p.rows);
       }
     }
     }
