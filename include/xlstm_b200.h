@@ -159,10 +159,39 @@ typedef struct xl_slstm_params {
   int32_t B, S, NH, DH;
   int32_t num_docs;
   int32_t dtype;
+  void* train_cache;     /* NULL for inference.  Training: xl_slstm_cache_bytes(B,S,NH,DH) bytes, 16-byte aligned, that the
+                            forward fills with what xl_slstm_backward needs (activated gates and states of every step; the
+                            reference's `states` and gate caches, slstm.cc:88-101).  Not with cu_seqlens. */
 } xl_slstm_params;
 
 /* Requires DH in {64,128,256}; any B (batch rows are tiled into groups of 16), dtype XL_BF16. */
 int xl_slstm_forward(const xl_slstm_params* p, void* cuda_stream);
+
+/* Size of the training cache of one forward call (0 for unsupported shapes).  Host only, no CUDA call. */
+int64_t xl_slstm_cache_bytes(int32_t B, int32_t S, int32_t NH, int32_t DH);
+
+/* sLSTM backward through time, one persistent kernel with the forward's mapping.  Replaces sLSTMFunc.backward
+ * (xlstm/blocks/slstm/src/cuda/slstm.cc:137-254): the host loop BackwardPass::Run (slstm_backward.cu) and
+ * SLSTMPointwiseBackward (slstm_pointwise.cu:118-196).  Per step the gate gradients are formed in registers from the
+ * cache, written out as dWx, and carried back through the recurrent matrix (held in registers) with a reduce-scatter
+ * between the CTAs of a cluster.  The stabiliser state m gets no gradient (dstate0[3] = 0), as in the reference.
+ * The gradients of R and of the bias are sums over (b,t) of h_{t-1} (x) dWx_t and of dWx_t -- plain matrix products
+ * over this kernel's output that the caller's GEMM library forms (the reference does the same after its loop). */
+typedef struct xl_slstm_bwd_params {
+  const void* cache;        /* written by xl_slstm_forward with train_cache set, same B,S,NH,DH */
+  const void* R;            /* (NH, DH_in, 4, DH_out), dtype `dtype` */
+  const void* dh;           /* (B, NH, S, DH) gradient of the forward's h_out, dtype `dtype` */
+  const float* dstate_out;  /* (4, B, NH*DH) gradient of the forward's final state (entry 3, m, is ignored), or NULL */
+  const float* state0;      /* the forward's initial state, or NULL = zeros */
+  void* dwx;                /* out (B, S, 4, NH, DH), dtype `dtype`: gradient of wx (= of the gate pre-activations) */
+  float* dstate0;           /* out (4, B, NH*DH): gradient of the initial state */
+  int32_t* status;
+  int32_t B, S, NH, DH;
+  int32_t dtype;
+} xl_slstm_bwd_params;
+
+/* Requires DH in {64,128,256}, dtype XL_BF16; no document offsets. */
+int xl_slstm_backward(const xl_slstm_bwd_params* p, void* cuda_stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Operators next to the mLSTM cell in the reference's layer (xlstm/xlstm_large/model.py:379-452), each one pass

@@ -31,8 +31,12 @@ import torch
 import torch.nn.functional as F
 
 
-def slstm_pointwise(raw, state, fresh_rule: str = "elementwise"):
-    """raw (B,4,H) pre-activations (i,f,z,o); state (4,B,H) = (h,c,n,m). fp32."""
+def slstm_pointwise(raw, state, fresh_rule: str = "elementwise", stabiliser_grad: bool = True):
+    """raw (B,4,H) pre-activations (i,f,z,o); state (4,B,H) = (h,c,n,m). fp32.  The function is differentiable (plain
+    torch operators), which makes autograd over it the oracle of the backward pass; with ``stabiliser_grad=False``
+    the new m is a constant of the step, the rule of the reference's backward kernel
+    (``slstm_pointwise.cu:118-196`` never differentiates m and returns a zero gradient for it) -- the two agree for
+    any loss on h, which does not depend on the stabiliser."""
     _, c, n, m = state.unbind(0)
     i_raw, f_raw, z_raw, o_raw = raw.unbind(1)
     logf_plus_m = m + F.logsigmoid(f_raw)
@@ -42,6 +46,8 @@ def slstm_pointwise(raw, state, fresh_rule: str = "elementwise"):
         m_new = i_raw if bool(torch.all(n == 0.0)) else torch.maximum(i_raw, logf_plus_m)
     else:
         raise ValueError(fresh_rule)
+    if not stabiliser_grad:
+        m_new = m_new.detach()
     i_gate = torch.exp(i_raw - m_new).clamp(max=1.0)
     f_gate = torch.exp(logf_plus_m - m_new).clamp(max=1.0)
     c_new = f_gate * c + i_gate * torch.tanh(z_raw)
@@ -51,7 +57,7 @@ def slstm_pointwise(raw, state, fresh_rule: str = "elementwise"):
 
 
 def slstm_forward(wx, R, bias, state=None, reset=None, fresh_rule: str = "elementwise",
-                  state_dtype: torch.dtype = torch.float32):
+                  state_dtype: torch.dtype = torch.float32, stabiliser_grad: bool = True):
     """Full sequence.
 
     wx (B,S,4H); R (NH,DH,4,DH); bias (NH,4,DH); state (4,B,H) or None;
@@ -69,13 +75,13 @@ def slstm_forward(wx, R, bias, state=None, reset=None, fresh_rule: str = "elemen
     b32 = bias.float().reshape(NH, 4, DH).permute(1, 0, 2).reshape(1, 4, H)
     st = torch.zeros(4, B, H) if state is None else state.float().clone()
     wx32 = wx.float().reshape(B, S, 4, H)
-    hs = torch.empty(S, B, H)
+    hs = []
     for t in range(S):
         if reset is not None:
             st = torch.where(reset[:, t].reshape(1, B, 1), torch.zeros_like(st), st)
         h = st[0].reshape(B, NH, 1, DH)
         ry = (h @ R32[None]).reshape(B, NH, 4, DH).permute(0, 2, 1, 3).reshape(B, 4, H)
-        st = slstm_pointwise(wx32[:, t] + ry + b32, st, fresh_rule).to(state_dtype).float()
-        hs[t] = st[0]
-    out = hs.reshape(S, B, NH, DH).permute(1, 2, 0, 3).contiguous()
+        st = slstm_pointwise(wx32[:, t] + ry + b32, st, fresh_rule, stabiliser_grad).to(state_dtype).float()
+        hs.append(st[0])
+    out = torch.stack(hs, 0).reshape(S, B, NH, DH).permute(1, 2, 0, 3).contiguous()
     return out, st

@@ -19,7 +19,7 @@ def test_library_exports_every_declared_symbol():
     l = _lib.lib()
     for name in declared:
         assert hasattr(l, name), name
-    assert l.xl_abi_version() == 2
+    assert l.xl_abi_version() == 3
     assert b"stride" in l.xl_strerror(-3)
 
 

@@ -19,6 +19,7 @@ EXPORTS = (
     "xl_add_rmsnorm", "xl_headnorm_gate", "xl_soft_cap", "xl_causal_conv1d",
     "xl_softcap_argmax", "xl_softcap_argmax_scratch_bytes", "xl_swiglu",
     "xl_softcap_argmax_noalloc", "xl_softcap_argmax_noalloc_max_rows", "xl_peer_reduce_add_rmsnorm", "xl_headwise_proj", "xl_mlstm_decode_cell",
+    "xl_slstm_backward", "xl_slstm_cache_bytes",
 )
 
 
@@ -60,7 +61,15 @@ class SlstmParams(C.Structure):
         ("wx", C.c_void_p), ("R", C.c_void_p), ("bias", C.c_void_p), ("state0", C.c_void_p),
         ("h_out", C.c_void_p), ("state_out", C.c_void_p), ("cu_seqlens", C.c_void_p), ("status", C.c_void_p),
         ("B", C.c_int32), ("S", C.c_int32), ("NH", C.c_int32), ("DH", C.c_int32),
-        ("num_docs", C.c_int32), ("dtype", C.c_int32),
+        ("num_docs", C.c_int32), ("dtype", C.c_int32), ("train_cache", C.c_void_p),
+    ]
+
+
+class SlstmBwdParams(C.Structure):
+    _fields_ = [
+        ("cache", C.c_void_p), ("R", C.c_void_p), ("dh", C.c_void_p), ("dstate_out", C.c_void_p),
+        ("state0", C.c_void_p), ("dwx", C.c_void_p), ("dstate0", C.c_void_p), ("status", C.c_void_p),
+        ("B", C.c_int32), ("S", C.c_int32), ("NH", C.c_int32), ("DH", C.c_int32), ("dtype", C.c_int32),
     ]
 
 
@@ -158,13 +167,16 @@ def lib() -> C.CDLL:
                             ("xl_add_rmsnorm", AddRmsnormParams), ("xl_headnorm_gate", HeadnormGateParams),
                             ("xl_soft_cap", SoftCapParams), ("xl_causal_conv1d", Conv1dParams),
                             ("xl_softcap_argmax", GreedyParams), ("xl_swiglu", SwigluParams),
-                            ("xl_softcap_argmax_noalloc", GreedyParams), ("xl_peer_reduce_add_rmsnorm", PeerReduceParams)):
+                            ("xl_softcap_argmax_noalloc", GreedyParams), ("xl_peer_reduce_add_rmsnorm", PeerReduceParams),
+                            ("xl_slstm_backward", SlstmBwdParams)):
             fn = getattr(l, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(ptype), C.c_void_p]
         l.xl_softcap_argmax_scratch_bytes.restype = C.c_int64
         l.xl_softcap_argmax_scratch_bytes.argtypes = [C.c_int32]
         l.xl_softcap_argmax_noalloc_max_rows.restype = C.c_int32
+        l.xl_slstm_cache_bytes.restype = C.c_int64
+        l.xl_slstm_cache_bytes.argtypes = [C.c_int32] * 4
         _lib = l
     return _lib
 

@@ -17,7 +17,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libxlstm_b200.so")
-SOURCES = ["capi.cu", "mlstm_step.cu", "mlstm_recurrent.cu", "mlstm_chunkwise.cu", "slstm_fwd.cu", "layer_adjacent.cu", "greedy_head.cu", "peer_reduce.cu", "headwise_proj.cu"]
+SOURCES = ["capi.cu", "mlstm_step.cu", "mlstm_recurrent.cu", "mlstm_chunkwise.cu", "slstm_fwd.cu", "slstm_bwd.cu", "layer_adjacent.cu", "greedy_head.cu", "peer_reduce.cu", "headwise_proj.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--shared", "-Xcompiler", "-fPIC",

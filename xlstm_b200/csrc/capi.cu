@@ -42,4 +42,4 @@ extern "C" const char* xl_strerror(int status) {
 
 extern "C" const char* xl_last_cuda_error(void) { return xl::g_last_cuda_error; }
 
-extern "C" int xl_abi_version(void) { return 2; }
+extern "C" int xl_abi_version(void) { return 3; }

@@ -19,61 +19,15 @@
 // pushed only after its last read of h_{t-1}, the previous content of that buffer.
 // Wx is streamed through an 8-step cp.async ring so that HBM latency is off the dependency chain.
 // A document boundary (cu_seqlens) zeroes h, c, n, m of that batch row inside the kernel.
+//
+// Training variant (TRAIN): every thread also writes one 96-byte record per step -- its activated gates
+// (i', raw f, tanh z, sigmoid o as bf16 pairs), its h' and its c', n', m' in fp32 -- into a cache that the backward
+// kernel (slstm_bwd.cu) reads back with the same thread mapping (the counterpart of the reference's `states` and
+// gate caches, slstm.cc:88-101).
 #include "common.cuh"
+#include "slstm_common.cuh"
 
 namespace xl {
-
-constexpr int SL_THREADS = 128;         // 4 warps; warp w owns units [8w, 8w+8) of the CTA's 32
-constexpr int SL_UNITS = 32;            // hidden units per CTA
-constexpr int SL_ROWS = 16;             // batch rows per cluster (mma M)
-constexpr int SL_RING = 8;              // Wx prefetch depth in time steps
-constexpr int SL_WX_ROW_BYTES = 4 * SL_UNITS * 2 + 16;  // 4 gates x 32 units bf16 + 16 B pad (bank spread)
-constexpr int SL_WX_STEP_BYTES = SL_ROWS * SL_WX_ROW_BYTES;
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-__device__ __forceinline__ void cluster_barrier() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-  return r;
-}
-// Bounded wait without back-off: this wait is the per-step latency chain, a sleep would land on it in full.
-__device__ __forceinline__ bool sl_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t it = 0; it < (1u << 26); ++it)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
-}
-// 4-byte store into (another) CTA's shared memory that adds its 4 bytes to the transaction count of an mbarrier there
-__device__ __forceinline__ void st_async_u32(uint32_t addr, uint32_t v, uint32_t remote_bar) {
-  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(addr), "r"(v), "r"(remote_bar)
-               : "memory");
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                               uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ float fast_tanh(float x) {
-  // 1 - 2/(1+e^{2x}); saturates cleanly for large |x|
-  const float e = __expf(2.f * x);
-  return 1.f - __fdividef(2.f, 1.f + e);
-}
-__device__ __forceinline__ float fast_logsigmoid(float x) { return fminf(x, 0.f) - __logf(1.f + __expf(-fabsf(x))); }
 
 // Advance `idx` past every boundary at or before time index `t_now` of batch row `gb`; return the time index
 // of the next boundary inside the row, or INT_MAX.  Repeated offsets (empty documents) are skipped.
@@ -85,7 +39,7 @@ __device__ __forceinline__ int next_boundary(const xl_slstm_params& p, int gb, i
   return pos < row0 + p.S ? (int)(pos - row0) : 0x7fffffff;
 }
 
-template <int DH>
+template <int DH, bool TRAIN>
 __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_slstm_params p) {
   constexpr int KSTEPS = DH / 16;
   constexpr int H_STRIDE = DH + 8;  // bf16 elements; +16 B keeps ldmatrix rows on distinct banks
@@ -214,6 +168,11 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
   const uint32_t ldm_off = ((lane & 15) * H_STRIDE + (lane >> 4) * 8) * 2;
 
   __nv_bfloat16* hout = reinterpret_cast<__nv_bfloat16*>(p.h_out);
+  // training cache: [cluster][CTA][step][thread] records of SL_REC_BYTES
+  uint4* rec = nullptr;
+  if constexpr (TRAIN)
+    rec = reinterpret_cast<uint4*>(p.train_cache) +
+          ((((size_t)bgroup * NH + head) * NCTA + rank) * (size_t)S * SL_THREADS + tid) * (SL_REC_BYTES / 16);
 
   bool ok = true;
   for (int t = 0; t < S; ++t) {
@@ -254,6 +213,7 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
     // pointwise update in registers
     const bool reset_next_a = (t + 1) == nxt_t[0], reset_next_b = (t + 1) == nxt_t[1];
     float hn[4];
+    [[maybe_unused]] float gi[4], gz[4], go[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float ir = acc[0][i], fr = acc[1][i], zr = acc[2][i], orr = acc[3][i];
@@ -261,12 +221,25 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
       const float mn = (n_[i] == 0.f) ? ir : fmaxf(ir, lfm);
       const float ig = fminf(1.f, __expf(ir - mn));
       const float fg = fminf(1.f, __expf(lfm - mn));
-      c_[i] = fmaf(fg, c_[i], ig * fast_tanh(zr));
+      const float zt = fast_tanh(zr), os = __fdividef(1.f, 1.f + __expf(-orr));
+      c_[i] = fmaf(fg, c_[i], ig * zt);
       n_[i] = fmaf(fg, n_[i], ig);
       m_[i] = mn;
-      hn[i] = __fdividef(c_[i], n_[i]) * __fdividef(1.f, 1.f + __expf(-orr));
+      hn[i] = __fdividef(c_[i], n_[i]) * os;
+      if constexpr (TRAIN) { gi[i] = ig; gz[i] = zt; go[i] = os; }
     }
     const uint32_t pa = pack_bf16x2(hn[0], hn[1]), pb = pack_bf16x2(hn[2], hn[3]);
+    if constexpr (TRAIN) {
+      // the record of this step (states AFTER the update; a reset below is not recorded: the training path takes no
+      // document offsets)
+      uint4* r = rec + (size_t)t * SL_THREADS * (SL_REC_BYTES / 16);
+      r[0] = make_uint4(pack_bf16x2(gi[0], gi[1]), pack_bf16x2(acc[1][0], acc[1][1]), pack_bf16x2(gz[0], gz[1]), pack_bf16x2(go[0], go[1]));
+      r[1] = make_uint4(pack_bf16x2(gi[2], gi[3]), pack_bf16x2(acc[1][2], acc[1][3]), pack_bf16x2(gz[2], gz[3]), pack_bf16x2(go[2], go[3]));
+      r[2] = make_uint4(pa, pb, 0u, 0u);
+      r[3] = make_uint4(__float_as_uint(c_[0]), __float_as_uint(c_[1]), __float_as_uint(c_[2]), __float_as_uint(c_[3]));
+      r[4] = make_uint4(__float_as_uint(n_[0]), __float_as_uint(n_[1]), __float_as_uint(n_[2]), __float_as_uint(n_[3]));
+      r[5] = make_uint4(__float_as_uint(m_[0]), __float_as_uint(m_[1]), __float_as_uint(m_[2]), __float_as_uint(m_[3]));
+    }
     // a row whose next token opens a new document restarts from the zero state
     uint32_t push_a = pa, push_b = pb;
     if (reset_next_a) {
@@ -320,11 +293,11 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
   }
 }
 
-template <int DH>
+template <int DH, bool TRAIN>
 static int launch_slstm(const xl_slstm_params* p, cudaStream_t st) {
   constexpr int NCTA = DH / SL_UNITS;
   const size_t smem = 2 * SL_ROWS * (DH + 8) * 2 + (size_t)SL_RING * SL_WX_STEP_BYTES + 16;  // + 2 mbarriers
-  XL_CUDA_TRY(cudaFuncSetAttribute(slstm_forward_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  XL_CUDA_TRY(cudaFuncSetAttribute(slstm_forward_kernel<DH, TRAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(NCTA, p->NH, (p->B + SL_ROWS - 1) / SL_ROWS);
   cfg.blockDim = dim3(SL_THREADS);
@@ -337,7 +310,7 @@ static int launch_slstm(const xl_slstm_params* p, cudaStream_t st) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  XL_CUDA_TRY(cudaLaunchKernelEx(&cfg, slstm_forward_kernel<DH>, *p));
+  XL_CUDA_TRY(cudaLaunchKernelEx(&cfg, slstm_forward_kernel<DH, TRAIN>, *p));
   return check_launch("xl_slstm_forward");
 }
 
@@ -353,10 +326,26 @@ extern "C" int xl_slstm_forward(const xl_slstm_params* p, void* cuda_stream) {
   if (!aligned16(p->wx) || (reinterpret_cast<uintptr_t>(p->h_out) & 3u)) return XL_ERR_BAD_ALIGNMENT;
   if (p->state0 && p->state0 == p->state_out) return XL_ERR_ALIASING;
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  if (p->train_cache) {
+    if (p->cu_seqlens) return XL_ERR_UNSUPPORTED;  // the backward pass takes no document offsets
+    if (!aligned16(p->train_cache)) return XL_ERR_BAD_ALIGNMENT;
+    switch (p->DH) {
+      case 64: return launch_slstm<64, true>(p, st);
+      case 128: return launch_slstm<128, true>(p, st);
+      case 256: return launch_slstm<256, true>(p, st);
+      default: return XL_ERR_UNSUPPORTED;
+    }
+  }
   switch (p->DH) {
-    case 64: return launch_slstm<64>(p, st);
-    case 128: return launch_slstm<128>(p, st);
-    case 256: return launch_slstm<256>(p, st);
+    case 64: return launch_slstm<64, false>(p, st);
+    case 128: return launch_slstm<128, false>(p, st);
+    case 256: return launch_slstm<256, false>(p, st);
     default: return XL_ERR_UNSUPPORTED;
   }
+}
+
+extern "C" int64_t xl_slstm_cache_bytes(int32_t B, int32_t S, int32_t NH, int32_t DH) {
+  if (B <= 0 || S <= 0 || NH <= 0 || DH <= 0 || DH % xl::SL_UNITS) return 0;
+  const int64_t groups = (B + xl::SL_ROWS - 1) / xl::SL_ROWS;
+  return groups * NH * (DH / xl::SL_UNITS) * (int64_t)S * xl::SL_THREADS * xl::SL_REC_BYTES;
 }

@@ -12,7 +12,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
-from ._lib import (AddRmsnormParams, Conv1dParams, HeadwiseParams, GreedyParams, HeadnormGateParams, MlstmDecodeCellParams, MlstmSeqParams, MlstmStepParams, SlstmParams, SoftCapParams, SwigluParams, XL_BF16, XL_F32,
+from ._lib import (AddRmsnormParams, Conv1dParams, HeadwiseParams, GreedyParams, HeadnormGateParams, MlstmDecodeCellParams, MlstmSeqParams, MlstmStepParams, SlstmParams, SlstmBwdParams, SoftCapParams, SwigluParams, XL_BF16, XL_F32,
                    check, lib)
 
 _DTYPES = {torch.float32: XL_F32, torch.bfloat16: XL_BF16}
@@ -322,9 +322,10 @@ def mlstm_decode_cell(q, k, v, gates_raw, gate_bias, gate_cap: float, ogate, nor
     return hg, state
 
 
-def slstm_forward(wx, R, bias, state0=None, cu_seqlens=None):
+def slstm_forward(wx, R, bias, state0=None, cu_seqlens=None, train_cache: bool = False):
     """sLSTM over a sequence.  wx (B,S,4*H) gate-major [i|f|z|o] each (NH,DH); R (NH,DH,4,DH); bias (NH,4,DH);
-    state0 (4,B,H) ordered (h,c,n,m) or None.  Returns h (B,NH,S,DH) in wx's dtype and the final fp32 state."""
+    state0 (4,B,H) ordered (h,c,n,m) or None.  Returns h (B,NH,S,DH) in wx's dtype and the final fp32 state; with
+    ``train_cache`` also the opaque cache ``slstm_backward`` needs (no document offsets then)."""
     _require_cuda(wx, R, bias, state0)
     if wx.dtype != torch.bfloat16:
         raise ValueError("the sLSTM kernel computes on bf16 inputs (fp32 state); cast wx and R to bfloat16")
@@ -353,9 +354,103 @@ def slstm_forward(wx, R, bias, state0=None, cu_seqlens=None):
         p.cu_seqlens = cu_dev.data_ptr()
     p.status = status_word(dev).data_ptr()
     p.B, p.S, p.NH, p.DH, p.num_docs, p.dtype = B, S, NH, DH, nd, XL_BF16
+    cache = None
+    if train_cache:
+        nbytes = lib().xl_slstm_cache_bytes(B, S, NH, DH)
+        if nbytes <= 0:
+            raise ValueError("the sLSTM training path needs a head size of 64, 128 or 256")
+        cache = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        p.train_cache = cache.data_ptr()
     with torch.cuda.device(dev):
         check(lib().xl_slstm_forward(C.byref(p), _stream_ptr(dev)), "xl_slstm_forward")
+    if train_cache:
+        return out, st, cache
     return out, st
+
+
+def slstm_backward(cache, R, dh, dstate_out=None, state0=None):
+    """Backward through time of ``slstm_forward(..., train_cache=True)``: ``cache`` from that call, R (NH,DH,4,DH),
+    dh (B,NH,S,DH) the gradient of its h, dstate_out (4,B,H) the gradient of its final state (m's entry is ignored)
+    or None, state0 its initial state or None.  Returns dwx (B,S,4*H) in bf16 and dstate0 (4,B,H) fp32 (zero for m).
+    Replaces sLSTMFunc.backward (xlstm/blocks/slstm/src/cuda/slstm.cc:137-254) up to the two sums ``slstm_weight_grads``
+    forms."""
+    _require_cuda(cache, R, dh, dstate_out, state0)
+    B, NH, S, DH = dh.shape
+    H = NH * DH
+    if R.shape != (NH, DH, 4, DH):
+        raise ValueError("inconsistent sLSTM shapes")
+    dev = dh.device
+    if cache.numel() != lib().xl_slstm_cache_bytes(B, S, NH, DH) or cache.dtype != torch.uint8:
+        raise ValueError("cache does not belong to a forward call of these sizes")
+    R = R.to(torch.bfloat16).contiguous()
+    dh = dh.to(torch.bfloat16).contiguous()
+    dwx = torch.empty(B, S, 4 * H, dtype=torch.bfloat16, device=dev)
+    ds0 = torch.empty(4, B, H, dtype=torch.float32, device=dev)
+    p = SlstmBwdParams()
+    p.cache, p.R, p.dh, p.dwx, p.dstate0 = cache.data_ptr(), R.data_ptr(), dh.data_ptr(), dwx.data_ptr(), ds0.data_ptr()
+    keep = []
+    for name, t in (("dstate_out", dstate_out), ("state0", state0)):
+        if t is not None:
+            t32 = t.float().contiguous()
+            if t32.shape != (4, B, H):
+                raise ValueError(f"{name} must be (4,B,H)")
+            keep.append(t32)
+            setattr(p, name, t32.data_ptr())
+    p.status = status_word(dev).data_ptr()
+    p.B, p.S, p.NH, p.DH, p.dtype = B, S, NH, DH, XL_BF16
+    with torch.cuda.device(dev):
+        check(lib().xl_slstm_backward(C.byref(p), _stream_ptr(dev)), "xl_slstm_backward")
+    return dwx, ds0
+
+
+def slstm_weight_grads(dwx, h, state0=None):
+    """Gradients of the recurrent matrix and the bias from the backward kernel's output: with h_{t-1} the forward's h
+    shifted by one step (h_{-1} from state0), dR[n,k,g,u] = sum_{b,t} h_{t-1}[b,n,k] dwx[b,t,g,n,u] and
+    dbias[n,g,u] = sum_{b,t} dwx[b,t,g,n,u] (the reference forms the same products after its time loop,
+    slstm_backward.cu).  Plain batched matrix products, fp32 results: (NH,DH,4,DH) and (NH,4,DH)."""
+    B, NH, S, DH = h.shape
+    dw = dwx.reshape(B, S, 4, NH, DH)
+    hprev = torch.empty(B, NH, S, DH, dtype=dwx.dtype, device=dwx.device)
+    hprev[:, :, 1:] = h[:, :, :-1]
+    if state0 is None:
+        hprev[:, :, 0] = 0
+    else:
+        hprev[:, :, 0] = state0[0].reshape(B, NH, DH).to(dwx.dtype)
+    a = hprev.permute(1, 3, 0, 2).reshape(NH, DH, B * S)                      # (NH, DH_in, B*S)
+    b = dw.permute(3, 0, 1, 2, 4).reshape(NH, B * S, 4 * DH)                  # (NH, B*S, 4*DH_out)
+    try:
+        dR = torch.bmm(a, b, out_dtype=torch.float32)
+    except TypeError:
+        dR = torch.bmm(a, b).float()
+    db = dw.sum(dim=(0, 1), dtype=torch.float32).permute(1, 0, 2).contiguous()
+    return dR.reshape(NH, DH, 4, DH), db
+
+
+class SlstmFunction(torch.autograd.Function):
+    """``slstm_forward`` with a backward pass: h, last = SlstmFunction.apply(wx, R, bias, state0)."""
+
+    @staticmethod
+    def forward(ctx, wx, R, bias, state0):
+        h, last, cache = slstm_forward(wx, R, bias, state0, train_cache=True)
+        ctx.save_for_backward(cache, R, h, state0 if state0 is not None else torch.empty(0, device=wx.device))
+        ctx.has_state0 = state0 is not None
+        ctx.dtypes = (wx.dtype, R.dtype, bias.dtype, None if state0 is None else state0.dtype)
+        ctx.bias_shape = bias.shape
+        return h, last
+
+    @staticmethod
+    def backward(ctx, dh, dlast):
+        cache, R, h, s0 = ctx.saved_tensors
+        s0 = s0 if ctx.has_state0 else None
+        if dh is None:
+            dh = torch.zeros_like(h)
+        dwx, ds0 = slstm_backward(cache, R, dh, dlast, s0)
+        dR = db = None
+        if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
+            dR, db = slstm_weight_grads(dwx, h, s0)
+            dR = dR.to(ctx.dtypes[1])
+            db = db.reshape(ctx.bias_shape).to(ctx.dtypes[2])
+        return (dwx.to(ctx.dtypes[0]), dR, db, ds0.to(ctx.dtypes[3]) if ctx.has_state0 else None)
 
 
 def add_rmsnorm(x, weight, y=None, eps: float = 1e-6, inplace: bool = False):
