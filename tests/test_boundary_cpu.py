@@ -31,7 +31,8 @@ def test_struct_layouts_match_header_field_order():
                           ("xl_headnorm_gate_params", _lib.HeadnormGateParams), ("xl_soft_cap_params", _lib.SoftCapParams),
                           ("xl_conv1d_params", _lib.Conv1dParams), ("xl_greedy_params", _lib.GreedyParams),
                           ("xl_swiglu_params", _lib.SwigluParams), ("xl_peer_reduce_params", _lib.PeerReduceParams),
-                          ("xl_headwise_params", _lib.HeadwiseParams), ("xl_mlstm_decode_cell_params", _lib.MlstmDecodeCellParams)):
+                          ("xl_headwise_params", _lib.HeadwiseParams), ("xl_mlstm_decode_cell_params", _lib.MlstmDecodeCellParams),
+                          ("xl_slstm_bwd_params", _lib.SlstmBwdParams)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), header, re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         body = re.sub(r"\[\d+\]", "", body)   # array members: the name is what counts
@@ -97,6 +98,23 @@ def test_newer_entry_points_validate_before_launching():
     dc.step.DHV = 128
     dc.gr_sb, dc.o_sb, dc.hg_sb = 2, 256, 256
     assert l.xl_mlstm_decode_cell(ctypes.byref(dc), None) == -3      # gate rows shorter than 2 * NH
+    sb = _lib.SlstmBwdParams()
+    assert l.xl_slstm_backward(ctypes.byref(sb), None) == -1         # null pointers
+    sb.cache = sb.R = sb.dh = sb.dwx = sb.dstate0 = 0x1000
+    sb.B, sb.S, sb.NH, sb.DH, sb.dtype = 2, 3, 2, 64, 0
+    assert l.xl_slstm_backward(ctypes.byref(sb), None) == -5         # bf16 only
+    sb.dtype, sb.DH = 1, 96
+    assert l.xl_slstm_backward(ctypes.byref(sb), None) == -6         # head size not covered
+    sb.DH, sb.dwx = 64, 0x1008
+    assert l.xl_slstm_backward(ctypes.byref(sb), None) == -4         # dwx leaves in 16-byte pieces
+    assert l.xl_slstm_cache_bytes(16, 2048, 4, 256) == 32 * 2048 * 128 * 96
+    assert l.xl_slstm_cache_bytes(17, 1, 1, 64) == 2 * 2 * 128 * 96   # two 16-row groups, two CTAs per cluster
+    assert l.xl_slstm_cache_bytes(4, 4, 1, 48) == 0
+    sl = _lib.SlstmParams()
+    sl.wx = sl.R = sl.bias = sl.h_out = sl.state_out = 0x1000
+    sl.B, sl.S, sl.NH, sl.DH, sl.dtype = 2, 3, 2, 64, 1
+    sl.train_cache, sl.cu_seqlens, sl.num_docs = 0x2000, 0x3000, 1
+    assert l.xl_slstm_forward(ctypes.byref(sl), None) == -6          # no training cache with document offsets
 
 
 def test_ops_refuse_cpu_tensors():

@@ -308,6 +308,54 @@ def test_reference_block_stack_b200_backend_against_vanilla_full_size():
         assert e < max(1e-2, 1.25 * ev)
 
 
+def test_reference_block_stack_trains_through_the_b200_backward_kernel():
+    """A training step of the unchanged ``xLSTMBlockStack`` (two sLSTM blocks, embedding 256, 4 heads, B=4, S=96) with
+    backend "b200": loss.backward() runs the backward-through-time kernel behind every cell.  Gradients of the input
+    and of ALL parameters (recurrent matrices and cell biases included) against the vanilla backend in fp32 on the
+    same bf16-representable weights; the vanilla backend in bf16 gives the noise level of a bf16 stack."""
+    import xlstm_b200
+    B, S, D = 4, 96, 256
+    ref32 = _slstm_stack("vanilla", torch.float32, num_blocks=2, embedding_dim=D)
+    _load_stack_weights(ref32, ref32, bf16_round=True)
+    ours = _slstm_stack("b200", torch.bfloat16, ref32, num_blocks=2, embedding_dim=D)
+    van16 = _slstm_stack("vanilla", torch.bfloat16, ref32, num_blocks=2, embedding_dim=D)
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(B, S, D, generator=g).bfloat16().float()
+    w = torch.randn(B, S, D, generator=g).bfloat16().float()
+
+    def grads(stack, dtype):
+        stack.train()
+        xi = x.cuda().to(dtype).requires_grad_()
+        (stack(xi).float() * w.cuda()).sum().backward()
+        out = {"input": xi.grad.float().cpu()}
+        for name, prm in stack.named_parameters():
+            if prm.grad is not None and "slstm_cell._" not in name:
+                out[name] = prm.grad.float().cpu()
+        # cell parameters in the external layout, which all backends share
+        for i, blk in enumerate(stack.blocks):
+            cell = blk.xlstm.slstm_cell
+            out[f"blocks.{i}.R"] = cell._recurrent_kernel_int2ext(cell._recurrent_kernel_.grad.float()).cpu()
+            out[f"blocks.{i}.bias"] = cell._bias_int2ext(cell._bias_.grad.float()).cpu()
+        return out
+
+    g_ref = grads(ref32, torch.float32)
+    g_our = grads(ours, torch.bfloat16)
+    xlstm_b200.check_device_status()
+    g_van = grads(van16, torch.bfloat16)
+    assert set(g_our) == set(g_ref)
+    worst = 0.0
+    for name in sorted(g_ref):
+        if float(g_ref[name].norm()) == 0.0:
+            continue
+        e, ev = rel_l2(g_our[name], g_ref[name]), rel_l2(g_van[name], g_ref[name])
+        worst = max(worst, e)
+        if name == "input" or name.endswith((".R", ".bias")):
+            print(f"{name}: b200 vs vanilla-fp32 {e:.2e}; vanilla-bf16 vs vanilla-fp32 {ev:.2e}")
+        assert torch.isfinite(g_our[name]).all(), name
+        assert e < max(3e-2, 2.0 * ev), (name, e, ev)   # parameter gradients of a bf16 stack: sums over B*S of bf16 terms
+    print(f"worst parameter gradient error {worst:.2e}")
+
+
 def test_reference_slstm_cell_b200_vs_vanilla_small_with_initial_state():
     """The reference's cell-level test shape (tests/test_slstm_cell_vanilla_vs_cuda.py:12-56: hidden 64, 4 heads,
     input (1,1,256)) plus a longer batch, with and without a random initial state, R initialised."""

@@ -39,3 +39,24 @@ def test_reset_equals_separate_documents():
     assert rel_l2(out[0, :, :5], a[0]) < 1e-6
     assert rel_l2(out[0, :, 5:], b[0]) < 1e-6
     assert rel_l2(last[:, 0], lb[:, 0]) < 1e-6
+
+
+@pytest.mark.parametrize("name", ["slstm_grad", "slstm_grad_state"])
+@pytest.mark.parametrize("stabiliser_grad", [True, False])
+def test_autograd_of_the_oracle_matches_reference_vanilla_gradients(name, stabiliser_grad):
+    """Autograd over the oracle is the oracle of the backward kernel: it reproduces the gradients autograd gives over
+    the reference's vanilla cell, with the stabiliser differentiated or held constant (the loss reads h only)."""
+    g = load_golden(name)
+    wx = g["wx"].clone().requires_grad_()
+    R = g["R"].clone().requires_grad_()
+    bias = g["bias"].clone().requires_grad_()
+    s0 = g["state0"].clone().requires_grad_() if "state0" in g else None
+    out, last = O.slstm_forward(wx, R, bias, s0, stabiliser_grad=stabiliser_grad)
+    assert rel_l2(out.detach(), g["out"]) < 1e-5
+    ((out * g["gh"]).sum() + (last[0] * g["gl"]).sum()).backward()
+    assert rel_l2(wx.grad, g["dwx"]) < 1e-4
+    assert rel_l2(R.grad, g["dR"]) < 1e-4
+    assert rel_l2(bias.grad, g["dbias"]) < 1e-4
+    if s0 is not None:
+        for i in range(3):  # h, c, n; the stabiliser's own gradient is a matter of convention
+            assert rel_l2(s0.grad[i], g["dstate0"][i]) < 1e-4

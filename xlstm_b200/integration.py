@@ -109,7 +109,14 @@ def install_slstm_backend():
             if state is not None:
                 assert state.shape == (self.config.num_states, input.shape[0], self.config.hidden_size)
             x, R, b, s0 = self._cast_inputs(input, state)
-            out, last = ops.slstm_forward(x, R, b, s0, cu_seqlens=self._cu_seqlens)
+            if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (x, R, b, s0)):
+                # training: the cache-writing forward with the backward-through-time kernel behind it
+                # (sLSTMCellFunction, cell.py:543-598)
+                if self._cu_seqlens is not None:
+                    raise ValueError("the b200 sLSTM backward pass takes no document offsets")
+                out, last = ops.SlstmFunction.apply(x, R, b, s0)
+            else:
+                out, last = ops.slstm_forward(x, R, b, s0, cu_seqlens=self._cu_seqlens)
             if torch.is_autocast_enabled():
                 return out, last
             return out.to(input.dtype), last.to(input.dtype)
