@@ -214,6 +214,68 @@ def slstm_reference_cuda(cfg, dev, our_ms):
         return {"reference_cuda_unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
 
 
+def slstm_training(cfg, dev):
+    """The training path of the same cell: the cache-writing forward, the backward-through-time kernel and the two sums
+    for the recurrent matrix and the bias (library GEMM), device-timed; beside it the reference's backend="cuda" cell
+    doing forward + backward at the same shape (slstm.cc:53-254: host loops of cuBLAS calls and pointwise kernels)."""
+    from xlstm_b200 import ops
+    B, S, NH, DH = cfg["B"], cfg["S"], cfg["NH"], cfg["DH"]
+    H = NH * DH
+    g = torch.Generator(device=dev).manual_seed(9)
+    wx = torch.randn(B, S, 4 * H, device=dev, generator=g).bfloat16()
+    R = ((torch.rand(NH, DH, 4, DH, device=dev, generator=g) * 2 - 1) / H ** 0.5).bfloat16()
+    bias = torch.randn(NH, 4, DH, device=dev, generator=g) * 0.5
+    gh = torch.randn(B, NH, S, DH, device=dev, generator=g).bfloat16()
+
+    def timed(fn, n=5):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    out = {}
+    h, last, cache = ops.slstm_forward(wx, R, bias, train_cache=True)
+    out["forward_with_cache_ms"] = timed(lambda: ops.slstm_forward(wx, R, bias, train_cache=True))
+    out["backward_kernel_ms"] = timed(lambda: ops.slstm_backward(cache, R, gh))
+    dwx, _ = ops.slstm_backward(cache, R, gh)
+    out["weight_grads_ms"] = timed(lambda: ops.slstm_weight_grads(dwx, h))
+    out["fwd_bwd_ms"] = out["forward_with_cache_ms"] + out["backward_kernel_ms"] + out["weight_grads_ms"]
+    out["cache_bytes"] = cache.numel()
+    out["kernel"] = "slstm_backward_kernel<%d>" % DH
+    del cache, dwx
+    root = reference_root()
+    if root is None:
+        out["reference_cuda_unavailable"] = "reference package not found (XLSTM_REFERENCE or baseline/_ref)"
+        return {"training": out}
+    try:
+        if root not in sys.path:
+            sys.path.insert(0, root)
+        os.environ.setdefault("TORCH_EXTENSIONS_DIR", os.path.join(ROOT, "baseline", "_ref_ext"))
+        from xlstm.blocks.slstm.cell import sLSTMCell, sLSTMCellConfig
+        torch.manual_seed(0)
+        cell = sLSTMCell(sLSTMCellConfig(hidden_size=H, num_heads=NH, backend="cuda", dtype="bfloat16", batch_size=B,
+                                         recurrent_weight_init="standard")).to(dev).train()
+        x = wx.clone().requires_grad_()
+
+        def ref_step():
+            cell.zero_grad(set_to_none=True)
+            x.grad = None
+            o, _ = cell(x)
+            o.backward(gh)
+
+        out["reference_cuda_fwd_bwd_ms"] = timed(ref_step, n=3)
+        out["speedup_vs_reference_cuda"] = out["reference_cuda_fwd_bwd_ms"] / out["fwd_bwd_ms"]
+    except Exception as e:
+        out["reference_cuda_unavailable"] = f"{type(e).__name__}: {str(e)[:200]}"
+    return {"training": out}
+
+
 def slstm_gate_projections(cfg, dev):
     """The front of the same sLSTM layer: four headwise gate projections + concatenation at the cell's shape, as ONE
     kernel (xl_headwise_proj) and as the reference layer's eager operators (four einsum calls and torch.cat,
@@ -332,7 +394,7 @@ def build_case(name, dev, rank):
                     kernel="slstm_forward_kernel<256>", h2d=wx_h.numel() * 2, d2h=o_host.numel() * 2,
                     l2="inputs (%d MB) exceed the 126 MB L2" % (slstm_bytes(**cfg) // 10 ** 6), launches=1,
                     traffic=323.9e6, traffic_source="constant: ncu dram__bytes_read.sum + dram__bytes_write.sum of ONE captured launch of this workload, not measured in this run",
-                    extra=lambda m: {**slstm_reference_cuda(cfg, dev, m["kernel_ms"]), **slstm_gate_projections(cfg, dev)})
+                    extra=lambda m: {**slstm_reference_cuda(cfg, dev, m["kernel_ms"]), **slstm_gate_projections(cfg, dev), **slstm_training(cfg, dev)})
     if name == "headwise":
         # the four headwise gate projections + concatenation in front of the sLSTM cell, at the cell's benchmark shape
         cfg = dict(SLSTM_CFG)

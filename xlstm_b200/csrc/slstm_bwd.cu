@@ -13,9 +13,12 @@
 //   dh_{t-1}[b,k] = sum_{g,u} dg_t[b,g,u] R[k,g,u].
 // The CTA holds exactly the slice of R the forward holds (all k, its own 32 units, four gates) as mma.sync
 // B-fragments in registers, now contracted over (g,u): it forms the PARTIAL sums of dh_{t-1} for all DH columns
-// from its own 128 gate gradients (M = 16 rows, N = DH, K = 128) and sends every 32-column block to the CTA that
-// owns those units with asynchronous distributed-shared-memory stores that count their bytes on the receiver's
-// mbarrier (a reduce-scatter: DH/32 x 2 KB per CTA and step); the receiver adds the DH/32 partials in rank order.
+// from its own 128 gate gradients (M = 16 rows, N = DH, K = 128), stages them per destination in shared memory and
+// sends every 32-column block to the CTA that owns those units with ONE bulk asynchronous copy into that CTA's
+// shared memory, which counts its bytes on the receiver's mbarrier (a reduce-scatter: DH/32 copies of 2.3 KB per CTA
+// and step; the same exchange as 2 048 eight-byte remote stores per CTA cost 1 200 cycles of issue per step); the
+// receiver adds the DH/32 partials in rank order.  Everything of a step's gate arithmetic that does not depend on
+// the incoming gradient is computed one step ahead, while the partials are in flight.
 // dWx_t = dg_t leaves as bf16 in the layout of Wx.  dR and dbias are sums over (b,t) of h_{t-1} (x) dg_t and of dg_t:
 // plain matrix products over the dWx this kernel writes, left to the caller's GEMM library.
 #include "common.cuh"
@@ -25,14 +28,16 @@ namespace xl {
 
 constexpr int SLB_DG_STRIDE = 4 * SL_UNITS + 8;          // bf16 elements per row of the dg tile (+16 B: bank spread)
 constexpr int SLB_REC_STEP = SL_THREADS * SL_REC_BYTES;  // cache bytes per CTA and step
+constexpr int SLB_PROW = SL_UNITS + 4;                   // floats per row of a partial block (+16 B: rows on distinct banks)
+constexpr int SLB_PBLOCK = SL_ROWS * SLB_PROW * 4;       // bytes of one (source, destination) block of partial sums
 
 __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
-// 8-byte store into (another) CTA's shared memory that adds its bytes to the transaction count of an mbarrier there
-__device__ __forceinline__ void st_async_f32x2(uint32_t addr, float a, float b, uint32_t remote_bar) {
-  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.b32 [%0], {%1, %2}, [%3];" ::"r"(addr),
-               "r"(__float_as_uint(a)), "r"(__float_as_uint(b)), "r"(remote_bar)
+// bulk copy from this CTA's shared memory into (another) CTA's, counted on an mbarrier of the destination CTA
+__device__ __forceinline__ void bulk_copy_to_cta(uint32_t remote_dst, uint32_t local_src, uint32_t bytes, uint32_t remote_bar) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(remote_dst),
+               "r"(local_src), "r"(bytes), "r"(remote_bar)
                : "memory");
 }
 
@@ -41,11 +46,12 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_backward_kernel(const xl_
   constexpr int NCTA = DH / SL_UNITS;
   constexpr int NTW = DH / 32;              // n8 tiles (8 columns of dh_{t-1}) per warp
   constexpr int KS = 4 * SL_UNITS / 16;     // k-steps over the CTA's 128 gate gradients
-  constexpr uint32_t RB_BYTES = NCTA * SL_ROWS * SL_UNITS * 4;   // what one step delivers to a CTA
+  constexpr uint32_t RB_BYTES = NCTA * SLB_PBLOCK;   // what one step delivers to a CTA
   extern __shared__ __align__(16) unsigned char slb_smem[];
   __nv_bfloat16* s_dg = reinterpret_cast<__nv_bfloat16*>(slb_smem);                   // [16][SLB_DG_STRIDE]
-  float* s_rb = reinterpret_cast<float*>(slb_smem + SL_ROWS * SLB_DG_STRIDE * 2);     // [2][NCTA][16][32]
-  unsigned char* s_rec = reinterpret_cast<unsigned char*>(s_rb) + 2 * RB_BYTES;       // [SL_RING][SLB_REC_STEP]
+  float* s_rb = reinterpret_cast<float*>(slb_smem + SL_ROWS * SLB_DG_STRIDE * 2);     // received: [2][source CTA][16][SLB_PROW]
+  float* s_st = s_rb + 2 * RB_BYTES / 4;                                              // staged: [2][destination CTA][16][SLB_PROW]
+  unsigned char* s_rec = reinterpret_cast<unsigned char*>(s_st) + 2 * RB_BYTES;       // [SL_RING][SLB_REC_STEP]
   uint32_t* s_dh = reinterpret_cast<uint32_t*>(s_rec + SL_RING * SLB_REC_STEP);       // [SL_RING][128][2]
   const uint32_t s_bar = smem_u32(s_dh + SL_RING * SL_THREADS * 2);                   // 2 mbarriers
 
@@ -120,19 +126,15 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_backward_kernel(const xl_
   for (int j = 0; j < SL_RING - 1; ++j) issue(S - 1 - j);
   cluster_barrier();  // every CTA's barriers exist before anything crosses over; also a CTA-wide barrier
 
-  const uint32_t s_dg_u32 = smem_u32(s_dg), s_rb_u32 = smem_u32(s_rb);
+  const uint32_t s_dg_u32 = smem_u32(s_dg), s_rb_u32 = smem_u32(s_rb), s_st_u32 = smem_u32(s_st);
   const uint32_t ldm_off = ((lane & 15) * SLB_DG_STRIDE + (lane >> 4) * 8) * 2;
   __nv_bfloat16* dwx = reinterpret_cast<__nv_bfloat16*>(p.dwx);
 
-  bool ok = true;
-  for (int it = 0; it < S; ++it) {
-    const int t = S - 1 - it;
-    const int buf = it & 1;
-    issue(t - (SL_RING - 1));
-    if (tid == 0) mbar_expect_tx(s_bar + 8u * buf, RB_BYTES);
-    cp_async_wait<SL_RING - 2>();   // the records of steps t and t-1 (this thread's) have landed
-
-    // ---- pointwise backward in registers
+  // Per pair, everything of a step that does not depend on the incoming gradient (formed one step ahead):
+  //   dc = dc_carry + dy pa;  dn = dn_carry - dy pb;  dg_i = pig (pzt dc + dn);  dg_f = pff (dc pcp + dn pnp);
+  //   dg_z = dc pz2;  dg_o = po2 dy;  carries <- pfg (dc, dn);  dy = dup + recurrent part
+  float pa[4], pb[4], pig[4], pzt[4], pfg[4], pff[4], pcp[4], pnp[4], pz2[4], po2[4], dup[4];
+  auto precompute = [&](int t) {
     const unsigned char* rt = s_rec + (t % SL_RING) * SLB_REC_STEP + tid * SL_REC_BYTES;
     const uint4 ga = *reinterpret_cast<const uint4*>(rt), gbw = *reinterpret_cast<const uint4*>(rt + 16);
     const uint2 hw = *reinterpret_cast<const uint2*>(rt + 32);
@@ -160,34 +162,58 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_backward_kernel(const xl_
       m_prev = make_float4(mp[0], mp[1], mp[2], mp[3]);
     }
     const uint2 dhw = *reinterpret_cast<const uint2*>(s_dh + (t % SL_RING) * (SL_THREADS * 2) + tid * 2);
-    float dgi[4], dgf[4], dgz[4], dgo[4];
-    {
-      const float2 ia = unpack_bf16x2(ga.x), fa = unpack_bf16x2(ga.y), za = unpack_bf16x2(ga.z), oa = unpack_bf16x2(ga.w);
-      const float2 ib = unpack_bf16x2(gbw.x), fb = unpack_bf16x2(gbw.y), zb = unpack_bf16x2(gbw.z), ob = unpack_bf16x2(gbw.w);
-      const float2 ya = unpack_bf16x2(hw.x), yb = unpack_bf16x2(hw.y);
-      const float2 da = unpack_bf16x2(dhw.x), db = unpack_bf16x2(dhw.y);
-      const float ig[4] = {ia.x, ia.y, ib.x, ib.y}, fr[4] = {fa.x, fa.y, fb.x, fb.y};
-      const float zt[4] = {za.x, za.y, zb.x, zb.y}, os[4] = {oa.x, oa.y, ob.x, ob.y};
-      const float yn[4] = {ya.x, ya.y, yb.x, yb.y};
-      const float dup[4] = {ok_a ? da.x : 0.f, ok_a ? da.y : 0.f, ok_b ? db.x : 0.f, ok_b ? db.y : 0.f};
-      const float nn[4] = {n_new.x, n_new.y, n_new.z, n_new.w}, mn[4] = {m_new.x, m_new.y, m_new.z, m_new.w};
-      const float cp[4] = {c_prev.x, c_prev.y, c_prev.z, c_prev.w}, np[4] = {n_prev.x, n_prev.y, n_prev.z, n_prev.w};
-      const float mp[4] = {m_prev.x, m_prev.y, m_prev.z, m_prev.w};
+    const float2 ia = unpack_bf16x2(ga.x), fa = unpack_bf16x2(ga.y), za = unpack_bf16x2(ga.z), oa = unpack_bf16x2(ga.w);
+    const float2 ib = unpack_bf16x2(gbw.x), fb = unpack_bf16x2(gbw.y), zb = unpack_bf16x2(gbw.z), ob = unpack_bf16x2(gbw.w);
+    const float2 ya = unpack_bf16x2(hw.x), yb = unpack_bf16x2(hw.y);
+    const float2 da = unpack_bf16x2(dhw.x), db = unpack_bf16x2(dhw.y);
+    const float ig[4] = {ia.x, ia.y, ib.x, ib.y}, fr[4] = {fa.x, fa.y, fb.x, fb.y};
+    const float zt[4] = {za.x, za.y, zb.x, zb.y}, os[4] = {oa.x, oa.y, ob.x, ob.y};
+    const float yn[4] = {ya.x, ya.y, yb.x, yb.y};
+    const float du[4] = {ok_a ? da.x : 0.f, ok_a ? da.y : 0.f, ok_b ? db.x : 0.f, ok_b ? db.y : 0.f};
+    const float nn[4] = {n_new.x, n_new.y, n_new.z, n_new.w}, mn[4] = {m_new.x, m_new.y, m_new.z, m_new.w};
+    const float cp[4] = {c_prev.x, c_prev.y, c_prev.z, c_prev.w}, np[4] = {n_prev.x, n_prev.y, n_prev.z, n_prev.w};
+    const float mp[4] = {m_prev.x, m_prev.y, m_prev.z, m_prev.w};
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float dy = dup[i] + dhrec[i];
-        const float dyi = __fdividef(dy, nn[i]);
-        const float dc = fmaf(dyi, os[i], dc_[i]);
-        const float dn = fmaf(-dyi, yn[i], dn_[i]);
-        const float fg = fminf(1.f, __expf(fast_logsigmoid(fr[i]) + mp[i] - mn[i]));
-        const float fsig = __fdividef(1.f, 1.f + __expf(-fr[i]));
-        dgi[i] = ig[i] * fmaf(zt[i], dc, dn);
-        dgf[i] = fg * fmaf(dc, cp[i], dn * np[i]) * (1.f - fsig);
-        dgz[i] = dc * ig[i] * (1.f - zt[i] * zt[i]);
-        dgo[i] = (1.f - os[i]) * yn[i] * dy;
-        dc_[i] = fg * dc;
-        dn_[i] = fg * dn;
-      }
+    for (int i = 0; i < 4; ++i) {
+      const float rn = __fdividef(1.f, nn[i]);
+      const float fg = fminf(1.f, __expf(fast_logsigmoid(fr[i]) + mp[i] - mn[i]));
+      const float fsig = __fdividef(1.f, 1.f + __expf(-fr[i]));
+      pa[i] = os[i] * rn;
+      pb[i] = yn[i] * rn;
+      pig[i] = ig[i];
+      pzt[i] = zt[i];
+      pfg[i] = fg;
+      pff[i] = fg * (1.f - fsig);
+      pcp[i] = cp[i];
+      pnp[i] = np[i];
+      pz2[i] = ig[i] * (1.f - zt[i] * zt[i]);
+      po2[i] = (1.f - os[i]) * yn[i];
+      dup[i] = du[i];
+    }
+  };
+  cp_async_wait<SL_RING - 3>();   // the records of the last two steps have landed (this thread's)
+  precompute(S - 1);
+
+  bool ok = true;
+  for (int it = 0; it < S; ++it) {
+    const int t = S - 1 - it;
+    const int buf = it & 1;
+    issue(t - (SL_RING - 1));
+    if (tid == 0) mbar_expect_tx(s_bar + 8u * buf, RB_BYTES);
+
+    // ---- the part of the pointwise backward that depends on the incoming gradient
+    float dgi[4], dgf[4], dgz[4], dgo[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float dy = dup[i] + dhrec[i];
+      const float dc = fmaf(dy, pa[i], dc_[i]);
+      const float dn = fmaf(-dy, pb[i], dn_[i]);
+      dgi[i] = pig[i] * fmaf(pzt[i], dc, dn);
+      dgf[i] = pff[i] * fmaf(dc, pcp[i], dn * pnp[i]);
+      dgz[i] = dc * pz2[i];
+      dgo[i] = po2[i] * dy;
+      dc_[i] = pfg[i] * dc;
+      dn_[i] = pfg[i] * dn;
     }
     // ---- dg_t of this CTA (16 rows x [4 gates x 32 units]) as the A operand of the recurrent product
     {
@@ -214,16 +240,29 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_backward_kernel(const xl_
 #pragma unroll
       for (int j = 0; j < NTW; ++j) mma_bf16_16816(acc[j], a0, a1, a2, a3, bfrag[j][ks][0], bfrag[j][ks][1]);
     }
-    // ---- every 8-column tile goes to the CTA that owns those units: slot [buf][this CTA][row][column]
+    // ---- stage the partials per destination CTA (columns 32 d .. 32 d + 31 belong to CTA d) ...
 #pragma unroll
     for (int j = 0; j < NTW; ++j) {
       const int tile = warp * NTW + j;                 // columns 8 tile .. 8 tile + 7 of the head
-      const uint32_t dst = (uint32_t)(tile >> 2);
-      const uint32_t col = (uint32_t)((tile & 3) * 8 + (lane & 3) * 2);
-      const uint32_t base = s_rb_u32 + (((uint32_t)buf * NCTA + rank) * SL_ROWS * SL_UNITS + col) * 4;
-      const uint32_t rbar = map_to_cta(s_bar + 8u * buf, dst);
-      st_async_f32x2(map_to_cta(base + row_a * (SL_UNITS * 4), dst), acc[j][0], acc[j][1], rbar);
-      st_async_f32x2(map_to_cta(base + row_b * (SL_UNITS * 4), dst), acc[j][2], acc[j][3], rbar);
+      float* blk = s_st + ((size_t)(buf * NCTA + (tile >> 2)) * SL_ROWS) * SLB_PROW + (tile & 3) * 8 + (lane & 3) * 2;
+      *reinterpret_cast<float2*>(blk + row_a * SLB_PROW) = make_float2(acc[j][0], acc[j][1]);
+      *reinterpret_cast<float2*>(blk + row_b * SLB_PROW) = make_float2(acc[j][2], acc[j][3]);
+    }
+    fence_proxy_async_smem();
+    // ... and send every block with one bulk copy into slot [buf][this CTA] of its owner.  A warp produces whole
+    // blocks when it covers at least 32 columns; otherwise the CTA synchronises first.
+    if constexpr (NTW >= 4) {
+      __syncwarp();
+      if (lane < NTW / 4) {
+        const uint32_t dst = (uint32_t)(warp * (NTW / 4) + lane);
+        bulk_copy_to_cta(map_to_cta(s_rb_u32 + ((uint32_t)buf * NCTA + rank) * SLB_PBLOCK, dst),
+                         s_st_u32 + ((uint32_t)buf * NCTA + dst) * SLB_PBLOCK, SLB_PBLOCK, map_to_cta(s_bar + 8u * buf, dst));
+      }
+    } else {
+      __syncthreads();
+      if (tid < NCTA)
+        bulk_copy_to_cta(map_to_cta(s_rb_u32 + ((uint32_t)buf * NCTA + rank) * SLB_PBLOCK, (uint32_t)tid),
+                         s_st_u32 + ((uint32_t)buf * NCTA + tid) * SLB_PBLOCK, SLB_PBLOCK, map_to_cta(s_bar + 8u * buf, (uint32_t)tid));
     }
     // ---- dWx_t = dg_t, (B, S, 4, NH, DH), from the tile: 16-byte pieces, two per thread (off the step-to-step chain)
 #pragma unroll
@@ -235,15 +274,18 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_backward_kernel(const xl_
         *reinterpret_cast<uint4*>(dwx + (((size_t)gb * S + t) * 4 + g) * H + (size_t)head * DH + rank * SL_UNITS + part * 8) =
             *reinterpret_cast<const uint4*>(s_dg + r * SLB_DG_STRIDE + g * SL_UNITS + part * 8);
     }
+    // ---- while the partials are in flight: the gradient-independent part of the next step (t - 1)
+    cp_async_wait<SL_RING - 3>();   // the records of steps t-1 and t-2 (this thread's) have landed
+    if (t >= 1) precompute(t - 1);
     // ---- the DH/32 partials of this CTA's own columns have landed: add them in rank order
     if (!sl_wait(s_bar + 8u * buf, (uint32_t)(it >> 1) & 1u)) ok = false;
     {
-      const float* rb0 = s_rb + (size_t)buf * NCTA * SL_ROWS * SL_UNITS + unit_l;
+      const float* rb0 = s_rb + (size_t)buf * NCTA * SL_ROWS * SLB_PROW + unit_l;
       float2 sa = make_float2(0.f, 0.f), sb = make_float2(0.f, 0.f);
 #pragma unroll
       for (int s = 0; s < NCTA; ++s) {
-        const float2 va = *reinterpret_cast<const float2*>(rb0 + (s * SL_ROWS + row_a) * SL_UNITS);
-        const float2 vb = *reinterpret_cast<const float2*>(rb0 + (s * SL_ROWS + row_b) * SL_UNITS);
+        const float2 va = *reinterpret_cast<const float2*>(rb0 + (s * SL_ROWS + row_a) * SLB_PROW);
+        const float2 vb = *reinterpret_cast<const float2*>(rb0 + (s * SL_ROWS + row_b) * SLB_PROW);
         sa.x += va.x; sa.y += va.y; sb.x += vb.x; sb.y += vb.y;
       }
       dhrec[0] = sa.x; dhrec[1] = sa.y; dhrec[2] = sb.x; dhrec[3] = sb.y;
@@ -273,7 +315,7 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_backward_kernel(const xl_
 template <int DH>
 static int launch_slstm_bwd(const xl_slstm_bwd_params* p, cudaStream_t st) {
   constexpr int NCTA = DH / SL_UNITS;
-  const size_t smem = (size_t)SL_ROWS * SLB_DG_STRIDE * 2 + 2 * (size_t)NCTA * SL_ROWS * SL_UNITS * 4 +
+  const size_t smem = (size_t)SL_ROWS * SLB_DG_STRIDE * 2 + 4 * (size_t)NCTA * SLB_PBLOCK +
                       (size_t)SL_RING * SLB_REC_STEP + (size_t)SL_RING * SL_THREADS * 8 + 16;
   XL_CUDA_TRY(cudaFuncSetAttribute(slstm_backward_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
