@@ -2,9 +2,12 @@
 // BackwardPass::Run + SLSTMPointwiseBackward: xlstm/blocks/slstm/src/cuda/slstm_backward.cu,
 // slstm_pointwise.cu:118-196).
 //
-// Same mapping as the forward kernel: one thread-block cluster of DH/32 CTAs per (head, 16-row batch group), CTA r
-// owns hidden units [32r, 32r+32) with all four gates, a thread owns four (row, unit) pairs and keeps their gradient
-// carries dc, dn in fp32 registers for the whole sequence.  Per step, walking t = S-1 .. 0:
+// Same decomposition as the forward kernel: one thread-block cluster of DH/32 CTAs per (head, 16-row batch group),
+// CTA r owns hidden units [32r, 32r+32) with all four gates.  A CTA has EIGHT warps here (the forward has four): warps
+// 2w and 2w+1 share the four (row, unit) pairs of forward thread (w, lane) -- the first takes the pairs of batch row
+// lane/4, the second those of row lane/4 + 8 -- and keep their gradient carries dc, dn in fp32 registers for the
+// whole sequence.  (With four warps every scheduler of the SM had one warp, whose ~1 000 instructions per step ran at
+// one instruction per ~3.7 cycles; two half-as-long instruction streams per scheduler interleave.)  Per step, walking t = S-1 .. 0:
 //   dy = dh_t (from above) + dh_t (recurrent);  dc += dy o / n';  dn -= dy h' / n'
 //   dg_i = i' (z dc + dn);  dg_f = f' (dc c + dn n)(1 - sigmoid(f));  dg_z = dc i' (1 - z^2);  dg_o = (1 - o) h' dy
 //   dc <- f' dc;  dn <- f' dn          (the stabiliser m is a constant of the step, as in the reference)
@@ -27,12 +30,21 @@
 namespace xl {
 
 constexpr int SLB_DG_STRIDE = 4 * SL_UNITS + 8;          // bf16 elements per row of the dg tile (+16 B: bank spread)
-constexpr int SLB_REC_STEP = SL_THREADS * SL_REC_BYTES;  // cache bytes per CTA and step
+constexpr int SLB_THREADS = 256;                         // 8 warps
+constexpr int SLB_REC_STEP = SL_THREADS * SL_REC_BYTES;  // cache bytes per CTA and step (records of the forward's 128 threads)
 constexpr int SLB_PROW = SL_UNITS + 4;                   // floats per row of a partial block (+16 B: rows on distinct banks)
 constexpr int SLB_PBLOCK = SL_ROWS * SLB_PROW * 4;       // bytes of one (source, destination) block of partial sums
 
-__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+// bulk copy global -> this CTA's shared memory, counted on one of its mbarriers
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+               "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t ldg_nc_u32(const void* ptr) {
+  uint32_t v;
+  asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(v) : "l"(ptr));
+  return v;
 }
 // bulk copy from this CTA's shared memory into (another) CTA's, counted on an mbarrier of the destination CTA
 __device__ __forceinline__ void bulk_copy_to_cta(uint32_t remote_dst, uint32_t local_src, uint32_t bytes, uint32_t remote_bar) {
@@ -42,28 +54,31 @@ __device__ __forceinline__ void bulk_copy_to_cta(uint32_t remote_dst, uint32_t l
 }
 
 template <int DH>
-__global__ void __launch_bounds__(SL_THREADS, 1) slstm_backward_kernel(const xl_slstm_bwd_params p) {
+__global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl_slstm_bwd_params p) {
   constexpr int NCTA = DH / SL_UNITS;
-  constexpr int NTW = DH / 32;              // n8 tiles (8 columns of dh_{t-1}) per warp
+  constexpr int NTW = DH / 64;              // n8 tiles (8 columns of dh_{t-1}) per warp
   constexpr int KS = 4 * SL_UNITS / 16;     // k-steps over the CTA's 128 gate gradients
   constexpr uint32_t RB_BYTES = NCTA * SLB_PBLOCK;   // what one step delivers to a CTA
   extern __shared__ __align__(16) unsigned char slb_smem[];
-  __nv_bfloat16* s_dg = reinterpret_cast<__nv_bfloat16*>(slb_smem);                   // [16][SLB_DG_STRIDE]
-  float* s_rb = reinterpret_cast<float*>(slb_smem + SL_ROWS * SLB_DG_STRIDE * 2);     // received: [2][source CTA][16][SLB_PROW]
+  __nv_bfloat16* s_dg = reinterpret_cast<__nv_bfloat16*>(slb_smem);                   // [2][16][SLB_DG_STRIDE]
+  float* s_rb = reinterpret_cast<float*>(slb_smem + 2 * SL_ROWS * SLB_DG_STRIDE * 2); // received: [2][source CTA][16][SLB_PROW]
   float* s_st = s_rb + 2 * RB_BYTES / 4;                                              // staged: [2][destination CTA][16][SLB_PROW]
   unsigned char* s_rec = reinterpret_cast<unsigned char*>(s_st) + 2 * RB_BYTES;       // [SL_RING][SLB_REC_STEP]
-  uint32_t* s_dh = reinterpret_cast<uint32_t*>(s_rec + SL_RING * SLB_REC_STEP);       // [SL_RING][128][2]
-  const uint32_t s_bar = smem_u32(s_dh + SL_RING * SL_THREADS * 2);                   // 2 mbarriers
+  const uint32_t s_bar = smem_u32(s_rec + SL_RING * SLB_REC_STEP);                    // 2 mbarriers: partials landed
+  const uint32_t s_full = s_bar + 16;                                                 // SL_RING mbarriers: record block landed
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t rank = cluster_ctarank();
   const int head = blockIdx.y, bgroup = blockIdx.z;
   const int B = p.B, S = p.S, NH = p.NH, H = NH * DH;
-  const int row_a = lane >> 2, row_b = row_a + 8;
-  const int unit_l = warp * 8 + (lane & 3) * 2;
-  const int unit_h = (int)rank * SL_UNITS + unit_l;
-  const int gb_a = bgroup * SL_ROWS + row_a, gb_b = bgroup * SL_ROWS + row_b;
-  const bool ok_a = gb_a < B, ok_b = gb_b < B;
+  const int fwarp = warp >> 1, half = warp & 1;           // the forward thread whose record this thread shares, and which row of it
+  const int ftid = fwarp * 32 + lane;
+  const int row = (lane >> 2) + 8 * half;                 // batch row within the group
+  const int unit_l = fwarp * 8 + (lane & 3) * 2;          // first of two adjacent units within the CTA
+  const int unit_h = (int)rank * SL_UNITS + unit_l;       // ... within the head
+  const int gb = bgroup * SL_ROWS + row;                  // global batch row
+  const bool ok_r = gb < B;
+  const size_t st_off = (size_t)(ok_r ? gb : 0) * H + (size_t)head * DH + unit_h;   // this thread's pair in a (4,B,H) state
 
   // ---- the CTA's slice of R as B fragments of dh[b,k] = sum_{(g,u)} dg[b,(g,u)] R[k,g,u]:  n = k, contraction index
   // kk = 32 g + (u - 32 rank); a fragment register holds two adjacent u of one (k, g)
@@ -84,46 +99,44 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_backward_kernel(const xl_
     }
   }
 
-  // ---- gradient carries and the recurrent part of dh for the thread's four pairs, from the gradient of the final state
-  float dc_[4], dn_[4], dhrec[4];
+  // ---- gradient carries and the recurrent part of dh for the thread's two pairs, from the gradient of the final state
+  float dc_[2], dn_[2], dhrec[2];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int gb = (i < 2) ? gb_a : gb_b;
-    const bool okr = (i < 2) ? ok_a : ok_b;
-    const size_t off = (size_t)gb * H + (size_t)head * DH + unit_h + (i & 1);
-    const bool have = p.dstate_out != nullptr && okr;
-    dhrec[i] = have ? p.dstate_out[0 * (size_t)B * H + off] : 0.f;
-    dc_[i] = have ? p.dstate_out[1 * (size_t)B * H + off] : 0.f;
-    dn_[i] = have ? p.dstate_out[2 * (size_t)B * H + off] : 0.f;
+  for (int i = 0; i < 2; ++i) {
+    const bool have = p.dstate_out != nullptr && ok_r;
+    dhrec[i] = have ? p.dstate_out[0 * (size_t)B * H + st_off + i] : 0.f;
+    dc_[i] = have ? p.dstate_out[1 * (size_t)B * H + st_off + i] : 0.f;
+    dn_[i] = have ? p.dstate_out[2 * (size_t)B * H + st_off + i] : 0.f;
   }
 
   if (tid == 0) {
     mbar_init(s_bar, 1);      // one arrival per phase: the local expect_tx
     mbar_init(s_bar + 8, 1);
+    for (int j = 0; j < SL_RING; ++j) mbar_init(s_full + 8u * j, 1);
     fence_barrier_init();
   }
 
-  // ---- cache and dh rings: every thread fetches ITS record (6 x 16 B) and its two dh words of a step
+  // ---- cache ring: the records of one step and CTA are 12 KB of contiguous global memory, fetched SL_RING - 1 steps
+  // ahead by ONE bulk copy that completes on the slot's mbarrier (one cp.async per 16 bytes from every thread cost
+  // 560 cycles of issue per step); record x sits in slot x % SL_RING, which it is use number (S-1-x) / SL_RING of
   const unsigned char* cache = reinterpret_cast<const unsigned char*>(p.cache) +
-                               ((((size_t)bgroup * NH + head) * NCTA + rank) * (size_t)S * SL_THREADS + tid) * SL_REC_BYTES;
-  const __nv_bfloat16* dh = reinterpret_cast<const __nv_bfloat16*>(p.dh);
-  const size_t dh_a = ((size_t)(ok_a ? gb_a : B - 1) * NH + head) * (size_t)S * DH + unit_h;
-  const size_t dh_b = ((size_t)(ok_b ? gb_b : B - 1) * NH + head) * (size_t)S * DH + unit_h;
-  const uint32_t s_rec_u32 = smem_u32(s_rec) + tid * SL_REC_BYTES, s_dh_u32 = smem_u32(s_dh) + tid * 8;
-  auto issue = [&](int t) {
+                               (((size_t)bgroup * NH + head) * NCTA + rank) * (size_t)S * SLB_REC_STEP;
+  const uint32_t s_rec_u32 = smem_u32(s_rec);
+  auto issue = [&](int t) {   // thread 0 only
     if (t >= 0) {
-      const unsigned char* src = cache + (size_t)t * SLB_REC_STEP;
-      const uint32_t dst = s_rec_u32 + (t % SL_RING) * SLB_REC_STEP;
-#pragma unroll
-      for (int j = 0; j < SL_REC_BYTES / 16; ++j) cp_async16(dst + j * 16, src + j * 16);
-      const uint32_t dd = s_dh_u32 + (t % SL_RING) * (SL_THREADS * 8);
-      cp_async4(dd, dh + dh_a + (size_t)t * DH);
-      cp_async4(dd + 4, dh + dh_b + (size_t)t * DH);
+      const uint32_t slot = (uint32_t)(t % SL_RING);
+      mbar_expect_tx(s_full + 8u * slot, SLB_REC_STEP);
+      bulk_load(s_rec_u32 + slot * SLB_REC_STEP, cache + (size_t)t * SLB_REC_STEP, SLB_REC_STEP, s_full + 8u * slot);
     }
-    cp_async_commit();
   };
-#pragma unroll
-  for (int j = 0; j < SL_RING - 1; ++j) issue(S - 1 - j);
+  auto record_landed = [&](int t) -> bool {
+    return sl_wait(s_full + 8u * (uint32_t)(t % SL_RING), (uint32_t)((S - 1 - t) / SL_RING) & 1u);
+  };
+  // the gradient from above, (B, NH, S, DH): one word (two units) per thread and step, loaded one step ahead
+  const __nv_bfloat16* dh = reinterpret_cast<const __nv_bfloat16*>(p.dh);
+  const size_t dh_off = ((size_t)(ok_r ? gb : B - 1) * NH + head) * (size_t)S * DH + unit_h;
+  if (tid == 0)
+    for (int j = 0; j < SL_RING - 1; ++j) issue(S - 1 - j);
   cluster_barrier();  // every CTA's barriers exist before anything crosses over; also a CTA-wide barrier
 
   const uint32_t s_dg_u32 = smem_u32(s_dg), s_rb_u32 = smem_u32(s_rb), s_st_u32 = smem_u32(s_st);
@@ -132,49 +145,35 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_backward_kernel(const xl_
 
   // Per pair, everything of a step that does not depend on the incoming gradient (formed one step ahead):
   //   dc = dc_carry + dy pa;  dn = dn_carry - dy pb;  dg_i = pig (pzt dc + dn);  dg_f = pff (dc pcp + dn pnp);
-  //   dg_z = dc pz2;  dg_o = po2 dy;  carries <- pfg (dc, dn);  dy = dup + recurrent part
-  float pa[4], pb[4], pig[4], pzt[4], pfg[4], pff[4], pcp[4], pnp[4], pz2[4], po2[4], dup[4];
+  //   dg_z = dc pz2;  dg_o = po2 dy;  carries <- pfg (dc, dn);  dy = gradient from above + recurrent part
+  float pa[2], pb[2], pig[2], pzt[2], pfg[2], pff[2], pcp[2], pnp[2], pz2[2], po2[2];
   auto precompute = [&](int t) {
-    const unsigned char* rt = s_rec + (t % SL_RING) * SLB_REC_STEP + tid * SL_REC_BYTES;
-    const uint4 ga = *reinterpret_cast<const uint4*>(rt), gbw = *reinterpret_cast<const uint4*>(rt + 16);
-    const uint2 hw = *reinterpret_cast<const uint2*>(rt + 32);
-    const float4 n_new = *reinterpret_cast<const float4*>(rt + 64), m_new = *reinterpret_cast<const float4*>(rt + 80);
-    float4 c_prev, n_prev, m_prev;
+    // the forward thread's record: gates of rows a | b (16 B each), h' of rows a | b (4 B each), 8 B pad, then c', n', m'
+    // as (row a: u0, u1, row b: u0, u1)
+    const unsigned char* rt = s_rec + (t % SL_RING) * SLB_REC_STEP + ftid * SL_REC_BYTES;
+    const uint4 gw = *reinterpret_cast<const uint4*>(rt + 16 * half);
+    const uint32_t hw = *reinterpret_cast<const uint32_t*>(rt + 32 + 4 * half);
+    const float2 n_new = *reinterpret_cast<const float2*>(rt + 64 + 8 * half);
+    const float2 m_new = *reinterpret_cast<const float2*>(rt + 80 + 8 * half);
+    float2 c_prev, n_prev, m_prev;
     if (t > 0) {
-      const unsigned char* rp = s_rec + ((t - 1) % SL_RING) * SLB_REC_STEP + tid * SL_REC_BYTES;
-      c_prev = *reinterpret_cast<const float4*>(rp + 48);
-      n_prev = *reinterpret_cast<const float4*>(rp + 64);
-      m_prev = *reinterpret_cast<const float4*>(rp + 80);
+      const unsigned char* rp = s_rec + ((t - 1) % SL_RING) * SLB_REC_STEP + ftid * SL_REC_BYTES;
+      c_prev = *reinterpret_cast<const float2*>(rp + 48 + 8 * half);
+      n_prev = *reinterpret_cast<const float2*>(rp + 64 + 8 * half);
+      m_prev = *reinterpret_cast<const float2*>(rp + 80 + 8 * half);
     } else {
-      float cp[4], np[4], mp[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int gb = (i < 2) ? gb_a : gb_b;
-        const bool okr = (i < 2) ? ok_a : ok_b;
-        const size_t off = (size_t)gb * H + (size_t)head * DH + unit_h + (i & 1);
-        const bool have = p.state0 != nullptr && okr;
-        cp[i] = have ? p.state0[1 * (size_t)B * H + off] : 0.f;
-        np[i] = have ? p.state0[2 * (size_t)B * H + off] : 0.f;
-        mp[i] = have ? p.state0[3 * (size_t)B * H + off] : 0.f;
-      }
-      c_prev = make_float4(cp[0], cp[1], cp[2], cp[3]);
-      n_prev = make_float4(np[0], np[1], np[2], np[3]);
-      m_prev = make_float4(mp[0], mp[1], mp[2], mp[3]);
+      const bool have = p.state0 != nullptr && ok_r;
+      c_prev = make_float2(have ? p.state0[1 * (size_t)B * H + st_off] : 0.f, have ? p.state0[1 * (size_t)B * H + st_off + 1] : 0.f);
+      n_prev = make_float2(have ? p.state0[2 * (size_t)B * H + st_off] : 0.f, have ? p.state0[2 * (size_t)B * H + st_off + 1] : 0.f);
+      m_prev = make_float2(have ? p.state0[3 * (size_t)B * H + st_off] : 0.f, have ? p.state0[3 * (size_t)B * H + st_off + 1] : 0.f);
     }
-    const uint2 dhw = *reinterpret_cast<const uint2*>(s_dh + (t % SL_RING) * (SL_THREADS * 2) + tid * 2);
-    const float2 ia = unpack_bf16x2(ga.x), fa = unpack_bf16x2(ga.y), za = unpack_bf16x2(ga.z), oa = unpack_bf16x2(ga.w);
-    const float2 ib = unpack_bf16x2(gbw.x), fb = unpack_bf16x2(gbw.y), zb = unpack_bf16x2(gbw.z), ob = unpack_bf16x2(gbw.w);
-    const float2 ya = unpack_bf16x2(hw.x), yb = unpack_bf16x2(hw.y);
-    const float2 da = unpack_bf16x2(dhw.x), db = unpack_bf16x2(dhw.y);
-    const float ig[4] = {ia.x, ia.y, ib.x, ib.y}, fr[4] = {fa.x, fa.y, fb.x, fb.y};
-    const float zt[4] = {za.x, za.y, zb.x, zb.y}, os[4] = {oa.x, oa.y, ob.x, ob.y};
-    const float yn[4] = {ya.x, ya.y, yb.x, yb.y};
-    const float du[4] = {ok_a ? da.x : 0.f, ok_a ? da.y : 0.f, ok_b ? db.x : 0.f, ok_b ? db.y : 0.f};
-    const float nn[4] = {n_new.x, n_new.y, n_new.z, n_new.w}, mn[4] = {m_new.x, m_new.y, m_new.z, m_new.w};
-    const float cp[4] = {c_prev.x, c_prev.y, c_prev.z, c_prev.w}, np[4] = {n_prev.x, n_prev.y, n_prev.z, n_prev.w};
-    const float mp[4] = {m_prev.x, m_prev.y, m_prev.z, m_prev.w};
+    const float2 iw = unpack_bf16x2(gw.x), fw = unpack_bf16x2(gw.y), zw = unpack_bf16x2(gw.z), ow = unpack_bf16x2(gw.w);
+    const float2 yw = unpack_bf16x2(hw);
+    const float ig[2] = {iw.x, iw.y}, fr[2] = {fw.x, fw.y}, zt[2] = {zw.x, zw.y}, os[2] = {ow.x, ow.y}, yn[2] = {yw.x, yw.y};
+    const float nn[2] = {n_new.x, n_new.y}, mn[2] = {m_new.x, m_new.y};
+    const float cp[2] = {c_prev.x, c_prev.y}, np[2] = {n_prev.x, n_prev.y}, mp[2] = {m_prev.x, m_prev.y};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 2; ++i) {
       const float rn = __fdividef(1.f, nn[i]);
       const float fg = fminf(1.f, __expf(fast_logsigmoid(fr[i]) + mp[i] - mn[i]));
       const float fsig = __fdividef(1.f, 1.f + __expf(-fr[i]));
@@ -188,23 +187,23 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_backward_kernel(const xl_
       pnp[i] = np[i];
       pz2[i] = ig[i] * (1.f - zt[i] * zt[i]);
       po2[i] = (1.f - os[i]) * yn[i];
-      dup[i] = du[i];
     }
   };
-  cp_async_wait<SL_RING - 3>();   // the records of the last two steps have landed (this thread's)
-  precompute(S - 1);
-
   bool ok = true;
+  if (!record_landed(S - 1) || (S >= 2 && !record_landed(S - 2))) ok = false;
+  precompute(S - 1);
+  uint32_t dh_w = ldg_nc_u32(dh + dh_off + (size_t)(S - 1) * DH);
+
   for (int it = 0; it < S; ++it) {
     const int t = S - 1 - it;
     const int buf = it & 1;
-    issue(t - (SL_RING - 1));
-    if (tid == 0) mbar_expect_tx(s_bar + 8u * buf, RB_BYTES);
 
     // ---- the part of the pointwise backward that depends on the incoming gradient
-    float dgi[4], dgf[4], dgz[4], dgo[4];
+    float dgi[2], dgf[2], dgz[2], dgo[2];
+    const float2 dw = unpack_bf16x2(dh_w);
+    const float dup[2] = {ok_r ? dw.x : 0.f, ok_r ? dw.y : 0.f};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 2; ++i) {
       const float dy = dup[i] + dhrec[i];
       const float dc = fmaf(dy, pa[i], dc_[i]);
       const float dn = fmaf(-dy, pb[i], dn_[i]);
@@ -217,26 +216,25 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_backward_kernel(const xl_
     }
     // ---- dg_t of this CTA (16 rows x [4 gates x 32 units]) as the A operand of the recurrent product
     {
-      uint32_t* ra = reinterpret_cast<uint32_t*>(s_dg + row_a * SLB_DG_STRIDE + unit_l);
-      uint32_t* rb = reinterpret_cast<uint32_t*>(s_dg + row_b * SLB_DG_STRIDE + unit_l);
-      ra[0 * (SL_UNITS / 2)] = pack_bf16x2(dgi[0], dgi[1]);
-      ra[1 * (SL_UNITS / 2)] = pack_bf16x2(dgf[0], dgf[1]);
-      ra[2 * (SL_UNITS / 2)] = pack_bf16x2(dgz[0], dgz[1]);
-      ra[3 * (SL_UNITS / 2)] = pack_bf16x2(dgo[0], dgo[1]);
-      rb[0 * (SL_UNITS / 2)] = pack_bf16x2(dgi[2], dgi[3]);
-      rb[1 * (SL_UNITS / 2)] = pack_bf16x2(dgf[2], dgf[3]);
-      rb[2 * (SL_UNITS / 2)] = pack_bf16x2(dgz[2], dgz[3]);
-      rb[3 * (SL_UNITS / 2)] = pack_bf16x2(dgo[2], dgo[3]);
+      uint32_t* rr = reinterpret_cast<uint32_t*>(s_dg + (buf * SL_ROWS + row) * SLB_DG_STRIDE + unit_l);
+      rr[0 * (SL_UNITS / 2)] = pack_bf16x2(dgi[0], dgi[1]);
+      rr[1 * (SL_UNITS / 2)] = pack_bf16x2(dgf[0], dgf[1]);
+      rr[2 * (SL_UNITS / 2)] = pack_bf16x2(dgz[0], dgz[1]);
+      rr[3 * (SL_UNITS / 2)] = pack_bf16x2(dgo[0], dgo[1]);
     }
-    __syncthreads();
-    // ---- partial dh_{t-1} for all DH columns: 16 x DH = (16 x 128) (128 x DH)
+    // The one CTA-wide barrier of a step.  It also orders the buffers that alternate between steps (dg tile, staged and
+    // received partials): whoever passes it has finished the previous step, and nothing of step it+2 can reach this
+    // CTA before its own copies of step it+1, which are issued behind this barrier, have arrived at the peers.  The
+    // same barrier tells every thread whether any wait expired.
+    if (__syncthreads_or(ok ? 0 : 1)) { ok = false; break; }
+    // ---- partial dh_{t-1} for all DH columns: 16 x DH = (16 x 128) (128 x DH); this warp's share is NTW 8-column tiles
     float acc[NTW][4];
 #pragma unroll
     for (int j = 0; j < NTW; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
       uint32_t a0, a1, a2, a3;
-      ldmatrix_x4(s_dg_u32 + ldm_off + ks * 32, a0, a1, a2, a3);
+      ldmatrix_x4(s_dg_u32 + buf * (SL_ROWS * SLB_DG_STRIDE * 2) + ldm_off + ks * 32, a0, a1, a2, a3);
 #pragma unroll
       for (int j = 0; j < NTW; ++j) mma_bf16_16816(acc[j], a0, a1, a2, a3, bfrag[j][ks][0], bfrag[j][ks][1]);
     }
@@ -245,8 +243,8 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_backward_kernel(const xl_
     for (int j = 0; j < NTW; ++j) {
       const int tile = warp * NTW + j;                 // columns 8 tile .. 8 tile + 7 of the head
       float* blk = s_st + ((size_t)(buf * NCTA + (tile >> 2)) * SL_ROWS) * SLB_PROW + (tile & 3) * 8 + (lane & 3) * 2;
-      *reinterpret_cast<float2*>(blk + row_a * SLB_PROW) = make_float2(acc[j][0], acc[j][1]);
-      *reinterpret_cast<float2*>(blk + row_b * SLB_PROW) = make_float2(acc[j][2], acc[j][3]);
+      *reinterpret_cast<float2*>(blk + (lane >> 2) * SLB_PROW) = make_float2(acc[j][0], acc[j][1]);
+      *reinterpret_cast<float2*>(blk + ((lane >> 2) + 8) * SLB_PROW) = make_float2(acc[j][2], acc[j][3]);
     }
     fence_proxy_async_smem();
     // ... and send every block with one bulk copy into slot [buf][this CTA] of its owner.  A warp produces whole
@@ -264,63 +262,63 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_backward_kernel(const xl_
         bulk_copy_to_cta(map_to_cta(s_rb_u32 + ((uint32_t)buf * NCTA + rank) * SLB_PBLOCK, (uint32_t)tid),
                          s_st_u32 + ((uint32_t)buf * NCTA + tid) * SLB_PBLOCK, SLB_PBLOCK, map_to_cta(s_bar + 8u * buf, (uint32_t)tid));
     }
-    // ---- dWx_t = dg_t, (B, S, 4, NH, DH), from the tile: 16-byte pieces, two per thread (off the step-to-step chain)
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int pidx = tid + j * SL_THREADS;
-      const int r = pidx >> 4, g = (pidx >> 2) & 3, part = pidx & 3;
-      const int gb = bgroup * SL_ROWS + r;
-      if (gb < B)
-        *reinterpret_cast<uint4*>(dwx + (((size_t)gb * S + t) * 4 + g) * H + (size_t)head * DH + rank * SL_UNITS + part * 8) =
-            *reinterpret_cast<const uint4*>(s_dg + r * SLB_DG_STRIDE + g * SL_UNITS + part * 8);
+    // ---- off the step-to-step chain from here to the wait: announce what this step delivers to this CTA (the barrier's
+    // phase cannot complete before this arrival, whatever has landed already), fetch ahead, write dWx_t
+    if (tid == 0) {
+      mbar_expect_tx(s_bar + 8u * buf, RB_BYTES);
+      issue(t - (SL_RING - 1));
+    }
+    if (t >= 1) dh_w = ldg_nc_u32(dh + dh_off + (size_t)(t - 1) * DH);
+    // dWx_t = dg_t, (B, S, 4, NH, DH), from the tile: one 16-byte piece per thread
+    {
+      const int r = tid >> 4, g = (tid >> 2) & 3, part = tid & 3;
+      const int gbr = bgroup * SL_ROWS + r;
+      if (gbr < B)
+        *reinterpret_cast<uint4*>(dwx + (((size_t)gbr * S + t) * 4 + g) * H + (size_t)head * DH + rank * SL_UNITS + part * 8) =
+            *reinterpret_cast<const uint4*>(s_dg + (buf * SL_ROWS + r) * SLB_DG_STRIDE + g * SL_UNITS + part * 8);
     }
     // ---- while the partials are in flight: the gradient-independent part of the next step (t - 1)
-    cp_async_wait<SL_RING - 3>();   // the records of steps t-1 and t-2 (this thread's) have landed
-    if (t >= 1) precompute(t - 1);
+    if (t >= 1) {
+      if (!record_landed(t - 1) || (t >= 2 && !record_landed(t - 2))) ok = false;
+      precompute(t - 1);
+    }
     // ---- the DH/32 partials of this CTA's own columns have landed: add them in rank order
     if (!sl_wait(s_bar + 8u * buf, (uint32_t)(it >> 1) & 1u)) ok = false;
     {
-      const float* rb0 = s_rb + (size_t)buf * NCTA * SL_ROWS * SLB_PROW + unit_l;
-      float2 sa = make_float2(0.f, 0.f), sb = make_float2(0.f, 0.f);
+      const float* rb0 = s_rb + ((size_t)buf * NCTA * SL_ROWS + row) * SLB_PROW + unit_l;
+      float2 sa = make_float2(0.f, 0.f);
 #pragma unroll
       for (int s = 0; s < NCTA; ++s) {
-        const float2 va = *reinterpret_cast<const float2*>(rb0 + (s * SL_ROWS + row_a) * SLB_PROW);
-        const float2 vb = *reinterpret_cast<const float2*>(rb0 + (s * SL_ROWS + row_b) * SLB_PROW);
-        sa.x += va.x; sa.y += va.y; sb.x += vb.x; sb.y += vb.y;
+        const float2 va = *reinterpret_cast<const float2*>(rb0 + s * SL_ROWS * SLB_PROW);
+        sa.x += va.x; sa.y += va.y;
       }
-      dhrec[0] = sa.x; dhrec[1] = sa.y; dhrec[2] = sb.x; dhrec[3] = sb.y;
+      dhrec[0] = sa.x; dhrec[1] = sa.y;
     }
-    // everybody is done with the dg tile and with this receive buffer; the same barrier tells every thread whether
-    // any wait expired
-    if (__syncthreads_or(ok ? 0 : 1)) { ok = false; break; }
   }
-  cp_async_wait<0>();
   if (!ok && p.status) atomicExch(p.status, 1);
   cluster_barrier();  // nobody leaves while a peer may still push into its buffers
 
   // gradient of the initial state (4, B, H): dh, dc, dn, 0
+  if (ok_r) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int gb = (i < 2) ? gb_a : gb_b;
-    const bool okr = (i < 2) ? ok_a : ok_b;
-    if (!okr) continue;
-    const size_t off = (size_t)gb * H + (size_t)head * DH + unit_h + (i & 1);
-    p.dstate0[0 * (size_t)B * H + off] = dhrec[i];
-    p.dstate0[1 * (size_t)B * H + off] = dc_[i];
-    p.dstate0[2 * (size_t)B * H + off] = dn_[i];
-    p.dstate0[3 * (size_t)B * H + off] = 0.f;
+    for (int i = 0; i < 2; ++i) {
+      p.dstate0[0 * (size_t)B * H + st_off + i] = dhrec[i];
+      p.dstate0[1 * (size_t)B * H + st_off + i] = dc_[i];
+      p.dstate0[2 * (size_t)B * H + st_off + i] = dn_[i];
+      p.dstate0[3 * (size_t)B * H + st_off + i] = 0.f;
+    }
   }
 }
 
 template <int DH>
 static int launch_slstm_bwd(const xl_slstm_bwd_params* p, cudaStream_t st) {
   constexpr int NCTA = DH / SL_UNITS;
-  const size_t smem = (size_t)SL_ROWS * SLB_DG_STRIDE * 2 + 4 * (size_t)NCTA * SLB_PBLOCK +
-                      (size_t)SL_RING * SLB_REC_STEP + (size_t)SL_RING * SL_THREADS * 8 + 16;
+  const size_t smem = 2 * (size_t)SL_ROWS * SLB_DG_STRIDE * 2 + 4 * (size_t)NCTA * SLB_PBLOCK +
+                      (size_t)SL_RING * SLB_REC_STEP + 16 + 8 * SL_RING;
   XL_CUDA_TRY(cudaFuncSetAttribute(slstm_backward_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(NCTA, p->NH, (p->B + SL_ROWS - 1) / SL_ROWS);
-  cfg.blockDim = dim3(SL_THREADS);
+  cfg.blockDim = dim3(SLB_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
