@@ -356,6 +356,32 @@ def test_reference_block_stack_trains_through_the_b200_backward_kernel():
     print(f"worst parameter gradient error {worst:.2e}")
 
 
+def test_fused_layer_operators_step_aside_when_gradients_are_needed():
+    """With the forward-only layer operators installed (convolution, gate projections, group norm), a training step
+    takes the reference's own differentiable operators around the cell and gives the gradients of the plain stack."""
+    from xlstm_b200.integration import fuse_slstm_gate_projections, pack_aware_slstm_layers
+    B, S, D = 2, 48, 256
+    ref32 = _slstm_stack("vanilla", torch.float32, num_blocks=1, embedding_dim=D)
+    _load_stack_weights(ref32, ref32, bf16_round=True)
+    plain = _slstm_stack("b200", torch.bfloat16, ref32, num_blocks=1, embedding_dim=D).train()
+    fused = _slstm_stack("b200", torch.bfloat16, ref32, num_blocks=1, embedding_dim=D).train()
+    assert pack_aware_slstm_layers(fused) == 1 and fuse_slstm_gate_projections(fused) == 1
+    x = torch.randn(B, S, D, generator=torch.Generator().manual_seed(5)).bfloat16().cuda()
+    grads = []
+    for stack in (plain, fused):
+        xi = x.clone().requires_grad_()
+        stack(xi).float().square().sum().backward()
+        grads.append((xi.grad.float().cpu(), {n.replace(".ref.", "."): p.grad.float().cpu() for n, p in stack.named_parameters() if p.grad is not None}))
+    assert rel_l2(grads[1][0], grads[0][0]) < 1e-3
+    assert set(grads[0][1]) == set(grads[1][1])
+    for name in grads[0][1]:
+        if float(grads[0][1][name].norm()) > 0:
+            assert rel_l2(grads[1][1][name], grads[0][1][name]) < 1e-3, name
+    # and without gradients the kernels run: same output as the plain stack within the operators' rounding
+    with torch.no_grad():
+        assert rel_l2(fused.eval()(x).float().cpu(), plain.eval()(x).float().cpu()) < 1e-2
+
+
 def test_reference_slstm_cell_b200_vs_vanilla_small_with_initial_state():
     """The reference's cell-level test shape (tests/test_slstm_cell_vanilla_vs_cuda.py:12-56: hidden 64, 4 heads,
     input (1,1,256)) plus a longer batch, with and without a random initial state, R initialised."""

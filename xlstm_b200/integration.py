@@ -143,6 +143,12 @@ def install_slstm_backend():
     return sLSTMCell_b200
 
 
+def _needs_grad(*tensors) -> bool:
+    """True when autograd would record an operator on these tensors: the forward-only kernels then step aside for the
+    reference's own differentiable operators."""
+    return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
+
+
 class PackAwareCausalConv1d(torch.nn.Module):
     """Stands in for the pair ``CausalConv1d`` + ``SiLU`` at the front of the reference's sLSTM layer
     (xlstm/blocks/slstm/layer.py:133-142).  It owns the SAME ``nn.Conv1d`` parameters (state dicts stay compatible) and
@@ -167,6 +173,14 @@ class PackAwareCausalConv1d(torch.nn.Module):
     def forward(self, x, conv_state=None, return_last_state: bool = False):
         if self.config.kernel_size == 0:
             return x
+        if _needs_grad(x, conv_state, self.ref.conv.weight, self.ref.conv.bias):
+            # training: the reference's module (the kernel has no backward pass)
+            if self._cu_seqlens is not None:
+                raise ValueError("the convolution kernel with document offsets is forward only")
+            if return_last_state:
+                y, state = self.ref(x, conv_state, return_last_state=True)
+                return torch.nn.functional.silu(y), state
+            return torch.nn.functional.silu(self.ref(x, conv_state, return_last_state=False))
         if conv_state is not None:
             if self._cu_seqlens is not None:
                 raise ValueError("a packed batch starts every document from an empty convolution state")
@@ -203,6 +217,8 @@ class HeadGroupNorm(torch.nn.Module):
     def forward(self, x):
         B, NH, S, DH = x.shape
         w = self.ref.weight_proxy
+        if _needs_grad(x, w):
+            return self.ref(x)      # training: the reference's module (the kernel has no backward pass)
         w = torch.ones(NH * DH, dtype=x.dtype, device=x.device) if w is None else w.to(x.dtype)
         out = ops.headnorm_gate(x, None, w, eps=self.ref.eps)            # (B, S, NH*DH)
         return out.view(B, S, NH, DH).transpose(1, 2)                   # the caller transposes back and flattens: views
@@ -224,6 +240,7 @@ def _slstm_layer_forward_fused(self, x, conv_state=None, slstm_state=None, retur
     gates = (self.fgate, self.igate, self.zgate, self.ogate)   # the order in which the reference concatenates them
     DH = gates[0].weight.shape[-1]
     fusable = (x.is_cuda and x.dtype == torch.bfloat16 and DH in (64, 128, 256)
+               and not _needs_grad(x, x_conv, *(g.weight for g in gates))     # forward-only kernel
                and all(g.bias is None and g.weight.shape[1] == DH and g.weight.dtype == torch.bfloat16 for g in gates))
     if fusable:
         wx = ops.headwise_proj([x, x_conv], [g.weight for g in gates], [1, 1, 0, 0])
