@@ -395,6 +395,41 @@ def build_case(name, dev, rank):
                     l2="inputs (%d MB) exceed the 126 MB L2" % (slstm_bytes(**cfg) // 10 ** 6), launches=1,
                     traffic=323.9e6, traffic_source="constant: ncu dram__bytes_read.sum + dram__bytes_write.sum of ONE captured launch of this workload, not measured in this run",
                     extra=lambda m: {**slstm_reference_cuda(cfg, dev, m["kernel_ms"]), **slstm_gate_projections(cfg, dev), **slstm_training(cfg, dev)})
+    if name == "slstm_train":
+        # one training step of the same cell: cache-writing forward, backward through time, dR / dbias GEMMs
+        from xlstm_b200 import ops
+        cfg = dict(SLSTM_CFG)
+        B, S, NH, DH = cfg["B"], cfg["S"], cfg["NH"], cfg["DH"]
+        H = NH * DH
+        g = torch.Generator().manual_seed(7 + rank)
+        wx_h = torch.randn(B, S, 4 * H, generator=g).bfloat16().pin_memory()
+        gh_h = torch.randn(B, NH, S, DH, generator=g).bfloat16().pin_memory()
+        R = ((torch.rand(NH, DH, 4, DH, generator=g) * 2 - 1) / H ** 0.5).bfloat16().to(dev)
+        bias = (torch.randn(NH, 4, DH, generator=g) * 0.5).to(dev)
+        wx, gh = wx_h.to(dev), gh_h.to(dev)
+        dwx_host = torch.empty(B, S, 4 * H, dtype=torch.bfloat16).pin_memory()
+
+        def train(wx_d, gh_d):
+            h, last, cache = ops.slstm_forward(wx_d, R, bias, train_cache=True)
+            dwx, ds0 = ops.slstm_backward(cache, R, gh_d)
+            dR, db = ops.slstm_weight_grads(dwx, h)
+            return dwx, dR, db
+
+        def step():
+            return train(wx, gh)
+
+        def e2e_step():
+            dwx, dR, db = train(wx_h.to(dev, non_blocking=True), gh_h.to(dev, non_blocking=True))
+            dwx_host.copy_(dwx, non_blocking=True)
+
+        cache_bytes = ((B + 15) // 16) * NH * (DH // 32) * S * 128 * 96
+        # Wx and h of the forward, the cache written and read back, dh in, dWx out, then h and dWx once more for the GEMMs
+        nbytes = slstm_bytes(**cfg) + 2 * cache_bytes + B * S * H * 2 + B * S * 4 * H * 2 + B * S * 5 * H * 2
+        return dict(step=step, e2e_step=e2e_step, units=B * S, unit="tokens/s", metric="slstm_forward_backward_tokens_per_s",
+                    workload="slstm_cell_training_config3", cfg=cfg, bytes=nbytes, flops=3 * S * B * NH * 2 * DH * 4 * DH,
+                    kernel="slstm_backward_kernel<256>", h2d=(wx_h.numel() + gh_h.numel()) * 2, d2h=dwx_host.numel() * 2,
+                    l2="cache and activations (%d MB per step) exceed the 126 MB L2" % (nbytes // 10 ** 6), launches=2,
+                    traffic=None, traffic_source="not captured")
     if name == "headwise":
         # the four headwise gate projections + concatenation in front of the sLSTM cell, at the cell's benchmark shape
         cfg = dict(SLSTM_CFG)
@@ -700,7 +735,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--case", default="all", choices=["all", "chunkwise", "chunkwise_b1", "step", "slstm", "headwise", "layer_ops", "model7b", "decode7b", "continuous7b"])
+    ap.add_argument("--case", default="all", choices=["all", "chunkwise", "chunkwise_b1", "step", "slstm", "slstm_train", "headwise", "layer_ops", "model7b", "decode7b", "continuous7b"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="profiling runs: device-resident loop only")
     args = ap.parse_args()
