@@ -29,6 +29,17 @@
 
 namespace xl {
 
+constexpr int SL_REC_SLOTS = 3;                          // staging slots of the training cache (one step's records each)
+constexpr int SL_REC_STEP = SL_THREADS * SL_REC_BYTES;   // bytes of one step's records of a CTA
+
+// bulk copy of this CTA's shared memory to global memory (bulk-group completion)
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+
 // Advance `idx` past every boundary at or before time index `t_now` of batch row `gb`; return the time index
 // of the next boundary inside the row, or INT_MAX.  Repeated offsets (empty documents) are skipped.
 __device__ __forceinline__ int next_boundary(const xl_slstm_params& p, int gb, int t_now, int& idx) {
@@ -48,6 +59,7 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
   unsigned char* s_wx = sl_smem + 2 * SL_ROWS * H_STRIDE * sizeof(__nv_bfloat16);    // SL_RING x SL_WX_STEP_BYTES
   const uint32_t s_bar = smem_u32(s_wx + SL_RING * SL_WX_STEP_BYTES);                // 2 mbarriers: h tile 0 / 1 complete
   constexpr uint32_t H_TILE_BYTES = SL_ROWS * DH * 2;                                // what one step delivers to a CTA
+  unsigned char* s_recst = s_wx + SL_RING * SL_WX_STEP_BYTES + 16;                   // TRAIN: SL_REC_SLOTS x SL_REC_STEP
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t rank = cluster_ctarank();       // which 32-unit slice of the head
@@ -168,11 +180,11 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
   const uint32_t ldm_off = ((lane & 15) * H_STRIDE + (lane >> 4) * 8) * 2;
 
   __nv_bfloat16* hout = reinterpret_cast<__nv_bfloat16*>(p.h_out);
-  // training cache: [cluster][CTA][step][thread] records of SL_REC_BYTES
-  uint4* rec = nullptr;
+  // training cache: [cluster][CTA][step][thread] records of SL_REC_BYTES.  The records of a step are staged in shared
+  // memory and leave as ONE 12 KB bulk copy (six 16-byte global stores per thread and step cost 350 cycles of a step)
+  unsigned char* rec = nullptr;
   if constexpr (TRAIN)
-    rec = reinterpret_cast<uint4*>(p.train_cache) +
-          ((((size_t)bgroup * NH + head) * NCTA + rank) * (size_t)S * SL_THREADS + tid) * (SL_REC_BYTES / 16);
+    rec = reinterpret_cast<unsigned char*>(p.train_cache) + (((size_t)bgroup * NH + head) * NCTA + rank) * (size_t)S * SL_REC_STEP;
 
   bool ok = true;
   for (int t = 0; t < S; ++t) {
@@ -229,17 +241,6 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
       if constexpr (TRAIN) { gi[i] = ig; gz[i] = zt; go[i] = os; }
     }
     const uint32_t pa = pack_bf16x2(hn[0], hn[1]), pb = pack_bf16x2(hn[2], hn[3]);
-    if constexpr (TRAIN) {
-      // the record of this step (states AFTER the update; a reset below is not recorded: the training path takes no
-      // document offsets)
-      uint4* r = rec + (size_t)t * SL_THREADS * (SL_REC_BYTES / 16);
-      r[0] = make_uint4(pack_bf16x2(gi[0], gi[1]), pack_bf16x2(acc[1][0], acc[1][1]), pack_bf16x2(gz[0], gz[1]), pack_bf16x2(go[0], go[1]));
-      r[1] = make_uint4(pack_bf16x2(gi[2], gi[3]), pack_bf16x2(acc[1][2], acc[1][3]), pack_bf16x2(gz[2], gz[3]), pack_bf16x2(go[2], go[3]));
-      r[2] = make_uint4(pa, pb, 0u, 0u);
-      r[3] = make_uint4(__float_as_uint(c_[0]), __float_as_uint(c_[1]), __float_as_uint(c_[2]), __float_as_uint(c_[3]));
-      r[4] = make_uint4(__float_as_uint(n_[0]), __float_as_uint(n_[1]), __float_as_uint(n_[2]), __float_as_uint(n_[3]));
-      r[5] = make_uint4(__float_as_uint(m_[0]), __float_as_uint(m_[1]), __float_as_uint(m_[2]), __float_as_uint(m_[3]));
-    }
     // a row whose next token opens a new document restarts from the zero state
     uint32_t push_a = pa, push_b = pb;
     if (reset_next_a) {
@@ -260,6 +261,18 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
       st_async_u32(map_to_cta(nb + slot_a, r), push_a, rbar);
       st_async_u32(map_to_cta(nb + slot_b, r), push_b, rbar);
     }
+    if constexpr (TRAIN) {
+      // the record of this step (states after the update; the training path takes no document offsets, so nothing was
+      // reset above) into this step's staging slot, behind the pushes like the output below
+      uint4* r = reinterpret_cast<uint4*>(s_recst + (t % SL_REC_SLOTS) * SL_REC_STEP + tid * SL_REC_BYTES);
+      r[0] = make_uint4(pack_bf16x2(gi[0], gi[1]), pack_bf16x2(acc[1][0], acc[1][1]), pack_bf16x2(gz[0], gz[1]), pack_bf16x2(go[0], go[1]));
+      r[1] = make_uint4(pack_bf16x2(gi[2], gi[3]), pack_bf16x2(acc[1][2], acc[1][3]), pack_bf16x2(gz[2], gz[3]), pack_bf16x2(go[2], go[3]));
+      r[2] = make_uint4(pa, pb, 0u, 0u);
+      r[3] = make_uint4(__float_as_uint(c_[0]), __float_as_uint(c_[1]), __float_as_uint(c_[2]), __float_as_uint(c_[3]));
+      r[4] = make_uint4(__float_as_uint(n_[0]), __float_as_uint(n_[1]), __float_as_uint(n_[2]), __float_as_uint(n_[3]));
+      r[5] = make_uint4(__float_as_uint(m_[0]), __float_as_uint(m_[1]), __float_as_uint(m_[2]), __float_as_uint(m_[3]));
+      fence_proxy_async_smem();
+    }
     // output h_t, (B, NH, S, DH) -- after the pushes: they are on the step-to-step chain, this store is not
     if (ok_a) *reinterpret_cast<uint32_t*>(hout + (((size_t)gb_a * NH + head) * S + t) * DH + unit_h) = pa;
     if (ok_b) *reinterpret_cast<uint32_t*>(hout + (((size_t)gb_b * NH + head) * S + t) * DH + unit_h) = pb;
@@ -268,6 +281,16 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
     cp_async_wait<SL_RING - 2>();  // this thread's part of step t+1 has landed
     // ... and everybody else's (CTA-wide only); the same barrier tells every thread whether any wait expired
     if (__syncthreads_or(ok ? 0 : 1)) { ok = false; break; }
+    if constexpr (TRAIN) {
+      if (tid == 0) {
+        bulk_store(rec + (size_t)t * SL_REC_STEP, smem_u32(s_recst) + (t % SL_REC_SLOTS) * SL_REC_STEP, SL_REC_STEP);
+        bulk_commit();
+        bulk_wait_read<1>();   // the copy of step t-1 has read its slot: step t+2, which reuses it, may stage (behind the next barrier)
+      }
+    }
+  }
+  if constexpr (TRAIN) {
+    if (tid == 0) bulk_wait<0>();
   }
   // The pushes of h_{S-1} are still on their way into tile S & 1 of every CTA; their completion is signalled on that
   // tile's mbarrier only, so it is waited for (bounded) before anybody may leave: a CTA that exits while a peer's
@@ -296,7 +319,8 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
 template <int DH, bool TRAIN>
 static int launch_slstm(const xl_slstm_params* p, cudaStream_t st) {
   constexpr int NCTA = DH / SL_UNITS;
-  const size_t smem = 2 * SL_ROWS * (DH + 8) * 2 + (size_t)SL_RING * SL_WX_STEP_BYTES + 16;  // + 2 mbarriers
+  const size_t smem = 2 * SL_ROWS * (DH + 8) * 2 + (size_t)SL_RING * SL_WX_STEP_BYTES + 16 +  // + 2 mbarriers
+                      (TRAIN ? (size_t)SL_REC_SLOTS * SL_REC_STEP : 0);
   XL_CUDA_TRY(cudaFuncSetAttribute(slstm_forward_kernel<DH, TRAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(NCTA, p->NH, (p->B + SL_ROWS - 1) / SL_ROWS);
