@@ -105,6 +105,7 @@ def _grads_kernel(wx, R, bias, st, gh, gl):
 
 
 @pytest.mark.parametrize("B,S,NH,DH,with_state,state_loss", [
+    (2, 1, 1, 64, True, False), (2, 2, 2, 64, False, False), (1, 9, 1, 128, True, True),
     (3, 5, 1, 64, False, False), (3, 37, 2, 64, True, False), (16, 64, 4, 256, True, False),
     (20, 33, 1, 128, True, True), (16, 200, 2, 256, False, True)])
 def test_backward_matches_autograd_of_the_oracle(B, S, NH, DH, with_state, state_loss):
