@@ -410,18 +410,22 @@ def slstm_weight_grads(dwx, h, state0=None):
     slstm_backward.cu).  Plain batched matrix products, fp32 results: (NH,DH,4,DH) and (NH,4,DH)."""
     B, NH, S, DH = h.shape
     dw = dwx.reshape(B, S, 4, NH, DH)
-    hprev = torch.empty(B, NH, S, DH, dtype=dwx.dtype, device=dwx.device)
-    hprev[:, :, 1:] = h[:, :, :-1]
-    if state0 is None:
-        hprev[:, :, 0] = 0
-    else:
-        hprev[:, :, 0] = state0[0].reshape(B, NH, DH).to(dwx.dtype)
-    a = hprev.permute(1, 3, 0, 2).reshape(NH, DH, B * S)                      # (NH, DH_in, B*S)
-    b = dw.permute(3, 0, 1, 2, 4).reshape(NH, B * S, 4 * DH)                  # (NH, B*S, 4*DH_out)
-    try:
-        dR = torch.bmm(a, b, out_dtype=torch.float32)
-    except TypeError:
-        dR = torch.bmm(a, b).float()
+
+    def mm(a, b):
+        try:
+            return torch.bmm(a, b, out_dtype=torch.float32)
+        except TypeError:
+            return torch.bmm(a, b).float()
+
+    dR = torch.zeros(NH, DH, 4 * DH, dtype=torch.float32, device=dwx.device)
+    if S > 1:   # steps 1 .. S-1 pair h_{t-1} = h[t-1] with dwx[t]: two shifted views, no shifted copy of h
+        a = h[:, :, :-1].permute(1, 3, 0, 2).reshape(NH, DH, B * (S - 1)).to(dwx.dtype)      # (NH, DH_in, B*(S-1))
+        b = dw[:, 1:].permute(3, 0, 1, 2, 4).reshape(NH, B * (S - 1), 4 * DH)                 # (NH, B*(S-1), 4*DH_out)
+        dR = mm(a, b)
+    if state0 is not None:   # step 0 pairs the initial h with dwx[0]
+        a0 = state0[0].reshape(B, NH, DH).permute(1, 2, 0).to(dwx.dtype).contiguous()         # (NH, DH_in, B)
+        b0 = dw[:, 0].permute(2, 0, 1, 3).reshape(NH, B, 4 * DH)                              # (NH, B, 4*DH_out)
+        dR = dR + mm(a0, b0)
     db = dw.sum(dim=(0, 1), dtype=torch.float32).permute(1, 0, 2).contiguous()
     return dR.reshape(NH, DH, 4, DH), db
 
