@@ -117,26 +117,25 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
   }
 
   // ---- cache ring: the records of one step and CTA are 12 KB of contiguous global memory, fetched SL_RING - 1 steps
-  // ahead by ONE bulk copy that completes on the slot's mbarrier (one cp.async per 16 bytes from every thread cost
-  // 560 cycles of issue per step); record x sits in slot x % SL_RING, which it is use number (S-1-x) / SL_RING of
+  // ahead; every thread copies three 16-byte granules of the block (anybody's: the step's CTA barrier publishes them)
   const unsigned char* cache = reinterpret_cast<const unsigned char*>(p.cache) +
                                (((size_t)bgroup * NH + head) * NCTA + rank) * (size_t)S * SLB_REC_STEP;
   const uint32_t s_rec_u32 = smem_u32(s_rec);
-  auto issue = [&](int t) {   // thread 0 only
+  auto issue = [&](int t) {
     if (t >= 0) {
-      const uint32_t slot = (uint32_t)(t % SL_RING);
-      mbar_expect_tx(s_full + 8u * slot, SLB_REC_STEP);
-      bulk_load(s_rec_u32 + slot * SLB_REC_STEP, cache + (size_t)t * SLB_REC_STEP, SLB_REC_STEP, s_full + 8u * slot);
+      const unsigned char* src = cache + (size_t)t * SLB_REC_STEP + tid * 16;
+      const uint32_t dst = s_rec_u32 + (uint32_t)(t % SL_RING) * SLB_REC_STEP + tid * 16;
+#pragma unroll
+      for (int j = 0; j < SLB_REC_STEP / (16 * SLB_THREADS); ++j) cp_async16(dst + j * (16 * SLB_THREADS), src + j * (16 * SLB_THREADS));
     }
-  };
-  auto record_landed = [&](int t) -> bool {
-    return sl_wait(s_full + 8u * (uint32_t)(t % SL_RING), (uint32_t)((S - 1 - t) / SL_RING) & 1u);
+    cp_async_commit();
   };
   // the gradient from above, (B, NH, S, DH): one word (two units) per thread and step, loaded one step ahead
   const __nv_bfloat16* dh = reinterpret_cast<const __nv_bfloat16*>(p.dh);
   const size_t dh_off = ((size_t)(ok_r ? gb : B - 1) * NH + head) * (size_t)S * DH + unit_h;
-  if (tid == 0)
-    for (int j = 0; j < SL_RING - 1; ++j) issue(S - 1 - j);
+#pragma unroll
+  for (int j = 0; j < SL_RING - 1; ++j) issue(S - 1 - j);
+  cp_async_wait<SL_RING - 4>();   // this thread's granules of the last three steps' records; everybody's behind the barrier
   cluster_barrier();  // every CTA's barriers exist before anything crosses over; also a CTA-wide barrier
 
   const uint32_t s_dg_u32 = smem_u32(s_dg), s_rb_u32 = smem_u32(s_rb), s_st_u32 = smem_u32(s_st);
@@ -190,7 +189,6 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
     }
   };
   bool ok = true;
-  if (!record_landed(S - 1) || (S >= 2 && !record_landed(S - 2))) ok = false;
   precompute(S - 1);
   uint32_t dh_w = ldg_nc_u32(dh + dh_off + (size_t)(S - 1) * DH);
 
@@ -264,10 +262,8 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
     }
     // ---- off the step-to-step chain from here to the wait: announce what this step delivers to this CTA (the barrier's
     // phase cannot complete before this arrival, whatever has landed already), fetch ahead, write dWx_t
-    if (tid == 0) {
-      mbar_expect_tx(s_bar + 8u * buf, RB_BYTES);
-      issue(t - (SL_RING - 1));
-    }
+    if (tid == 0) mbar_expect_tx(s_bar + 8u * buf, RB_BYTES);
+    issue(t - (SL_RING - 1));
     if (t >= 1) dh_w = ldg_nc_u32(dh + dh_off + (size_t)(t - 1) * DH);
     // dWx_t = dg_t, (B, S, 4, NH, DH), from the tile: one 16-byte piece per thread
     {
@@ -278,10 +274,8 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
             *reinterpret_cast<const uint4*>(s_dg + (buf * SL_ROWS + r) * SLB_DG_STRIDE + g * SL_UNITS + part * 8);
     }
     // ---- while the partials are in flight: the gradient-independent part of the next step (t - 1)
-    if (t >= 1) {
-      if (!record_landed(t - 1) || (t >= 2 && !record_landed(t - 2))) ok = false;
-      precompute(t - 1);
-    }
+    if (t >= 1) precompute(t - 1);   // records t-1, t-2: waited for a step ago, published by this step's barrier
+    cp_async_wait<SL_RING - 4>();    // this thread's granules of records t-2 and t-3, which the next step reads
     // ---- the DH/32 partials of this CTA's own columns have landed: add them in rank order
     if (!sl_wait(s_bar + 8u * buf, (uint32_t)(it >> 1) & 1u)) ok = false;
     {
