@@ -16,11 +16,11 @@
 //   dh_{t-1}[b,k] = sum_{g,u} dg_t[b,g,u] R[k,g,u].
 // The CTA holds exactly the slice of R the forward holds (all k, its own 32 units, four gates) as mma.sync
 // B-fragments in registers, now contracted over (g,u): it forms the PARTIAL sums of dh_{t-1} for all DH columns
-// from its own 128 gate gradients (M = 16 rows, N = DH, K = 128), stages them per destination in shared memory and
+// from its own 128 gate gradients (M = 16 rows, N = DH, K = 128), stages them as bf16 per destination in shared memory and
 // sends every 32-column block to the CTA that owns those units with ONE bulk asynchronous copy into that CTA's
-// shared memory, which counts its bytes on the receiver's mbarrier (a reduce-scatter: DH/32 copies of 2.3 KB per CTA
+// shared memory, which counts its bytes on the receiver's mbarrier (a reduce-scatter: DH/32 copies of 1.3 KB per CTA
 // and step; the same exchange as 2 048 eight-byte remote stores per CTA cost 1 200 cycles of issue per step); the
-// receiver adds the DH/32 partials in rank order.  Everything of a step's gate arithmetic that does not depend on
+// receiver adds the DH/32 partials in fp32 in rank order.  Everything of a step's gate arithmetic that does not depend on
 // the incoming gradient is computed one step ahead, while the partials are in flight.
 // dWx_t = dg_t leaves as bf16 in the layout of Wx.  dR and dbias are sums over (b,t) of h_{t-1} (x) dg_t and of dg_t:
 // plain matrix products over the dWx this kernel writes, left to the caller's GEMM library.
@@ -32,8 +32,10 @@ namespace xl {
 constexpr int SLB_DG_STRIDE = 4 * SL_UNITS + 8;          // bf16 elements per row of the dg tile (+16 B: bank spread)
 constexpr int SLB_THREADS = 256;                         // 8 warps
 constexpr int SLB_REC_STEP = SL_THREADS * SL_REC_BYTES;  // cache bytes per CTA and step (records of the forward's 128 threads)
-constexpr int SLB_PROW = SL_UNITS + 4;                   // floats per row of a partial block (+16 B: rows on distinct banks)
-constexpr int SLB_PBLOCK = SL_ROWS * SLB_PROW * 4;       // bytes of one (source, destination) block of partial sums
+constexpr int SLB_PROW = SL_UNITS + 8;                   // bf16 elements per row of a partial block (+16 B: rows on distinct banks)
+constexpr int SLB_PBLOCK = SL_ROWS * SLB_PROW * 2;       // bytes of one (source, destination) block of partial sums (bf16: a
+                                                         // CTA takes in ~32 B of distributed shared memory per cycle, so the
+                                                         // exchange time follows the bytes; the sums are formed in fp32)
 
 // bulk copy global -> this CTA's shared memory, counted on one of its mbarriers
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -61,8 +63,8 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
   constexpr uint32_t RB_BYTES = NCTA * SLB_PBLOCK;   // what one step delivers to a CTA
   extern __shared__ __align__(16) unsigned char slb_smem[];
   __nv_bfloat16* s_dg = reinterpret_cast<__nv_bfloat16*>(slb_smem);                   // [2][16][SLB_DG_STRIDE]
-  float* s_rb = reinterpret_cast<float*>(slb_smem + 2 * SL_ROWS * SLB_DG_STRIDE * 2); // received: [2][source CTA][16][SLB_PROW]
-  float* s_st = s_rb + 2 * RB_BYTES / 4;                                              // staged: [2][destination CTA][16][SLB_PROW]
+  __nv_bfloat16* s_rb = reinterpret_cast<__nv_bfloat16*>(slb_smem + 2 * SL_ROWS * SLB_DG_STRIDE * 2);  // received: [2][source CTA][16][SLB_PROW]
+  __nv_bfloat16* s_st = s_rb + 2 * RB_BYTES / 2;                                      // staged: [2][destination CTA][16][SLB_PROW]
   unsigned char* s_rec = reinterpret_cast<unsigned char*>(s_st) + 2 * RB_BYTES;       // [SL_RING][SLB_REC_STEP]
   const uint32_t s_bar = smem_u32(s_rec + SL_RING * SLB_REC_STEP);                    // 2 mbarriers: partials landed
   const uint32_t s_full = s_bar + 16;                                                 // SL_RING mbarriers: record block landed
@@ -240,9 +242,9 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
 #pragma unroll
     for (int j = 0; j < NTW; ++j) {
       const int tile = warp * NTW + j;                 // columns 8 tile .. 8 tile + 7 of the head
-      float* blk = s_st + ((size_t)(buf * NCTA + (tile >> 2)) * SL_ROWS) * SLB_PROW + (tile & 3) * 8 + (lane & 3) * 2;
-      *reinterpret_cast<float2*>(blk + (lane >> 2) * SLB_PROW) = make_float2(acc[j][0], acc[j][1]);
-      *reinterpret_cast<float2*>(blk + ((lane >> 2) + 8) * SLB_PROW) = make_float2(acc[j][2], acc[j][3]);
+      __nv_bfloat16* blk = s_st + ((size_t)(buf * NCTA + (tile >> 2)) * SL_ROWS) * SLB_PROW + (tile & 3) * 8 + (lane & 3) * 2;
+      *reinterpret_cast<uint32_t*>(blk + (lane >> 2) * SLB_PROW) = pack_bf16x2(acc[j][0], acc[j][1]);
+      *reinterpret_cast<uint32_t*>(blk + ((lane >> 2) + 8) * SLB_PROW) = pack_bf16x2(acc[j][2], acc[j][3]);
     }
     fence_proxy_async_smem();
     // ... and send every block with one bulk copy into slot [buf][this CTA] of its owner.  A warp produces whole
@@ -279,11 +281,11 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
     // ---- the DH/32 partials of this CTA's own columns have landed: add them in rank order
     if (!sl_wait(s_bar + 8u * buf, (uint32_t)(it >> 1) & 1u)) ok = false;
     {
-      const float* rb0 = s_rb + ((size_t)buf * NCTA * SL_ROWS + row) * SLB_PROW + unit_l;
+      const __nv_bfloat16* rb0 = s_rb + ((size_t)buf * NCTA * SL_ROWS + row) * SLB_PROW + unit_l;
       float2 sa = make_float2(0.f, 0.f);
 #pragma unroll
       for (int s = 0; s < NCTA; ++s) {
-        const float2 va = *reinterpret_cast<const float2*>(rb0 + s * SL_ROWS * SLB_PROW);
+        const float2 va = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(rb0 + s * SL_ROWS * SLB_PROW));
         sa.x += va.x; sa.y += va.y;
       }
       dhrec[0] = sa.x; dhrec[1] = sa.y;
