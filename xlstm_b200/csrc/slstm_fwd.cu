@@ -53,10 +53,18 @@ __device__ __forceinline__ int next_boundary(const xl_slstm_params& p, int gb, i
 template <int DH, bool TRAIN>
 __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_slstm_params p) {
   constexpr int KSTEPS = DH / 16;
-  constexpr int H_STRIDE = DH + 8;  // bf16 elements; +16 B keeps ldmatrix rows on distinct banks
+  // h tile: 16-byte granules (eight consecutive units of one batch row, what one ldmatrix row reads), laid out so that
+  // the granules of rows r and r + 8 of one unit group share a 32-byte sector: a warp's push then fills whole sectors of
+  // the destination CTA, which takes in distributed shared memory sector by sector (~32 B per cycle), where separate
+  // 4-byte stores per row pair arrived as twice as many half-filled ones.  Which half of its sector a granule takes
+  // flips with bit 2 of the row, which keeps the eight rows of an ldmatrix matrix on distinct banks.
+  constexpr int H_TILE = SL_ROWS * DH;   // bf16 elements of one tile (dense)
+  auto granule_off = [](int row, int kgroup) -> uint32_t {   // byte offset of granule (batch row, unit / 8) in a tile
+    return (uint32_t)(kgroup * 256 + (row & 7) * 32 + ((((row >> 3) ^ (row >> 2)) & 1) * 16));
+  };
   extern __shared__ __align__(16) unsigned char sl_smem[];
-  __nv_bfloat16* s_h = reinterpret_cast<__nv_bfloat16*>(sl_smem);                    // 2 x 16 x H_STRIDE
-  unsigned char* s_wx = sl_smem + 2 * SL_ROWS * H_STRIDE * sizeof(__nv_bfloat16);    // SL_RING x SL_WX_STEP_BYTES
+  __nv_bfloat16* s_h = reinterpret_cast<__nv_bfloat16*>(sl_smem);                    // 2 x H_TILE
+  unsigned char* s_wx = sl_smem + 2 * H_TILE * sizeof(__nv_bfloat16);                // SL_RING x SL_WX_STEP_BYTES
   const uint32_t s_bar = smem_u32(s_wx + SL_RING * SL_WX_STEP_BYTES);                // 2 mbarriers: h tile 0 / 1 complete
   constexpr uint32_t H_TILE_BYTES = SL_ROWS * DH * 2;                                // what one step delivers to a CTA
   unsigned char* s_recst = s_wx + SL_RING * SL_WX_STEP_BYTES + 16;                   // TRAIN: SL_REC_SLOTS x SL_REC_STEP
@@ -135,7 +143,7 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
   }
 
   // ---- h tile (both buffers) of this CTA: buffer 0 holds h_{-1}; every CTA fills its own copy completely
-  for (int i = tid; i < 2 * SL_ROWS * H_STRIDE; i += SL_THREADS) s_h[i] = __float2bfloat16_rn(0.f);
+  for (int i = tid; i < 2 * H_TILE; i += SL_THREADS) s_h[i] = __float2bfloat16_rn(0.f);
   if (tid == 0) {
     mbar_init(s_bar, 1);      // one arrival per phase: the local expect_tx
     mbar_init(s_bar + 8, 1);
@@ -146,7 +154,7 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
     for (int i = tid; i < SL_ROWS * DH; i += SL_THREADS) {
       const int r = i / DH, d = i % DH;
       const int gb = bgroup * SL_ROWS + r;
-      if (gb < B) s_h[r * H_STRIDE + d] = __float2bfloat16_rn(p.state0[(size_t)gb * H + (size_t)head * DH + d]);
+      if (gb < B) s_h[granule_off(r, d >> 3) / 2 + (d & 7)] = __float2bfloat16_rn(p.state0[(size_t)gb * H + (size_t)head * DH + d]);
     }
   }
 
@@ -175,9 +183,13 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
 
   // remote addresses of this thread's four h slots in every CTA of the cluster
   const uint32_t s_h_u32 = smem_u32(s_h);
-  const uint32_t slot_a = (row_a * H_STRIDE + unit_h) * 2, slot_b = (row_b * H_STRIDE + unit_h) * 2;
+  // Pushes: lanes 0..15 of a warp send the granule of batch row `lane` (gathered from the quad that computed it) to one
+  // CTA, lanes 16..31 the same granules to the next CTA: four 16-byte stores per lane reach all eight CTAs.
+  const int prow = lane & 15;
+  const uint32_t pslot = granule_off(prow, unit_h >> 3 /* same for the whole warp */);
+  const int psrc = 4 * (prow & 7);   // first lane of the quad that holds row prow (in pa if prow < 8, else in pb)
   // ldmatrix source row/column for this lane
-  const uint32_t ldm_off = ((lane & 15) * H_STRIDE + (lane >> 4) * 8) * 2;
+  const uint32_t ldm_off = granule_off(lane & 15, lane >> 4);   // + 512 B per k-step (two unit groups)
 
   __nv_bfloat16* hout = reinterpret_cast<__nv_bfloat16*>(p.h_out);
   // training cache: [cluster][CTA][step][thread] records of SL_REC_BYTES.  The records of a step are staged in shared
@@ -214,11 +226,11 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
       }
     }
     // h_{t-1} (16 x DH) times the register-resident R slice
-    const uint32_t hbase = s_h_u32 + cur * (SL_ROWS * H_STRIDE * 2) + ldm_off;
+    const uint32_t hbase = s_h_u32 + cur * (H_TILE * 2) + ldm_off;
 #pragma unroll
     for (int ks = 0; ks < KSTEPS; ++ks) {
       uint32_t a0, a1, a2, a3;
-      ldmatrix_x4(hbase + ks * 32, a0, a1, a2, a3);
+      ldmatrix_x4(hbase + ks * 512, a0, a1, a2, a3);
 #pragma unroll
       for (int g = 0; g < 4; ++g) mma_bf16_16816(acc[g], a0, a1, a2, a3, rfrag[ks][g][0], rfrag[ks][g][1]);
     }
@@ -254,12 +266,23 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
       nxt_t[1] = next_boundary(p, gb_b, t + 1, nxt_idx[1]);
     }
     // broadcast h_t into buffer `nxt` of every CTA in the cluster
-    const uint32_t nb = s_h_u32 + nxt * (SL_ROWS * H_STRIDE * 2);
+    const uint32_t nb = s_h_u32 + nxt * (H_TILE * 2);
+    {
+      uint32_t gr[4];
 #pragma unroll
-    for (int r = 0; r < NCTA; ++r) {
-      const uint32_t rbar = map_to_cta(s_bar + 8u * nxt, r);
-      st_async_u32(map_to_cta(nb + slot_a, r), push_a, rbar);
-      st_async_u32(map_to_cta(nb + slot_b, r), push_b, rbar);
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t va = __shfl_sync(0xffffffffu, push_a, psrc + i), vb = __shfl_sync(0xffffffffu, push_b, psrc + i);
+        gr[i] = prow < 8 ? va : vb;
+      }
+      if constexpr (NCTA >= 2) {
+#pragma unroll
+        for (int r = 0; r < NCTA; r += 2) {
+          const uint32_t dst = (uint32_t)(r + (lane >> 4));
+          st_async_v4(map_to_cta(nb + pslot, dst), gr, map_to_cta(s_bar + 8u * nxt, dst));
+        }
+      } else {
+        if (lane < 16) st_async_v4(map_to_cta(nb + pslot, 0), gr, map_to_cta(s_bar + 8u * nxt, 0));
+      }
     }
     if constexpr (TRAIN) {
       // the record of this step (states after the update; the training path takes no document offsets, so nothing was
@@ -319,7 +342,7 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
 template <int DH, bool TRAIN>
 static int launch_slstm(const xl_slstm_params* p, cudaStream_t st) {
   constexpr int NCTA = DH / SL_UNITS;
-  const size_t smem = 2 * SL_ROWS * (DH + 8) * 2 + (size_t)SL_RING * SL_WX_STEP_BYTES + 16 +  // + 2 mbarriers
+  const size_t smem = 2 * SL_ROWS * DH * 2 + (size_t)SL_RING * SL_WX_STEP_BYTES + 16 +  // + 2 mbarriers
                       (TRAIN ? (size_t)SL_REC_SLOTS * SL_REC_STEP : 0);
   XL_CUDA_TRY(cudaFuncSetAttribute(slstm_forward_kernel<DH, TRAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
