@@ -65,6 +65,11 @@ __device__ __forceinline__ float fast_tanh(float x) {
   const float e = __expf(2.f * x);
   return 1.f - __fdividef(2.f, 1.f + e);
 }
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float fast_logsigmoid(float x) { return fminf(x, 0.f) - __logf(1.f + __expf(-fabsf(x))); }
 
 

@@ -242,10 +242,16 @@ __global__ void __launch_bounds__(SL_THREADS, 1) slstm_forward_kernel(const xl_s
     for (int i = 0; i < 4; ++i) {
       const float ir = acc[0][i], fr = acc[1][i], zr = acc[2][i], orr = acc[3][i];
       const float lfm = m_[i] + fast_logsigmoid(fr);
-      const float mn = (n_[i] == 0.f) ? ir : fmaxf(ir, lfm);
-      const float ig = fminf(1.f, __expf(ir - mn));
-      const float fg = fminf(1.f, __expf(lfm - mn));
-      const float zt = fast_tanh(zr), os = __fdividef(1.f, 1.f + __expf(-orr));
+      // One of the two stabilised gates is exp(0): with d = lfm - i, the other one is exp(-|d|) (a fresh unit, n == 0,
+      // takes m' = i: its input gate is 1 and its forget gate min(1, e^d)).  One exponential instead of two.
+      const bool fresh = n_[i] == 0.f;
+      const float d = lfm - ir;
+      const float mn = (fresh || d <= 0.f) ? ir : lfm;
+      const float e = __expf(-fabsf(d));
+      const float ig = (d > 0.f && !fresh) ? e : 1.f;
+      const float fg = (d <= 0.f) ? e : 1.f;
+      // tanh and the sigmoid (0.5 tanh(x/2) + 0.5) on the hardware tanh: one special-function instruction each
+      const float zt = tanh_approx(zr), os = fmaf(0.5f, tanh_approx(0.5f * orr), 0.5f);
       c_[i] = fmaf(fg, c_[i], ig * zt);
       n_[i] = fmaf(fg, n_[i], ig);
       m_[i] = mn;
