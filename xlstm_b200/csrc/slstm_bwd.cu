@@ -16,12 +16,15 @@
 //   dh_{t-1}[b,k] = sum_{g,u} dg_t[b,g,u] R[k,g,u].
 // The CTA holds exactly the slice of R the forward holds (all k, its own 32 units, four gates) as mma.sync
 // B-fragments in registers, now contracted over (g,u): it forms the PARTIAL sums of dh_{t-1} for all DH columns
-// from its own 128 gate gradients (M = 16 rows, N = DH, K = 128), stages them as bf16 per destination in shared memory and
-// sends every 32-column block to the CTA that owns those units with ONE bulk asynchronous copy into that CTA's
-// shared memory, which counts its bytes on the receiver's mbarrier (a reduce-scatter: DH/32 copies of 1.3 KB per CTA
-// and step; the same exchange as 2 048 eight-byte remote stores per CTA cost 1 200 cycles of issue per step); the
-// receiver adds the DH/32 partials in fp32 in rank order.  Everything of a step's gate arithmetic that does not depend on
-// the incoming gradient is computed one step ahead, while the partials are in flight.
+// from its own 128 gate gradients (M = 16 rows, N = DH, K = 128) and sends every 32-column block, as bf16, to the CTA
+// that owns those units with asynchronous distributed-shared-memory stores that count their bytes on the receiver's
+// mbarrier (a reduce-scatter, 1 KB per CTA pair and step).  A CTA takes in distributed shared memory in 32-byte
+// sectors at ~32 B per cycle, so the stores are shaped for whole sectors: a warp regroups its products into 16-byte
+// granules (eight columns of one row) and the lanes of one store cover whole rows of the destination block -- two
+// 16-byte stores per thread and step (2 048 eight-byte stores per CTA cost 1 200 cycles of issue and twice the sectors;
+// staged blocks sent by bulk copies needed a proxy fence of ~250 cycles on the chain).  The receiver adds the DH/32
+// partials in fp32 in rank order.  Everything of a step's gate arithmetic that does not depend on the incoming gradient
+// is computed one step ahead, while the partials are in flight.
 // dWx_t = dg_t leaves as bf16 in the layout of Wx.  dR and dbias are sums over (b,t) of h_{t-1} (x) dg_t and of dg_t:
 // plain matrix products over the dWx this kernel writes, left to the caller's GEMM library.
 #include "common.cuh"
@@ -32,29 +35,16 @@ namespace xl {
 constexpr int SLB_DG_STRIDE = 4 * SL_UNITS + 8;          // bf16 elements per row of the dg tile (+16 B: bank spread)
 constexpr int SLB_THREADS = 256;                         // 8 warps
 constexpr int SLB_REC_STEP = SL_THREADS * SL_REC_BYTES;  // cache bytes per CTA and step (records of the forward's 128 threads)
-constexpr int SLB_PROW = SL_UNITS + 8;                   // bf16 elements per row of a partial block (+16 B: rows on distinct banks)
+constexpr int SLB_PROW = SL_UNITS;                       // bf16 elements per row of a partial block: 64 B = four 16-byte granules
 constexpr int SLB_PBLOCK = SL_ROWS * SLB_PROW * 2;       // bytes of one (source, destination) block of partial sums (bf16: a
                                                          // CTA takes in ~32 B of distributed shared memory per cycle, so the
                                                          // exchange time follows the bytes; the sums are formed in fp32)
 
-// bulk copy global -> this CTA's shared memory, counted on one of its mbarriers
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
-               "r"(bytes), "r"(bar)
-               : "memory");
-}
 __device__ __forceinline__ uint32_t ldg_nc_u32(const void* ptr) {
   uint32_t v;
   asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(v) : "l"(ptr));
   return v;
 }
-// bulk copy from this CTA's shared memory into (another) CTA's, counted on an mbarrier of the destination CTA
-__device__ __forceinline__ void bulk_copy_to_cta(uint32_t remote_dst, uint32_t local_src, uint32_t bytes, uint32_t remote_bar) {
-  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(remote_dst),
-               "r"(local_src), "r"(bytes), "r"(remote_bar)
-               : "memory");
-}
-
 template <int DH>
 __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl_slstm_bwd_params p) {
   constexpr int NCTA = DH / SL_UNITS;
@@ -64,10 +54,9 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
   extern __shared__ __align__(16) unsigned char slb_smem[];
   __nv_bfloat16* s_dg = reinterpret_cast<__nv_bfloat16*>(slb_smem);                   // [2][16][SLB_DG_STRIDE]
   __nv_bfloat16* s_rb = reinterpret_cast<__nv_bfloat16*>(slb_smem + 2 * SL_ROWS * SLB_DG_STRIDE * 2);  // received: [2][source CTA][16][SLB_PROW]
-  __nv_bfloat16* s_st = s_rb + 2 * RB_BYTES / 2;                                      // staged: [2][destination CTA][16][SLB_PROW]
-  unsigned char* s_rec = reinterpret_cast<unsigned char*>(s_st) + 2 * RB_BYTES;       // [SL_RING][SLB_REC_STEP]
+  __nv_bfloat16* s_st = s_rb + 2 * RB_BYTES / 2;                                      // per warp: [16 rows][8 NTW columns], its own products
+  unsigned char* s_rec = reinterpret_cast<unsigned char*>(s_st) + SL_ROWS * DH * 2;   // [SL_RING][SLB_REC_STEP]
   const uint32_t s_bar = smem_u32(s_rec + SL_RING * SLB_REC_STEP);                    // 2 mbarriers: partials landed
-  const uint32_t s_full = s_bar + 16;                                                 // SL_RING mbarriers: record block landed
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t rank = cluster_ctarank();
@@ -114,7 +103,6 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
   if (tid == 0) {
     mbar_init(s_bar, 1);      // one arrival per phase: the local expect_tx
     mbar_init(s_bar + 8, 1);
-    for (int j = 0; j < SL_RING; ++j) mbar_init(s_full + 8u * j, 1);
     fence_barrier_init();
   }
 
@@ -140,7 +128,7 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
   cp_async_wait<SL_RING - 4>();   // this thread's granules of the last three steps' records; everybody's behind the barrier
   cluster_barrier();  // every CTA's barriers exist before anything crosses over; also a CTA-wide barrier
 
-  const uint32_t s_dg_u32 = smem_u32(s_dg), s_rb_u32 = smem_u32(s_rb), s_st_u32 = smem_u32(s_st);
+  const uint32_t s_dg_u32 = smem_u32(s_dg), s_rb_u32 = smem_u32(s_rb);
   const uint32_t ldm_off = ((lane & 15) * SLB_DG_STRIDE + (lane >> 4) * 8) * 2;
   __nv_bfloat16* dwx = reinterpret_cast<__nv_bfloat16*>(p.dwx);
 
@@ -238,29 +226,33 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
 #pragma unroll
       for (int j = 0; j < NTW; ++j) mma_bf16_16816(acc[j], a0, a1, a2, a3, bfrag[j][ks][0], bfrag[j][ks][1]);
     }
-    // ---- stage the partials per destination CTA (columns 32 d .. 32 d + 31 belong to CTA d) ...
+    // ---- every 32-column block goes to the CTA that owns those units, slot [buf][this CTA] there.  The warp turns its
+    // products (a thread holds two columns of two rows per tile) into 16-byte granules (eight columns of one row) through
+    // a buffer of its own, and lane g of store k sends granule 32 k + g = (row, tile): the lanes of a store cover whole rows
+    // of the destination block, i.e. full 32-byte sectors.  Which granule of its row a tile takes is XOR-ed with bits 1-2
+    // of the row, so that the receiver's loads (eight rows per warp) fall on distinct banks.
+    {
+      __nv_bfloat16* wb = s_st + warp * (SL_ROWS * NTW * 8);
 #pragma unroll
-    for (int j = 0; j < NTW; ++j) {
-      const int tile = warp * NTW + j;                 // columns 8 tile .. 8 tile + 7 of the head
-      __nv_bfloat16* blk = s_st + ((size_t)(buf * NCTA + (tile >> 2)) * SL_ROWS) * SLB_PROW + (tile & 3) * 8 + (lane & 3) * 2;
-      *reinterpret_cast<uint32_t*>(blk + (lane >> 2) * SLB_PROW) = pack_bf16x2(acc[j][0], acc[j][1]);
-      *reinterpret_cast<uint32_t*>(blk + ((lane >> 2) + 8) * SLB_PROW) = pack_bf16x2(acc[j][2], acc[j][3]);
-    }
-    fence_proxy_async_smem();
-    // ... and send every block with one bulk copy into slot [buf][this CTA] of its owner.  A warp produces whole
-    // blocks when it covers at least 32 columns; otherwise the CTA synchronises first.
-    if constexpr (NTW >= 4) {
-      __syncwarp();
-      if (lane < NTW / 4) {
-        const uint32_t dst = (uint32_t)(warp * (NTW / 4) + lane);
-        bulk_copy_to_cta(map_to_cta(s_rb_u32 + ((uint32_t)buf * NCTA + rank) * SLB_PBLOCK, dst),
-                         s_st_u32 + ((uint32_t)buf * NCTA + dst) * SLB_PBLOCK, SLB_PBLOCK, map_to_cta(s_bar + 8u * buf, dst));
+      for (int j = 0; j < NTW; ++j) {
+        *reinterpret_cast<uint32_t*>(wb + ((lane >> 2) * NTW + j) * 8 + (lane & 3) * 2) = pack_bf16x2(acc[j][0], acc[j][1]);
+        *reinterpret_cast<uint32_t*>(wb + (((lane >> 2) + 8) * NTW + j) * 8 + (lane & 3) * 2) = pack_bf16x2(acc[j][2], acc[j][3]);
       }
-    } else {
-      __syncthreads();
-      if (tid < NCTA)
-        bulk_copy_to_cta(map_to_cta(s_rb_u32 + ((uint32_t)buf * NCTA + rank) * SLB_PBLOCK, (uint32_t)tid),
-                         s_st_u32 + ((uint32_t)buf * NCTA + tid) * SLB_PBLOCK, SLB_PBLOCK, map_to_cta(s_bar + 8u * buf, (uint32_t)tid));
+      __syncwarp();
+      constexpr int NST = (SL_ROWS * NTW + 31) / 32;   // stores per lane
+#pragma unroll
+      for (int k = 0; k < NST; ++k) {
+        const int gidx = 32 * k + lane;
+        if (SL_ROWS * NTW >= 32 || gidx < SL_ROWS * NTW) {
+          const int prow = gidx / NTW, tile = warp * NTW + gidx % NTW;       // tile: columns 8 tile .. 8 tile + 7 of the head
+          const uint4 gr = *reinterpret_cast<const uint4*>(wb + gidx * 8);
+          const uint32_t dst = (uint32_t)(tile >> 2);
+          const uint32_t off = (((uint32_t)buf * NCTA + rank) * SL_ROWS + prow) * (SLB_PROW * 2) + (uint32_t)(((tile & 3) ^ ((prow >> 1) & 3)) * 16);
+          const uint32_t v[4] = {gr.x, gr.y, gr.z, gr.w};
+          st_async_v4(map_to_cta(s_rb_u32 + off, dst), v, map_to_cta(s_bar + 8u * buf, dst));
+        }
+      }
+      __syncwarp();   // the buffer is rewritten in the next step
     }
     // ---- off the step-to-step chain from here to the wait: announce what this step delivers to this CTA (the barrier's
     // phase cannot complete before this arrival, whatever has landed already), fetch ahead, write dWx_t
@@ -281,7 +273,7 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
     // ---- the DH/32 partials of this CTA's own columns have landed: add them in rank order
     if (!sl_wait(s_bar + 8u * buf, (uint32_t)(it >> 1) & 1u)) ok = false;
     {
-      const __nv_bfloat16* rb0 = s_rb + ((size_t)buf * NCTA * SL_ROWS + row) * SLB_PROW + unit_l;
+      const __nv_bfloat16* rb0 = s_rb + ((size_t)buf * NCTA * SL_ROWS + row) * SLB_PROW + ((fwarp ^ ((row >> 1) & 3)) * 8) + (lane & 3) * 2;
       float2 sa = make_float2(0.f, 0.f);
 #pragma unroll
       for (int s = 0; s < NCTA; ++s) {
@@ -309,7 +301,7 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
 template <int DH>
 static int launch_slstm_bwd(const xl_slstm_bwd_params* p, cudaStream_t st) {
   constexpr int NCTA = DH / SL_UNITS;
-  const size_t smem = 2 * (size_t)SL_ROWS * SLB_DG_STRIDE * 2 + 4 * (size_t)NCTA * SLB_PBLOCK +
+  const size_t smem = 2 * (size_t)SL_ROWS * SLB_DG_STRIDE * 2 + 2 * (size_t)NCTA * SLB_PBLOCK + (size_t)SL_ROWS * DH * 2 +
                       (size_t)SL_RING * SLB_REC_STEP + 16 + 8 * SL_RING;
   XL_CUDA_TRY(cudaFuncSetAttribute(slstm_backward_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
