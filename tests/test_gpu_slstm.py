@@ -168,3 +168,24 @@ def test_training_forward_equals_inference_forward_and_long_backward_is_finite()
     h_o, _ = O.slstm_forward(wx_o, R.float(), bias, mid.cpu())
     (h_o * gh[:, :, -T:].float()).sum().backward()
     assert rel_l2(dwx[:, -T:].float().cpu(), wx_o.grad) < TOL
+
+
+def test_forward_and_backward_are_bit_identical_from_run_to_run():
+    """Partial sums cross the cluster through double-buffered tiles and are added in rank order: repeated runs must
+    agree to the last bit (a race on one of the alternating buffers would show up here).  Three batch groups with a
+    ragged last one, three heads."""
+    import xlstm_b200
+    from xlstm_b200 import ops
+    wx, R, bias, _ = _case(10, 37, 300, 3, 128)
+    gh = torch.randn(37, 3, 300, 128, generator=torch.Generator().manual_seed(5)).bfloat16().cuda()
+    wx, R, bias = wx.cuda(), R.cuda(), bias.cuda()
+    first = None
+    for _ in range(6):
+        h, last, cache = ops.slstm_forward(wx, R, bias, train_cache=True)
+        dwx, ds0 = ops.slstm_backward(cache, R, gh)
+        cur = (h, last, dwx, ds0)
+        if first is None:
+            first = cur
+        else:
+            assert all(torch.equal(a, b) for a, b in zip(first, cur))
+    xlstm_b200.check_device_status()
