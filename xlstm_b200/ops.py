@@ -443,6 +443,7 @@ class SlstmFunction(torch.autograd.Function):
         return h, last
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, dh, dlast):
         cache, R, h, s0 = ctx.saved_tensors
         s0 = s0 if ctx.has_state0 else None
