@@ -219,13 +219,29 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
     float acc[NTW][4];
 #pragma unroll
     for (int j = 0; j < NTW; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    uint32_t af[KS][4];
 #pragma unroll
-    for (int ks = 0; ks < KS; ++ks) {
-      uint32_t a0, a1, a2, a3;
-      ldmatrix_x4(s_dg_u32 + buf * (SL_ROWS * SLB_DG_STRIDE * 2) + ldm_off + ks * 32, a0, a1, a2, a3);
-#pragma unroll
-      for (int j = 0; j < NTW; ++j) mma_bf16_16816(acc[j], a0, a1, a2, a3, bfrag[j][ks][0], bfrag[j][ks][1]);
+    for (int ks = 0; ks < KS; ++ks)
+      ldmatrix_x4(s_dg_u32 + buf * (SL_ROWS * SLB_DG_STRIDE * 2) + ldm_off + ks * 32, af[ks][0], af[ks][1], af[ks][2], af[ks][3]);
+    // Behind the fragment loads and in front of the products, which keep the warp busy without touching the load/store
+    // unit: everything of this step that is off the step-to-step chain but goes through that unit -- the ring fetch, the
+    // gradient from above for the next step, dWx_t.  (Issued after the copies below, these instructions sat in the
+    // unit's in-order queue in front of the next step's record loads and held them up for ~800 cycles.)
+    if (tid == 0) mbar_expect_tx(s_bar + 8u * buf, RB_BYTES);   // what this step delivers to this CTA: the barrier's phase
+                                                                // cannot complete before this arrival, whatever has landed
+    issue(t - (SL_RING - 1));
+    if (t >= 1) dh_w = ldg_nc_u32(dh + dh_off + (size_t)(t - 1) * DH);
+    {  // dWx_t = dg_t, (B, S, 4, NH, DH), from the tile: one 16-byte piece per thread
+      const int r = tid >> 4, g = (tid >> 2) & 3, part = tid & 3;
+      const int gbr = bgroup * SL_ROWS + r;
+      if (gbr < B)
+        *reinterpret_cast<uint4*>(dwx + (((size_t)gbr * S + t) * 4 + g) * H + (size_t)head * DH + rank * SL_UNITS + part * 8) =
+            *reinterpret_cast<const uint4*>(s_dg + (buf * SL_ROWS + r) * SLB_DG_STRIDE + g * SL_UNITS + part * 8);
     }
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+      for (int j = 0; j < NTW; ++j) mma_bf16_16816(acc[j], af[ks][0], af[ks][1], af[ks][2], af[ks][3], bfrag[j][ks][0], bfrag[j][ks][1]);
     // ---- every 32-column block goes to the CTA that owns those units, slot [buf][this CTA] there.  The warp turns its
     // products (a thread holds two columns of two rows per tile) into 16-byte granules (eight columns of one row) through
     // a buffer of its own, and lane g of store k sends granule 32 k + g = (row, tile): the lanes of a store cover whole rows
@@ -253,19 +269,6 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
         }
       }
       __syncwarp();   // the buffer is rewritten in the next step
-    }
-    // ---- off the step-to-step chain from here to the wait: announce what this step delivers to this CTA (the barrier's
-    // phase cannot complete before this arrival, whatever has landed already), fetch ahead, write dWx_t
-    if (tid == 0) mbar_expect_tx(s_bar + 8u * buf, RB_BYTES);
-    issue(t - (SL_RING - 1));
-    if (t >= 1) dh_w = ldg_nc_u32(dh + dh_off + (size_t)(t - 1) * DH);
-    // dWx_t = dg_t, (B, S, 4, NH, DH), from the tile: one 16-byte piece per thread
-    {
-      const int r = tid >> 4, g = (tid >> 2) & 3, part = tid & 3;
-      const int gbr = bgroup * SL_ROWS + r;
-      if (gbr < B)
-        *reinterpret_cast<uint4*>(dwx + (((size_t)gbr * S + t) * 4 + g) * H + (size_t)head * DH + rank * SL_UNITS + part * 8) =
-            *reinterpret_cast<const uint4*>(s_dg + (buf * SL_ROWS + r) * SLB_DG_STRIDE + g * SL_UNITS + part * 8);
     }
     // ---- while the partials are in flight: the gradient-independent part of the next step (t - 1)
     if (t >= 1) precompute(t - 1);   // records t-1, t-2: waited for a step ago, published by this step's barrier
