@@ -17,13 +17,19 @@
 // barrier and no release/acquire fence on the per-step chain (that barrier was 2/3 of the step time).  The data
 // dependency itself orders buffer reuse: whoever pushes h_{t+1} into a tile has consumed h_t, which every CTA
 // pushed only after its last read of h_{t-1}, the previous content of that buffer.
+// A CTA takes in distributed shared memory in 32-byte sectors (~32 B per cycle), so the tile is laid out in 16-byte
+// granules -- eight units of one batch row, what one ldmatrix row reads -- with rows r and r+8 of a unit group in one
+// sector, and the pushes are whole granules gathered from the quad that computed them: the lanes of one store fill
+// full sectors (8 KB of h per step = 256 sectors; 4-byte stores per row pair arrived as 512 half-filled ones).
+// Gate arithmetic: one of i', f' is exp(0), the other exp(-|m + logsig(f) - i|); tanh and the sigmoid run on the
+// hardware tanh (six special-function instructions per (row, unit) instead of nine).
 // Wx is streamed through an 8-step cp.async ring so that HBM latency is off the dependency chain.
 // A document boundary (cu_seqlens) zeroes h, c, n, m of that batch row inside the kernel.
 //
 // Training variant (TRAIN): every thread also writes one 96-byte record per step -- its activated gates
 // (i', raw f, tanh z, sigmoid o as bf16 pairs), its h' and its c', n', m' in fp32 -- into a cache that the backward
-// kernel (slstm_bwd.cu) reads back with the same thread mapping (the counterpart of the reference's `states` and
-// gate caches, slstm.cc:88-101).
+// kernel (slstm_bwd.cu) reads back by the same (warp, lane) index (the counterpart of the reference's `states` and
+// gate caches, slstm.cc:88-101).  The 12 KB of a step are staged in shared memory and leave as one bulk copy.
 #include "common.cuh"
 #include "slstm_common.cuh"
 
