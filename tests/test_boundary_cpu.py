@@ -207,3 +207,30 @@ def test_reference_slstm_switch_accepts_b200():
     cfg = xLSTMBlockStackConfig(slstm_block=sLSTMBlockConfig(slstm=sLSTMLayerConfig(num_heads=2, conv1d_kernel_size=4, backend="b200")),
                                 num_blocks=2, embedding_dim=128, slstm_at="all")
     xLSTMBlockStack(cfg)
+
+
+def test_slstm_weight_grads_equal_autograd_over_the_oracle():
+    """dR and dbias are sums over (b,t) of h_{t-1} (x) dWx_t and dWx_t (host-side matrix products over the backward
+    kernel's output): with dWx and h taken from the oracle they must reproduce autograd's gradients of R and the bias,
+    the initial h included."""
+    from oracle import slstm as O
+    from xlstm_b200 import ops
+    from conftest import rel_l2
+    torch.manual_seed(0)
+    B, S, NH, DH = 3, 11, 2, 8
+    H = NH * DH
+    for with_state in (True, False):
+        wx = torch.randn(B, S, 4 * H, requires_grad=True)
+        R = (torch.randn(NH, DH, 4, DH) * 0.3).requires_grad_()
+        bias = torch.randn(NH, 4, DH, requires_grad=True)
+        s0 = None
+        if with_state:
+            s0 = torch.randn(4, B, H)
+            s0[2] = s0[2].abs() + 0.5
+        h, _ = O.slstm_forward(wx, R, bias, s0)
+        (h * torch.randn_like(h)).sum().backward()
+        dR, db = ops.slstm_weight_grads(wx.grad, h.detach(), s0)
+        assert rel_l2(dR, R.grad) < 1e-5 and rel_l2(db, bias.grad) < 1e-5
+    # a single step: only the initial h contributes
+    dR1, _ = ops.slstm_weight_grads(wx.grad[:, :1], h.detach()[:, :, :1], None)
+    assert float(dR1.abs().max()) == 0.0

@@ -411,11 +411,13 @@ def slstm_weight_grads(dwx, h, state0=None):
     B, NH, S, DH = h.shape
     dw = dwx.reshape(B, S, 4, NH, DH)
 
-    def mm(a, b):
-        try:
-            return torch.bmm(a, b, out_dtype=torch.float32)
-        except TypeError:
-            return torch.bmm(a, b).float()
+    def mm(a, b):   # fp32 result; half-precision operands stay as they are where the GEMM library accumulates in fp32
+        if a.is_cuda and a.dtype in (torch.bfloat16, torch.float16):
+            try:
+                return torch.bmm(a, b, out_dtype=torch.float32)
+            except (TypeError, NotImplementedError, RuntimeError):
+                pass
+        return torch.bmm(a.float(), b.float())
 
     dR = torch.zeros(NH, DH, 4 * DH, dtype=torch.float32, device=dwx.device)
     if S > 1:   # steps 1 .. S-1 pair h_{t-1} = h[t-1] with dwx[t]: two shifted views, no shifted copy of h
