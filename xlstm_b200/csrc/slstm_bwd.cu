@@ -210,9 +210,9 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
       rr[2 * (SL_UNITS / 2)] = pack_bf16x2(dgz[0], dgz[1]);
       rr[3 * (SL_UNITS / 2)] = pack_bf16x2(dgo[0], dgo[1]);
     }
-    // The one CTA-wide barrier of a step.  It also orders the buffers that alternate between steps (dg tile, staged and
-    // received partials): whoever passes it has finished the previous step, and nothing of step it+2 can reach this
-    // CTA before its own copies of step it+1, which are issued behind this barrier, have arrived at the peers.  The
+    // The one CTA-wide barrier of a step.  It also orders the buffers that alternate between steps (dg tile, received
+    // partials): whoever passes it has finished the previous step, and nothing of step it+2 can reach this
+    // CTA before its own stores of step it+1, which are issued behind this barrier, have arrived at the peers.  The
     // same barrier tells every thread whether any wait expired.
     if (__syncthreads_or(ok ? 0 : 1)) { ok = false; break; }
     // ---- partial dh_{t-1} for all DH columns: 16 x DH = (16 x 128) (128 x DH); this warp's share is NTW 8-column tiles
@@ -225,7 +225,7 @@ __global__ void __launch_bounds__(SLB_THREADS, 1) slstm_backward_kernel(const xl
       ldmatrix_x4(s_dg_u32 + buf * (SL_ROWS * SLB_DG_STRIDE * 2) + ldm_off + ks * 32, af[ks][0], af[ks][1], af[ks][2], af[ks][3]);
     // Behind the fragment loads and in front of the products, which keep the warp busy without touching the load/store
     // unit: everything of this step that is off the step-to-step chain but goes through that unit -- the ring fetch, the
-    // gradient from above for the next step, dWx_t.  (Issued after the copies below, these instructions sat in the
+    // gradient from above for the next step, dWx_t.  (Issued after the pushes below, these instructions sat in the
     // unit's in-order queue in front of the next step's record loads and held them up for ~800 cycles.)
     if (tid == 0) mbar_expect_tx(s_bar + 8u * buf, RB_BYTES);   // what this step delivers to this CTA: the barrier's phase
                                                                 // cannot complete before this arrival, whatever has landed
